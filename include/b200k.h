@@ -1,0 +1,223 @@
+/*
+ * b200k — C ABI of the B200 (sm_100a) dense-contraction kernel library.
+ *
+ * This is the boundary that replaces the native launch path underneath iree-turbine's
+ * operator surface.  In the reference every custom op ends in
+ * `eager_dispatch` (iree/turbine/runtime/op_reg/eager.py:58-206), which JIT-compiles an IREE
+ * module (runtime/op_reg/compiler.py:105-220), imports torch tensors through dlpack
+ * (runtime/device.py:561-591) and invokes the VM after a host-side stream synchronize
+ * (runtime/invoke.py:28-75, runtime/device.py:158-162).  For the Wave kernel templates the same
+ * role is played by the `wave_runtime` native module named in requirements-wave-runtime.txt:2.
+ * The functions below take what that path takes after marshalling: raw device pointers,
+ * sizes, strides, scalars and the caller's CUDA stream.
+ *
+ * Conventions
+ *   - All pointers are device pointers unless a comment says "host".
+ *   - `stream` is a `cudaStream_t` passed as `void*` (0 = the legacy default stream).
+ *     Every launch is asynchronous on that stream; no function synchronizes the host.
+ *   - The library never allocates or frees tensor memory.  Outputs and workspaces are
+ *     allocated by the caller (see the *_workspace_bytes queries).
+ *   - Every function returns a b200k_status.  Arguments are validated before any launch;
+ *     on failure nothing has been enqueued.  b200k_last_error() returns a thread-local
+ *     human-readable message for the most recent non-OK status on the calling thread.
+ *   - No exceptions cross this boundary and nothing aborts the process.
+ */
+#ifndef B200K_H_
+#define B200K_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200K_ABI_VERSION 1
+
+typedef enum b200k_status {
+  B200K_OK = 0,
+  B200K_ERR_BAD_SHAPE = -1,        /* a dimension is non-positive or unsupported          */
+  B200K_ERR_BAD_ALIGN = -2,        /* a pointer or stride violates the 16-byte rules       */
+  B200K_ERR_BAD_DTYPE = -3,        /* dtype combination not implemented                    */
+  B200K_ERR_UNSUPPORTED_ARCH = -4, /* current device is not compute capability 10.x        */
+  B200K_ERR_CUDA = -5,             /* a CUDA runtime / driver call failed                  */
+  B200K_ERR_NULL = -6,             /* a required pointer is NULL                           */
+  B200K_ERR_TIMEOUT = -7,          /* reported through the status word: a device wait gave up */
+  B200K_ERR_WORKSPACE = -8         /* workspace too small                                  */
+} b200k_status;
+
+typedef enum b200k_dtype {
+  B200K_F16 = 0,
+  B200K_BF16 = 1,
+  B200K_F32 = 2,
+  B200K_E4M3 = 3 /* float8_e4m3fn */
+} b200k_dtype;
+
+/* ---- library ---------------------------------------------------------------------- */
+
+/* Returns B200K_ABI_VERSION of the built library. */
+int b200k_abi_version(void);
+
+/* Thread-local message describing the last non-OK status returned on this thread. */
+const char* b200k_last_error(void);
+
+/* Human-readable name of a status code. */
+const char* b200k_status_string(int status);
+
+/*
+ * Device status word.  Kernels that wait on barriers bound every wait; when one gives up the
+ * kernel ORs a non-zero code into this word and exits cleanly.  The word lives in device
+ * memory owned by the caller (4 bytes, zero-initialised by the caller).  Passing NULL in the
+ * args structs is allowed; the code is then dropped.
+ */
+
+/* ---- GEMM:  C[M,N] = A[M,K] * B[N,K]^T  ------------------------------------------- */
+/*
+ * Replaces the Wave GEMM template launch (A row-major M x K, B stored N x K, fp32
+ * accumulate).  The same NT convention is what the reference's GEMMForward computes with
+ * transpose_b (iree/turbine/kernel/boo/op_exports/gemm.py:217-230).
+ *
+ *   in_dtype  F16 | BF16  -> out_dtype F32 | F16 | BF16
+ *   in_dtype  E4M3        -> out_dtype BF16 | F32, result multiplied by (*scale_a) * (*scale_b)
+ *
+ * lda / ldb / ldc are row strides in ELEMENTS.  A, B: 16-byte aligned base, row stride a
+ * multiple of 16 bytes.  C: base aligned to 16 bytes, ldc * sizeof(out) a multiple of 16.
+ * K tails, M tails and N tails are handled (out-of-range operand elements read as zero).
+ */
+typedef struct b200k_gemm_args {
+  const void* a;
+  const void* b;
+  void* c;
+  int64_t m, n, k;
+  int64_t lda, ldb, ldc;
+  int32_t in_dtype;
+  int32_t out_dtype;
+  const float* scale_a; /* device scalar, E4M3 only, may be NULL (= 1.0) */
+  const float* scale_b; /* device scalar, E4M3 only, may be NULL (= 1.0) */
+  int32_t* status;      /* device status word, may be NULL */
+  int32_t tile_n;       /* 0 = choose; else 128 or 256 */
+  int32_t reserved;
+} b200k_gemm_args;
+
+int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);
+
+/* ---- attention forward (vanilla and causal) ---------------------------------------- */
+/*
+ * Replaces the Wave vanilla / causal attention template launch.
+ * O = softmax(scale * Q K^T [+ causal mask]) V per (batch, head); fp32 scores, running max
+ * and running sum; output in the input dtype.  The blockwise online-softmax structure is the
+ * one stated in the reference's tests/kernel/fused_attention_test.py:43-77, with natural-base
+ * softmax semantics as in aten::scaled_dot_product_attention (which the reference rewrites
+ * SDPA variants to, iree/turbine/kernel/boo/fusion/replacement.py:239-290).
+ *
+ * Layout: Q [batch, q_heads, seq_q, head_dim], K/V [batch, kv_heads, seq_kv, head_dim],
+ * O like Q; innermost dimension contiguous; strides below are in ELEMENTS.
+ * q_heads must be a multiple of kv_heads (query head h reads kv head h / (q_heads/kv_heads)).
+ * head_dim must be 128.  Causal masking aligns the last query with the last key
+ * (query i sees keys j <= i + seq_kv - seq_q).
+ */
+typedef struct b200k_attention_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  int32_t batch, q_heads, kv_heads, seq_q, seq_kv, head_dim;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  int64_t v_stride_b, v_stride_h, v_stride_s;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  int32_t dtype; /* F16 | BF16 */
+  int32_t causal;
+  float scale;
+  int32_t* status; /* device status word, may be NULL */
+} b200k_attention_args;
+
+int b200k_attention_fwd(const b200k_attention_args* args, void* stream);
+
+/* ---- decode / paged-decode attention (split-KV + reduction) ------------------------ */
+/*
+ * Replaces the Wave decode and paged-decode attention template launches: one query token per
+ * sequence against that sequence's KV history, grouped-query heads, phase 1 over KV chunks
+ * followed by a reduction kernel that merges the per-chunk (max, sum, partial output).
+ *
+ * q            [num_seqs, q_heads, head_dim]                       (contiguous)
+ * o            [num_seqs, q_heads, head_dim]                       (contiguous, dtype of q)
+ * seq_lens     int32 [num_seqs], 0 <= len; a zero-length sequence yields zeros
+ *
+ * block_table != NULL  (paged):
+ *   k_cache/v_cache [num_pages, kv_heads, page_size, head_dim]; token t of sequence s lives in
+ *   page block_table[s * block_table_stride + t / page_size], row t % page_size.
+ * block_table == NULL  (contiguous):
+ *   k_cache/v_cache [num_seqs, kv_heads, kv_seq_stride/head_dim rows, head_dim]; token t of
+ *   sequence s is at  s * kv_batch_stride + h * kv_head_stride + t * head_dim  (elements).
+ *
+ * head_dim must be 128, page_size a multiple of 16, chunk_tokens a multiple of 64 (0 = choose).
+ * workspace: b200k_decode_workspace_bytes() bytes, 256-byte aligned; contents are scratch.
+ */
+typedef struct b200k_decode_args {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  void* o;
+  void* workspace;
+  uint64_t workspace_bytes;
+  int32_t num_seqs, q_heads, kv_heads, head_dim;
+  int32_t page_size;          /* paged only */
+  int32_t num_pages;          /* paged only: pages in the pool (bounds check of table entries) */
+  int32_t block_table_stride; /* paged only: entries per sequence row */
+  int32_t max_seq_len;        /* upper bound of seq_lens (sizes the grid and the workspace) */
+  int64_t kv_batch_stride;    /* contiguous only, elements */
+  int64_t kv_head_stride;     /* paged: elements between kv heads inside a page (page_size*head_dim);
+                                 contiguous: elements between kv heads of one sequence */
+  int64_t kv_page_stride;     /* paged only: elements between pages */
+  int32_t dtype;              /* F16 | BF16 */
+  int32_t chunk_tokens;       /* KV tokens per split; 0 = choose */
+  float scale;
+  int32_t reserved;
+} b200k_decode_args;
+
+/* Bytes of scratch the call needs for the given problem (depends on num_seqs, q_heads,
+ * head_dim, max_seq_len and chunk_tokens only). */
+uint64_t b200k_decode_workspace_bytes(const b200k_decode_args* args);
+
+/* The chunk size the library would choose for chunk_tokens == 0. */
+int32_t b200k_decode_default_chunk(const b200k_decode_args* args);
+
+int b200k_decode_attention(const b200k_decode_args* args, void* stream);
+
+/*
+ * Gathers the K or V rows of every sequence through the block table into a contiguous buffer
+ *   out[s, h, t, :] = cache[block_table[s, t / page_size], h, t % page_size, :]
+ * with out laid out [num_seqs, kv_heads, max_seq_len, head_dim].  Rows t >= seq_lens[s] are
+ * left untouched.  It uses the same address function as the paged decode kernel and exists so
+ * that the index arithmetic can be checked bit-for-bit against a host gather.
+ */
+int b200k_paged_gather(const void* cache, const int32_t* block_table, const int32_t* seq_lens, void* out,
+                       int32_t num_seqs, int32_t kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                       int32_t block_table_stride, int32_t max_seq_len, int64_t kv_page_stride,
+                       int64_t kv_head_stride, int32_t elem_bytes, void* stream);
+
+/* ---- per-tensor fp8 quantisation helper -------------------------------------------- */
+/*
+ * scale = max|x| / 448 (1.0 if the tensor is all zero), y = e4m3(x / scale).
+ * x: float32 [n]; y: e4m3 [n]; scale_out: device float; amax_scratch: device uint32 (zeroed by
+ * the call).  Two launches on `stream`.
+ */
+int b200k_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n, void* stream);
+
+/* ---- host-buffer convenience entry points (copies inside the call) ------------------ */
+/*
+ * Same operations with HOST pointers: the call stages inputs to the device buffers given in
+ * `dev` (same struct, device pointers, caller-allocated), launches, and copies the output back
+ * to the host pointer, all on `stream`, then returns without synchronizing.  Host buffers
+ * should be pinned for the copies to be asynchronous.
+ */
+int b200k_gemm_nt_host(const b200k_gemm_args* host, const b200k_gemm_args* dev, void* stream);
+int b200k_attention_fwd_host(const b200k_attention_args* host, const b200k_attention_args* dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200K_H_ */

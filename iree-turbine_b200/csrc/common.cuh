@@ -1,0 +1,57 @@
+// Shared host/device declarations for the kernel translation units and the C-ABI layer.
+#pragma once
+#include <cstdint>
+#include <cstddef>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/b200k.h"
+
+namespace b200k {
+
+// Codes OR-ed into the caller's device status word by kernels whose bounded waits gave up.
+enum : int32_t {
+  kStatusGemmTimeout = 1,
+  kStatusAttnTimeout = 2,
+  kStatusDecodeBadPage = 4,
+};
+
+// ---- host-side error plumbing (abi.cu) ----
+int set_error(int status, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+int ensure_sm100();
+int num_sms();
+
+// Encodes a tiled tensor map with 128-byte swizzle.  dims/strides innermost-first; strides in
+// bytes for dimensions 1..rank-1.
+int encode_tmap(CUtensorMap* out, int dtype, int rank, void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                const uint32_t* box, bool swizzle128 = true);
+
+// ---- launchers implemented next to their kernels ----
+int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream);
+int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream);
+int launch_decode(const b200k_decode_args& a, cudaStream_t stream);
+uint64_t decode_workspace_bytes(const b200k_decode_args& a);
+int32_t decode_default_chunk(const b200k_decode_args& a);
+int launch_paged_gather(const void* cache, const int32_t* block_table, const int32_t* seq_lens, void* out,
+                        int32_t num_seqs, int32_t kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                        int32_t block_table_stride, int32_t max_seq_len, int64_t kv_page_stride, int64_t kv_head_stride,
+                        int32_t elem_bytes, cudaStream_t stream);
+int launch_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n,
+                         cudaStream_t stream);
+
+inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case B200K_F16:
+    case B200K_BF16:
+      return 2;
+    case B200K_F32:
+      return 4;
+    case B200K_E4M3:
+      return 1;
+    default:
+      return 0;
+  }
+}
+
+}  // namespace b200k

@@ -1,0 +1,379 @@
+// C[M,N] = A[M,K] * B[N,K]^T on sm_100a: TMA-fed shared-memory ring, tcgen05.mma with fp32
+// accumulators in tensor memory, persistent CTAs with double-buffered accumulators so the
+// epilogue of one tile overlaps the main loop of the next.
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs,
+// warps 2..5 drain accumulators (each warp its own 32-lane quarter of tensor memory).
+//
+// Data layout.  A and B are K-contiguous, so both are "K-major" UMMA operands.  One pipeline
+// stage holds a 128 x 128-byte tile of A and a BN x 128-byte tile of B, written by TMA with the
+// 128-byte swizzle; each UMMA consumes 32 bytes of K (16 half-precision or 32 fp8 elements), so
+// a stage feeds four MMAs whose descriptors advance by 32 bytes inside the swizzle atom.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200k {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBKBytes = 128;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 16;  // m-tiles per rasterisation group (keeps one wave's operands L2-resident)
+
+enum GemmKind : int { kKindF16 = 0, kKindBF16 = 1, kKindE4M3 = 2 };
+
+struct GemmParams {
+  void* c;
+  const float* scale_a;
+  const float* scale_b;
+  int32_t* status;
+  int64_t ldc;
+  int32_t m, n;
+  int32_t tiles_m, tiles_n, num_kb;
+  int32_t vec_store_ok;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kABytes = kBM * kBKBytes;
+  static constexpr int kBBytes = BN * kBKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // slack for 1024-byte alignment of the tiles
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int group_size = kGroupM * tiles_n;
+  const int group = t / group_size;
+  const int first_m = group * kGroupM;
+  const int gm = min(tiles_m - first_m, kGroupM);
+  const int r = t - group * group_size;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT to_out(float v);
+template <>
+__device__ __forceinline__ float to_out<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __half to_out<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// Stores 32 consecutive columns of one output row.
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t (&r)[32], float scale, int valid_cols,
+                                            bool vec_ok) {
+  if (valid_cols >= 32 && vec_ok) {
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float4 v = make_float4(__uint_as_float(r[4 * i]) * scale, __uint_as_float(r[4 * i + 1]) * scale,
+                               __uint_as_float(r[4 * i + 2]) * scale, __uint_as_float(r[4 * i + 3]) * scale);
+        reinterpret_cast<float4*>(dst)[i] = v;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        union {
+          uint4 u;
+          OutT h[8];
+        } pk;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pk.h[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * scale);
+        reinterpret_cast<uint4*>(dst)[i] = pk.u;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid_cols) dst[i] = to_out<OutT>(__uint_as_float(r[i]) * scale);
+  }
+}
+
+template <int BN, int KIND, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int kElemsPerStage = (KIND == kKindE4M3) ? 128 : 64;  // K elements in 128 bytes
+  constexpr uint32_t kFmt = (KIND == kKindBF16) ? kFmtBF16 : (KIND == kKindF16 ? kFmtF16 : kFmtE4M3);
+  constexpr uint32_t kIdesc = make_idesc(kFmt, kFmt, kBM, BN, 0, 0);
+  constexpr uint32_t kTmemCols = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty = full + S::kStages;
+  uint64_t* tfull = empty + S::kStages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_word = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull + a, 1);
+      mbar_init(tempty + a, 4);
+    }
+    *abort_word = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(empty + stage, phase ^ 1, abort_word)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          mbar_arrive_expect_tx(full + stage, S::kStageBytes);
+          tma_load_2d(sa, &tmap_a, full + stage, kb * kElemsPerStage, tm * kBM);
+          tma_load_2d(sa + S::kABytes, &tmap_b, full + stage, kb * kElemsPerStage, tn * BN);
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tempty + acc, acc_phase ^ 1, abort_word)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(full + stage, phase, abort_word)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+          const uint64_t a_desc = make_desc_kmajor_sw128(sa);
+          const uint64_t b_desc = make_desc_kmajor_sw128(sa + S::kABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            if constexpr (KIND == kKindE4M3)
+              umma_f8_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, accum);
+            else
+              umma_f16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, accum);
+          }
+          umma_commit(empty + stage);  // frees the stage once these MMAs have read it
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(tfull + acc);  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue warps ----------------
+    const int quarter = warp & 3;
+    float scale = 1.0f;
+    if constexpr (KIND == kKindE4M3) {
+      const float sa = p.scale_a ? *p.scale_a : 1.0f;
+      const float sb = p.scale_b ? *p.scale_b : 1.0f;
+      scale = sa * sb;
+    }
+    OutT* cbase = reinterpret_cast<OutT*>(p.c);
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      bool ok = mbar_wait(tfull + acc, acc_phase, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * kBM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 2
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_wait_ld();
+        const int col = tn * BN + c * 32;
+        if (row < p.m && col < p.n) {
+          store_chunk<OutT>(cbase + static_cast<int64_t>(row) * p.ldc + col, r, scale, p.n - col,
+                            p.vec_store_ok != 0);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty + acc);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    // A wait gave up: give copies that may still be in flight time to land before the shared
+    // memory is released, then report.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusGemmTimeout);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN, int KIND, typename OutT>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  auto kfn = gemm_nt_kernel<BN, KIND, OutT>;
+  static bool configured = false;  // per instantiation; benign race (idempotent attribute set)
+  if (!configured) {
+    int rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
+                        "cudaFuncSetAttribute(gemm smem)");
+    if (rc) return rc;
+    configured = true;
+  }
+  kfn<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "gemm_nt_kernel launch");
+}
+
+template <int BN>
+int dispatch_dtype(int in_dtype, int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                   int grid, cudaStream_t stream) {
+  if (in_dtype == B200K_F16 && out_dtype == B200K_F32)
+    return launch_one<BN, kKindF16, float>(ta, tb, p, grid, stream);
+  if (in_dtype == B200K_F16 && out_dtype == B200K_F16)
+    return launch_one<BN, kKindF16, __half>(ta, tb, p, grid, stream);
+  if (in_dtype == B200K_BF16 && out_dtype == B200K_F32)
+    return launch_one<BN, kKindBF16, float>(ta, tb, p, grid, stream);
+  if (in_dtype == B200K_BF16 && out_dtype == B200K_BF16)
+    return launch_one<BN, kKindBF16, __nv_bfloat16>(ta, tb, p, grid, stream);
+  if (in_dtype == B200K_E4M3 && out_dtype == B200K_BF16)
+    return launch_one<BN, kKindE4M3, __nv_bfloat16>(ta, tb, p, grid, stream);
+  if (in_dtype == B200K_E4M3 && out_dtype == B200K_F32)
+    return launch_one<BN, kKindE4M3, float>(ta, tb, p, grid, stream);
+  return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: unsupported dtype pair in=%d out=%d", in_dtype, out_dtype);
+}
+
+}  // namespace
+
+int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream) {
+  if (!a.a || !a.b || !a.c) return set_error(B200K_ERR_NULL, "gemm_nt: a, b and c must be non-NULL");
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0 || a.m > INT32_MAX || a.n > INT32_MAX || a.k > INT32_MAX)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: m, n, k must be in [1, 2^31)");
+  const size_t in_es = dtype_size(a.in_dtype);
+  const size_t out_es = dtype_size(a.out_dtype);
+  if (in_es == 0 || out_es == 0 || a.in_dtype == B200K_F32)
+    return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: unsupported dtype in=%d out=%d", a.in_dtype, a.out_dtype);
+  if (a.lda < a.k || a.ldb < a.k || a.ldc < a.n)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: leading dimensions smaller than the row length");
+  if ((reinterpret_cast<uintptr_t>(a.a) & 15) || (reinterpret_cast<uintptr_t>(a.b) & 15) ||
+      (a.lda * in_es) % 16 != 0 || (a.ldb * in_es) % 16 != 0)
+    return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt: A/B base and row stride must be multiples of 16 bytes");
+  if (reinterpret_cast<uintptr_t>(a.c) % out_es != 0)
+    return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt: C is not aligned to its element size");
+  if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_n must be 0, 128 or 256");
+  int rc = ensure_sm100();
+  if (rc) return rc;
+
+  const int sms = num_sms();
+  const int tiles_m = static_cast<int>((a.m + kBM - 1) / kBM);
+  auto waves_cost = [&](int bn) {
+    const int64_t tiles = static_cast<int64_t>(tiles_m) * ((a.n + bn - 1) / bn);
+    return ((tiles + sms - 1) / sms) * bn;
+  };
+  int bn = a.tile_n;
+  if (bn == 0) bn = (a.n > 128 && waves_cost(256) <= waves_cost(128)) ? 256 : 128;
+  const int tiles_n = static_cast<int>((a.n + bn - 1) / bn);
+  const int k_per_stage = a.in_dtype == B200K_E4M3 ? 128 : 64;
+
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m)};
+    uint64_t strides[1] = {static_cast<uint64_t>(a.lda) * in_es};
+    uint32_t box[2] = {static_cast<uint32_t>(k_per_stage), static_cast<uint32_t>(kBM)};
+    rc = encode_tmap(&ta, a.in_dtype, 2, const_cast<void*>(a.a), dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n)};
+    uint64_t strides[1] = {static_cast<uint64_t>(a.ldb) * in_es};
+    uint32_t box[2] = {static_cast<uint32_t>(k_per_stage), static_cast<uint32_t>(bn)};
+    rc = encode_tmap(&tb, a.in_dtype, 2, const_cast<void*>(a.b), dims, strides, box);
+    if (rc) return rc;
+  }
+
+  GemmParams p;
+  p.c = a.c;
+  p.scale_a = a.scale_a;
+  p.scale_b = a.scale_b;
+  p.status = a.status;
+  p.ldc = a.ldc;
+  p.m = static_cast<int32_t>(a.m);
+  p.n = static_cast<int32_t>(a.n);
+  p.tiles_m = tiles_m;
+  p.tiles_n = tiles_n;
+  p.num_kb = static_cast<int32_t>((a.k + k_per_stage - 1) / k_per_stage);
+  p.vec_store_ok = ((reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && (a.ldc * out_es) % 16 == 0) ? 1 : 0;
+
+  const int64_t num_tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+  const int grid = static_cast<int>(num_tiles < sms ? num_tiles : sms);
+  if (bn == 256) return dispatch_dtype<256>(a.in_dtype, a.out_dtype, ta, tb, p, grid, stream);
+  return dispatch_dtype<128>(a.in_dtype, a.out_dtype, ta, tb, p, grid, stream);
+}
+
+}  // namespace b200k

@@ -1,0 +1,406 @@
+"""The op library: ``torch.ops.b200k.*``.
+
+Each op is a ``CustomOp`` registered the way the reference registers its op libraries
+(iree/turbine/ops/__init__.py:7-11; e.g. iree/turbine/ops/conv_fwd.py:62-89 for a ``select``):
+a schema string, a ``select`` that types every argument and declares the result meta tensors
+(which also is the Meta implementation, so fake tensors and ``torch.compile`` tracing work), and
+a CUDA implementation.  The CUDA implementation is ``eager_execute`` calling the C ABI on the
+current stream; there is no CPU implementation, so a CPU tensor fails in the dispatcher with
+torch's own "not implemented for CPU" error.
+
+Output shape/dtype rules live in ``select`` only; ``eager_execute`` allocates outputs from the
+same rules.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+from torch import Tensor
+
+from . import _launcher as L
+from .op_reg import CustomOp, KernelSelection, def_library
+
+__all__ = [
+    "LIBRARY",
+    "gemm_nt",
+    "gemm_fp8_nt",
+    "attention",
+    "decode_attention",
+    "paged_decode_attention",
+    "quantize_e4m3",
+    "paged_gather",
+    "device_status",
+    "reset_device_status",
+]
+
+LIBRARY = def_library("b200k")
+
+_HALF_TYPES = (torch.float16, torch.bfloat16)
+
+# One int32 status word per device: kernels OR a code into it if a bounded device-side wait gave
+# up (see include/b200k.h).  Reading it synchronizes, so it is only read on request.
+_status_words: dict[int, Tensor] = {}
+
+
+def _status_ptr(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = w
+    return w.data_ptr()
+
+
+def device_status(device=None) -> int:
+    """Returns the device status word (0 = no kernel reported a timed-out wait).  Synchronizes."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _status_ptr(dev)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    return int(_status_words[idx].item())
+
+
+def reset_device_status(device=None) -> None:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _status_ptr(dev)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    _status_words[idx].zero_()
+
+
+def _stream(t: Tensor) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _row_major_2d(t: Tensor) -> Tensor:
+    """A 2-D view whose last dim is contiguous and whose row stride is a multiple of 16 bytes."""
+    if t.stride(1) != 1 or (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------------
+def _gemm_out_dtype(in_dtype: torch.dtype, out_dtype) -> torch.dtype:
+    if in_dtype in _HALF_TYPES:
+        od = torch.float32 if out_dtype is None else out_dtype
+        torch._check(od in (torch.float32, in_dtype), lambda: f"gemm_nt: out_dtype must be float32 or {in_dtype}")
+        return od
+    od = torch.bfloat16 if out_dtype is None else out_dtype
+    torch._check(od in (torch.bfloat16, torch.float32), lambda: "gemm_fp8_nt: out_dtype must be bfloat16 or float32")
+    return od
+
+
+def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: int = 0) -> None:
+    a = _row_major_2d(a)
+    b = _row_major_2d(b)
+    args = L.GemmArgs()
+    args.a, args.b, args.c = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k = a.size(0), b.size(0), a.size(1)
+    args.lda, args.ldb, args.ldc = a.stride(0), b.stride(0), out.stride(0)
+    args.in_dtype = L.DTYPE_CODES[a.dtype]
+    args.out_dtype = L.DTYPE_CODES[out.dtype]
+    args.scale_a = scale_a.data_ptr() if scale_a is not None else None
+    args.scale_b = scale_b.data_ptr() if scale_b is not None else None
+    args.status = _status_ptr(a.device)
+    args.tile_n = tile_n
+    L.check(L.lib().b200k_gemm_nt(C.byref(args), _stream(a)))
+
+
+@CustomOp.register(library=LIBRARY)
+class gemm_nt(CustomOp):
+    """C[M,N] = A[M,K] @ B[N,K]^T, f16 or bf16 operands, fp32 accumulation.
+
+    Output dtype: float32 unless ``out_dtype`` names the operand dtype.
+    """
+
+    signature = "gemm_nt(Tensor a, Tensor b, ScalarType? out_dtype=None) -> Tensor"
+
+    def select(self, sel: KernelSelection):
+        a = sel.arg_tensor(0)
+        b = sel.arg_tensor(1)
+        od = sel.attr_optional(2)
+        torch._check(a.t.dim() == 2 and b.t.dim() == 2, lambda: "gemm_nt: a and b must be 2-D")
+        torch._check(a.t.dtype in _HALF_TYPES, lambda: f"gemm_nt: dtype must be float16 or bfloat16, got {a.t.dtype}")
+        torch._check(a.t.dtype == b.t.dtype, lambda: "gemm_nt: a and b must have the same dtype")
+        torch._check(a.t.size(1) == b.t.size(1), lambda: f"gemm_nt: K mismatch: a is {list(a.t.shape)}, b is {list(b.t.shape)}")
+        torch._check(a.t.size(1) % 8 == 0, lambda: "gemm_nt: K must be a multiple of 8")
+        a.specialize_dims(1)
+        b.specialize_dims(1)
+        sel.return_new_tensor([a.t.size(0), b.t.size(0)], _gemm_out_dtype(a.t.dtype, od.v))
+
+    def eager_execute(self, a, b, out_dtype=None):
+        out = torch.empty((a.size(0), b.size(0)), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
+        _launch_gemm(a, b, out, None, None)
+        return out
+
+
+@CustomOp.register(library=LIBRARY)
+class gemm_fp8_nt(CustomOp):
+    """C = (A8 @ B8^T) * scale_a * scale_b with float8_e4m3fn operands and per-tensor fp32 scales.
+
+    ``scale_a`` / ``scale_b`` are one-element float32 device tensors.  Output bfloat16 (default)
+    or float32.
+    """
+
+    signature = (
+        "gemm_fp8_nt(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, ScalarType? out_dtype=None) -> Tensor"
+    )
+
+    def select(self, sel: KernelSelection):
+        a = sel.arg_tensor(0)
+        b = sel.arg_tensor(1)
+        sa = sel.arg_tensor(2)
+        sb = sel.arg_tensor(3)
+        od = sel.attr_optional(4)
+        torch._check(a.t.dim() == 2 and b.t.dim() == 2, lambda: "gemm_fp8_nt: a and b must be 2-D")
+        torch._check(
+            a.t.dtype == torch.float8_e4m3fn and b.t.dtype == torch.float8_e4m3fn,
+            lambda: "gemm_fp8_nt: a and b must be float8_e4m3fn",
+        )
+        torch._check(a.t.size(1) == b.t.size(1), lambda: "gemm_fp8_nt: K mismatch")
+        torch._check(a.t.size(1) % 16 == 0, lambda: "gemm_fp8_nt: K must be a multiple of 16")
+        torch._check(
+            sa.t.numel() == 1 and sb.t.numel() == 1 and sa.t.dtype == torch.float32 and sb.t.dtype == torch.float32,
+            lambda: "gemm_fp8_nt: scales must be one-element float32 tensors",
+        )
+        sel.return_new_tensor([a.t.size(0), b.t.size(0)], _gemm_out_dtype(a.t.dtype, od.v))
+
+    def eager_execute(self, a, b, scale_a, scale_b, out_dtype=None):
+        out = torch.empty((a.size(0), b.size(0)), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
+        _launch_gemm(a, b, out, scale_a, scale_b)
+        return out
+
+
+@CustomOp.register(library=LIBRARY)
+class quantize_e4m3(CustomOp):
+    """Per-tensor quantisation: returns (x / s cast to float8_e4m3fn, s) with s = max|x| / 448."""
+
+    signature = "quantize_e4m3(Tensor x) -> (Tensor, Tensor)"
+
+    def select(self, sel: KernelSelection):
+        x = sel.arg_tensor(0)
+        torch._check(x.t.dtype == torch.float32, lambda: "quantize_e4m3: x must be float32")
+        sel.return_new_tensor(list(x.t.shape), torch.float8_e4m3fn)
+        sel.return_new_tensor([1], torch.float32)
+
+    def eager_execute(self, x):
+        x = x.contiguous()
+        y = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+        scale = torch.empty(1, dtype=torch.float32, device=x.device)
+        scratch = torch.empty(1, dtype=torch.int32, device=x.device)
+        L.check(
+            L.lib().b200k_quantize_e4m3(
+                x.data_ptr(), y.data_ptr(), scale.data_ptr(), scratch.data_ptr(), x.numel(), _stream(x)
+            )
+        )
+        return y, scale
+
+
+# ---------------------------------------------------------------------------------------------
+# attention forward
+# ---------------------------------------------------------------------------------------------
+def _bhsd(t: Tensor) -> Tensor:
+    ok = (
+        t.stride(3) == 1
+        and all(s > 0 and s % 8 == 0 for s in t.stride()[:3])
+        and t.data_ptr() % 16 == 0
+    )
+    return t if ok else t.contiguous()
+
+
+def _fill_attention_args(q: Tensor, k: Tensor, v: Tensor, o: Tensor, scale: float, causal: bool) -> L.AttentionArgs:
+    args = L.AttentionArgs()
+    args.q, args.k, args.v, args.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    args.batch, args.q_heads, args.seq_q, args.head_dim = q.size(0), q.size(1), q.size(2), q.size(3)
+    args.kv_heads, args.seq_kv = k.size(1), k.size(2)
+    args.q_stride_b, args.q_stride_h, args.q_stride_s = q.stride(0), q.stride(1), q.stride(2)
+    args.k_stride_b, args.k_stride_h, args.k_stride_s = k.stride(0), k.stride(1), k.stride(2)
+    args.v_stride_b, args.v_stride_h, args.v_stride_s = v.stride(0), v.stride(1), v.stride(2)
+    args.o_stride_b, args.o_stride_h, args.o_stride_s = o.stride(0), o.stride(1), o.stride(2)
+    args.dtype = L.DTYPE_CODES[q.dtype]
+    args.causal = 1 if causal else 0
+    args.scale = float(scale)
+    return args
+
+
+@CustomOp.register(library=LIBRARY)
+class attention(CustomOp):
+    """O = softmax(scale * Q K^T [causal]) V.  q [B,Hq,Sq,128], k/v [B,Hkv,Skv,128] -> [B,Hq,Sq,128]."""
+
+    signature = "attention(Tensor q, Tensor k, Tensor v, float scale, bool is_causal) -> Tensor"
+
+    def select(self, sel: KernelSelection):
+        q = sel.arg_tensor(0)
+        k = sel.arg_tensor(1)
+        v = sel.arg_tensor(2)
+        sel.attr_float(3)
+        sel.attr_bool(4)
+        torch._check(q.t.dim() == 4 and k.t.dim() == 4 and v.t.dim() == 4, lambda: "attention: q, k, v must be 4-D [B,H,S,D]")
+        torch._check(q.t.dtype in _HALF_TYPES, lambda: f"attention: dtype must be float16 or bfloat16, got {q.t.dtype}")
+        torch._check(q.t.dtype == k.t.dtype == v.t.dtype, lambda: "attention: q, k, v must share a dtype")
+        torch._check(q.t.size(3) == 128 and k.t.size(3) == 128 and v.t.size(3) == 128, lambda: "attention: head dim must be 128")
+        torch._check(k.t.shape == v.t.shape, lambda: "attention: k and v must have the same shape")
+        torch._check(q.t.size(0) == k.t.size(0), lambda: "attention: batch mismatch")
+        torch._check(q.t.size(1) % k.t.size(1) == 0, lambda: "attention: query heads must be a multiple of kv heads")
+        q.specialize_dims(3)
+        sel.return_new_tensor(list(q.t.shape), q.t.dtype)
+
+    def eager_execute(self, q, k, v, scale, is_causal):
+        q, k, v = _bhsd(q), _bhsd(k), _bhsd(v)
+        o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        args = _fill_attention_args(q, k, v, o, scale, is_causal)
+        args.status = _status_ptr(q.device)
+        L.check(L.lib().b200k_attention_fwd(C.byref(args), _stream(q)))
+        return o
+
+
+# ---------------------------------------------------------------------------------------------
+# decode / paged decode
+# ---------------------------------------------------------------------------------------------
+def _decode_common_checks(name: str, q: Tensor, kc: Tensor, vc: Tensor, lens: Tensor):
+    torch._check(q.dim() == 3, lambda: f"{name}: q must be [num_seqs, q_heads, 128]")
+    torch._check(q.dtype in _HALF_TYPES, lambda: f"{name}: dtype must be float16 or bfloat16, got {q.dtype}")
+    torch._check(q.dtype == kc.dtype == vc.dtype, lambda: f"{name}: q and the KV cache must share a dtype")
+    torch._check(q.size(2) == 128, lambda: f"{name}: head dim must be 128")
+    torch._check(kc.dim() == 4 and kc.shape == vc.shape, lambda: f"{name}: k and v caches must be 4-D and equal in shape")
+    torch._check(kc.size(3) == 128, lambda: f"{name}: cache head dim must be 128")
+    torch._check(lens.dtype == torch.int32 and lens.dim() == 1 and lens.size(0) == q.size(0),
+                 lambda: f"{name}: seq_lens must be int32 [num_seqs]")
+    torch._check(q.size(1) % kc.size(1) == 0 and q.size(1) // kc.size(1) <= 16,
+                 lambda: f"{name}: query heads must be a multiple (at most 16x) of kv heads")
+
+
+def _launch_decode(args: L.DecodeArgs, q: Tensor) -> None:
+    lib = L.lib()
+    need = lib.b200k_decode_workspace_bytes(C.byref(args))
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    args.workspace = ws.data_ptr()
+    args.workspace_bytes = need
+    L.check(lib.b200k_decode_attention(C.byref(args), _stream(q)))
+
+
+@CustomOp.register(library=LIBRARY)
+class decode_attention(CustomOp):
+    """One query token per sequence against a contiguous KV history.
+
+    q [num_seqs, Hq, 128]; k, v [num_seqs, Hkv, max_len, 128]; seq_lens int32 [num_seqs]
+    (tokens t >= seq_lens[s] are ignored).  Returns [num_seqs, Hq, 128].
+    """
+
+    signature = (
+        "decode_attention(Tensor q, Tensor k, Tensor v, Tensor seq_lens, float scale, int chunk_tokens=0) -> Tensor"
+    )
+
+    def select(self, sel: KernelSelection):
+        q = sel.arg_tensor(0)
+        k = sel.arg_tensor(1)
+        v = sel.arg_tensor(2)
+        lens = sel.arg_tensor(3)
+        sel.attr_float(4)
+        sel.attr_int(5)
+        _decode_common_checks("decode_attention", q.t, k.t, v.t, lens.t)
+        torch._check(k.t.size(0) == q.t.size(0), lambda: "decode_attention: k must have one history per sequence")
+        sel.return_new_tensor(list(q.t.shape), q.t.dtype)
+
+    def eager_execute(self, q, k, v, seq_lens, scale, chunk_tokens=0):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o = torch.empty_like(q)
+        args = L.DecodeArgs()
+        args.q, args.k_cache, args.v_cache, args.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+        args.block_table = None
+        args.seq_lens = seq_lens.data_ptr()
+        args.num_seqs, args.q_heads, args.head_dim = q.size(0), q.size(1), q.size(2)
+        args.kv_heads = k.size(1)
+        args.max_seq_len = k.size(2)
+        args.kv_batch_stride, args.kv_head_stride = k.stride(0), k.stride(1)
+        args.dtype = L.DTYPE_CODES[q.dtype]
+        args.chunk_tokens = int(chunk_tokens)
+        args.scale = float(scale)
+        _launch_decode(args, q)
+        return o
+
+
+@CustomOp.register(library=LIBRARY)
+class paged_decode_attention(CustomOp):
+    """One query token per sequence against a paged KV cache.
+
+    q [num_seqs, Hq, 128]; k_cache, v_cache [num_pages, Hkv, page_size, 128];
+    block_table int32 [num_seqs, max_pages]: physical page of logical page p of sequence s;
+    seq_lens int32 [num_seqs].  Returns [num_seqs, Hq, 128].
+    """
+
+    signature = (
+        "paged_decode_attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_table, Tensor seq_lens, "
+        "float scale, int chunk_tokens=0) -> Tensor"
+    )
+
+    def select(self, sel: KernelSelection):
+        q = sel.arg_tensor(0)
+        kc = sel.arg_tensor(1)
+        vc = sel.arg_tensor(2)
+        bt = sel.arg_tensor(3)
+        lens = sel.arg_tensor(4)
+        sel.attr_float(5)
+        sel.attr_int(6)
+        _decode_common_checks("paged_decode_attention", q.t, kc.t, vc.t, lens.t)
+        torch._check(bt.t.dtype == torch.int32 and bt.t.dim() == 2 and bt.t.size(0) == q.t.size(0),
+                     lambda: "paged_decode_attention: block_table must be int32 [num_seqs, max_pages]")
+        torch._check(kc.t.size(2) % 16 == 0, lambda: "paged_decode_attention: page size must be a multiple of 16")
+        sel.return_new_tensor(list(q.t.shape), q.t.dtype)
+
+    def eager_execute(self, q, k_cache, v_cache, block_table, seq_lens, scale, chunk_tokens=0):
+        q, k_cache, v_cache = q.contiguous(), k_cache.contiguous(), v_cache.contiguous()
+        block_table = block_table.contiguous()
+        o = torch.empty_like(q)
+        args = L.DecodeArgs()
+        args.q, args.k_cache, args.v_cache, args.o = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), o.data_ptr()
+        args.block_table = block_table.data_ptr()
+        args.seq_lens = seq_lens.data_ptr()
+        args.num_seqs, args.q_heads, args.head_dim = q.size(0), q.size(1), q.size(2)
+        args.kv_heads = k_cache.size(1)
+        args.page_size = k_cache.size(2)
+        args.num_pages = k_cache.size(0)
+        args.block_table_stride = block_table.stride(0)
+        args.max_seq_len = block_table.size(1) * k_cache.size(2)
+        args.kv_page_stride, args.kv_head_stride = k_cache.stride(0), k_cache.stride(1)
+        args.dtype = L.DTYPE_CODES[q.dtype]
+        args.chunk_tokens = int(chunk_tokens)
+        args.scale = float(scale)
+        _launch_decode(args, q)
+        return o
+
+
+@CustomOp.register(library=LIBRARY)
+class paged_gather(CustomOp):
+    """out[s, h, t, :] = cache[block_table[s, t // page], h, t % page, :] for t < seq_lens[s].
+
+    Uses the paged decode kernel's address function; rows beyond seq_lens[s] are zero.
+    """
+
+    signature = "paged_gather(Tensor cache, Tensor block_table, Tensor seq_lens, int max_seq_len) -> Tensor"
+
+    def select(self, sel: KernelSelection):
+        c = sel.arg_tensor(0)
+        bt = sel.arg_tensor(1)
+        lens = sel.arg_tensor(2)
+        n = sel.attr_int(3)
+        torch._check(c.t.dim() == 4, lambda: "paged_gather: cache must be [num_pages, heads, page_size, head_dim]")
+        torch._check(bt.t.dtype == torch.int32 and bt.t.dim() == 2, lambda: "paged_gather: block_table must be int32 2-D")
+        torch._check(lens.t.dtype == torch.int32 and lens.t.dim() == 1, lambda: "paged_gather: seq_lens must be int32 1-D")
+        sel.return_new_tensor([bt.t.size(0), c.t.size(1), n.v, c.t.size(3)], c.t.dtype)
+
+    def eager_execute(self, cache, block_table, seq_lens, max_seq_len):
+        cache = cache.contiguous()
+        block_table = block_table.contiguous()
+        out = torch.zeros((block_table.size(0), cache.size(1), max_seq_len, cache.size(3)), dtype=cache.dtype,
+                          device=cache.device)
+        L.check(
+            L.lib().b200k_paged_gather(
+                cache.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), block_table.size(0),
+                cache.size(1), cache.size(3), cache.size(2), cache.size(0), block_table.stride(0), max_seq_len,
+                cache.stride(0), cache.stride(1), cache.element_size(), _stream(cache),
+            )
+        )
+        return out

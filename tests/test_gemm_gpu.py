@@ -1,0 +1,156 @@
+"""GEMM parity on the GPU: CUDA kernel (through torch.ops.b200k -> C ABI) vs. the CPU oracle.
+
+Tolerances are the path's: rtol = atol = 1e-2 for f16/bf16 operands against the fp32 oracle,
+3e-2 relative for fp8 (against the fp32 product of the dequantised operands)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import iree_turbine_b200 as tb
+from iree_turbine_b200 import ops
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _run(a, b, out_dtype=None, tile_n=0):
+    a, b = a.to(DEV), b.to(DEV)
+    if tile_n == 0:
+        c = torch.ops.b200k.gemm_nt(a, b, out_dtype)
+    else:
+        c = torch.empty(a.size(0), b.size(0), dtype=out_dtype or torch.float32, device=DEV)
+        ops._launch_gemm(a, b, c, None, None, tile_n=tile_n)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0, "a kernel reported a timed-out wait"
+    return c
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 64), (128, 128, 256), (256, 512, 512)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_small_exact_tiles(m, n, k, tile_n):
+    a, b = oracle.make_gemm_inputs(m, n, k, torch.float16, seed=1)
+    oracle.assert_close_half(_run(a, b, tile_n=tile_n), oracle.gemm_nt(a, b))
+
+
+def test_golden_fixture():
+    z = np.load(os.path.join(GOLDEN, "gemm_f16_96x80x64.npz"))
+    a = torch.from_numpy(z["a"].copy()).view(torch.float16)
+    b = torch.from_numpy(z["b"].copy()).view(torch.float16)
+    oracle.assert_close_half(_run(a, b), torch.from_numpy(z["c"]))
+
+
+@pytest.mark.parametrize("m,n,k", [(200, 136, 72), (1, 8, 8), (130, 260, 1032), (1000, 24, 4096)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_ragged_shapes(m, n, k, dtype):
+    a, b = oracle.make_gemm_inputs(m, n, k, dtype, seed=2)
+    oracle.assert_close_half(_run(a, b), oracle.gemm_nt(a, b))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_half_output(dtype):
+    a, b = oracle.make_gemm_inputs(384, 200, 320, dtype, seed=3)
+    c = _run(a, b, out_dtype=dtype)
+    assert c.dtype == dtype
+    # the only extra error is the final rounding of the output (2^-11 / 2^-8 relative)
+    rt = 1e-2 if dtype == torch.float16 else 2e-2
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b), rtol=rt, atol=rt)
+
+
+def test_config_2048_cubed_f16_fp32_out():
+    a, b = oracle.make_gemm_inputs(2048, 2048, 2048, torch.float16, seed=10)
+    c = _run(a, b)
+    assert c.dtype == torch.float32 and c.shape == (2048, 2048)
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b))
+    # repeat-run determinism (catches races): bitwise equal
+    c2 = _run(a, b)
+    assert torch.equal(c, c2)
+    # both tile widths give the same math
+    oracle.assert_close_half(_run(a, b, tile_n=128), oracle.gemm_nt(a, b))
+
+
+def test_block_of_ones_lands_where_it_should():
+    """Structured indexing check (cf. the reference's block-of-ones numerics test,
+    iree/turbine/kernel/boo/driver/numerics.py:319-355)."""
+    m, n, k = 512, 768, 256
+    a = torch.zeros(m, k, dtype=torch.float16)
+    b = torch.zeros(n, k, dtype=torch.float16)
+    a[130:190, 64:128] = 1
+    b[300:517, 100:164] = 1
+    c = _run(a, b).cpu()
+    exp = torch.zeros(m, n)
+    exp[130:190, 300:517] = 28  # overlap of k ranges: 100..127
+    assert torch.equal(c, exp)
+
+
+def test_non_contiguous_inputs_are_handled():
+    a, b = oracle.make_gemm_inputs(256, 128, 192, torch.float16, seed=4)
+    a_wide = torch.zeros(256, 256, dtype=torch.float16)
+    a_wide[:, :192] = a
+    av = a_wide.to(DEV)[:, :192]  # row stride 256 elements: used in place
+    bt = b.t().contiguous().to(DEV).t()  # column-major: copied to row-major by the op
+    c = torch.ops.b200k.gemm_nt(av, bt)
+    torch.cuda.synchronize()
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b))
+
+
+def test_template_constructor_runs():
+    shape = tb.GemmShape(256, 384, 128)
+    kern = tb.get_gemm_kernel(shape, torch.bfloat16, out_dtype=torch.bfloat16)
+    a, b = oracle.make_gemm_inputs(256, 384, 128, torch.bfloat16, seed=5)
+    c = kern(a.to(DEV), b.to(DEV))
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b), rtol=2e-2, atol=2e-2)
+
+
+# ---- fp8 ----
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (200, 72, 1040)])
+def test_fp8_small(m, n, k):
+    a8, b8, sa, sb = oracle.make_fp8_gemm_inputs(m, n, k, seed=6)
+    c = torch.ops.b200k.gemm_fp8_nt(a8.to(DEV), b8.to(DEV), sa.to(DEV), sb.to(DEV))
+    torch.cuda.synchronize()
+    assert c.dtype == torch.bfloat16
+    fro, mx = oracle.fp8_errors(c, oracle.gemm_fp8_nt(a8, b8, sa, sb))
+    assert fro <= 3e-2 and mx <= 3e-2, (fro, mx)
+    c32 = torch.ops.b200k.gemm_fp8_nt(a8.to(DEV), b8.to(DEV), sa.to(DEV), sb.to(DEV), torch.float32)
+    fro32, _ = oracle.fp8_errors(c32, oracle.gemm_fp8_nt(a8, b8, sa, sb))
+    assert fro32 <= 2e-3, fro32  # products of e4m3 values are exact in fp32; only the accumulation differs
+
+
+def test_fp8_config_8192_slices():
+    """Full 8192^3 problem on the GPU; the oracle checks row/column slices (the CPU fp32 product of
+    the whole problem takes minutes) and linearity covers the rest: C(A, [B1;B2]) = [C(A,B1), C(A,B2)]."""
+    m = n = k = 8192
+    g = torch.Generator(device=DEV).manual_seed(10)
+    a = torch.randn(m, k, generator=g, device=DEV)
+    b = torch.randn(n, k, generator=g, device=DEV)
+    a8, sa = torch.ops.b200k.quantize_e4m3(a)
+    b8, sb = torch.ops.b200k.quantize_e4m3(b)
+    c = torch.ops.b200k.gemm_fp8_nt(a8, b8, sa, sb)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8191])
+    cols = torch.tensor([0, 255, 256, 4097, 8191])
+    a8c, b8c, sac, sbc = a8.cpu(), b8.cpu(), sa.cpu(), sb.cpu()
+    ref_rows = oracle.gemm_fp8_nt(a8c[rows], b8c, sac, sbc)
+    fro, mx = oracle.fp8_errors(c[rows.to(DEV)], ref_rows)
+    assert fro <= 3e-2 and mx <= 3e-2, (fro, mx)
+    ref_cols = oracle.gemm_fp8_nt(a8c, b8c[cols], sac, sbc)
+    fro, mx = oracle.fp8_errors(c[:, cols.to(DEV)], ref_cols)
+    assert fro <= 3e-2 and mx <= 3e-2, (fro, mx)
+    # column-parallel decomposition (what sharding over N computes) is bitwise the same
+    c_lo = torch.ops.b200k.gemm_fp8_nt(a8, b8[:4096], sa, sb)
+    c_hi = torch.ops.b200k.gemm_fp8_nt(a8, b8[4096:], sa, sb)
+    assert torch.equal(torch.cat([c_lo, c_hi], dim=1), c)
+
+
+def test_quantize_matches_oracle_bitwise():
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(513, 257, generator=g)
+    y, s = torch.ops.b200k.quantize_e4m3(x.to(DEV))
+    yo, so = oracle.quantize_e4m3(x)
+    assert torch.equal(s.cpu(), so)
+    assert torch.equal(y.cpu().view(torch.uint8), yo.view(torch.uint8))

@@ -1,0 +1,122 @@
+"""Pins the CPU oracle: against torch's own operators, against itself (blockwise vs. full,
+paged vs. contiguous) and against the committed fixtures in tests/golden/."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import oracle
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _from_bits(arr, bf16=False):
+    t = torch.from_numpy(arr.copy())
+    return t.view(torch.bfloat16 if bf16 else torch.float16)
+
+
+def test_gemm_matches_torch_mm_and_fixture():
+    z = np.load(os.path.join(GOLDEN, "gemm_f16_96x80x64.npz"))
+    a, b = _from_bits(z["a"]), _from_bits(z["b"])
+    a2, b2 = oracle.make_gemm_inputs(96, 80, 64, torch.float16, seed=10)
+    assert torch.equal(a, a2) and torch.equal(b, b2), "seeded input generator drifted from the fixture"
+    c = oracle.gemm_nt(a, b)
+    torch.testing.assert_close(c, torch.from_numpy(z["c"]), rtol=1e-6, atol=1e-5)
+    torch.testing.assert_close(c, torch.mm(a.float(), b.float().t()), rtol=1e-6, atol=1e-5)
+    # float64 cross-check: fp32 accumulation error is far inside the 1e-2 tolerance of the path
+    c64 = a.double() @ b.double().t()
+    assert float((c.double() - c64).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("name", ["attn_f16_noncausal", "attn_bf16_causal_gqa", "attn_f16_causal_offset"])
+def test_attention_matches_fixture(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    bf16 = bool(z["bf16"])
+    q, k, v = (_from_bits(z[n], bf16) for n in ("q", "k", "v"))
+    o = oracle.attention(q, k, v, float(z["scale"]), bool(z["causal"]))
+    torch.testing.assert_close(o, torch.from_numpy(z["o"]), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_matches_sdpa(causal):
+    q, k, v = oracle.make_attention_inputs(2, 4, 4, 96, 96, 128, torch.float16, seed=3)
+    scale = 128 ** -0.5
+    ref = F.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=causal, scale=scale)
+    torch.testing.assert_close(oracle.attention(q, k, v, scale, causal), ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("causal,sq,skv", [(False, 200, 328), (True, 256, 256), (True, 100, 300)])
+def test_blockwise_online_softmax_equals_full(causal, sq, skv):
+    q, k, v = oracle.make_attention_inputs(1, 2, 1, sq, skv, 128, torch.float16, seed=4)
+    scale = 128 ** -0.5
+    full = oracle.attention(q, k, v, scale, causal)
+    blk = oracle.attention_blockwise(q, k, v, scale, causal, 128, 128)
+    torch.testing.assert_close(blk, full, rtol=2e-5, atol=2e-5)
+    # rounding P to 16 bits before P V (what the kernels do) stays far inside the 1e-2 tolerance
+    blk16 = oracle.attention_blockwise(q, k, v, scale, causal, 128, 128, p_dtype=torch.float16)
+    assert float((blk16 - full).abs().max()) < 2e-3
+
+
+def test_quantize_e4m3_range_and_roundtrip():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(64, 96, generator=g)
+    y, s = oracle.quantize_e4m3(x)
+    assert y.dtype == torch.float8_e4m3fn and s.shape == (1,)
+    assert float(y.float().abs().max()) == 448.0
+    rel = float(((y.float() * s) - x).norm() / x.norm())
+    assert rel < 0.04  # e4m3 has 3 mantissa bits: relative rounding error <= 2^-4 per element
+    yz, sz = oracle.quantize_e4m3(torch.zeros(4, 4))
+    assert float(sz) == 1.0 and float(yz.float().abs().max()) == 0.0
+
+
+def test_fp8_gemm_oracle_is_dequantised_product():
+    a8, b8, sa, sb = oracle.make_fp8_gemm_inputs(48, 40, 64, seed=6)
+    c = oracle.gemm_fp8_nt(a8, b8, sa, sb)
+    ref = (a8.float() * sa) @ (b8.float() * sb).t()
+    torch.testing.assert_close(c, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_paged_fixture_and_index_math():
+    z = np.load(os.path.join(GOLDEN, "paged_decode_f16.npz"))
+    q, kc, vc = _from_bits(z["q"]), _from_bits(z["k_cache"]), _from_bits(z["v_cache"])
+    bt, sl = torch.from_numpy(z["block_table"]), torch.from_numpy(z["seq_lens"])
+    scale = float(z["scale"])
+    o = oracle.paged_decode_attention(q, kc, vc, bt, sl, scale)
+    torch.testing.assert_close(o, torch.from_numpy(z["o"]), rtol=1e-5, atol=1e-5)
+    # gather: bit-exact against the per-token loop stored in the fixture
+    gk = oracle.paged_gather(kc, bt, sl, int(sl.max()))
+    assert torch.equal(gk.view(torch.int16), torch.from_numpy(z["gathered_k"]))
+    # index function: every offset addresses the element the 4-D index names
+    pages, hkv, page, d = kc.shape
+    flat = kc.reshape(-1)
+    for s in range(bt.shape[0]):
+        n = int(sl[s])
+        for h in range(hkv):
+            off = oracle.paged_row_offsets(bt.numpy(), s, h, n, page, hkv, d)
+            assert off.dtype == np.int64
+            for t in (0, n // 2, n - 1) if n else ():
+                assert torch.equal(flat[off[t]:off[t] + d], kc[int(bt[s, t // page]), h, t % page])
+
+
+def test_paged_inputs_block_table_is_a_permutation():
+    q, kc, vc, bt, sl = oracle.make_paged_decode_inputs(num_seqs=8, min_len=5, max_len=200, seed=7)
+    used = bt[bt >= 0]
+    assert used.numel() == kc.shape[0]
+    assert torch.equal(torch.sort(used).values, torch.arange(kc.shape[0], dtype=torch.int32))
+    pages = (sl + 15) // 16
+    assert int(pages.sum()) == kc.shape[0]
+    for s in range(8):
+        assert (bt[s, : int(pages[s])] >= 0).all() and (bt[s, int(pages[s]):] == -1).all()
+
+
+def test_decode_equals_attention_with_one_query():
+    q, k, v = oracle.make_attention_inputs(3, 8, 2, 1, 77, 128, torch.float16, seed=8)
+    lens = torch.tensor([77, 1, 40], dtype=torch.int32)
+    o = oracle.decode_attention(q[:, :, 0], k, v, lens, 0.1)
+    for s in range(3):
+        n = int(lens[s])
+        ref = oracle.attention(q[s:s + 1], k[s:s + 1, :, :n], v[s:s + 1, :, :n], 0.1, False)
+        torch.testing.assert_close(o[s], ref[0, :, 0], rtol=1e-6, atol=1e-6)
