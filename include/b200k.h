@@ -188,6 +188,30 @@ int32_t b200k_decode_default_chunk(const b200k_decode_args* args);
 int b200k_decode_attention(const b200k_decode_args* args, void* stream);
 
 /*
+ * Decode attention for callers that cannot supply scratch memory.
+ * (No counterpart in the reference: its runtime always owns allocation.)
+ *
+ * Same arguments, same kernels and same results as b200k_decode_attention, except that
+ * args->workspace and args->workspace_bytes are ignored: the split-KV partial results go into a
+ * fixed array that is part of the library image.  Meant for hosts that pass a plug-in only its
+ * input and output buffers and keep all device allocation to themselves, and for request paths
+ * that must not call cudaMalloc (it can stall the device and can fail under fragmentation).
+ * The call performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *
+ *  - Limit: the problem's b200k_decode_workspace_bytes() must not exceed
+ *    B200K_DECODE_STATIC_SCRATCH_BYTES, otherwise B200K_ERR_WORKSPACE is returned and nothing is
+ *    launched (raise chunk_tokens or split the batch).  The array is reserved on every GPU that
+ *    loads the library, for the life of the process.
+ *  - The first call on each device looks up the array's device address (once, cached); make
+ *    that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps whatever the previous call left.
+ *    The kernels never depend on old contents, but two calls whose kernels overlap on the GPU
+ *    (different streams, no ordering) race on it: order such calls.
+ */
+#define B200K_DECODE_STATIC_SCRATCH_BYTES (32u << 20)
+int b200k_decode_attention_static(const b200k_decode_args* args, void* stream);
+
+/*
  * Gathers the K or V rows of every sequence through the block table into a contiguous buffer
  *   out[s, h, t, :] = cache[block_table[s, t / page_size], h, t % page_size, :]
  * with out laid out [num_seqs, kv_heads, max_seq_len, head_dim].  Rows t >= seq_lens[s] are

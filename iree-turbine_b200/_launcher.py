@@ -43,6 +43,9 @@ ERR_NULL = -6
 ERR_TIMEOUT = -7
 ERR_WORKSPACE = -8
 
+# Capacity of the library-owned decode scratch (B200K_DECODE_STATIC_SCRATCH_BYTES).
+DECODE_STATIC_SCRATCH_BYTES = 32 << 20
+
 # b200k_dtype
 F16, BF16, F32, E4M3 = 0, 1, 2, 3
 
@@ -146,6 +149,7 @@ EXPORTED_SYMBOLS = {
     "b200k_decode_workspace_bytes": (C.c_uint64, [C.POINTER(DecodeArgs)]),
     "b200k_decode_default_chunk": (C.c_int32, [C.POINTER(DecodeArgs)]),
     "b200k_decode_attention": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "b200k_decode_attention_static": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "b200k_paged_gather": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

@@ -184,6 +184,11 @@ int b200k_decode_attention(const b200k_decode_args* args, void* stream) {
   return launch_decode(*args, static_cast<cudaStream_t>(stream));
 }
 
+int b200k_decode_attention_static(const b200k_decode_args* args, void* stream) {
+  if (!args) return set_error(B200K_ERR_NULL, "decode_attention_static: args is NULL");
+  return launch_decode_static(*args, static_cast<cudaStream_t>(stream));
+}
+
 int b200k_paged_gather(const void* cache, const int32_t* block_table, const int32_t* seq_lens, void* out,
                        int32_t num_seqs, int32_t kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
                        int32_t block_table_stride, int32_t max_seq_len, int64_t kv_page_stride,

@@ -31,6 +31,7 @@ int encode_tmap(CUtensorMap* out, int dtype, int rank, void* base, const uint64_
 int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream);
 int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream);
 int launch_decode(const b200k_decode_args& a, cudaStream_t stream);
+int launch_decode_static(const b200k_decode_args& a, cudaStream_t stream);
 uint64_t decode_workspace_bytes(const b200k_decode_args& a);
 int32_t decode_default_chunk(const b200k_decode_args& a);
 int launch_paged_gather(const void* cache, const int32_t* block_table, const int32_t* seq_lens, void* out,

@@ -13,6 +13,7 @@
 //
 // Shared memory tile layout: 16 rows (tokens) x 256 bytes (128 halves); the 16-byte chunk c of
 // row r is stored at chunk position c ^ (r & 7) so ldmatrix reads are bank-conflict free.
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -535,6 +536,69 @@ int launch_paged_gather(const void* cache, const int32_t* block_table, const int
       reinterpret_cast<const uint8_t*>(cache), block_table, seq_lens, reinterpret_cast<uint8_t*>(out), kv_heads,
       head_dim, page_size, num_pages, block_table_stride, max_seq_len, kv_page_stride, kv_head_stride, elem_bytes);
   return check_cuda(cudaGetLastError(), "paged_gather_kernel launch");
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode with scratch that lives inside the library.
+//
+// Some callers have no way to hand over scratch memory: a host runtime that gives a plug-in
+// kernel only its input and output buffers and keeps every device allocation to itself, or a
+// serving loop that runs inside a fixed, pre-planned memory budget where cudaMalloc (which may
+// synchronize the device, and may fail once memory is fragmented) is not allowed on the request
+// path.  For them the split-KV partials go into the fixed array below instead of a caller
+// buffer.  The array is part of the loaded module, so every GPU that loads this library keeps
+// B200K_DECODE_STATIC_SCRATCH_BYTES of device memory reserved until the process exits.
+//
+// In host code `g_decode_scratch` is only a handle for the runtime, not a device address, so it
+// is never passed to a kernel directly: the address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and cached.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_decode_scratch[B200K_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_scratch_mu;
+void* g_scratch_addr[64] = {};  // indexed by device ordinal
+
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  int rc = check_cuda(cudaGetDevice(&dev), "decode_attention_static: cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) return set_error(B200K_ERR_CUDA, "decode_attention_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (!g_scratch_addr[dev]) {
+    void* addr = nullptr;
+    rc = check_cuda(cudaGetSymbolAddress(&addr, g_decode_scratch), "decode_attention_static: cudaGetSymbolAddress");
+    if (rc) return rc;
+    if (!addr) return set_error(B200K_ERR_CUDA, "decode_attention_static: scratch symbol resolved to NULL");
+    g_scratch_addr[dev] = addr;
+  }
+  *out = g_scratch_addr[dev];
+  return B200K_OK;
+}
+}  // namespace
+
+int launch_decode_static(const b200k_decode_args& a, cudaStream_t stream) {
+  int rc = validate_decode(a);
+  if (rc) return rc;
+  const uint64_t need = decode_workspace_bytes(a);
+  if (need > B200K_DECODE_STATIC_SCRATCH_BYTES)
+    return set_error(B200K_ERR_WORKSPACE,
+                     "decode_attention_static: this problem needs %llu bytes of scratch but the built-in array holds "
+                     "%llu; use a larger chunk_tokens, fewer sequences per call, or b200k_decode_attention with a "
+                     "caller-provided workspace",
+                     static_cast<unsigned long long>(need),
+                     static_cast<unsigned long long>(B200K_DECODE_STATIC_SCRATCH_BYTES));
+  rc = ensure_sm100();
+  if (rc) return rc;
+  void* scratch = nullptr;
+  rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  // Nothing in the scratch has to start at zero: the reduction reads only the slots of chunks
+  // below ceil(len / chunk) of each sequence, and phase 1 of the same call writes exactly those.
+  b200k_decode_args with_scratch = a;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_bytes = B200K_DECODE_STATIC_SCRATCH_BYTES;
+  return launch_decode(with_scratch, stream);
 }
 
 }  // namespace b200k
