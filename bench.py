@@ -49,6 +49,9 @@ def load_peaks():
 # workloads
 # ---------------------------------------------------------------------------------------------
 class Workload:
+    # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, one launch, from the ncu
+    # capture summarised under profiles/ (None = no capture for this workload yet)
+    traffic_bytes = None
     name = ""
     metric = ""
     unit = "TFLOP/s"
@@ -70,8 +73,9 @@ class Workload:
 
 
 class AttentionWL(Workload):
-    def __init__(self, name, batch, heads, seq, dtype, causal, std):
+    def __init__(self, name, batch, heads, seq, dtype, causal, std, traffic=None):
         self.name = name
+        self.traffic_bytes = traffic
         self.b, self.h, self.s = batch, heads, seq
         self.tdtype = dtype
         self.dtype = "f16" if dtype == torch.float16 else "bf16"
@@ -137,6 +141,7 @@ class GemmWL(Workload):
 
     def __init__(self, name, n, fp8):
         self.name, self.n, self.fp8 = name, n, fp8
+        self.traffic_bytes = None if fp8 else 16.8e6
         self.dtype = "e4m3" if fp8 else "f16"
         out = "bf16" if fp8 else "f32"
         self.metric = f"GEMM TFLOP/s ({self.dtype} NT M=N=K={n}, fp32 accumulate, {out} out)"
@@ -209,6 +214,8 @@ class PagedDecodeWL(Workload):
     launches_per_step = 2
     metric = "paged-decode HBM GB/s (f16, 64 seqs, 32 q-heads / 8 kv-heads, D128, len U[512,8192], page 16)"
 
+    traffic_bytes = 1178.0e6
+
     def __init__(self, name):
         self.name = name
 
@@ -267,7 +274,7 @@ class PagedDecodeWL(Workload):
 
 
 WORKLOADS = {
-    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0),
+    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 245.9e6),
     "attn_causal": lambda: AttentionWL("attn_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
     "gemm_f16": lambda: GemmWL("gemm_f16", 2048, False),
     "gemm_fp8": lambda: GemmWL("gemm_fp8", 8192, True),
@@ -442,7 +449,7 @@ def run_ours(wl: Workload, args) -> dict:
         "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(),
         "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": wl.unit,
-                     "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"] + " (burst)",
+                     "frac": achieved / peak, "traffic": wl.traffic_bytes, "peak_source": peaks["source"] + " (burst)",
                      "min_ms": min(ms), "median_ms": statistics.median(ms)},
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
