@@ -3,10 +3,13 @@
 // One CTA owns 256 query rows of one (batch, head): two 128-row query tiles that ping-pong on
 // the tensor core so that the softmax of one tile overlaps the MMAs of the other.
 //
-//   warp 0        TMA loads: Q tiles once, then K_j and V_j into two 2-stage rings
-//   warp 1        issues every tcgen05.mma and owns tensor memory
-//   warps 2..5    softmax + correction + epilogue for query tile 0
-//   warps 6..9    the same for query tile 1
+//   warps 0..3    softmax + correction + epilogue for query tile 0   (warpgroup 0)
+//   warps 4..7    the same for query tile 1                          (warpgroup 1)
+//   warp 8        TMA loads: Q tiles once, then K_j and V_j into two 2-stage rings
+//   warp 9        issues every tcgen05.mma and owns tensor memory
+//   warps 10, 11  idle; they complete warpgroup 2 so that it can hand its registers
+//                 (setmaxnreg) to the two softmax warpgroups, which keep a whole score row
+//                 (128 fp32) per thread in registers
 //
 // Tensor memory (512 columns x 128 lanes):  S0 | S1 | O0 | O1, 128 fp32 columns each.  The
 // probabilities P (16-bit, two per column) overwrite the first 64 columns of their S tile and
@@ -28,7 +31,11 @@
 namespace b200k {
 namespace {
 
-constexpr int kAttnThreads = 320;
+constexpr int kAttnThreads = 384;
+constexpr int kRegsSoftmax = 216;  // per SM sub-partition the CTA owns 3 warps x 168 registers = 504 per lane at launch;
+                                    // setmaxnreg only redistributes that: 2*216 + 72 = 504 (anything larger never completes);
+                                    // this split compiles both roles without spills
+constexpr int kRegsOther = 72;
 constexpr int kTileRows = 128;  // query rows per tile, KV rows per tile
 constexpr int kD = 128;
 constexpr int kHalfTileBytes = kTileRows * 128;     // one 64-element column block: 16 KB
@@ -58,6 +65,28 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// 2^x for a pair on the FMA pipe instead of the special-function unit: x = j + f with j = rint(x)
+// taken from the low mantissa bits of x + 1.5 * 2^23, 2^f on [-0.5, 0.5] by a degree-3 polynomial
+// (max relative error 7.5e-5, far below the rounding of P to 16 bits), exponent added as an integer.
+// Inputs below -125 (including -inf from masking) give about 2^-125, which rounds to nothing in P.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = fadd2(x, make_float2(12582912.f, 12582912.f));
+  const float2 j = fadd2(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = ffma2(j, make_float2(-1.f, -1.f), x);
+  float2 p = ffma2(f, make_float2(0.0551716648f, 0.0551716648f), make_float2(0.2426111251f, 0.2426111251f));
+  p = ffma2(p, f, make_float2(0.6932609677f, 0.6932609677f));
+  p = ffma2(p, f, make_float2(0.9999280572f, 0.9999280572f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
+// Which of every 8 consecutive column pairs take the polynomial instead of ex2.approx (bit i = pair i).
+constexpr uint32_t kPolyPairMask = 0x92u;  // 3 of 8
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
 template <>
@@ -78,6 +107,25 @@ __device__ __forceinline__ int kv_tiles_for(int r0, const AttnParams& p, int kv_
   if (last_col < 0) return 0;
   return min(last_col / kTileRows + 1, kv_tiles_total);
 }
+
+// Optional timeline capture (compile with -DB200K_ATTN_TRACE): block (0,0,0) records
+// (tag, clock64) pairs per role into the buffer passed as the status pointer, 256 events per role:
+// role 0 = TMA thread, 1 = MMA thread, 2 = softmax tile 0 (thread 0), 3 = softmax tile 1.
+#ifdef B200K_ATTN_TRACE
+#define ATTN_TRACE(role, tag)                                                          \
+  do {                                                                                 \
+    if (trace_on && trace_n < 256) {                                                   \
+      long long* tb = reinterpret_cast<long long*>(p.status) + ((role)*256 + trace_n) * 2; \
+      tb[0] = (tag);                                                                   \
+      tb[1] = clock64();                                                               \
+      ++trace_n;                                                                       \
+    }                                                                                  \
+  } while (0)
+#else
+#define ATTN_TRACE(role, tag) \
+  do {                        \
+  } while (0)
+#endif
 
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -103,6 +151,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef B200K_ATTN_TRACE
+  const bool trace_on = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && p.status != nullptr && lane == 0;
+  int trace_n = 0;
+#endif
 
   // Heaviest blocks first: under a causal mask the last query rows see the most keys.
   const int qblock = p.num_q_blocks - 1 - static_cast<int>(blockIdx.x);
@@ -131,7 +183,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
   }
-  if (warp == 1) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -140,7 +192,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp >= 8) {
+    // Warpgroup 2 (TMA, MMA, two idle warps) gives registers back for the softmax warpgroups.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+    if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0 && n1 > 0) {
       mbar_arrive_expect_tx(q_full, 2 * kTileBytes);
@@ -154,12 +209,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(k_empty + st, ph ^ 1, abort_word)) break;
+        ATTN_TRACE(0, 100 + j);
         mbar_arrive_expect_tx(k_full + st, kTileBytes);
 #pragma unroll
         for (int db = 0; db < 2; ++db)
           tma_load_4d(smem + kKOffset + st * kTileBytes + db * kHalfTileBytes, &tmap_k, k_full + st, db * 64,
                       j * kTileRows, kv_head, batch);
         if (!mbar_wait(v_empty + st, ph ^ 1, abort_word)) break;
+        ATTN_TRACE(0, 200 + j);
         mbar_arrive_expect_tx(v_full + st, kTileBytes);
 #pragma unroll
         for (int db = 0; db < 2; ++db)
@@ -168,29 +225,49 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+    } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && n1 > 0) {
       const uint32_t sq = smem_u32(smem + kQOffset);
       const uint32_t sk = smem_u32(smem + kKOffset);
       const uint32_t sv = smem_u32(smem + kVOffset);
+      // The issuing thread runs scalar, latency-bound code, and a 128x128x16 MMA lasts only 64
+      // cycles, so the per-MMA issue cost must stay at a handful of instructions: descriptors are
+      // split into a constant high word and a low word that is a precomputed base plus a
+      // compile-time offset.
+      const uint32_t hi_k = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
+      const uint32_t hi_mn = static_cast<uint32_t>(make_desc_mnmajor_sw128(0, kHalfTileBytes) >> 32);
+      const uint32_t q_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sq));
+      const uint32_t k_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sk));
+      const uint32_t v_lo = static_cast<uint32_t>(make_desc_mnmajor_sw128(sv, kHalfTileBytes));
+      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
       // S_tile = Q_tile K^T : 8 k-steps of 16 over the head dimension (two 64-wide blocks).
       auto issue_s = [&](int tile, int kstage) {
+        const uint32_t a0 = q_lo + tile * (kTileBytes >> 4);
+        const uint32_t b0 = k_lo + kstage * (kTileBytes >> 4);
+        const uint32_t d = tmem_base + tile * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t a_desc = make_desc_kmajor_sw128(sq + tile * kTileBytes + (ks >> 2) * kHalfTileBytes) + 2 * (ks & 3);
-          const uint64_t b_desc = make_desc_kmajor_sw128(sk + kstage * kTileBytes + (ks >> 2) * kHalfTileBytes) + 2 * (ks & 3);
-          umma_f16_ss(tmem_base + tile * 128, a_desc, b_desc, kIdescS, ks > 0 ? 1u : 0u);
+          const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
+          umma_f16_ss(d, desc(a0 + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
         }
         umma_commit(s_full + tile);
       };
       // O_tile += P_tile V : 8 k-steps of 16 KV rows; A from tensor memory, B = V (MN-major).
       auto issue_pv = [&](int tile, int vstage, bool first) {
-        const uint64_t b_desc0 = make_desc_mnmajor_sw128(sv + vstage * kTileBytes, kHalfTileBytes);
+        const uint32_t b0 = v_lo + vstage * (kTileBytes >> 4);
+        const uint32_t d = tmem_base + 256 + tile * 128;
+        const uint32_t a = tmem_base + tile * 128;
+        umma_f16_ts(d, a, desc(b0, hi_mn), kIdescPV, first ? 0u : 1u);
+#ifdef B200K_ATTN_TRACE_FINE
+        ATTN_TRACE(1, 7000);
+#endif
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          umma_f16_ts(tmem_base + 256 + tile * 128, tmem_base + tile * 128 + ks * 8, b_desc0 + ks * (2048 >> 4),
-                      kIdescPV, (!first || ks > 0) ? 1u : 0u);
+        for (int ks = 1; ks < 8; ++ks) {
+          umma_f16_ts(d, a + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, 1u);
+#ifdef B200K_ATTN_TRACE_FINE
+          ATTN_TRACE(1, 7000 + ks);
+#endif
         }
         umma_commit(o_done + tile);
       };
@@ -198,9 +275,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       bool ok = mbar_wait(q_full, 0, abort_word) && mbar_wait(k_full + 0, 0, abort_word);
       if (ok) {
         tc_fence_after();
+        ATTN_TRACE(1, 1000);
         if (n0 > 0) issue_s(0, 0);
         issue_s(1, 0);
         umma_commit(k_empty + 0);
+        ATTN_TRACE(1, 1001);
       }
       for (int j = 0; j < n1 && ok; ++j) {
         const int st = j & 1;
@@ -209,30 +288,40 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         const int nst = (j + 1) & 1;
         const uint32_t nph = ((j + 1) >> 1) & 1;
         if (!mbar_wait(v_full + st, ph, abort_word)) { ok = false; break; }
+        ATTN_TRACE(1, 2000 + j);  // V_j landed
         if (j < n0) {
           if (!mbar_wait(p_full + 0, j & 1, abort_word)) { ok = false; break; }
           tc_fence_after();
+          ATTN_TRACE(1, 3000 + j);  // P0_j ready, issuing PV0_j
           issue_pv(0, st, j == 0);
+          ATTN_TRACE(1, 3500 + j);  // PV0_j issued
         }
         if (has_next) {
           if (!mbar_wait(k_full + nst, nph, abort_word)) { ok = false; break; }
           tc_fence_after();
+          ATTN_TRACE(1, 4000 + j);  // K_{j+1} landed, issuing S0_{j+1}
           if (j + 1 < n0) issue_s(0, nst);
+          ATTN_TRACE(1, 4500 + j);  // S0_{j+1} issued
         }
         if (!mbar_wait(p_full + 1, j & 1, abort_word)) { ok = false; break; }
         tc_fence_after();
+        ATTN_TRACE(1, 5000 + j);  // P1_j ready, issuing PV1_j (+ S1_{j+1})
         issue_pv(1, st, j == 0);
+        ATTN_TRACE(1, 5500 + j);  // PV1_j issued
         umma_commit(v_empty + st);
         if (has_next) {
           issue_s(1, nst);
           umma_commit(k_empty + nst);
         }
+        ATTN_TRACE(1, 6000 + j);
       }
     }
     __syncwarp();
+    }
   } else {
     // ---------------- softmax / correction / epilogue ----------------
-    const int tile = (warp - 2) >> 2;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int tile = warp >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const int tile_r0 = qblock * 256 + tile * kTileRows;
@@ -244,14 +333,22 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const float scale_log2 = p.scale_log2;
 
     float m_used = -INFINITY;
-    float l = 0.f;
+    float2 l2 = make_float2(0.f, 0.f);
     bool ok = true;
     for (int j = 0; j < n_mine; ++j) {
       ok = mbar_wait(s_full + tile, j & 1, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (quarter == 0) ATTN_TRACE(2 + tile, 100 + j);  // S_j visible
 
+#ifdef B200K_ATTN_EXPERIMENT_NO_SOFTMAX
+      // timing experiment: hand P back immediately (results are meaningless)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + tile);
+      continue;
+#endif
       const int col0 = j * kTileRows;
       const bool need_mask =
           (p.causal && col0 + kTileRows - 1 > tile_r0 + p.causal_offset) || (col0 + kTileRows > p.seq_kv);
@@ -262,22 +359,36 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         limit = vis - col0;
       }
 
-      // pass 1: row max
-      float mx = -INFINITY;
+      // The whole score row (128 fp32) lives in registers: load it in two halves so the max of
+      // the first half overlaps the load of the second.
+      uint32_t sr[128];
+      tmem_ld_32x32b_x64(t_s, sr);
+      tmem_wait_ld();
+      tmem_ld_32x32b_x64(t_s + 64, sr + 64);
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, r);
-        tmem_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c * 32 + i < limit) ? __uint_as_float(r[i]) : -INFINITY);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < 64; ++i)
+          if (i >= limit) sr[i] = 0xff800000u;  // -inf
       }
-      const float m_new = mx * scale_log2;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+      }
+      tmem_wait_ld();
+      if (need_mask) {
+#pragma unroll
+        for (int i = 64; i < 128; ++i)
+          if (i >= limit) sr[i] = 0xff800000u;
+      }
+#pragma unroll
+      for (int i = 64; i < 128; i += 4) {
+        mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+      }
+      if (quarter == 0) ATTN_TRACE(2 + tile, 200 + j);  // row loaded, max done
+      const float m_new = fmaxf(mx0, mx1) * scale_log2;
       const bool grow = m_new > m_used + kRescaleThreshold;  // also true for the first finite max
       float alpha = 1.f;
       if (grow) {
@@ -296,33 +407,33 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           tmem_st_32x32b_x32(t_o + c * 32, r);
         }
       }
-      l *= alpha;
+      l2.x *= alpha;
+      l2.y *= alpha;
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      const float2 scale2 = make_float2(scale_log2, scale_log2);
+      const float2 negm2 = make_float2(-m_sub, -m_sub);
 
-      // pass 2: probabilities -> tensor memory (16-bit pairs over the first 64 columns of S)
+      // probabilities -> tensor memory (16-bit pairs over the first 64 columns of S); masked
+      // scores are -inf and give exactly 0
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, r);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float e0 = ex2(fmaf(__uint_as_float(r[2 * i]), scale_log2, -m_sub));
-          float e1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2, -m_sub));
-          if (need_mask) {
-            if (c * 32 + 2 * i >= limit) e0 = 0.f;
-            if (c * 32 + 2 * i + 1 >= limit) e1 = 0.f;
-          }
-          l += e0 + e1;
-          pk[i] = pack_pair<T>(e0, e1);
+          const float2 x = ffma2(make_float2(__uint_as_float(sr[c * 32 + 2 * i]), __uint_as_float(sr[c * 32 + 2 * i + 1])),
+                                 scale2, negm2);
+          const float2 e = ((kPolyPairMask >> (i & 7)) & 1u) ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
+          l2 = fadd2(l2, e);
+          pk[i] = pack_pair<T>(e.x, e.y);
         }
         tmem_st_32x32b_x16(t_s + c * 16, pk);
       }
+      if (quarter == 0) ATTN_TRACE(2 + tile, 300 + j);  // exponentials issued, P stores issued
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + tile);
+      if (quarter == 0) ATTN_TRACE(2 + tile, 400 + j);  // P signalled
     }
 
     // ---- epilogue: O / l -> global ----
@@ -332,6 +443,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     if (ok) {
       tc_fence_after();
+      const float l = l2.x + l2.y;
       const float inv = (l > 0.f) ? 1.0f / l : 0.f;
       T* orow = reinterpret_cast<T*>(p.o) + batch * p.o_stride_b + head * p.o_stride_h +
                 static_cast<int64_t>(q_row) * p.o_stride_s;
@@ -370,7 +482,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusAttnTimeout);
     __syncthreads();
   }
-  if (warp == 1) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
