@@ -96,7 +96,7 @@ typedef struct b200k_gemm_args {
   const float* scale_b; /* device scalar, E4M3 only, may be NULL (= 1.0) */
   int32_t* status;      /* device status word, may be NULL */
   int32_t tile_n;       /* 0 = choose; else 128 or 256 */
-  int32_t reserved;
+  int32_t tile_m;       /* 0 = choose; else 128 or 256 (256 needs tile_n 256 or 0) */
 } b200k_gemm_args;
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);

@@ -76,7 +76,7 @@ class GemmArgs(C.Structure):
         ("scale_b", C.c_void_p),
         ("status", C.c_void_p),
         ("tile_n", C.c_int32),
-        ("reserved", C.c_int32),
+        ("tile_m", C.c_int32),
     ]
 
 

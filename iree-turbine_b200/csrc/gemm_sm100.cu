@@ -2,6 +2,10 @@
 // accumulators in tensor memory, persistent CTAs with double-buffered accumulators so the
 // epilogue of one tile overlaps the main loop of the next.
 //
+// Tile shapes.  A 128 x 256 tile needs 96 bytes of operands per tensor-core cycle, more than an
+// SM can pull from L2, so large problems use a 256 x 256 tile: two 128-row halves share each B
+// stage (64 bytes per cycle) at the price of a single, not double-buffered, accumulator set.
+//
 // CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs,
 // warps 2..5 drain accumulators (each warp its own 32-lane quarter of tensor memory).
 //
@@ -9,6 +13,8 @@
 // stage holds a 128 x 128-byte tile of A and a BN x 128-byte tile of B, written by TMA with the
 // 128-byte swizzle; each UMMA consumes 32 bytes of K (16 half-precision or 32 fp8 elements), so
 // a stage feeds four MMAs whose descriptors advance by 32 bytes inside the swizzle atom.
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -29,17 +35,21 @@ struct GemmParams {
   int32_t* status;
   int64_t ldc;
   int32_t m, n;
-  int32_t tiles_m, tiles_n, num_kb;
+  int32_t tiles_m, tiles_n, num_kb;  // tiles_m counts MT * 128-row tiles
   int32_t vec_store_ok;
+  int32_t tma_store_ok;  // C is 16-byte aligned with a 16-byte-multiple row pitch: epilogue uses TMA stores
 };
 
-template <int BN>
+template <int BN, int MT>
 struct GemmSmem {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
-  static constexpr int kABytes = kBM * kBKBytes;
+  static constexpr int kStages = MT == 2 ? 3 : (BN == 256 ? 4 : 6);
+  static constexpr int kABytes = MT * kBM * kBKBytes;
   static constexpr int kBBytes = BN * kBKBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  // epilogue staging: per epilogue warp two 32-row x 128-byte buffers (TMA store source)
+  static constexpr int kStagingOffset = kStages * kStageBytes;
+  static constexpr int kStagingBytes = 4 * 2 * 32 * 128;
+  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack for 1024-byte alignment of the tiles
@@ -101,15 +111,19 @@ __device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t (&r)[32], 
   }
 }
 
-template <int BN, int KIND, typename OutT>
+template <int BN, int MT, int KIND, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const GemmParams p) {
-  using S = GemmSmem<BN>;
+                   const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+  using S = GemmSmem<BN, MT>;
   constexpr int kElemsPerStage = (KIND == kKindE4M3) ? 128 : 64;  // K elements in 128 bytes
   constexpr uint32_t kFmt = (KIND == kKindBF16) ? kFmtBF16 : (KIND == kKindF16 ? kFmtF16 : kFmtE4M3);
   constexpr uint32_t kIdesc = make_idesc(kFmt, kFmt, kBM, BN, 0, 0);
   constexpr uint32_t kTmemCols = 2 * BN;
+  // MT == 1: two accumulator buffers of BN columns (epilogue overlaps the next tile's main loop);
+  // MT == 2: one buffer holding the two 128-row halves side by side.
+  constexpr int kAccBufs = MT == 1 ? 2 : 1;
+  constexpr int kTileM = MT * kBM;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -137,6 +151,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     fence_proxy_async_smem();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -165,7 +180,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           uint8_t* sa = smem + stage * S::kStageBytes;
           mbar_arrive_expect_tx(full + stage, S::kStageBytes);
-          tma_load_2d(sa, &tmap_a, full + stage, kb * kElemsPerStage, tm * kBM);
+          tma_load_2d(sa, &tmap_a, full + stage, kb * kElemsPerStage, tm * kTileM);
           tma_load_2d(sa + S::kABytes, &tmap_b, full + stage, kb * kElemsPerStage, tn * BN);
           if (++stage == S::kStages) {
             stage = 0;
@@ -182,31 +197,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      // Descriptors: constant high word; low word = precomputed stage base + compile-time offset, so
+      // the scalar issue path stays a few instructions per MMA.
+      const uint32_t hi = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
+      const uint32_t lo0 = static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem)));
+      auto desc = [](uint32_t lo, uint32_t h) { return (static_cast<uint64_t>(h) << 32) | lo; };
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
-        const int acc = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
+        const int acc = it % kAccBufs;
+        const uint32_t acc_phase = (it / kAccBufs) & 1;
         if (!mbar_wait(tempty + acc, acc_phase ^ 1, abort_word)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (MT == 1 ? acc * BN : 0);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(full + stage, phase, abort_word)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
-          const uint64_t a_desc = make_desc_kmajor_sw128(sa);
-          const uint64_t b_desc = make_desc_kmajor_sw128(sa + S::kABytes);
+          const uint32_t a_lo = lo0 + stage * (S::kStageBytes >> 4);
+          const uint32_t b_lo = a_lo + (S::kABytes >> 4);
+          const uint32_t accum0 = kb != 0 ? 1u : 0u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
-            if constexpr (KIND == kKindE4M3)
-              umma_f8_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, accum);
-            else
-              umma_f16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, accum);
+            const uint32_t accum = k == 0 ? accum0 : 1u;
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {
+              const uint64_t a_desc = desc(a_lo + h * ((kBM * kBKBytes) >> 4) + 2 * k, hi);
+              const uint64_t b_desc = desc(b_lo + 2 * k, hi);
+              if constexpr (KIND == kKindE4M3)
+                umma_f8_ss(d_tmem + h * BN, a_desc, b_desc, kIdesc, accum);
+              else
+                umma_f16_ss(d_tmem + h * BN, a_desc, b_desc, kIdesc, accum);
+            }
           }
           umma_commit(empty + stage);  // frees the stage once these MMAs have read it
           if (++stage == S::kStages) {
@@ -228,33 +253,91 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       scale = sa * sb;
     }
     OutT* cbase = reinterpret_cast<OutT*>(p.c);
+    uint8_t* staging = smem + S::kStagingOffset + (warp - 2) * (2 * 4096);
+    uint32_t stg_count = 0;
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
+      const int acc = it % kAccBufs;
+      const uint32_t acc_phase = (it / kAccBufs) & 1;
       bool ok = mbar_wait(tfull + acc, acc_phase, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = tm * kBM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll
+      for (int h = 0; h < MT; ++h) {
+        const int row0 = tm * kTileM + h * kBM + quarter * 32;
+        const int row = row0 + lane;
+        const uint32_t taddr =
+            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (MT == 1 ? acc * BN : h * BN);
+        if (p.tma_store_ok) {
+          // 128 bytes of each of this warp's 32 rows per step: registers -> swizzled staging
+          // buffer -> one TMA store (full 128-byte lines, clipped at the matrix edge by the
+          // tensor map).  Two buffers per warp; a buffer is reused once its store has been read.
+          constexpr int kCols = 128 / static_cast<int>(sizeof(OutT));
+#pragma unroll 1
+          for (int c = 0; c < BN / kCols; ++c) {
+            uint8_t* buf = staging + (stg_count & 1) * 4096;
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            uint4 v[8];
+            if constexpr (sizeof(OutT) == 4) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(taddr + c * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                v[i] = make_uint4(__float_as_uint(__uint_as_float(r[4 * i]) * scale),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 1]) * scale),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 2]) * scale),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 3]) * scale));
+            } else {
+              uint32_t r[64];
+              tmem_ld_32x32b_x64(taddr + c * 64, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                union {
+                  uint4 u;
+                  OutT e[8];
+                } pk;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * scale);
+                v[i] = pk.u;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((i ^ (lane & 7)) << 4)) = v[i];
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, buf, tn * BN + c * kCols, row0);
+              tma_store_commit();
+            }
+            ++stg_count;
+          }
+        } else {
 #pragma unroll 2
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_wait_ld();
-        const int col = tn * BN + c * 32;
-        if (row < p.m && col < p.n) {
-          store_chunk<OutT>(cbase + static_cast<int64_t>(row) * p.ldc + col, r, scale, p.n - col,
-                            p.vec_store_ok != 0);
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, r);
+            tmem_wait_ld();
+            const int col = tn * BN + c * 32;
+            if (row < p.m && col < p.n) {
+              store_chunk<OutT>(cbase + static_cast<int64_t>(row) * p.ldc + col, r, scale, p.n - col,
+                                p.vec_store_ok != 0);
+            }
+          }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + acc);
     }
+    if (lane == 0) tma_store_wait<0>();  // staging memory must outlive the last stores
+    __syncwarp();
   }
 
   // ---------------- teardown ----------------
@@ -275,10 +358,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-template <int BN, int KIND, typename OutT>
-int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  using S = GemmSmem<BN>;
-  auto kfn = gemm_nt_kernel<BN, KIND, OutT>;
+template <int BN, int MT, int KIND, typename OutT>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
+               cudaStream_t stream) {
+  using S = GemmSmem<BN, MT>;
+  auto kfn = gemm_nt_kernel<BN, MT, KIND, OutT>;
   static bool configured = false;  // per instantiation; benign race (idempotent attribute set)
   if (!configured) {
     int rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
@@ -286,25 +370,25 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
     if (rc) return rc;
     configured = true;
   }
-  kfn<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tb, p);
+  kfn<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tb, tc, p);
   return check_cuda(cudaGetLastError(), "gemm_nt_kernel launch");
 }
 
-template <int BN>
-int dispatch_dtype(int in_dtype, int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-                   int grid, cudaStream_t stream) {
+template <int BN, int MT>
+int dispatch_dtype(int in_dtype, int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                   const GemmParams& p, int grid, cudaStream_t stream) {
   if (in_dtype == B200K_F16 && out_dtype == B200K_F32)
-    return launch_one<BN, kKindF16, float>(ta, tb, p, grid, stream);
+    return launch_one<BN, MT, kKindF16, float>(ta, tb, tc, p, grid, stream);
   if (in_dtype == B200K_F16 && out_dtype == B200K_F16)
-    return launch_one<BN, kKindF16, __half>(ta, tb, p, grid, stream);
+    return launch_one<BN, MT, kKindF16, __half>(ta, tb, tc, p, grid, stream);
   if (in_dtype == B200K_BF16 && out_dtype == B200K_F32)
-    return launch_one<BN, kKindBF16, float>(ta, tb, p, grid, stream);
+    return launch_one<BN, MT, kKindBF16, float>(ta, tb, tc, p, grid, stream);
   if (in_dtype == B200K_BF16 && out_dtype == B200K_BF16)
-    return launch_one<BN, kKindBF16, __nv_bfloat16>(ta, tb, p, grid, stream);
+    return launch_one<BN, MT, kKindBF16, __nv_bfloat16>(ta, tb, tc, p, grid, stream);
   if (in_dtype == B200K_E4M3 && out_dtype == B200K_BF16)
-    return launch_one<BN, kKindE4M3, __nv_bfloat16>(ta, tb, p, grid, stream);
+    return launch_one<BN, MT, kKindE4M3, __nv_bfloat16>(ta, tb, tc, p, grid, stream);
   if (in_dtype == B200K_E4M3 && out_dtype == B200K_F32)
-    return launch_one<BN, kKindE4M3, float>(ta, tb, p, grid, stream);
+    return launch_one<BN, MT, kKindE4M3, float>(ta, tb, tc, p, grid, stream);
   return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: unsupported dtype pair in=%d out=%d", in_dtype, out_dtype);
 }
 
@@ -327,17 +411,31 @@ int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream) {
     return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt: C is not aligned to its element size");
   if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_n must be 0, 128 or 256");
+  if (a.tile_m != 0 && a.tile_m != 128 && a.tile_m != 256)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_m must be 0, 128 or 256");
   int rc = ensure_sm100();
   if (rc) return rc;
 
   const int sms = num_sms();
-  const int tiles_m = static_cast<int>((a.m + kBM - 1) / kBM);
-  auto waves_cost = [&](int bn) {
-    const int64_t tiles = static_cast<int64_t>(tiles_m) * ((a.n + bn - 1) / bn);
-    return ((tiles + sms - 1) / sms) * bn;
+  // Tile choice: estimated time = waves * tile area / efficiency, where a 128-row tile is limited
+  // by operand delivery (96 bytes per tensor-core cycle) and a 256 x 256 tile is not.
+  auto cost = [&](int bm, int bn) {
+    const int64_t tiles = ((a.m + bm - 1) / bm) * ((a.n + bn - 1) / bn);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    // measured: 256 x 256 tiles are 4..9% faster per flop than 128 x 256 on large problems
+    const double eff = bm == 256 ? 0.72 : 0.67;
+    return static_cast<double>(waves) * bm * bn / eff;
   };
-  int bn = a.tile_n;
-  if (bn == 0) bn = (a.n > 128 && waves_cost(256) <= waves_cost(128)) ? 256 : 128;
+  int bm = a.tile_m, bn = a.tile_n;
+  if (bm == 256 && bn == 0) bn = 256;
+  if (bn == 0) {
+    bn = (a.n > 128 && cost(128, 256) <= cost(128, 128)) ? 256 : 128;
+    if (bm == 0) bm = (bn == 256 && a.m > 128 && cost(256, 256) < cost(128, 256)) ? 256 : 128;
+  }
+  if (bm == 0) bm = 128;
+  if (bm == 256 && bn != 256)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_m 256 requires tile_n 256");
+  const int tiles_m = static_cast<int>((a.m + bm - 1) / bm);
   const int tiles_n = static_cast<int>((a.n + bn - 1) / bn);
   const int k_per_stage = a.in_dtype == B200K_E4M3 ? 128 : 64;
 
@@ -345,7 +443,7 @@ int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream) {
   {
     uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m)};
     uint64_t strides[1] = {static_cast<uint64_t>(a.lda) * in_es};
-    uint32_t box[2] = {static_cast<uint32_t>(k_per_stage), static_cast<uint32_t>(kBM)};
+    uint32_t box[2] = {static_cast<uint32_t>(k_per_stage), static_cast<uint32_t>(bm)};
     rc = encode_tmap(&ta, a.in_dtype, 2, const_cast<void*>(a.a), dims, strides, box);
     if (rc) return rc;
   }
@@ -370,10 +468,21 @@ int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream) {
   p.num_kb = static_cast<int32_t>((a.k + k_per_stage - 1) / k_per_stage);
   p.vec_store_ok = ((reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && (a.ldc * out_es) % 16 == 0) ? 1 : 0;
 
+  p.tma_store_ok = p.vec_store_ok;
+  CUtensorMap tc;
+  memset(&tc, 0, sizeof(tc));
+  if (p.tma_store_ok) {
+    uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m)};
+    uint64_t strides[1] = {static_cast<uint64_t>(a.ldc) * out_es};
+    uint32_t box[2] = {static_cast<uint32_t>(128 / out_es), 32u};
+    rc = encode_tmap(&tc, a.out_dtype, 2, a.c, dims, strides, box);
+    if (rc) return rc;
+  }
   const int64_t num_tiles = static_cast<int64_t>(tiles_m) * tiles_n;
   const int grid = static_cast<int>(num_tiles < sms ? num_tiles : sms);
-  if (bn == 256) return dispatch_dtype<256>(a.in_dtype, a.out_dtype, ta, tb, p, grid, stream);
-  return dispatch_dtype<128>(a.in_dtype, a.out_dtype, ta, tb, p, grid, stream);
+  if (bm == 256) return dispatch_dtype<256, 2>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
+  if (bn == 256) return dispatch_dtype<256, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
+  return dispatch_dtype<128, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
 }
 
 }  // namespace b200k

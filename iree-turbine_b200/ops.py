@@ -92,7 +92,7 @@ def _gemm_out_dtype(in_dtype: torch.dtype, out_dtype) -> torch.dtype:
     return od
 
 
-def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: int = 0) -> None:
+def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: int = 0, tile_m: int = 0) -> None:
     a = _row_major_2d(a)
     b = _row_major_2d(b)
     args = L.GemmArgs()
@@ -105,6 +105,7 @@ def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: in
     args.scale_b = scale_b.data_ptr() if scale_b is not None else None
     args.status = _status_ptr(a.device)
     args.tile_n = tile_n
+    args.tile_m = tile_m
     L.check(L.lib().b200k_gemm_nt(C.byref(args), _stream(a)))
 
 

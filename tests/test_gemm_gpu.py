@@ -18,13 +18,13 @@ DEV = "cuda"
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-def _run(a, b, out_dtype=None, tile_n=0):
+def _run(a, b, out_dtype=None, tile_n=0, tile_m=0):
     a, b = a.to(DEV), b.to(DEV)
-    if tile_n == 0:
+    if tile_n == 0 and tile_m == 0:
         c = torch.ops.b200k.gemm_nt(a, b, out_dtype)
     else:
         c = torch.empty(a.size(0), b.size(0), dtype=out_dtype or torch.float32, device=DEV)
-        ops._launch_gemm(a, b, c, None, None, tile_n=tile_n)
+        ops._launch_gemm(a, b, c, None, None, tile_n=tile_n, tile_m=tile_m)
     torch.cuda.synchronize()
     assert tb.device_status() == 0, "a kernel reported a timed-out wait"
     return c
@@ -42,6 +42,17 @@ def test_golden_fixture():
     a = torch.from_numpy(z["a"].copy()).view(torch.float16)
     b = torch.from_numpy(z["b"].copy()).view(torch.float16)
     oracle.assert_close_half(_run(a, b), torch.from_numpy(z["c"]))
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 320), (300, 300, 136), (1, 8, 8), (1280, 2304, 512)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_256x256_tiles(m, n, k, dtype):
+    """Forced 256 x 256 tiles (two 128-row halves sharing each B stage), exact and ragged shapes;
+    1280 x 2304 gives 45 tiles so several CTAs run more than one tile through the single accumulator set."""
+    a, b = oracle.make_gemm_inputs(m, n, k, dtype, seed=8)
+    c = _run(a, b, tile_m=256)
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b))
+    assert torch.equal(c, _run(a, b, tile_m=256))
 
 
 @pytest.mark.parametrize("m,n,k", [(200, 136, 72), (1, 8, 8), (130, 260, 1032), (1000, 24, 4096)])
@@ -69,8 +80,9 @@ def test_config_2048_cubed_f16_fp32_out():
     # repeat-run determinism (catches races): bitwise equal
     c2 = _run(a, b)
     assert torch.equal(c, c2)
-    # both tile widths give the same math
+    # every tile shape gives the same math
     oracle.assert_close_half(_run(a, b, tile_n=128), oracle.gemm_nt(a, b))
+    oracle.assert_close_half(_run(a, b, tile_m=256), oracle.gemm_nt(a, b))
 
 
 def test_block_of_ones_lands_where_it_should():
