@@ -60,8 +60,12 @@ class Workload:
     launches_per_step = 1
     needs_flush = False
 
+    scaling = "weak"  # per-GPU work fixed as N grows, unless a workload says otherwise
+
     def config(self) -> dict: ...
     def setup(self, dev): ...
+    def shard(self, world: int, rank: int):
+        """Called before setup() when N > 1; default: every rank runs the whole workload (independent units)."""
     def step(self): ...
     def units_per_step(self) -> float:
         """flops (tensor-bound) or bytes (hbm-bound) per step."""
@@ -148,8 +152,21 @@ class GemmWL(Workload):
         self.needs_flush = (2 * n * n * (1 if fp8 else 2) + n * n * (2 if fp8 else 4)) < 200e6
 
     def config(self):
-        return {"workload": self.name, "m": self.n, "n": self.n, "k": self.n,
-                "l2": "L2 flushed between steps (256 MB write)" if self.needs_flush else "operands larger than L2"}
+        cfg = {"workload": self.name, "m": self.n, "n": self.n, "k": self.n,
+               "l2": "L2 flushed between steps (256 MB write)" if self.needs_flush else "operands larger than L2"}
+        if self.world > 1:
+            cfg["parallelism"] = (f"column-parallel over N on {self.world} GPUs, all-gather of C fused into the "
+                                  "GEMM epilogue (peer stores) + cross-rank barrier inside the timed step")
+        return cfg
+
+    world, rank = 1, 0
+
+    def shard(self, world, rank):
+        # fp8 GEMM: column-parallel over N, all-gather of C fused into the epilogue (strong scaling).
+        # f16 2048^3 is too small to shard: independent replicas.
+        if self.fp8:
+            self.world, self.rank = world, rank
+            self.scaling = "strong"
 
     def setup(self, dev):
         g = torch.Generator(device=dev).manual_seed(10)
@@ -160,19 +177,34 @@ class GemmWL(Workload):
             self.b, self.sb = torch.ops.b200k.quantize_e4m3(b)
         else:
             self.a, self.b = a.half(), b.half()
+        if self.world > 1:
+            from iree_turbine_b200 import dist as tdist
+
+            lo, hi = tdist.shard_range(self.n, self.world, self.rank)
+            self.b = self.b[lo:hi].contiguous()
+            self.fused = tdist.FusedColumnParallelGemm(self.n, self.n, torch.bfloat16)
 
     def step(self):
-        if self.fp8:
+        if self.world > 1:
+            self.fused(self.a, self.b, self.sa, self.sb)
+            self.c = self.fused.finish()
+        elif self.fp8:
             self.c = torch.ops.b200k.gemm_fp8_nt(self.a, self.b, self.sa, self.sb)
         else:
             self.c = torch.ops.b200k.gemm_nt(self.a, self.b)
 
     def units_per_step(self):
-        return 2.0 * self.n ** 3
+        return 2.0 * self.n ** 3 / self.world
 
     def setup_e2e(self, dev):
         from iree_turbine_b200 import host_api
 
+        if self.world > 1:
+            # sharded run: the rank's operands come from pinned host memory each step, the full C
+            # is read back by every rank
+            self.ha, self.hb = self.a.cpu().pin_memory(), self.b.cpu().pin_memory()
+            self.hc = torch.empty(self.n, self.n, dtype=torch.bfloat16).pin_memory()
+            return
         self.setup(dev)
         self.ha, self.hb = self.a.cpu().pin_memory(), self.b.cpu().pin_memory()
         out_dtype = torch.bfloat16 if self.fp8 else torch.float32
@@ -180,13 +212,20 @@ class GemmWL(Workload):
         self.e2e = host_api.GemmHost(self.n, self.n, self.n, self.a.dtype, out_dtype, dev)
 
     def step_e2e(self):
-        if self.fp8:
+        if self.world > 1:
+            self.a.copy_(self.ha, non_blocking=True)
+            self.b.copy_(self.hb, non_blocking=True)
+            self.fused(self.a, self.b, self.sa, self.sb)
+            self.hc.copy_(self.fused.finish(), non_blocking=True)
+        elif self.fp8:
             self.e2e(self.ha, self.hb, self.hc, self.sa, self.sb)
         else:
             self.e2e(self.ha, self.hb, self.hc)
 
     def e2e_bytes(self):
         es = 1 if self.fp8 else 2
+        if self.world > 1:
+            return self.n * self.n * es + self.b.numel() * es, self.n * self.n * 2
         return 2 * self.n * self.n * es, self.n * self.n * (2 if self.fp8 else 4)
 
     def cpu_sample(self):
@@ -397,6 +436,8 @@ def run_ours(wl: Workload, args) -> dict:
     peaks = load_peaks()
     stream = torch.cuda.current_stream()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if wl.needs_flush else None
+    if world > 1:
+        wl.shard(world, rank)
     wl.setup(dev)
     units = wl.units_per_step()
     scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
@@ -446,7 +487,7 @@ def run_ours(wl: Workload, args) -> dict:
                         "sample": cdesc}
     out = {
         "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": wl.scaling,
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(),
         "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": wl.unit,
                      "frac": achieved / peak, "traffic": wl.traffic_bytes, "peak_source": peaks["source"] + " (burst)",

@@ -101,6 +101,33 @@ typedef struct b200k_gemm_args {
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);
 
+/*
+ * Column-parallel GEMM fused with the all-gather of its result (the exchange step of the fp8
+ * GEMM when it is sharded over N across the GPUs of one box; no counterpart in the reference,
+ * which has no collective call site).  The rank computes C[:, col_offset : col_offset + n] from
+ * its rows of B and writes every tile directly into the FULL matrix of each rank listed in
+ * peer_c (its own included), with plain 16-byte stores to peer-mapped memory: the transfer
+ * overlaps the math tile by tile and no staging copy or separate collective is needed.
+ *
+ *   gemm        the local problem (a, b, m, n = shard width, k, lda, ldb, dtypes, scales);
+ *               gemm.c and gemm.ldc are ignored
+ *   peer_c[i]   base of rank i's full [m, peer_ldc] output, addressable from this device
+ *   peer_ldc    row pitch of the full matrix in elements; col_offset: first column of the shard
+ * Row pitch, column offset and shard width must be multiples of 16 bytes.  Completion on this
+ * stream only means this rank's stores were issued and are visible at system scope after a
+ * stream synchronize; readers on other ranks need a cross-rank barrier after that.
+ */
+typedef struct b200k_gemm_allgather_args {
+  b200k_gemm_args gemm;
+  void* peer_c[8];
+  int32_t num_peers;
+  int32_t reserved;
+  int64_t peer_ldc;
+  int64_t col_offset;
+} b200k_gemm_allgather_args;
+
+int b200k_gemm_nt_allgather(const b200k_gemm_allgather_args* args, void* stream);
+
 /* ---- attention forward (vanilla and causal) ---------------------------------------- */
 /*
  * Replaces the Wave vanilla / causal attention template launch.

@@ -21,6 +21,7 @@ __all__ = [
     "B200kError",
     "DTYPE_CODES",
     "GemmArgs",
+    "GemmAllGatherArgs",
     "AttentionArgs",
     "DecodeArgs",
     "lib",
@@ -77,6 +78,17 @@ class GemmArgs(C.Structure):
         ("status", C.c_void_p),
         ("tile_n", C.c_int32),
         ("tile_m", C.c_int32),
+    ]
+
+
+class GemmAllGatherArgs(C.Structure):
+    _fields_ = [
+        ("gemm", GemmArgs),
+        ("peer_c", C.c_void_p * 8),
+        ("num_peers", C.c_int32),
+        ("reserved", C.c_int32),
+        ("peer_ldc", C.c_int64),
+        ("col_offset", C.c_int64),
     ]
 
 
@@ -145,6 +157,7 @@ EXPORTED_SYMBOLS = {
     "b200k_last_error": (C.c_char_p, []),
     "b200k_status_string": (C.c_char_p, [C.c_int]),
     "b200k_gemm_nt": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "b200k_gemm_nt_allgather": (C.c_int, [C.POINTER(GemmAllGatherArgs), C.c_void_p]),
     "b200k_attention_fwd": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p]),
     "b200k_decode_workspace_bytes": (C.c_uint64, [C.POINTER(DecodeArgs)]),
     "b200k_decode_default_chunk": (C.c_int32, [C.POINTER(DecodeArgs)]),

@@ -164,6 +164,11 @@ int b200k_gemm_nt(const b200k_gemm_args* args, void* stream) {
   return launch_gemm_nt(*args, static_cast<cudaStream_t>(stream));
 }
 
+int b200k_gemm_nt_allgather(const b200k_gemm_allgather_args* args, void* stream) {
+  if (!args) return set_error(B200K_ERR_NULL, "gemm_nt_allgather: args is NULL");
+  return launch_gemm_nt_allgather(*args, static_cast<cudaStream_t>(stream));
+}
+
 int b200k_attention_fwd(const b200k_attention_args* args, void* stream) {
   if (!args) return set_error(B200K_ERR_NULL, "attention_fwd: args is NULL");
   return launch_attention_fwd(*args, static_cast<cudaStream_t>(stream));

@@ -38,6 +38,12 @@ struct GemmParams {
   int32_t tiles_m, tiles_n, num_kb;  // tiles_m counts MT * 128-row tiles
   int32_t vec_store_ok;
   int32_t tma_store_ok;  // C is 16-byte aligned with a 16-byte-multiple row pitch: epilogue uses TMA stores
+  // Fused all-gather of a column shard: when num_peers > 0 every output tile is written with plain
+  // 16-byte stores into each peer's full matrix (peer-mapped memory) at column peer_col0.
+  int32_t num_peers;
+  int64_t peer_ldc;
+  int64_t peer_col0;
+  void* peers[8];
 };
 
 template <int BN, int MT>
@@ -271,7 +277,62 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int row = row0 + lane;
         const uint32_t taddr =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (MT == 1 ? acc * BN : h * BN);
-        if (p.tma_store_ok) {
+        if (p.num_peers > 0) {
+          // Column shard written straight into every rank's full C (own copy included): registers ->
+          // swizzled staging buffer -> each store instruction writes four full 128-byte row segments
+          // to one peer, so the NVLink traffic is made of whole lines.
+          constexpr int kCols = 128 / static_cast<int>(sizeof(OutT));
+#pragma unroll 1
+          for (int c = 0; c < BN / kCols; ++c) {
+            uint8_t* buf = staging;
+            uint4 v[8];
+            if constexpr (sizeof(OutT) == 4) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(taddr + c * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                v[i] = make_uint4(__float_as_uint(__uint_as_float(r[4 * i]) * scale),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 1]) * scale),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 2]) * scale),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 3]) * scale));
+            } else {
+              uint32_t r[64];
+              tmem_ld_32x32b_x64(taddr + c * 64, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                union {
+                  uint4 u;
+                  OutT e[8];
+                } pk;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * scale);
+                v[i] = pk.u;
+              }
+            }
+            __syncwarp();  // previous chunk's reads of the staging buffer are done
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((i ^ (lane & 7)) << 4)) = v[i];
+            __syncwarp();
+            const int col = tn * BN + c * kCols;  // column inside the shard
+            const int chunk = lane & 7;
+            const int ecol = col + chunk * (16 / static_cast<int>(sizeof(OutT)));
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+              const int lr = rr * 4 + (lane >> 3);
+              const int grow = row0 + lr;
+              const uint4 val = *reinterpret_cast<const uint4*>(buf + lr * 128 + ((chunk ^ (lr & 7)) << 4));
+              if (grow < p.m && ecol < p.n) {
+                const int64_t off = (static_cast<int64_t>(grow) * p.peer_ldc + p.peer_col0 + ecol) *
+                                    static_cast<int64_t>(sizeof(OutT));
+                for (int pe = 0; pe < p.num_peers; ++pe)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peers[pe]) + off) = val;
+              }
+            }
+          }
+        } else if (p.tma_store_ok) {
           // 128 bytes of each of this warp's 32 rows per step: registers -> swizzled staging
           // buffer -> one TMA store (full 128-byte lines, clipped at the matrix edge by the
           // tensor map).  Two buffers per warp; a buffer is reused once its store has been read.
@@ -394,20 +455,57 @@ int dispatch_dtype(int in_dtype, int out_dtype, const CUtensorMap& ta, const CUt
 
 }  // namespace
 
+namespace {
+struct PeerTargets {
+  int num = 0;
+  void* c[8] = {};
+  int64_t ldc = 0;
+  int64_t col0 = 0;
+};
+int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStream_t stream);
+}  // namespace
+
 int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream) {
-  if (!a.a || !a.b || !a.c) return set_error(B200K_ERR_NULL, "gemm_nt: a, b and c must be non-NULL");
+  if (!a.c) return set_error(B200K_ERR_NULL, "gemm_nt: a, b and c must be non-NULL");
+  return launch_gemm_impl(a, PeerTargets{}, stream);
+}
+
+int launch_gemm_nt_allgather(const b200k_gemm_allgather_args& g, cudaStream_t stream) {
+  if (g.num_peers < 1 || g.num_peers > 8)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_allgather: num_peers must be in [1, 8]");
+  const size_t out_es = dtype_size(g.gemm.out_dtype);
+  if (out_es == 0) return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt_allgather: bad out dtype");
+  if (g.col_offset < 0 || g.peer_ldc < g.col_offset + g.gemm.n)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_allgather: column shard does not fit in the row pitch of the full matrix");
+  if ((g.peer_ldc * out_es) % 16 != 0 || (g.col_offset * out_es) % 16 != 0 || (g.gemm.n * out_es) % 16 != 0)
+    return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt_allgather: row pitch, column offset and shard width must be multiples of 16 bytes");
+  PeerTargets t;
+  t.num = g.num_peers;
+  t.ldc = g.peer_ldc;
+  t.col0 = g.col_offset;
+  for (int i = 0; i < g.num_peers; ++i) {
+    if (!g.peer_c[i] || (reinterpret_cast<uintptr_t>(g.peer_c[i]) & 15))
+      return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt_allgather: every peer_c must be non-NULL and 16-byte aligned");
+    t.c[i] = g.peer_c[i];
+  }
+  return launch_gemm_impl(g.gemm, t, stream);
+}
+
+namespace {
+int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStream_t stream) {
+  if (!a.a || !a.b) return set_error(B200K_ERR_NULL, "gemm_nt: a, b and c must be non-NULL");
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || a.m > INT32_MAX || a.n > INT32_MAX || a.k > INT32_MAX)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: m, n, k must be in [1, 2^31)");
   const size_t in_es = dtype_size(a.in_dtype);
   const size_t out_es = dtype_size(a.out_dtype);
   if (in_es == 0 || out_es == 0 || a.in_dtype == B200K_F32)
     return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: unsupported dtype in=%d out=%d", a.in_dtype, a.out_dtype);
-  if (a.lda < a.k || a.ldb < a.k || a.ldc < a.n)
+  if (a.lda < a.k || a.ldb < a.k || (peers.num == 0 && a.ldc < a.n))
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: leading dimensions smaller than the row length");
   if ((reinterpret_cast<uintptr_t>(a.a) & 15) || (reinterpret_cast<uintptr_t>(a.b) & 15) ||
       (a.lda * in_es) % 16 != 0 || (a.ldb * in_es) % 16 != 0)
     return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt: A/B base and row stride must be multiples of 16 bytes");
-  if (reinterpret_cast<uintptr_t>(a.c) % out_es != 0)
+  if (peers.num == 0 && reinterpret_cast<uintptr_t>(a.c) % out_es != 0)
     return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt: C is not aligned to its element size");
   if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_n must be 0, 128 or 256");
@@ -467,6 +565,11 @@ int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream) {
   p.tiles_n = tiles_n;
   p.num_kb = static_cast<int32_t>((a.k + k_per_stage - 1) / k_per_stage);
   p.vec_store_ok = ((reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && (a.ldc * out_es) % 16 == 0) ? 1 : 0;
+  p.num_peers = peers.num;
+  p.peer_ldc = peers.ldc;
+  p.peer_col0 = peers.col0;
+  for (int i = 0; i < 8; ++i) p.peers[i] = peers.c[i];
+  if (peers.num > 0) p.vec_store_ok = 0;
 
   p.tma_store_ok = p.vec_store_ok;
   CUtensorMap tc;
@@ -484,5 +587,6 @@ int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream) {
   if (bn == 256) return dispatch_dtype<256, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
   return dispatch_dtype<128, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
 }
+}  // namespace
 
 }  // namespace b200k

@@ -16,7 +16,7 @@ from typing import Callable, Optional
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "head_shard", "column_parallel_gemm", "gather_columns"]
+__all__ = ["shard_range", "head_shard", "column_parallel_gemm", "gather_columns", "FusedColumnParallelGemm"]
 
 
 def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
@@ -66,3 +66,60 @@ def column_parallel_gemm(gemm: Callable[[torch.Tensor], torch.Tensor], b_full_ro
     lo, hi = shard_range(b_full_rows, world, rank)
     c_local = gemm(lo, hi)
     return gather_columns(c_local, group) if gather else c_local
+
+
+class FusedColumnParallelGemm:
+    """Column-parallel C = A @ B^T whose all-gather is done by the GEMM kernel itself.
+
+    Each rank holds all of A and ``n / world`` rows of B.  The full C lives in symmetric
+    (peer-mapped) memory; the kernel's epilogue stores every tile of the local column shard into
+    every rank's copy (``b200k_gemm_nt_allgather``), so the transfer over NVLink overlaps the math
+    and there is no separate collective.  ``finish()`` is the cross-rank barrier after which every
+    rank may read the full matrix.
+    """
+
+    def __init__(self, m: int, n: int, out_dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if n % self.world:
+            raise ValueError(f"N = {n} is not divisible by {self.world} ranks")
+        self.m, self.n = m, n
+        self.c = symm_mem.empty((m, n), dtype=out_dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.c, self.group)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def __call__(self, a: torch.Tensor, b_local: torch.Tensor, scale_a=None, scale_b=None) -> torch.Tensor:
+        import ctypes as C
+
+        from . import _launcher as L
+        from .ops import _row_major_2d, _status_ptr
+
+        lo, hi = shard_range(self.n, self.world, self.rank)
+        if b_local.size(0) != hi - lo or a.size(0) != self.m or a.size(1) != b_local.size(1):
+            raise ValueError("operand shapes do not match the sharded problem")
+        a, b_local = _row_major_2d(a), _row_major_2d(b_local)
+        g = L.GemmAllGatherArgs()
+        g.gemm.a, g.gemm.b, g.gemm.c = a.data_ptr(), b_local.data_ptr(), None
+        g.gemm.m, g.gemm.n, g.gemm.k = self.m, hi - lo, a.size(1)
+        g.gemm.lda, g.gemm.ldb, g.gemm.ldc = a.stride(0), b_local.stride(0), 0
+        g.gemm.in_dtype = L.DTYPE_CODES[a.dtype]
+        g.gemm.out_dtype = L.DTYPE_CODES[self.c.dtype]
+        g.gemm.scale_a = scale_a.data_ptr() if scale_a is not None else None
+        g.gemm.scale_b = scale_b.data_ptr() if scale_b is not None else None
+        g.gemm.status = _status_ptr(a.device)
+        for i, ptr in enumerate(self.peer_ptrs):
+            g.peer_c[i] = ptr
+        g.num_peers = self.world
+        g.peer_ldc = self.c.stride(0)
+        g.col_offset = lo
+        stream = C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)
+        L.check(L.lib().b200k_gemm_nt_allgather(C.byref(g), stream))
+        return self.c
+
+    def finish(self) -> torch.Tensor:
+        """Cross-rank barrier on the current stream; afterwards ``self.c`` is complete on every rank."""
+        self.handle.barrier()
+        return self.c
