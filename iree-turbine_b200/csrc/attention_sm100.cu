@@ -1,28 +1,36 @@
 // Attention forward (vanilla and causal) on sm_100a.
 //
-// One CTA owns 256 query rows of one (batch, head): two 128-row query tiles that ping-pong on
-// the tensor core so that the softmax of one tile overlaps the MMAs of the other.
+// Persistent CTAs, one per SM.  A work item is one 128-row query tile of one (batch, head); a CTA
+// takes items blockIdx.x, blockIdx.x + gridDim.x, ... from a list ordered (batch, head)-major with
+// the heaviest query tiles of a head first, so CTAs that run at the same time share K/V in L2.
 //
-//   warps 0..3    softmax + correction + epilogue for query tile 0   (warpgroup 0)
-//   warps 4..7    the same for query tile 1                          (warpgroup 1)
-//   warp 8        TMA loads: Q tiles once, then K_j and V_j into two 2-stage rings
+//   warps 0..3    softmax + correction (one thread = one query row)             warpgroup 0
+//   warps 4..7    epilogue: O / rowsum -> global, one item behind the others     warpgroup 1
+//   warp 8        TMA loads: Q of the next item, then K_j (3 stages) / V_j (2)    warpgroup 2
 //   warp 9        issues every tcgen05.mma and owns tensor memory
-//   warps 10, 11  idle; they complete warpgroup 2 so that it can hand its registers
-//                 (setmaxnreg) to the two softmax warpgroups, which keep a whole score row
-//                 (128 fp32) per thread in registers
+//   warps 10, 11  idle (complete warpgroup 2 for the setmaxnreg register hand-off)
 //
-// Tensor memory (512 columns x 128 lanes):  S0 | S1 | O0 | O1, 128 fp32 columns each.  The
-// probabilities P (16-bit, two per column) overwrite the first 64 columns of their S tile and
-// feed the second MMA directly from tensor memory, so they never touch shared memory.
+// Tensor memory (512 columns x 128 lanes):  S[0] | S[1] | O[0] | O[1], 128 fp32 columns each.
+//   * Two score buffers: the tensor core computes S(j+1) while the softmax works on S(j), so the
+//     softmax never waits for scores and the per-step chain "softmax -> P V -> next scores" of a
+//     single-buffer design is gone.  What remains is a throughput balance: about 1230 cycles of
+//     softmax instructions per 128 x 128 tile on the four SM sub-partitions against 1024 cycles of
+//     MMA (both measured with single-SM micro-benchmarks).
+//   * Two output accumulators: the epilogue of item i runs while item i+1 is being computed.
+//   * The probabilities P (16-bit, two per column) overwrite the first 64 columns of their score
+//     buffer and are the A operand of the second MMA straight from tensor memory.  MMAs issued by
+//     one thread complete in order, so issuing S(j+2) after "O += P(j) V(j)" is all that is needed
+//     to reuse a buffer.
 //
-// Per KV tile j and query tile i:  S_i = Q_i K_j^T  ->  softmax warps read S_i (one thread owns
-// one row, so row max / row sum need no cross-thread traffic), write P_i  ->  O_i += P_i V_j.
-// MMAs issued by one thread complete in order, so "S_i(j+1) is issued after O_i += P_i(j) V_j"
-// is all that is needed to let P and S share columns.
+// Epilogue: accumulator -> registers -> 16-bit -> 128-byte-swizzled staging tile in shared memory
+// -> two TMA stores (rows past the end of the sequence are clipped by the tensor map).  Direct
+// row-per-thread global stores were measured at about 3000 cycles per item and delayed the TMA
+// loads of the next item; the staged store is a few hundred.
 //
-// The running max is kept in log2 units (scores are multiplied by scale * log2(e) inside the
-// exponent's FMA).  O is only rescaled when a row's max grows by more than 2^8; until then the
-// stale max is used for both P and the running sum, which is exact after the final division.
+// Softmax: running max in log2 units (scores are multiplied by scale * log2(e) inside the
+// exponent's FMA); O is only rescaled when a row's max grows by more than 2^8 (stale max used for
+// both P and the running sum, exact after the final division); 3 of every 8 column pairs take a
+// degree-3 polynomial on the FMA pipe instead of ex2.approx to balance the special-function unit.
 #include <type_traits>
 
 #include "common.cuh"
@@ -32,19 +40,26 @@ namespace b200k {
 namespace {
 
 constexpr int kAttnThreads = 384;
-constexpr int kRegsSoftmax = 216;  // per SM sub-partition the CTA owns 3 warps x 168 registers = 504 per lane at launch;
-                                    // setmaxnreg only redistributes that: 2*216 + 72 = 504 (anything larger never completes);
-                                    // this split compiles both roles without spills
+// Registers: 3 warps per SM sub-partition x 168 at launch = 504 per lane, redistributed.
+constexpr int kRegsSoftmax = 232;
+constexpr int kRegsEpilogue = 128;
 constexpr int kRegsOther = 72;
-constexpr int kTileRows = 128;  // query rows per tile, KV rows per tile
+static_assert(kRegsSoftmax + kRegsEpilogue + kRegsOther <= 504, "setmaxnreg.inc would never complete");
+constexpr int kTileRows = 128;  // query rows per item, KV rows per tile
 constexpr int kD = 128;
-constexpr int kHalfTileBytes = kTileRows * 128;     // one 64-element column block: 16 KB
-constexpr int kTileBytes = 2 * kHalfTileBytes;      // 32 KB
-constexpr int kQOffset = 0;                         // 2 tiles
-constexpr int kKOffset = 2 * kTileBytes;            // 2 stages
-constexpr int kVOffset = 4 * kTileBytes;            // 2 stages
-constexpr int kBarOffset = 6 * kTileBytes;          // 192 KB
-constexpr int kNumBars = 15;
+constexpr int kHalfTileBytes = kTileRows * 128;  // one 64-element column block: 16 KB
+constexpr int kTileBytes = 2 * kHalfTileBytes;   // 32 KB
+constexpr int kKStages = 3;
+constexpr int kVStages = 2;
+constexpr int kQOffset = 0;
+constexpr int kKOffset = kTileBytes;
+constexpr int kVOffset = kKOffset + kKStages * kTileBytes;
+constexpr int kOStageOffset = kVOffset + kVStages * kTileBytes;  // epilogue staging tile (layout of a Q tile)
+constexpr int kLsumOffset = kOStageOffset + kTileBytes;          // float [2][128]: row sums for the epilogue
+constexpr int kBarOffset = kLsumOffset + 2 * kTileRows * 4;
+// q_full q_empty | k_full[3] k_empty[3] v_full[2] v_empty[2] | s_full[2] p_full[2] | o_done |
+// o_full[2] o_free[2] l_full[2] l_free[2]
+constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 4 + 1 + 8;
 constexpr int kAttnSmem = kBarOffset + kNumBars * 8 + 16 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
@@ -54,7 +69,8 @@ struct AttnParams {
   int64_t o_stride_b, o_stride_h, o_stride_s;
   int32_t batch, q_heads, kv_heads, seq_q, seq_kv;
   int32_t causal, causal_offset;
-  int32_t num_q_blocks;
+  int32_t num_q_tiles;  // ceil(seq_q / 128)
+  int32_t num_items;    // batch * q_heads * num_q_tiles
   float scale_log2;
   int32_t* status;
 };
@@ -100,14 +116,6 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi)
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Number of KV tiles a query tile starting at row r0 has to visit.
-__device__ __forceinline__ int kv_tiles_for(int r0, const AttnParams& p, int kv_tiles_total) {
-  if (!p.causal) return kv_tiles_total;
-  const int last_col = r0 + kTileRows - 1 + p.causal_offset;
-  if (last_col < 0) return 0;
-  return min(last_col / kTileRows + 1, kv_tiles_total);
-}
-
 // Optional timeline capture (compile with -DB200K_ATTN_TRACE): block (0,0,0) records
 // (tag, clock64) pairs per role into the buffer passed as the status pointer, 256 events per role:
 // role 0 = TMA thread, 1 = MMA thread, 2 = softmax tile 0 (thread 0), 3 = softmax tile 1.
@@ -127,61 +135,90 @@ __device__ __forceinline__ int kv_tiles_for(int r0, const AttnParams& p, int kv_
   } while (0)
 #endif
 
+
+struct Item {
+  int qtile, head, batch, n;  // n = number of 128-row KV tiles this item visits
+};
+
+__device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
+  Item it;
+  const int bh = idx / p.num_q_tiles;
+  it.qtile = p.num_q_tiles - 1 - (idx - bh * p.num_q_tiles);  // heaviest tiles of a head first
+  it.batch = bh / p.q_heads;
+  it.head = bh - it.batch * p.q_heads;
+  const int kv_tiles_total = (p.seq_kv + kTileRows - 1) / kTileRows;
+  if (!p.causal) {
+    it.n = kv_tiles_total;
+  } else {
+    const int last_col = it.qtile * kTileRows + kTileRows - 1 + p.causal_offset;
+    it.n = last_col < 0 ? 0 : min(last_col / kTileRows + 1, kv_tiles_total);
+  }
+  return it;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                    const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                    const AttnParams p) {
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
   constexpr uint32_t kIdescS = make_idesc(kFmt, kFmt, 128, 128, 0, 0);   // Q, K both K-major
   constexpr uint32_t kIdescPV = make_idesc(kFmt, kFmt, 128, 128, 0, 1);  // V is MN-major
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  float* lsum = reinterpret_cast<float*>(smem + kLsumOffset);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOffset);
-  uint64_t* q_full = bars;         // 1
-  uint64_t* k_full = bars + 1;     // 2
-  uint64_t* k_empty = bars + 3;    // 2
-  uint64_t* v_full = bars + 5;     // 2
-  uint64_t* v_empty = bars + 7;    // 2
-  uint64_t* s_full = bars + 9;     // 2 (per query tile)
-  uint64_t* p_full = bars + 11;    // 2
-  uint64_t* o_done = bars + 13;    // 2
+  uint64_t* q_full = bars;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* k_full = bars + 2;
+  uint64_t* k_empty = k_full + kKStages;
+  uint64_t* v_full = k_empty + kKStages;
+  uint64_t* v_empty = v_full + kVStages;
+  uint64_t* s_full = v_empty + kVStages;  // [score buffer]
+  uint64_t* p_full = s_full + 2;          // [score buffer]
+  uint64_t* o_done = p_full + 2;          // one phase per "O += P V"
+  uint64_t* o_full = o_done + 1;          // [output buffer] last P V of an item complete
+  uint64_t* o_free = o_full + 2;          // [output buffer] epilogue has read it
+  uint64_t* l_full = o_free + 2;          // [output buffer] row sums written
+  uint64_t* l_free = l_full + 2;          // [output buffer] row sums read
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 #ifdef B200K_ATTN_TRACE
-  const bool trace_on = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && p.status != nullptr && lane == 0;
+  const bool trace_on = blockIdx.x == 0 && p.status != nullptr && lane == 0;
   int trace_n = 0;
 #endif
 
-  // Heaviest blocks first: under a causal mask the last query rows see the most keys.
-  const int qblock = p.num_q_blocks - 1 - static_cast<int>(blockIdx.x);
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
-  const int kv_head = head / (p.q_heads / p.kv_heads);
-  const int kv_tiles_total = (p.seq_kv + kTileRows - 1) / kTileRows;
-  const int n0 = kv_tiles_for(qblock * 256, p, kv_tiles_total);
-  const int n1 = kv_tiles_for(qblock * 256 + kTileRows, p, kv_tiles_total);  // n1 >= n0
-
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(q_empty, 1);
+    for (int i = 0; i < kKStages; ++i) {
       mbar_init(k_full + i, 1);
       mbar_init(k_empty + i, 1);
+    }
+    for (int i = 0; i < kVStages; ++i) {
       mbar_init(v_full + i, 1);
       mbar_init(v_empty + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(s_full + i, 1);
       mbar_init(p_full + i, 4);
-      mbar_init(o_done + i, 1);
+      mbar_init(o_full + i, 1);
+      mbar_init(o_free + i, 4);
+      mbar_init(l_full + i, 4);
+      mbar_init(l_free + i, 4);
     }
+    mbar_init(o_done, 1);
     *abort_word = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_o);
   }
   if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
@@ -191,284 +228,343 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int group = p.q_heads / p.kv_heads;
 
   if (warp >= 8) {
-    // Warpgroup 2 (TMA, MMA, two idle warps) gives registers back for the softmax warpgroups.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     if (warp == 8) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0 && n1 > 0) {
-      mbar_arrive_expect_tx(q_full, 2 * kTileBytes);
+      // ---------------- TMA producer ----------------
+      if (lane == 0) {
+        uint32_t qc = 0, kc = 0, vc = 0;  // Q loads, K tiles, V tiles issued so far
+        bool ok = true;
+        for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
+          const Item it = decode_item(idx, p);
+          if (it.n == 0) continue;
+          const int kv_head = it.head / group;
+          if (!mbar_wait(q_empty, (qc & 1) ^ 1, abort_word)) break;
+          mbar_arrive_expect_tx(q_full, kTileBytes);
 #pragma unroll
-      for (int tile = 0; tile < 2; ++tile)
+          for (int db = 0; db < 2; ++db)
+            tma_load_4d(smem + kQOffset + db * kHalfTileBytes, &tmap_q, q_full, db * 64, it.qtile * kTileRows, it.head,
+                        it.batch);
+          ++qc;
+          ATTN_TRACE(0, 9000);
+          // Order: K_0, K_1, then V_j followed by K_(j+2): score tiles run two steps ahead of the
+          // second MMA, so their operands are requested first.
+          auto load_k = [&](int j) {
+            const int ks = kc % kKStages;
+            if (!mbar_wait(k_empty + ks, ((kc / kKStages) & 1) ^ 1, abort_word)) return false;
+            mbar_arrive_expect_tx(k_full + ks, kTileBytes);
 #pragma unroll
-        for (int db = 0; db < 2; ++db)
-          tma_load_4d(smem + kQOffset + tile * kTileBytes + db * kHalfTileBytes, &tmap_q, q_full, db * 64,
-                      qblock * 256 + tile * kTileRows, head, batch);
-      for (int j = 0; j < n1; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(k_empty + st, ph ^ 1, abort_word)) break;
-        ATTN_TRACE(0, 100 + j);
-        mbar_arrive_expect_tx(k_full + st, kTileBytes);
+            for (int db = 0; db < 2; ++db)
+              tma_load_4d(smem + kKOffset + ks * kTileBytes + db * kHalfTileBytes, &tmap_k, k_full + ks, db * 64,
+                          j * kTileRows, kv_head, it.batch);
+            ++kc;
+            return true;
+          };
+          for (int jj = 0; jj < 2 && jj < it.n && ok; ++jj) ok = load_k(jj);
+          for (int j = 0; j < it.n && ok; ++j) {
+            const int vs = vc % kVStages;
+            if (!mbar_wait(v_empty + vs, ((vc / kVStages) & 1) ^ 1, abort_word)) { ok = false; break; }
+            mbar_arrive_expect_tx(v_full + vs, kTileBytes);
 #pragma unroll
-        for (int db = 0; db < 2; ++db)
-          tma_load_4d(smem + kKOffset + st * kTileBytes + db * kHalfTileBytes, &tmap_k, k_full + st, db * 64,
-                      j * kTileRows, kv_head, batch);
-        if (!mbar_wait(v_empty + st, ph ^ 1, abort_word)) break;
-        ATTN_TRACE(0, 200 + j);
-        mbar_arrive_expect_tx(v_full + st, kTileBytes);
-#pragma unroll
-        for (int db = 0; db < 2; ++db)
-          tma_load_4d(smem + kVOffset + st * kTileBytes + db * kHalfTileBytes, &tmap_v, v_full + st, db * 64,
-                      j * kTileRows, kv_head, batch);
-      }
-    }
-    __syncwarp();
-    } else if (warp == 9) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0 && n1 > 0) {
-      const uint32_t sq = smem_u32(smem + kQOffset);
-      const uint32_t sk = smem_u32(smem + kKOffset);
-      const uint32_t sv = smem_u32(smem + kVOffset);
-      // The issuing thread runs scalar, latency-bound code, and a 128x128x16 MMA lasts only 64
-      // cycles, so the per-MMA issue cost must stay at a handful of instructions: descriptors are
-      // split into a constant high word and a low word that is a precomputed base plus a
-      // compile-time offset.
-      const uint32_t hi_k = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
-      const uint32_t hi_mn = static_cast<uint32_t>(make_desc_mnmajor_sw128(0, kHalfTileBytes) >> 32);
-      const uint32_t q_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sq));
-      const uint32_t k_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sk));
-      const uint32_t v_lo = static_cast<uint32_t>(make_desc_mnmajor_sw128(sv, kHalfTileBytes));
-      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
-      // S_tile = Q_tile K^T : 8 k-steps of 16 over the head dimension (two 64-wide blocks).
-      auto issue_s = [&](int tile, int kstage) {
-        const uint32_t a0 = q_lo + tile * (kTileBytes >> 4);
-        const uint32_t b0 = k_lo + kstage * (kTileBytes >> 4);
-        const uint32_t d = tmem_base + tile * 128;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
-          umma_f16_ss(d, desc(a0 + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(s_full + tile);
-      };
-      // O_tile += P_tile V : 8 k-steps of 16 KV rows; A from tensor memory, B = V (MN-major).
-      auto issue_pv = [&](int tile, int vstage, bool first) {
-        const uint32_t b0 = v_lo + vstage * (kTileBytes >> 4);
-        const uint32_t d = tmem_base + 256 + tile * 128;
-        const uint32_t a = tmem_base + tile * 128;
-        umma_f16_ts(d, a, desc(b0, hi_mn), kIdescPV, first ? 0u : 1u);
-#ifdef B200K_ATTN_TRACE_FINE
-        ATTN_TRACE(1, 7000);
-#endif
-#pragma unroll
-        for (int ks = 1; ks < 8; ++ks) {
-          umma_f16_ts(d, a + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, 1u);
-#ifdef B200K_ATTN_TRACE_FINE
-          ATTN_TRACE(1, 7000 + ks);
-#endif
-        }
-        umma_commit(o_done + tile);
-      };
-
-      bool ok = mbar_wait(q_full, 0, abort_word) && mbar_wait(k_full + 0, 0, abort_word);
-      if (ok) {
-        tc_fence_after();
-        ATTN_TRACE(1, 1000);
-        if (n0 > 0) issue_s(0, 0);
-        issue_s(1, 0);
-        umma_commit(k_empty + 0);
-        ATTN_TRACE(1, 1001);
-      }
-      for (int j = 0; j < n1 && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const bool has_next = j + 1 < n1;
-        const int nst = (j + 1) & 1;
-        const uint32_t nph = ((j + 1) >> 1) & 1;
-        if (!mbar_wait(v_full + st, ph, abort_word)) { ok = false; break; }
-        ATTN_TRACE(1, 2000 + j);  // V_j landed
-        if (j < n0) {
-          if (!mbar_wait(p_full + 0, j & 1, abort_word)) { ok = false; break; }
-          tc_fence_after();
-          ATTN_TRACE(1, 3000 + j);  // P0_j ready, issuing PV0_j
-          issue_pv(0, st, j == 0);
-          ATTN_TRACE(1, 3500 + j);  // PV0_j issued
-        }
-        if (has_next) {
-          if (!mbar_wait(k_full + nst, nph, abort_word)) { ok = false; break; }
-          tc_fence_after();
-          ATTN_TRACE(1, 4000 + j);  // K_{j+1} landed, issuing S0_{j+1}
-          if (j + 1 < n0) issue_s(0, nst);
-          ATTN_TRACE(1, 4500 + j);  // S0_{j+1} issued
-        }
-        if (!mbar_wait(p_full + 1, j & 1, abort_word)) { ok = false; break; }
-        tc_fence_after();
-        ATTN_TRACE(1, 5000 + j);  // P1_j ready, issuing PV1_j (+ S1_{j+1})
-        issue_pv(1, st, j == 0);
-        ATTN_TRACE(1, 5500 + j);  // PV1_j issued
-        umma_commit(v_empty + st);
-        if (has_next) {
-          issue_s(1, nst);
-          umma_commit(k_empty + nst);
-        }
-        ATTN_TRACE(1, 6000 + j);
-      }
-    }
-    __syncwarp();
-    }
-  } else {
-    // ---------------- softmax / correction / epilogue ----------------
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-    const int tile = warp >> 2;
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
-    const int tile_r0 = qblock * 256 + tile * kTileRows;
-    const int q_row = tile_r0 + row_in_tile;
-    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_field + tile * 128;
-    const uint32_t t_o = tmem_base + lane_field + 256 + tile * 128;
-    const int n_mine = tile == 0 ? n0 : n1;
-    const float scale_log2 = p.scale_log2;
-
-    float m_used = -INFINITY;
-    float2 l2 = make_float2(0.f, 0.f);
-    bool ok = true;
-    for (int j = 0; j < n_mine; ++j) {
-      ok = mbar_wait(s_full + tile, j & 1, abort_word);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      if (quarter == 0) ATTN_TRACE(2 + tile, 100 + j);  // S_j visible
-
-#ifdef B200K_ATTN_EXPERIMENT_NO_SOFTMAX
-      // timing experiment: hand P back immediately (results are meaningless)
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full + tile);
-      continue;
-#endif
-      const int col0 = j * kTileRows;
-      const bool need_mask =
-          (p.causal && col0 + kTileRows - 1 > tile_r0 + p.causal_offset) || (col0 + kTileRows > p.seq_kv);
-      int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
-      if (need_mask) {
-        int vis = p.seq_kv;
-        if (p.causal) vis = min(vis, q_row + p.causal_offset + 1);
-        limit = vis - col0;
-      }
-
-      // The whole score row (128 fp32) lives in registers: load it in two halves so the max of
-      // the first half overlaps the load of the second.
-      uint32_t sr[128];
-      tmem_ld_32x32b_x64(t_s, sr);
-      tmem_wait_ld();
-      tmem_ld_32x32b_x64(t_s + 64, sr + 64);
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i >= limit) sr[i] = 0xff800000u;  // -inf
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-        mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
-      }
-      tmem_wait_ld();
-      if (need_mask) {
-#pragma unroll
-        for (int i = 64; i < 128; ++i)
-          if (i >= limit) sr[i] = 0xff800000u;
-      }
-#pragma unroll
-      for (int i = 64; i < 128; i += 4) {
-        mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-        mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
-      }
-      if (quarter == 0) ATTN_TRACE(2 + tile, 200 + j);  // row loaded, max done
-      const float m_new = fmaxf(mx0, mx1) * scale_log2;
-      const bool grow = m_new > m_used + kRescaleThreshold;  // also true for the first finite max
-      float alpha = 1.f;
-      if (grow) {
-        alpha = ex2(m_used - m_new);  // m_used = -inf gives 0
-        m_used = m_new;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // S_j complete implies O += P V of step j-1 is complete (in-order completion), so O is idle.
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_o + c * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32b_x32(t_o + c * 32, r);
-        }
-      }
-      l2.x *= alpha;
-      l2.y *= alpha;
-      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      const float2 scale2 = make_float2(scale_log2, scale_log2);
-      const float2 negm2 = make_float2(-m_sub, -m_sub);
-
-      // probabilities -> tensor memory (16-bit pairs over the first 64 columns of S); masked
-      // scores are -inf and give exactly 0
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 x = ffma2(make_float2(__uint_as_float(sr[c * 32 + 2 * i]), __uint_as_float(sr[c * 32 + 2 * i + 1])),
-                                 scale2, negm2);
-          const float2 e = ((kPolyPairMask >> (i & 7)) & 1u) ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
-          l2 = fadd2(l2, e);
-          pk[i] = pack_pair<T>(e.x, e.y);
-        }
-        tmem_st_32x32b_x16(t_s + c * 16, pk);
-      }
-      if (quarter == 0) ATTN_TRACE(2 + tile, 300 + j);  // exponentials issued, P stores issued
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full + tile);
-      if (quarter == 0) ATTN_TRACE(2 + tile, 400 + j);  // P signalled
-    }
-
-    // ---- epilogue: O / l -> global ----
-    if (ok && n_mine > 0) {
-      ok = mbar_wait(o_done + tile, (n_mine - 1) & 1, abort_word);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after();
-      const float l = l2.x + l2.y;
-      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-      T* orow = reinterpret_cast<T*>(p.o) + batch * p.o_stride_b + head * p.o_stride_h +
-                static_cast<int64_t>(q_row) * p.o_stride_s;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        if (n_mine > 0) {
-          tmem_ld_32x32b_x32(t_o + c * 32, r);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
-        }
-        if (q_row < p.seq_q) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 u;
-            u.x = pack_pair<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
-            u.y = pack_pair<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
-            u.z = pack_pair<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
-            u.w = pack_pair<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
-            reinterpret_cast<uint4*>(orow + c * 32)[v] = u;
+            for (int db = 0; db < 2; ++db)
+              tma_load_4d(smem + kVOffset + vs * kTileBytes + db * kHalfTileBytes, &tmap_v, v_full + vs, db * 64,
+                          j * kTileRows, kv_head, it.batch);
+            ++vc;
+            if (j + 2 < it.n) ok = load_k(j + 2);
           }
         }
       }
+      __syncwarp();
+    } else if (warp == 9) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0) {
+        const uint32_t sq = smem_u32(smem + kQOffset);
+        const uint32_t sk = smem_u32(smem + kKOffset);
+        const uint32_t sv = smem_u32(smem + kVOffset);
+        // The issuing thread runs scalar, latency-bound code: descriptors are a constant high word
+        // plus a low word that is a precomputed base plus a compile-time offset.
+        const uint32_t hi_k = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
+        const uint32_t hi_mn = static_cast<uint32_t>(make_desc_mnmajor_sw128(0, kHalfTileBytes) >> 32);
+        const uint32_t q_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sq));
+        const uint32_t k_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sk));
+        const uint32_t v_lo = static_cast<uint32_t>(make_desc_mnmajor_sw128(sv, kHalfTileBytes));
+        auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+        // S[buf] = Q K^T : 8 k-steps of 16 over the head dimension (two 64-wide blocks).
+        auto issue_s = [&](int buf, int kstage) {
+          const uint32_t b0 = k_lo + kstage * (kTileBytes >> 4);
+          const uint32_t d = tmem_base + buf * 128;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
+            umma_f16_ss(d, desc(q_lo + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(s_full + buf);
+          umma_commit(k_empty + kstage);
+        };
+        // O[ob] (+)= P[buf] V : 8 k-steps of 16 KV rows; A from tensor memory, B = V (MN-major).
+        auto issue_pv = [&](int ob, int buf, int vstage, bool first) {
+          const uint32_t b0 = v_lo + vstage * (kTileBytes >> 4);
+          const uint32_t d = tmem_base + 256 + ob * 128;
+          const uint32_t a = tmem_base + buf * 128;
+          umma_f16_ts(d, a, desc(b0, hi_mn), kIdescPV, first ? 0u : 1u);
+#pragma unroll
+          for (int ks = 1; ks < 8; ++ks) umma_f16_ts(d, a + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, 1u);
+          umma_commit(v_empty + vstage);
+          umma_commit(o_done);
+        };
+
+        uint32_t qc = 0, kc = 0, vc = 0, g = 0, ic = 0;  // Q tiles, K tiles, V tiles, KV steps, items so far
+        bool ok = true;
+        for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
+          const Item it = decode_item(idx, p);
+          if (it.n == 0) continue;
+          const int ob = ic & 1;
+          if (!mbar_wait(q_full, qc & 1, abort_word)) break;
+          ++qc;
+          // the first two score tiles of the item
+          for (int jj = 0; jj < 2 && jj < it.n; ++jj) {
+            const int ks = kc % kKStages;
+            if (!mbar_wait(k_full + ks, (kc / kKStages) & 1, abort_word)) { ok = false; break; }
+            tc_fence_after();
+            ATTN_TRACE(1, 1000 + jj);
+            issue_s((g + jj) & 1, ks);
+            ++kc;
+          }
+          if (!ok) break;
+          if (it.n <= 2) umma_commit(q_empty);  // Q is free once the item's last score MMA has run
+          for (int j = 0; j < it.n; ++j, ++g) {
+            const int buf = g & 1;
+            const int vs = vc % kVStages;
+            if (!mbar_wait(v_full + vs, (vc / kVStages) & 1, abort_word)) { ok = false; break; }
+            if (!mbar_wait(p_full + buf, (g >> 1) & 1, abort_word)) { ok = false; break; }
+            if (j == 0 && !mbar_wait(o_free + ob, ((ic >> 1) & 1) ^ 1, abort_word)) { ok = false; break; }
+            tc_fence_after();
+            ATTN_TRACE(1, 3000 + j);  // P_j ready
+            issue_pv(ob, buf, vs, j == 0);
+            ++vc;
+            if (j == it.n - 1) umma_commit(o_full + ob);
+            if (j + 2 < it.n) {
+              const int ks = kc % kKStages;
+              if (!mbar_wait(k_full + ks, (kc / kKStages) & 1, abort_word)) { ok = false; break; }
+              tc_fence_after();
+              issue_s(buf, ks);
+              ++kc;
+              if (j + 2 == it.n - 1) umma_commit(q_empty);
+            }
+            ATTN_TRACE(1, 6000 + j);
+          }
+          ++ic;
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp >= 4) {
+    // ---------------- epilogue: O / rowsum -> global, one item behind ----------------
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    uint8_t* stage = smem + kOStageOffset;
+    const bool store_thread = (warp == 4 && lane == 0);
+    auto epi_barrier = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+    uint32_t ic = 0;
+    bool ok = true;
+    for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
+      const Item it = decode_item(idx, p);
+      if (it.n == 0) {
+        // no visible key: zeros (rare; plain stores)
+        const int q_row = it.qtile * kTileRows + row_in_tile;
+        if (q_row < p.seq_q) {
+          T* orow = reinterpret_cast<T*>(p.o) + it.batch * p.o_stride_b + it.head * p.o_stride_h +
+                    static_cast<int64_t>(q_row) * p.o_stride_s;
+#pragma unroll
+          for (int v = 0; v < 16; ++v) reinterpret_cast<uint4*>(orow)[v] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        continue;
+      }
+      const int ob = ic & 1;
+      const uint32_t par = (ic >> 1) & 1;
+      ok = mbar_wait(o_full + ob, par, abort_word) && mbar_wait(l_full + ob, par, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (quarter == 0) ATTN_TRACE(3, 100);
+      const float l = lsum[ob * kTileRows + row_in_tile];
+      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+      const uint32_t t_o = tmem_base + lane_field + 256 + ob * 128;
+      // the staging tile is free once the previous item's TMA stores have read it
+      if (store_thread) tma_store_wait_read<0>();
+      epi_barrier();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_o + c * 32, r);
+        tmem_wait_ld();
+        uint8_t* blk = stage + (c >> 1) * kHalfTileBytes + row_in_tile * 128;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 u;
+          u.x = pack_pair<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+          u.y = pack_pair<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+          u.z = pack_pair<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+          u.w = pack_pair<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+          const int chunk = (c & 1) * 4 + v;
+          *reinterpret_cast<uint4*>(blk + ((chunk ^ (row_in_tile & 7)) << 4)) = u;
+        }
+      }
+      // accumulator and row sums have been read: release them for the item after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(o_free + ob);
+        mbar_arrive(l_free + ob);
+      }
+      fence_proxy_async_smem();
+      epi_barrier();
+      if (store_thread) {
+        tma_store_4d(&tmap_o, stage, 0, it.qtile * kTileRows, it.head, it.batch);
+        tma_store_4d(&tmap_o, stage + kHalfTileBytes, 64, it.qtile * kTileRows, it.head, it.batch);
+        tma_store_commit();
+      }
+      if (quarter == 0) ATTN_TRACE(3, 200);
+      ++ic;
+    }
+    if (store_thread) tma_store_wait<0>();
+  } else {
+    // ---------------- softmax / correction ----------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const float scale_log2 = p.scale_log2;
+    uint32_t g = 0, ic = 0;  // KV steps and items so far
+    bool ok = true;
+    for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
+      const Item it = decode_item(idx, p);
+      if (it.n == 0) continue;
+      const int ob = ic & 1;
+      const int tile_r0 = it.qtile * kTileRows;
+      const int q_row = tile_r0 + row_in_tile;
+      const uint32_t t_o = tmem_base + lane_field + 256 + ob * 128;
+      float m_used = -INFINITY;
+      float2 l2 = make_float2(0.f, 0.f);
+      for (int j = 0; j < it.n; ++j, ++g) {
+        const int buf = g & 1;
+        const uint32_t t_s = tmem_base + lane_field + buf * 128;
+        ok = mbar_wait(s_full + buf, (g >> 1) & 1, abort_word);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (quarter == 0) ATTN_TRACE(2, 100 + j);  // S_j visible
+
+        const int col0 = j * kTileRows;
+        const bool need_mask =
+            (p.causal && col0 + kTileRows - 1 > tile_r0 + p.causal_offset) || (col0 + kTileRows > p.seq_kv);
+        int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
+        if (need_mask) {
+          int vis = p.seq_kv;
+          if (p.causal) vis = min(vis, q_row + p.causal_offset + 1);
+          limit = vis - col0;
+        }
+
+        // The whole score row (128 fp32) lives in registers: load it in two halves so the max of
+        // the first half overlaps the load of the second.
+        uint32_t sr[128];
+        tmem_ld_32x32b_x64(t_s, sr);
+        tmem_wait_ld();
+        tmem_ld_32x32b_x64(t_s + 64, sr + 64);
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i >= limit) sr[i] = 0xff800000u;  // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        }
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 64; i < 128; ++i)
+            if (i >= limit) sr[i] = 0xff800000u;
+        }
+#pragma unroll
+        for (int i = 64; i < 128; i += 4) {
+          mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        }
+        if (quarter == 0) ATTN_TRACE(2, 200 + j);  // row loaded, max done
+        const float m_new = fmaxf(mx0, mx1) * scale_log2;
+        const bool grow = m_new > m_used + kRescaleThreshold;  // also true for the first finite max
+        // Every phase of o_done is observed exactly once, in order, and always before P of this
+        // step is handed over: a parity wait only works within one phase of the barrier's current
+        // one, and the score buffers run ahead of the second MMA.
+        bool seen_prev_pv = (g == 0);
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          float alpha = 1.f;
+          if (grow) alpha = ex2(m_used - m_new);  // m_used = -inf gives 0
+          ok = mbar_wait(o_done, (g - 1) & 1, abort_word);  // O += P V of the previous step is done
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          seen_prev_pv = true;
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(t_o + c * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x16(t_o + c * 16, r);
+          }
+          l2.x *= alpha;
+          l2.y *= alpha;
+        }
+        if (grow) m_used = m_new;
+        const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+        const float2 scale2 = make_float2(scale_log2, scale_log2);
+        const float2 negm2 = make_float2(-m_sub, -m_sub);
+
+        // probabilities -> tensor memory (16-bit pairs over the first 64 columns of this buffer);
+        // masked scores are -inf and give (almost) exactly 0
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float2 x = ffma2(make_float2(__uint_as_float(sr[c * 32 + 2 * i]), __uint_as_float(sr[c * 32 + 2 * i + 1])),
+                                   scale2, negm2);
+            const float2 e = ((kPolyPairMask >> (i & 7)) & 1u) ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
+            l2 = fadd2(l2, e);
+            pk[i] = pack_pair<T>(e.x, e.y);
+          }
+          tmem_st_32x32b_x16(t_s + c * 16, pk);
+        }
+        if (quarter == 0) ATTN_TRACE(2, 300 + j);  // exponentials done, P stores issued
+        if (!seen_prev_pv) {
+          ok = mbar_wait(o_done, (g - 1) & 1, abort_word);  // long complete by now
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full + buf);
+        if (quarter == 0) ATTN_TRACE(2, 400 + j);  // P signalled
+      }
+      if (!ok) break;
+      // hand the row sums to the epilogue warps
+      ok = mbar_wait(l_free + ob, ((ic >> 1) & 1) ^ 1, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      lsum[ob * kTileRows + row_in_tile] = l2.x + l2.y;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(l_full + ob);
+      ++ic;
     }
   }
 
@@ -489,8 +585,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 }
 
 template <typename T>
-int launch_typed(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
-                 cudaStream_t stream) {
+int launch_typed(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+                 const AttnParams& p, cudaStream_t stream) {
   auto kfn = attn_fwd_kernel<T>;
   static bool configured = false;
   if (!configured) {
@@ -499,8 +595,9 @@ int launch_typed(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap
     if (rc) return rc;
     configured = true;
   }
-  dim3 grid(p.num_q_blocks, p.q_heads, p.batch);
-  kfn<<<grid, kAttnThreads, kAttnSmem, stream>>>(tq, tk, tv, p);
+  const int sms = num_sms();
+  const int grid = p.num_items < sms ? p.num_items : sms;
+  kfn<<<grid, kAttnThreads, kAttnSmem, stream>>>(tq, tk, tv, to, p);
   return check_cuda(cudaGetLastError(), "attn_fwd_kernel launch");
 }
 
@@ -515,8 +612,6 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
     return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: q_heads must be a multiple of kv_heads");
   if (a.dtype != B200K_F16 && a.dtype != B200K_BF16)
     return set_error(B200K_ERR_BAD_DTYPE, "attention_fwd: dtype must be F16 or BF16");
-  if (a.batch > 65535 || a.q_heads > 65535)
-    return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: batch and q_heads must be <= 65535");
   const int64_t strides[] = {a.q_stride_b, a.q_stride_h, a.q_stride_s, a.k_stride_b, a.k_stride_h, a.k_stride_s,
                              a.v_stride_b, a.v_stride_h, a.v_stride_s, a.o_stride_b, a.o_stride_h, a.o_stride_s};
   for (int64_t s : strides)
@@ -529,7 +624,7 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   int rc = ensure_sm100();
   if (rc) return rc;
 
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   const uint32_t box[4] = {64, kTileRows, 1, 1};
   {
     uint64_t dims[4] = {kD, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
@@ -552,6 +647,15 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
     if (rc) return rc;
   }
 
+  {
+    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
+                        static_cast<uint64_t>(a.batch)};
+    uint64_t st[3] = {static_cast<uint64_t>(a.o_stride_s) * 2, static_cast<uint64_t>(a.o_stride_h) * 2,
+                      static_cast<uint64_t>(a.o_stride_b) * 2};
+    rc = encode_tmap(&to, a.dtype, 4, a.o, dims, st, box);
+    if (rc) return rc;
+  }
+
   AttnParams p;
   p.o = a.o;
   p.o_stride_b = a.o_stride_b;
@@ -564,11 +668,14 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   p.seq_kv = a.seq_kv;
   p.causal = a.causal ? 1 : 0;
   p.causal_offset = a.seq_kv - a.seq_q;
-  p.num_q_blocks = (a.seq_q + 255) / 256;
+  p.num_q_tiles = (a.seq_q + kTileRows - 1) / kTileRows;
+  const int64_t items = static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles;
+  if (items > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: too many query tiles");
+  p.num_items = static_cast<int32_t>(items);
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
-  if (a.dtype == B200K_F16) return launch_typed<__half>(tq, tk, tv, p, stream);
-  return launch_typed<__nv_bfloat16>(tq, tk, tv, p, stream);
+  if (a.dtype == B200K_F16) return launch_typed<__half>(tq, tk, tv, to, p, stream);
+  return launch_typed<__nv_bfloat16>(tq, tk, tv, to, p, stream);
 }
 
 }  // namespace b200k
