@@ -317,23 +317,47 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
         uint32_t qc = 0, kc = 0, vc = 0, g = 0, ic = 0;  // Q tiles, K tiles, V tiles, KV steps, items so far
         bool ok = true;
+        // Score tiles form one stream over all of this CTA's items and run two KV steps ahead of
+        // the second MMA, across item boundaries: while the last two steps of an item finish, the
+        // first two score tiles of the next item are already being computed.
+        int s_idx = blockIdx.x;  // item the score cursor is in
+        int s_j = 0;             // next score tile of that item
+        Item s_it = {0, 0, 0, 0};
+        auto seek_item = [&]() {  // positions the cursor on the next item that has work
+          while (s_idx < p.num_items) {
+            s_it = decode_item(s_idx, p);
+            if (s_it.n > 0) return;
+            s_idx += gridDim.x;
+          }
+        };
+        uint32_t gs = 0;  // score tiles issued so far (global step index of the next one)
+        auto issue_next_score = [&]() -> bool {
+          if (s_idx >= p.num_items) return true;  // nothing left
+          if (s_j == 0) {
+            if (!mbar_wait(q_full, qc & 1, abort_word)) return false;
+            ++qc;
+          }
+          const int ks = kc % kKStages;
+          if (!mbar_wait(k_full + ks, (kc / kKStages) & 1, abort_word)) return false;
+          tc_fence_after();
+          ATTN_TRACE(1, 1000 + s_j);
+          issue_s(gs & 1, ks);
+          ++kc;
+          ++gs;
+          if (++s_j == s_it.n) {
+            umma_commit(q_empty);  // Q is free once the item's last score MMA has run
+            s_j = 0;
+            s_idx += gridDim.x;
+            seek_item();
+          }
+          return true;
+        };
+        seek_item();
+        ok = issue_next_score() && issue_next_score();  // fill both score buffers
         for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
           const Item it = decode_item(idx, p);
           if (it.n == 0) continue;
           const int ob = ic & 1;
-          if (!mbar_wait(q_full, qc & 1, abort_word)) break;
-          ++qc;
-          // the first two score tiles of the item
-          for (int jj = 0; jj < 2 && jj < it.n; ++jj) {
-            const int ks = kc % kKStages;
-            if (!mbar_wait(k_full + ks, (kc / kKStages) & 1, abort_word)) { ok = false; break; }
-            tc_fence_after();
-            ATTN_TRACE(1, 1000 + jj);
-            issue_s((g + jj) & 1, ks);
-            ++kc;
-          }
-          if (!ok) break;
-          if (it.n <= 2) umma_commit(q_empty);  // Q is free once the item's last score MMA has run
           for (int j = 0; j < it.n; ++j, ++g) {
             const int buf = g & 1;
             const int vs = vc % kVStages;
@@ -345,14 +369,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             issue_pv(ob, buf, vs, j == 0);
             ++vc;
             if (j == it.n - 1) umma_commit(o_full + ob);
-            if (j + 2 < it.n) {
-              const int ks = kc % kKStages;
-              if (!mbar_wait(k_full + ks, (kc / kKStages) & 1, abort_word)) { ok = false; break; }
-              tc_fence_after();
-              issue_s(buf, ks);
-              ++kc;
-              if (j + 2 == it.n - 1) umma_commit(q_empty);
-            }
+            // the score buffer just consumed is refilled with the tile two steps ahead
+            if (!issue_next_score()) { ok = false; break; }
             ATTN_TRACE(1, 6000 + j);
           }
           ++ic;
