@@ -4,26 +4,36 @@
 // takes items blockIdx.x, blockIdx.x + gridDim.x, ... from a list ordered (batch, head)-major with
 // the heaviest query tiles of a head first, so CTAs that run at the same time share K/V in L2.
 //
-//   warps 0..3    softmax + correction (one thread = one query row)             warpgroup 0
-//   warps 4..7    epilogue: O / rowsum -> global, one item behind the others     warpgroup 1
-//   warp 8        TMA loads: Q of the next item, then K_j (3 stages) / V_j (2)    warpgroup 2
-//   warp 9        issues every tcgen05.mma and owns tensor memory
-//   warps 10, 11  idle (complete warpgroup 2 for the setmaxnreg register hand-off)
+//   warps 0..3    softmax + correction, score columns 0..63 of every tile (thread = query row)
+//   warps 4..7    the same for score columns 64..127
+//   warps 8..11   epilogue: O / rowsum -> global, one item behind the others
+//   warp 12       TMA loads: Q of the next item, K_j (3 stages), V_j (2 stages)
+//   warp 13       issues the score MMAs (S = Q K^T) and owns tensor memory
+//   warp 14       issues the second MMAs (O += P V)
+//   warp 15       idle (completes the fourth warpgroup for the setmaxnreg register hand-off)
 //
-// Tensor memory (512 columns x 128 lanes):  S[0] | S[1] | O[0] | O[1], 128 fp32 columns each.
-//   * Two score buffers: the tensor core computes S(j+1) while the softmax works on S(j), so the
-//     softmax never waits for scores and the per-step chain "softmax -> P V -> next scores" of a
-//     single-buffer design is gone.  What remains is a throughput balance: about 1230 cycles of
-//     softmax instructions per 128 x 128 tile on the four SM sub-partitions against 1024 cycles of
-//     MMA (both measured with single-SM micro-benchmarks).
-//   * Two output accumulators: the epilogue of item i runs while item i+1 is being computed.
-//   * The probabilities P (16-bit, two per column) overwrite the first 64 columns of their score
-//     buffer and are the A operand of the second MMA straight from tensor memory.  MMAs issued by
-//     one thread complete in order, so issuing S(j+2) after "O += P(j) V(j)" is all that is needed
-//     to reuse a buffer.
+// Tensor memory (512 columns x 128 lanes):  S[0] | S[1] (128 fp32 columns each) | P[0] | P[1]
+// (64 columns each: 128 16-bit probabilities per row) | O (128 fp32 columns).
+//   * Two threads share a score row, 64 columns each, and exchange their partial row maximum
+//     through shared memory once per step.  One 128-column softmax step is about 650
+//     instructions on three different pipes (FMA, special function, ALU); one warp per SM
+//     sub-partition runs them nearly back to back (about 2100 cycles per step, measured), two
+//     warps overlap them.
+//   * A softmax thread holds its part of the score row in registers, so a score buffer is free
+//     again early in the step, as soon as the row has been loaded: S(j+2) is issued then.  The
+//     probabilities have buffers of their own for that reason.  The tensor core is never what the
+//     softmax waits for: neither the scores of the next step nor "O += P V" of the last one is on
+//     its critical path.
+//   * Two threads issue MMAs.  A tcgen05.mma does not return until the tensor pipe has room for
+//     it, so a group of eight blocks its thread for about as long as it executes (plus some 300
+//     cycles when the pipe was idle); with one issuing thread every wait of one kind of MMA
+//     delayed the other.
+//   * One output accumulator is enough: the first "O = P V" of an item is needed a whole softmax
+//     step after the last one of the previous item, and the epilogue reads O in less than that.
+//   * P is the A operand of the second MMA straight from tensor memory.
 //
-// Epilogue: accumulator -> registers -> 16-bit -> 128-byte-swizzled staging tile in shared memory
-// -> two TMA stores (rows past the end of the sequence are clipped by the tensor map).  Direct
+// Epilogue: accumulator -> registers -> 16-bit -> 128-byte-swizzled staging block (64 columns) in
+// shared memory -> TMA store, twice (rows past the end of the sequence are clipped by the tensor map).  Direct
 // row-per-thread global stores were measured at about 3000 cycles per item and delayed the TMA
 // loads of the next item; the staged store is a few hundred.
 //
@@ -39,12 +49,15 @@
 namespace b200k {
 namespace {
 
-constexpr int kAttnThreads = 384;
-// Registers: 3 warps per SM sub-partition x 168 at launch = 504 per lane, redistributed.
-constexpr int kRegsSoftmax = 232;
-constexpr int kRegsEpilogue = 128;
+constexpr int kAttnThreads = 512;
+constexpr int kTmaWarp = 12;
+constexpr int kScoreWarp = 13;
+constexpr int kPvWarp = 14;
+// Registers: 4 warps per SM sub-partition x 128 at launch = 512 per lane, redistributed.
+constexpr int kRegsSoftmax = 152;
+constexpr int kRegsEpilogue = 120;
 constexpr int kRegsOther = 72;
-static_assert(kRegsSoftmax + kRegsEpilogue + kRegsOther <= 504, "setmaxnreg.inc would never complete");
+static_assert(2 * kRegsSoftmax + kRegsEpilogue + kRegsOther <= 512, "setmaxnreg.inc would never complete");
 constexpr int kTileRows = 128;  // query rows per item, KV rows per tile
 constexpr int kD = 128;
 constexpr int kHalfTileBytes = kTileRows * 128;  // one 64-element column block: 16 KB
@@ -54,12 +67,17 @@ constexpr int kVStages = 2;
 constexpr int kQOffset = 0;
 constexpr int kKOffset = kTileBytes;
 constexpr int kVOffset = kKOffset + kKStages * kTileBytes;
-constexpr int kOStageOffset = kVOffset + kVStages * kTileBytes;  // epilogue staging tile (layout of a Q tile)
-constexpr int kLsumOffset = kOStageOffset + kTileBytes;          // float [2][128]: row sums for the epilogue
+constexpr int kOStageOffset = kVOffset + kVStages * kTileBytes;  // epilogue staging: one 64-column block
+constexpr int kMaxOffset = kOStageOffset + kHalfTileBytes;       // float [step parity][column half][128 rows]
+constexpr int kLsumOffset = kMaxOffset + 2 * 2 * kTileRows * 4;  // float [column half][128]: partial row sums
 constexpr int kBarOffset = kLsumOffset + 2 * kTileRows * 4;
-// q_full q_empty | k_full[3] k_empty[3] v_full[2] v_empty[2] | s_full[2] p_full[2] | o_done |
-// o_full[2] o_free[2] l_full[2] l_free[2]
-constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 4 + 1 + 8;
+// q_full q_empty | k_full[3] k_empty[3] v_full[2] v_empty[2] | s_full[2] s_free[2] p_full[2] x_full[2] |
+// o_done | o_full o_free l_full l_free
+constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 8 + 1 + 4;
+// tensor memory columns
+constexpr uint32_t kTmemS = 0;    // + 128 * buffer
+constexpr uint32_t kTmemP = 256;  // + 64 * buffer
+constexpr uint32_t kTmemO = 384;
 constexpr int kAttnSmem = kBarOffset + kNumBars * 8 + 16 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
@@ -118,16 +136,17 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi)
 
 // Optional timeline capture (compile with -DB200K_ATTN_TRACE): block (0,0,0) records
 // (tag, clock64) pairs per role into the buffer passed as the status pointer, 256 events per role:
-// role 0 = TMA thread, 1 = MMA thread, 2 = softmax tile 0 (thread 0), 3 = softmax tile 1.
+// role 0 = TMA thread, 1 = score MMA thread, 2 = softmax warp 0, 3 = epilogue (first warp), 4 = softmax warp 4.
 #ifdef B200K_ATTN_TRACE
-#define ATTN_TRACE(role, tag)                                                          \
-  do {                                                                                 \
-    if (trace_on && trace_n < 256) {                                                   \
-      long long* tb = reinterpret_cast<long long*>(p.status) + ((role)*256 + trace_n) * 2; \
-      tb[0] = (tag);                                                                   \
-      tb[1] = clock64();                                                               \
-      ++trace_n;                                                                       \
-    }                                                                                  \
+#define ATTN_TRACE(role, tag)                                                                        \
+  do {                                                                                               \
+    if (trace_on && trace_n < 256) {                                                                 \
+      longlong2 ev;                                                                                  \
+      ev.x = (tag);                                                                                  \
+      ev.y = clock64();                                                                              \
+      *reinterpret_cast<longlong2*>(reinterpret_cast<long long*>(p.status) + ((role)*256 + trace_n) * 2) = ev; \
+      ++trace_n;                                                                                     \
+    }                                                                                                \
   } while (0)
 #else
 #define ATTN_TRACE(role, tag) \
@@ -168,6 +187,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   float* lsum = reinterpret_cast<float*>(smem + kLsumOffset);
+  float* xmax = reinterpret_cast<float*>(smem + kMaxOffset);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOffset);
   uint64_t* q_full = bars;
   uint64_t* q_empty = bars + 1;
@@ -175,13 +195,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint64_t* k_empty = k_full + kKStages;
   uint64_t* v_full = k_empty + kKStages;
   uint64_t* v_empty = v_full + kVStages;
-  uint64_t* s_full = v_empty + kVStages;  // [score buffer]
-  uint64_t* p_full = s_full + 2;          // [score buffer]
-  uint64_t* o_done = p_full + 2;          // one phase per "O += P V"
-  uint64_t* o_full = o_done + 1;          // [output buffer] last P V of an item complete
-  uint64_t* o_free = o_full + 2;          // [output buffer] epilogue has read it
-  uint64_t* l_full = o_free + 2;          // [output buffer] row sums written
-  uint64_t* l_free = l_full + 2;          // [output buffer] row sums read
+  uint64_t* s_full = v_empty + kVStages;  // [buffer] score tile written
+  uint64_t* s_free = s_full + 2;          // [buffer] score tile is in the softmax threads' registers
+  uint64_t* p_full = s_free + 2;          // [buffer] probabilities written
+  uint64_t* x_full = p_full + 2;          // [step parity] both partial row maxima written
+  uint64_t* o_done = x_full + 2;          // one phase per "O += P V"
+  uint64_t* o_full = o_done + 1;          // last P V of an item complete
+  uint64_t* o_free = o_full + 1;          // epilogue has read the accumulator
+  uint64_t* l_full = o_free + 1;          // row sums written
+  uint64_t* l_free = l_full + 1;          // row sums read
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -190,6 +212,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 #ifdef B200K_ATTN_TRACE
   const bool trace_on = blockIdx.x == 0 && p.status != nullptr && lane == 0;
   int trace_n = 0;
+  const uint64_t trace_t0 = globaltimer_ns();
+  const long long trace_c0 = clock64();
 #endif
 
   if (threadIdx.x == 0) {
@@ -205,13 +229,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full + i, 1);
-      mbar_init(p_full + i, 4);
-      mbar_init(o_full + i, 1);
-      mbar_init(o_free + i, 4);
-      mbar_init(l_full + i, 4);
-      mbar_init(l_free + i, 4);
+      mbar_init(s_free + i, 8);
+      mbar_init(p_full + i, 8);
+      mbar_init(x_full + i, 8);
     }
     mbar_init(o_done, 1);
+    mbar_init(o_full, 1);
+    mbar_init(o_free, 4);
+    mbar_init(l_full, 8);
+    mbar_init(l_free, 4);
     *abort_word = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -220,7 +246,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     prefetch_tmap(&tmap_v);
     prefetch_tmap(&tmap_o);
   }
-  if (warp == 9) {
+  if (warp == kScoreWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -230,18 +256,28 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   const uint32_t tmem_base = *tmem_slot;
   const int group = p.q_heads / p.kv_heads;
 
-  if (warp >= 8) {
+  if (warp >= 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-    if (warp == 8) {
+    if (warp == kTmaWarp) {
       // ---------------- TMA producer ----------------
       if (lane == 0) {
         uint32_t qc = 0, kc = 0, vc = 0;  // Q loads, K tiles, V tiles issued so far
         bool ok = true;
-        for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-          const Item it = decode_item(idx, p);
-          if (it.n == 0) continue;
-          const int kv_head = it.head / group;
-          if (!mbar_wait(q_empty, (qc & 1) ^ 1, abort_word)) break;
+        auto load_k = [&](const Item& it, int j) {
+          const int ks = kc % kKStages;
+          if (!mbar_wait(k_empty + ks, ((kc / kKStages) & 1) ^ 1, abort_word)) return false;
+          mbar_arrive_expect_tx(k_full + ks, kTileBytes);
+#pragma unroll
+          for (int db = 0; db < 2; ++db)
+            tma_load_4d(smem + kKOffset + ks * kTileBytes + db * kHalfTileBytes, &tmap_k, k_full + ks, db * 64,
+                        j * kTileRows, it.head / group, it.batch);
+          ++kc;
+          return true;
+        };
+        // Q and the first K tiles of an item.  Q's buffer is free once the previous item's last
+        // score MMA has run, which is earlier than the release of its last V stage.
+        auto load_head = [&](const Item& it) {
+          if (!mbar_wait(q_empty, (qc & 1) ^ 1, abort_word)) return false;
           mbar_arrive_expect_tx(q_full, kTileBytes);
 #pragma unroll
           for (int db = 0; db < 2; ++db)
@@ -249,143 +285,159 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
                         it.batch);
           ++qc;
           ATTN_TRACE(0, 9000);
-          // Order: K_0, K_1, then V_j followed by K_(j+2): score tiles run two steps ahead of the
-          // second MMA, so their operands are requested first.
-          auto load_k = [&](int j) {
-            const int ks = kc % kKStages;
-            if (!mbar_wait(k_empty + ks, ((kc / kKStages) & 1) ^ 1, abort_word)) return false;
-            mbar_arrive_expect_tx(k_full + ks, kTileBytes);
-#pragma unroll
-            for (int db = 0; db < 2; ++db)
-              tma_load_4d(smem + kKOffset + ks * kTileBytes + db * kHalfTileBytes, &tmap_k, k_full + ks, db * 64,
-                          j * kTileRows, kv_head, it.batch);
-            ++kc;
-            return true;
-          };
-          for (int jj = 0; jj < 2 && jj < it.n && ok; ++jj) ok = load_k(jj);
+          for (int jj = 0; jj < kKStages && jj < it.n; ++jj)
+            if (!load_k(it, jj)) return false;
+          return true;
+        };
+        auto next_item = [&](int idx, Item& nx) {  // next item of this CTA that has work; num_items if none
+          for (idx += gridDim.x; idx < p.num_items; idx += gridDim.x) {
+            nx = decode_item(idx, p);
+            if (nx.n > 0) return idx;
+          }
+          return p.num_items;
+        };
+        Item it = {0, 0, 0, 0};
+        int idx = next_item(static_cast<int>(blockIdx.x) - static_cast<int>(gridDim.x), it);
+        if (idx < p.num_items) ok = load_head(it);
+        while (idx < p.num_items && ok) {
+          Item nx = {0, 0, 0, 0};
+          const int nidx = next_item(idx, nx);
+          const bool have_next = nidx < p.num_items;
+          // Order within an item: V_j, then K_(j+3); a K stage is released (by the score MMA that
+          // read it) earlier than a V stage.  The head of the next item goes before the last V.
           for (int j = 0; j < it.n && ok; ++j) {
+            if (j == it.n - 1 && have_next) {
+              ok = load_head(nx);
+              if (!ok) break;
+            }
             const int vs = vc % kVStages;
             if (!mbar_wait(v_empty + vs, ((vc / kVStages) & 1) ^ 1, abort_word)) { ok = false; break; }
             mbar_arrive_expect_tx(v_full + vs, kTileBytes);
 #pragma unroll
             for (int db = 0; db < 2; ++db)
               tma_load_4d(smem + kVOffset + vs * kTileBytes + db * kHalfTileBytes, &tmap_v, v_full + vs, db * 64,
-                          j * kTileRows, kv_head, it.batch);
+                          j * kTileRows, it.head / group, it.batch);
             ++vc;
-            if (j + 2 < it.n) ok = load_k(j + 2);
+            if (j + kKStages < it.n) ok = load_k(it, j + kKStages);
+            if (j == 0 && have_next) {
+              // The first tiles of the next item are wanted soon after this item's last score MMA
+              // frees Q, less than a trip to HBM later: ask for them in L2 now.
+              const int nkv = nx.head / group;
+#pragma unroll
+              for (int db = 0; db < 2; ++db) tma_prefetch_4d(&tmap_q, db * 64, nx.qtile * kTileRows, nx.head, nx.batch);
+              for (int jj = 0; jj < kKStages && jj < nx.n; ++jj) {
+#pragma unroll
+                for (int db = 0; db < 2; ++db) tma_prefetch_4d(&tmap_k, db * 64, jj * kTileRows, nkv, nx.batch);
+              }
+              for (int jj = 0; jj < kVStages && jj < nx.n; ++jj) {
+#pragma unroll
+                for (int db = 0; db < 2; ++db) tma_prefetch_4d(&tmap_v, db * 64, jj * kTileRows, nkv, nx.batch);
+              }
+            }
+          }
+          it = nx;
+          idx = nidx;
+        }
+      }
+      __syncwarp();
+    } else if (warp == kScoreWarp) {
+      // ---------------- score MMAs: S[g & 1] = Q K_g^T for every KV step g of this CTA ----------------
+      // Two threads issue MMAs, this one and the one below.  A tcgen05.mma does not return until
+      // the tensor pipe has room for it, so a group of eight blocks its thread for about as long
+      // as it executes (plus some 300 cycles when the pipe was idle): one thread for both kinds
+      // was busy nearly the whole step and every wait of one kind delayed the other.  The streams
+      // are independent: each orders itself through barriers (score buffer taken by the softmax,
+      // P written, stages loaded), never through issue order.
+      if (lane == 0) {
+        // The issuing thread runs scalar, latency-bound code: descriptors are a constant high word
+        // plus a low word that is a precomputed base plus a compile-time offset.
+        const uint32_t hi_k = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
+        const uint32_t q_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem + kQOffset)));
+        const uint32_t k_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem + kKOffset)));
+        auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+        uint32_t g = 0;                // score tiles issued so far
+        uint32_t kstage = 0, kpar = 0; // K ring position
+        uint32_t qpar = 0;
+        bool ok = true;
+        for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
+          const Item it = decode_item(idx, p);
+          if (it.n == 0) continue;
+          if (!mbar_wait(q_full, qpar, abort_word)) break;
+          qpar ^= 1;
+          for (int j = 0; j < it.n; ++j, ++g) {
+            const uint32_t buf = g & 1;
+            if (!mbar_wait(k_full + kstage, kpar, abort_word)) { ok = false; break; }
+            // the buffer last held tile g - 2; the softmax threads have it in registers
+            // (passes at once for the first two tiles)
+            if (!mbar_wait(s_free + buf, ((g >> 1) & 1) ^ 1, abort_word)) { ok = false; break; }
+            tc_fence_after();
+            ATTN_TRACE(1, 1000 + j);
+            const uint32_t b0 = k_lo + kstage * (kTileBytes >> 4);
+            const uint32_t d = tmem_base + kTmemS + buf * 128;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {  // 8 k-steps of 16 over the head dimension (two 64-wide blocks)
+              const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
+              umma_f16_ss(d, desc(q_lo + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
+            }
+            umma_commit(s_full + buf);
+            umma_commit(k_empty + kstage);
+            if (j == it.n - 1) umma_commit(q_empty);  // Q is free once the item's last score MMA has run
+            ATTN_TRACE(1, 2000 + j);
+            if (++kstage == kKStages) {
+              kstage = 0;
+              kpar ^= 1;
+            }
           }
         }
       }
       __syncwarp();
-    } else if (warp == 9) {
-      // ---------------- MMA issuer ----------------
+    } else if (warp == kPvWarp) {
+      // ---------------- second MMAs: O (+)= P[g & 1] V_g ----------------
       if (lane == 0) {
-        const uint32_t sq = smem_u32(smem + kQOffset);
-        const uint32_t sk = smem_u32(smem + kKOffset);
-        const uint32_t sv = smem_u32(smem + kVOffset);
-        // The issuing thread runs scalar, latency-bound code: descriptors are a constant high word
-        // plus a low word that is a precomputed base plus a compile-time offset.
-        const uint32_t hi_k = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
         const uint32_t hi_mn = static_cast<uint32_t>(make_desc_mnmajor_sw128(0, kHalfTileBytes) >> 32);
-        const uint32_t q_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sq));
-        const uint32_t k_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(sk));
-        const uint32_t v_lo = static_cast<uint32_t>(make_desc_mnmajor_sw128(sv, kHalfTileBytes));
+        const uint32_t v_lo = static_cast<uint32_t>(make_desc_mnmajor_sw128(smem_u32(smem + kVOffset), kHalfTileBytes));
         auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
-        // S[buf] = Q K^T : 8 k-steps of 16 over the head dimension (two 64-wide blocks).
-        auto issue_s = [&](int buf, int kstage) {
-          const uint32_t b0 = k_lo + kstage * (kTileBytes >> 4);
-          const uint32_t d = tmem_base + buf * 128;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
-            umma_f16_ss(d, desc(q_lo + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
-          }
-          umma_commit(s_full + buf);
-          umma_commit(k_empty + kstage);
-        };
-        // O[ob] (+)= P[buf] V : 8 k-steps of 16 KV rows; A from tensor memory, B = V (MN-major).
-        auto issue_pv = [&](int ob, int buf, int vstage, bool first) {
-          const uint32_t b0 = v_lo + vstage * (kTileBytes >> 4);
-          const uint32_t d = tmem_base + 256 + ob * 128;
-          const uint32_t a = tmem_base + buf * 128;
-          umma_f16_ts(d, a, desc(b0, hi_mn), kIdescPV, first ? 0u : 1u);
-#pragma unroll
-          for (int ks = 1; ks < 8; ++ks) umma_f16_ts(d, a + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, 1u);
-          umma_commit(v_empty + vstage);
-          umma_commit(o_done);
-        };
-
-        uint32_t qc = 0, kc = 0, vc = 0, g = 0, ic = 0;  // Q tiles, K tiles, V tiles, KV steps, items so far
+        uint32_t g = 0, ic = 0;  // KV steps and items so far
+        uint32_t vstage = 0, vpar = 0;
         bool ok = true;
-        // Score tiles form one stream over all of this CTA's items and run two KV steps ahead of
-        // the second MMA, across item boundaries: while the last two steps of an item finish, the
-        // first two score tiles of the next item are already being computed.
-        int s_idx = blockIdx.x;  // item the score cursor is in
-        int s_j = 0;             // next score tile of that item
-        Item s_it = {0, 0, 0, 0};
-        auto seek_item = [&]() {  // positions the cursor on the next item that has work
-          while (s_idx < p.num_items) {
-            s_it = decode_item(s_idx, p);
-            if (s_it.n > 0) return;
-            s_idx += gridDim.x;
-          }
-        };
-        uint32_t gs = 0;  // score tiles issued so far (global step index of the next one)
-        auto issue_next_score = [&]() -> bool {
-          if (s_idx >= p.num_items) return true;  // nothing left
-          if (s_j == 0) {
-            if (!mbar_wait(q_full, qc & 1, abort_word)) return false;
-            ++qc;
-          }
-          const int ks = kc % kKStages;
-          if (!mbar_wait(k_full + ks, (kc / kKStages) & 1, abort_word)) return false;
-          tc_fence_after();
-          ATTN_TRACE(1, 1000 + s_j);
-          issue_s(gs & 1, ks);
-          ++kc;
-          ++gs;
-          if (++s_j == s_it.n) {
-            umma_commit(q_empty);  // Q is free once the item's last score MMA has run
-            s_j = 0;
-            s_idx += gridDim.x;
-            seek_item();
-          }
-          return true;
-        };
-        seek_item();
-        ok = issue_next_score() && issue_next_score();  // fill both score buffers
         for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
           const Item it = decode_item(idx, p);
           if (it.n == 0) continue;
-          const int ob = ic & 1;
           for (int j = 0; j < it.n; ++j, ++g) {
-            const int buf = g & 1;
-            const int vs = vc % kVStages;
-            if (!mbar_wait(v_full + vs, (vc / kVStages) & 1, abort_word)) { ok = false; break; }
+            const uint32_t buf = g & 1;
+            if (!mbar_wait(v_full + vstage, vpar, abort_word)) { ok = false; break; }
             if (!mbar_wait(p_full + buf, (g >> 1) & 1, abort_word)) { ok = false; break; }
-            if (j == 0 && !mbar_wait(o_free + ob, ((ic >> 1) & 1) ^ 1, abort_word)) { ok = false; break; }
+            // the accumulator is read by the epilogue of the previous item
+            if (j == 0 && !mbar_wait(o_free, (ic & 1) ^ 1, abort_word)) { ok = false; break; }
             tc_fence_after();
-            ATTN_TRACE(1, 3000 + j);  // P_j ready
-            issue_pv(ob, buf, vs, j == 0);
-            ++vc;
-            if (j == it.n - 1) umma_commit(o_full + ob);
-            // the score buffer just consumed is refilled with the tile two steps ahead
-            if (!issue_next_score()) { ok = false; break; }
-            ATTN_TRACE(1, 6000 + j);
+            // 8 k-steps of 16 KV rows; A = P from tensor memory, B = V (MN-major)
+            const uint32_t b0 = v_lo + vstage * (kTileBytes >> 4);
+            const uint32_t d = tmem_base + kTmemO;
+            const uint32_t a = tmem_base + kTmemP + buf * 64;
+            umma_f16_ts(d, a, desc(b0, hi_mn), kIdescPV, j == 0 ? 0u : 1u);
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks) umma_f16_ts(d, a + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, 1u);
+            umma_commit(v_empty + vstage);
+            umma_commit(o_done);
+            if (j == it.n - 1) umma_commit(o_full);
+            if (++vstage == kVStages) {
+              vstage = 0;
+              vpar ^= 1;
+            }
           }
           ++ic;
         }
       }
       __syncwarp();
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 8) {
     // ---------------- epilogue: O / rowsum -> global, one item behind ----------------
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     uint8_t* stage = smem + kOStageOffset;
-    const bool store_thread = (warp == 4 && lane == 0);
+    const bool store_thread = (warp == 8 && lane == 0);
     auto epi_barrier = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
     uint32_t ic = 0;
     bool ok = true;
@@ -402,97 +454,113 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         }
         continue;
       }
-      const int ob = ic & 1;
-      const uint32_t par = (ic >> 1) & 1;
-      ok = mbar_wait(o_full + ob, par, abort_word) && mbar_wait(l_full + ob, par, abort_word);
+      const uint32_t par = ic & 1;
+      ok = mbar_wait(o_full, par, abort_word) && mbar_wait(l_full, par, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       if (quarter == 0) ATTN_TRACE(3, 100);
-      const float l = lsum[ob * kTileRows + row_in_tile];
+      const float l = lsum[row_in_tile] + lsum[kTileRows + row_in_tile];
       const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-      const uint32_t t_o = tmem_base + lane_field + 256 + ob * 128;
-      // the staging tile is free once the previous item's TMA stores have read it
-      if (store_thread) tma_store_wait_read<0>();
-      epi_barrier();
+      const uint32_t t_o = tmem_base + lane_field + kTmemO;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_o + c * 32, r);
-        tmem_wait_ld();
-        uint8_t* blk = stage + (c >> 1) * kHalfTileBytes + row_in_tile * 128;
+      for (int c2 = 0; c2 < 2; ++c2) {  // one 64-column block at a time
+        // the staging block is free once the previous TMA store has read it
+        if (store_thread) tma_store_wait_read<0>();
+        epi_barrier();
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 u;
-          u.x = pack_pair<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
-          u.y = pack_pair<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
-          u.z = pack_pair<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
-          u.w = pack_pair<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
-          const int chunk = (c & 1) * 4 + v;
-          *reinterpret_cast<uint4*>(blk + ((chunk ^ (row_in_tile & 7)) << 4)) = u;
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_o + (c2 * 2 + cc) * 32, r);
+          tmem_wait_ld();
+          uint8_t* blk = stage + row_in_tile * 128;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 u;
+            u.x = pack_pair<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+            u.y = pack_pair<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+            u.z = pack_pair<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+            u.w = pack_pair<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+            const int chunk = cc * 4 + v;
+            *reinterpret_cast<uint4*>(blk + ((chunk ^ (row_in_tile & 7)) << 4)) = u;
+          }
         }
-      }
-      // accumulator and row sums have been read: release them for the item after next
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(o_free + ob);
-        mbar_arrive(l_free + ob);
-      }
-      fence_proxy_async_smem();
-      epi_barrier();
-      if (store_thread) {
-        tma_store_4d(&tmap_o, stage, 0, it.qtile * kTileRows, it.head, it.batch);
-        tma_store_4d(&tmap_o, stage + kHalfTileBytes, 64, it.qtile * kTileRows, it.head, it.batch);
-        tma_store_commit();
+        if (c2 == 1) {
+          // accumulator and row sums have been read: release them for the next item
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(o_free);
+            mbar_arrive(l_free);
+          }
+        }
+        fence_proxy_async_smem();
+        epi_barrier();
+        if (store_thread) {
+          tma_store_4d(&tmap_o, stage, c2 * 64, it.qtile * kTileRows, it.head, it.batch);
+          tma_store_commit();
+        }
       }
       if (quarter == 0) ATTN_TRACE(3, 200);
       ++ic;
     }
     if (store_thread) tma_store_wait<0>();
   } else {
-    // ---------------- softmax / correction ----------------
+    // ---------------- softmax / correction: half h of the score columns ----------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int h = warp >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t t_o = tmem_base + lane_field + kTmemO + h * 64;
     const float scale_log2 = p.scale_log2;
+    const float2 scale2 = make_float2(scale_log2, scale_log2);
     uint32_t g = 0, ic = 0;  // KV steps and items so far
     bool ok = true;
+    // This thread's 64 scores live in registers.  The load of the next tile is issued at the end
+    // of a step, when the registers are dead, so that its latency and the completion of the P
+    // stores overlap.
+    uint32_t sr[64];
+    bool inflight = false;  // the load of tile g has been issued
     for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
       const Item it = decode_item(idx, p);
       if (it.n == 0) continue;
-      const int ob = ic & 1;
+      bool has_next_item = false;
+      for (int nidx = idx + gridDim.x; nidx < p.num_items && !has_next_item; nidx += gridDim.x)
+        has_next_item = decode_item(nidx, p).n > 0;
       const int tile_r0 = it.qtile * kTileRows;
       const int q_row = tile_r0 + row_in_tile;
-      const uint32_t t_o = tmem_base + lane_field + 256 + ob * 128;
       float m_used = -INFINITY;
       float2 l2 = make_float2(0.f, 0.f);
       for (int j = 0; j < it.n; ++j, ++g) {
-        const int buf = g & 1;
-        const uint32_t t_s = tmem_base + lane_field + buf * 128;
-        ok = mbar_wait(s_full + buf, (g >> 1) & 1, abort_word);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        if (quarter == 0) ATTN_TRACE(2, 100 + j);  // S_j visible
+        const uint32_t buf = g & 1;
+        const uint32_t t_s = tmem_base + lane_field + kTmemS + buf * 128 + h * 64;
+        const uint32_t t_p = tmem_base + lane_field + kTmemP + buf * 64 + h * 32;
+        if (!inflight) {
+          ok = mbar_wait(s_full + buf, (g >> 1) & 1, abort_word);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          tmem_ld_32x32b_x64(t_s, sr);
+        }
+        inflight = false;
 
         const int col0 = j * kTileRows;
         const bool need_mask =
             (p.causal && col0 + kTileRows - 1 > tile_r0 + p.causal_offset) || (col0 + kTileRows > p.seq_kv);
-        int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
+        int limit = 64;  // columns [0, limit) of this thread's half are visible to this row
         if (need_mask) {
           int vis = p.seq_kv;
           if (p.causal) vis = min(vis, q_row + p.causal_offset + 1);
-          limit = vis - col0;
+          limit = vis - col0 - h * 64;
         }
 
-        // The whole score row (128 fp32) lives in registers: load it in two halves so the max of
-        // the first half overlaps the load of the second.
-        uint32_t sr[128];
-        tmem_ld_32x32b_x64(t_s, sr);
         tmem_wait_ld();
-        tmem_ld_32x32b_x64(t_s + 64, sr + 64);
+        // the row is in registers: the tensor core may write the tile two steps ahead over it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free + buf);
+        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 100 + j);  // S_j in registers
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
@@ -504,19 +572,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
           mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
         }
-        tmem_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int i = 64; i < 128; ++i)
-            if (i >= limit) sr[i] = 0xff800000u;
-        }
-#pragma unroll
-        for (int i = 64; i < 128; i += 4) {
-          mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
-        }
-        if (quarter == 0) ATTN_TRACE(2, 200 + j);  // row loaded, max done
-        const float m_new = fmaxf(mx0, mx1) * scale_log2;
+        // exchange the partial maxima of the two halves of the row
+        const float m_loc = fmaxf(mx0, mx1);
+        xmax[(buf * 2 + h) * kTileRows + row_in_tile] = m_loc;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x_full + buf);
+        ok = mbar_wait(x_full + buf, (g >> 1) & 1, abort_word);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float m_oth = xmax[(buf * 2 + (h ^ 1)) * kTileRows + row_in_tile];
+        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 200 + j);  // row max known
+        const float m_new = fmaxf(m_loc, m_oth) * scale_log2;
         const bool grow = m_new > m_used + kRescaleThreshold;  // also true for the first finite max
         // Every phase of o_done is observed exactly once, in order, and always before P of this
         // step is handed over: a parity wait only works within one phase of the barrier's current
@@ -531,7 +597,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           seen_prev_pv = true;
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < 4; ++c) {  // this thread's 64 columns of the accumulator
             uint32_t r[16];
             tmem_ld_32x32b_x16(t_o + c * 16, r);
             tmem_wait_ld();
@@ -544,13 +610,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         }
         if (grow) m_used = m_new;
         const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-        const float2 scale2 = make_float2(scale_log2, scale_log2);
         const float2 negm2 = make_float2(-m_sub, -m_sub);
 
-        // probabilities -> tensor memory (16-bit pairs over the first 64 columns of this buffer);
-        // masked scores are -inf and give (almost) exactly 0
+        // probabilities -> tensor memory (16-bit pairs); masked scores are -inf and give (almost)
+        // exactly 0.  The second MMA that read this P buffer two steps ago was seen complete in
+        // the previous step.
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -560,9 +626,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             l2 = fadd2(l2, e);
             pk[i] = pack_pair<T>(e.x, e.y);
           }
-          tmem_st_32x32b_x16(t_s + c * 16, pk);
+          tmem_st_32x32b_x16(t_p + c * 16, pk);
         }
-        if (quarter == 0) ATTN_TRACE(2, 300 + j);  // exponentials done, P stores issued
+        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 300 + j);  // exponentials done, P stores issued
+        // Start on the next tile if it is already there (it is, except when the first tile of the
+        // next item has late operands: then P is handed over first and the next step waits).
+        if (j + 1 < it.n || has_next_item) {
+          const uint32_t nbuf = buf ^ 1;
+          if (__all_sync(0xffffffffu, mbar_test_wait(s_full + nbuf, ((g + 1) >> 1) & 1))) {
+            tc_fence_after();
+            tmem_ld_32x32b_x64(tmem_base + lane_field + kTmemS + nbuf * 128 + h * 64, sr);
+            inflight = true;
+          }
+        }
         if (!seen_prev_pv) {
           ok = mbar_wait(o_done, (g - 1) & 1, abort_word);  // long complete by now
           ok = __all_sync(0xffffffffu, ok);
@@ -572,16 +648,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full + buf);
-        if (quarter == 0) ATTN_TRACE(2, 400 + j);  // P signalled
+        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 400 + j);  // P signalled
       }
       if (!ok) break;
-      // hand the row sums to the epilogue warps
-      ok = mbar_wait(l_free + ob, ((ic >> 1) & 1) ^ 1, abort_word);
+      // hand the partial row sums to the epilogue warps
+      ok = mbar_wait(l_free, (ic & 1) ^ 1, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      lsum[ob * kTileRows + row_in_tile] = l2.x + l2.y;
+      lsum[h * kTileRows + row_in_tile] = l2.x + l2.y;
       __syncwarp();
-      if (lane == 0) mbar_arrive(l_full + ob);
+      if (lane == 0) mbar_arrive(l_full);
       ++ic;
     }
   }
@@ -589,6 +665,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
+#ifdef B200K_ATTN_TRACE
+  if (threadIdx.x == 0 && p.status != nullptr) {
+    long long* tb = reinterpret_cast<long long*>(p.status) + 5 * 256 * 2 + blockIdx.x * 2;
+    tb[0] = static_cast<long long>(trace_t0);
+    tb[1] = static_cast<long long>(globaltimer_ns());
+    if (blockIdx.x == 0) {
+      long long* tc = reinterpret_cast<long long*>(p.status) + 5 * 256 * 2 + 148 * 2;
+      tc[0] = clock64() - trace_c0;
+    }
+  }
+#endif
   if (*abort_word != 0) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) {
@@ -596,7 +683,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusAttnTimeout);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == kScoreWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
