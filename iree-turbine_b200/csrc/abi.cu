@@ -124,6 +124,39 @@ int encode_tmap(CUtensorMap* out, int dtype, int rank, void* base, const uint64_
   return B200K_OK;
 }
 
+// Copy-back stream of the host-buffer entry points, one per device, created on first use and kept
+// for the life of the process (a stream and two events; no device memory).  Results go back to the
+// host on this stream while the caller's stream is already uploading the next slice, so the two
+// copy directions overlap.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ready = nullptr;  // a slice's result is complete on the caller's stream
+  cudaEvent_t done = nullptr;   // all copy-backs are complete on the side stream
+};
+
+int get_side_stream(SideStream* out) {
+  static std::mutex mu;
+  static SideStream cache[64];
+  int dev = 0;
+  int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) return set_error(B200K_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  SideStream& c = cache[dev];
+  if (!c.stream) {
+    SideStream n;
+    rc = check_cuda(cudaStreamCreateWithFlags(&n.stream, cudaStreamNonBlocking), "create copy-back stream");
+    if (rc) return rc;
+    rc = check_cuda(cudaEventCreateWithFlags(&n.ready, cudaEventDisableTiming), "create event");
+    if (rc) return rc;
+    rc = check_cuda(cudaEventCreateWithFlags(&n.done, cudaEventDisableTiming), "create event");
+    if (rc) return rc;
+    c = n;
+  }
+  *out = c;
+  return 0;
+}
+
 }  // namespace b200k
 
 using namespace b200k;
@@ -215,20 +248,46 @@ int b200k_gemm_nt_host(const b200k_gemm_args* host, const b200k_gemm_args* dev, 
   const size_t in_es = dtype_size(dev->in_dtype), out_es = dtype_size(dev->out_dtype);
   if (in_es == 0 || out_es == 0) return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt_host: bad dtype");
   if (dev->m <= 0 || dev->n <= 0 || dev->k <= 0) return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: bad shape");
-  // Row pitches may differ between the host and device images.
-  int rc = check_cuda(cudaMemcpy2DAsync(const_cast<void*>(dev->a), dev->lda * in_es, host->a, host->lda * in_es,
-                                        dev->k * in_es, dev->m, cudaMemcpyHostToDevice, s),
-                      "gemm_nt_host: copy A");
+  // Row pitches may differ between the host and device images.  B goes up first; then A is
+  // uploaded, multiplied and C copied back in row blocks, the copy-back of one block (on the
+  // library's copy-back stream) overlapping the upload of the next.
+  SideStream side;
+  int rc = get_side_stream(&side);
   if (rc) return rc;
   rc = check_cuda(cudaMemcpy2DAsync(const_cast<void*>(dev->b), dev->ldb * in_es, host->b, host->ldb * in_es,
                                     dev->k * in_es, dev->n, cudaMemcpyHostToDevice, s),
                   "gemm_nt_host: copy B");
   if (rc) return rc;
-  rc = launch_gemm_nt(*dev, s);
-  if (rc) return rc;
-  return check_cuda(cudaMemcpy2DAsync(host->c, host->ldc * out_es, dev->c, dev->ldc * out_es, dev->n * out_es, dev->m,
-                                      cudaMemcpyDeviceToHost, s),
+  // blocks of whole 256-row tiles, at least 8 MB of A each so that a block keeps every SM busy
+  int64_t rows = dev->m;
+  const int64_t min_rows = ((int64_t(8) << 20) / (dev->k * int64_t(in_es)) + 255) / 256 * 256;
+  if (dev->m >= 2 * min_rows) rows = min_rows > 1024 ? min_rows : 1024;
+  for (int64_t r0 = 0; r0 < dev->m; r0 += rows) {
+    const int64_t nr = dev->m - r0 < rows ? dev->m - r0 : rows;
+    b200k_gemm_args blk = *dev;
+    blk.m = nr;
+    blk.a = static_cast<const char*>(dev->a) + r0 * dev->lda * in_es;
+    blk.c = static_cast<char*>(dev->c) + r0 * dev->ldc * out_es;
+    rc = check_cuda(cudaMemcpy2DAsync(const_cast<void*>(blk.a), dev->lda * in_es,
+                                      static_cast<const char*>(host->a) + r0 * host->lda * in_es, host->lda * in_es,
+                                      dev->k * in_es, nr, cudaMemcpyHostToDevice, s),
+                    "gemm_nt_host: copy A");
+    if (rc) return rc;
+    rc = launch_gemm_nt(blk, s);
+    if (rc) return rc;
+    rc = check_cuda(cudaEventRecord(side.ready, s), "record");
+    if (rc) return rc;
+    rc = check_cuda(cudaStreamWaitEvent(side.stream, side.ready, 0), "wait");
+    if (rc) return rc;
+    rc = check_cuda(cudaMemcpy2DAsync(static_cast<char*>(host->c) + r0 * host->ldc * out_es, host->ldc * out_es, blk.c,
+                                      dev->ldc * out_es, dev->n * out_es, nr, cudaMemcpyDeviceToHost, side.stream),
                     "gemm_nt_host: copy C");
+    if (rc) return rc;
+  }
+  // the caller's stream completes only when every copy-back has
+  rc = check_cuda(cudaEventRecord(side.done, side.stream), "record");
+  if (rc) return rc;
+  return check_cuda(cudaStreamWaitEvent(s, side.done, 0), "wait");
 }
 
 int b200k_attention_fwd_host(const b200k_attention_args* host, const b200k_attention_args* dev, void* stream) {
@@ -251,15 +310,42 @@ int b200k_attention_fwd_host(const b200k_attention_args* host, const b200k_atten
   };
   if (!dense(dev) || !dense(host))
     return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd_host: host and device images must be dense [b,h,s,d]");
-  int rc = check_cuda(cudaMemcpyAsync(const_cast<void*>(dev->q), host->q, qn, cudaMemcpyHostToDevice, s), "copy Q");
+  // One batch element at a time: upload, compute, and copy the result back on the library's
+  // copy-back stream while the next element is being uploaded.
+  SideStream side;
+  int rc = get_side_stream(&side);
   if (rc) return rc;
-  rc = check_cuda(cudaMemcpyAsync(const_cast<void*>(dev->k), host->k, kn, cudaMemcpyHostToDevice, s), "copy K");
+  const size_t q1 = qn / dev->batch, k1 = kn / dev->batch;
+  for (int32_t b = 0; b < dev->batch; ++b) {
+    b200k_attention_args one = *dev;
+    one.batch = 1;
+    one.q = static_cast<const char*>(dev->q) + b * q1;
+    one.k = static_cast<const char*>(dev->k) + b * k1;
+    one.v = static_cast<const char*>(dev->v) + b * k1;
+    one.o = static_cast<char*>(dev->o) + b * q1;
+    rc = check_cuda(cudaMemcpyAsync(const_cast<void*>(one.q), static_cast<const char*>(host->q) + b * q1, q1,
+                                    cudaMemcpyHostToDevice, s), "copy Q");
+    if (rc) return rc;
+    rc = check_cuda(cudaMemcpyAsync(const_cast<void*>(one.k), static_cast<const char*>(host->k) + b * k1, k1,
+                                    cudaMemcpyHostToDevice, s), "copy K");
+    if (rc) return rc;
+    rc = check_cuda(cudaMemcpyAsync(const_cast<void*>(one.v), static_cast<const char*>(host->v) + b * k1, k1,
+                                    cudaMemcpyHostToDevice, s), "copy V");
+    if (rc) return rc;
+    rc = launch_attention_fwd(one, s);
+    if (rc) return rc;
+    rc = check_cuda(cudaEventRecord(side.ready, s), "record");
+    if (rc) return rc;
+    rc = check_cuda(cudaStreamWaitEvent(side.stream, side.ready, 0), "wait");
+    if (rc) return rc;
+    rc = check_cuda(cudaMemcpyAsync(static_cast<char*>(host->o) + b * q1, one.o, q1, cudaMemcpyDeviceToHost,
+                                    side.stream), "copy O");
+    if (rc) return rc;
+  }
+  // the caller's stream completes only when every copy-back has
+  rc = check_cuda(cudaEventRecord(side.done, side.stream), "record");
   if (rc) return rc;
-  rc = check_cuda(cudaMemcpyAsync(const_cast<void*>(dev->v), host->v, kn, cudaMemcpyHostToDevice, s), "copy V");
-  if (rc) return rc;
-  rc = launch_attention_fwd(*dev, s);
-  if (rc) return rc;
-  return check_cuda(cudaMemcpyAsync(host->o, dev->o, qn, cudaMemcpyDeviceToHost, s), "copy O");
+  return check_cuda(cudaStreamWaitEvent(s, side.done, 0), "wait");
 }
 
 }  // extern "C"
