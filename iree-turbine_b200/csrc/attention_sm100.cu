@@ -54,9 +54,9 @@ constexpr int kTmaWarp = 12;
 constexpr int kScoreWarp = 13;
 constexpr int kPvWarp = 14;
 // Registers: 4 warps per SM sub-partition x 128 at launch = 512 per lane, redistributed.
-constexpr int kRegsSoftmax = 152;
-constexpr int kRegsEpilogue = 120;
-constexpr int kRegsOther = 72;
+constexpr int kRegsSoftmax = 184;
+constexpr int kRegsEpilogue = 80;
+constexpr int kRegsOther = 64;
 static_assert(2 * kRegsSoftmax + kRegsEpilogue + kRegsOther <= 512, "setmaxnreg.inc would never complete");
 constexpr int kTileRows = 128;  // query rows per item, KV rows per tile
 constexpr int kD = 128;
@@ -68,12 +68,12 @@ constexpr int kQOffset = 0;
 constexpr int kKOffset = kTileBytes;
 constexpr int kVOffset = kKOffset + kKStages * kTileBytes;
 constexpr int kOStageOffset = kVOffset + kVStages * kTileBytes;  // epilogue staging: one 64-column block
-constexpr int kMaxOffset = kOStageOffset + kHalfTileBytes;       // float [step parity][column half][128 rows]
-constexpr int kLsumOffset = kMaxOffset + 2 * 2 * kTileRows * 4;  // float [column half][128]: partial row sums
-constexpr int kBarOffset = kLsumOffset + 2 * kTileRows * 4;
+constexpr int kMaxOffset = kOStageOffset + kHalfTileBytes;   // float [warpgroup][128 rows]: running max it published
+constexpr int kLsumOffset = kMaxOffset + 2 * kTileRows * 4;  // float [warpgroup][max, sum][128 rows] for the epilogue
+constexpr int kBarOffset = kLsumOffset + 2 * 2 * kTileRows * 4;
 // q_full q_empty | k_full[3] k_empty[3] v_full[2] v_empty[2] | s_full[2] s_free[2] p_full[2] x_full[2] |
-// o_done | o_full o_free l_full l_free
-constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 8 + 1 + 4;
+// o_done[2] | o_full o_free l_full l_free
+constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 8 + 2 + 4;
 // tensor memory columns
 constexpr uint32_t kTmemS = 0;    // + 128 * buffer
 constexpr uint32_t kTmemP = 256;  // + 64 * buffer
@@ -81,6 +81,10 @@ constexpr uint32_t kTmemO = 384;
 constexpr int kAttnSmem = kBarOffset + kNumBars * 8 + 16 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
+#ifndef B200K_ATTN_PREFETCH
+#define B200K_ATTN_PREFETCH 0
+#endif
+constexpr bool kPrefetchNext = B200K_ATTN_PREFETCH != 0;
 
 struct AttnParams {
   void* o;
@@ -198,9 +202,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint64_t* s_full = v_empty + kVStages;  // [buffer] score tile written
   uint64_t* s_free = s_full + 2;          // [buffer] score tile is in the softmax threads' registers
   uint64_t* p_full = s_free + 2;          // [buffer] probabilities written
-  uint64_t* x_full = p_full + 2;          // [step parity] both partial row maxima written
-  uint64_t* o_done = x_full + 2;          // one phase per "O += P V"
-  uint64_t* o_full = o_done + 1;          // last P V of an item complete
+  uint64_t* x_full = p_full + 2;          // [warpgroup] it has published the row maxima after its step
+  uint64_t* o_done = x_full + 2;          // [step parity] "O += P V" of that step complete
+  uint64_t* o_full = o_done + 2;          // last P V of an item complete
   uint64_t* o_free = o_full + 1;          // epilogue has read the accumulator
   uint64_t* l_full = o_free + 1;          // row sums written
   uint64_t* l_free = l_full + 1;          // row sums read
@@ -229,11 +233,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full + i, 1);
-      mbar_init(s_free + i, 8);
-      mbar_init(p_full + i, 8);
-      mbar_init(x_full + i, 8);
+      mbar_init(s_free + i, 4);
+      mbar_init(p_full + i, 4);
+      mbar_init(x_full + i, 4);
+      mbar_init(o_done + i, 1);
     }
-    mbar_init(o_done, 1);
     mbar_init(o_full, 1);
     mbar_init(o_free, 4);
     mbar_init(l_full, 8);
@@ -319,7 +323,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
                           j * kTileRows, it.head / group, it.batch);
             ++vc;
             if (j + kKStages < it.n) ok = load_k(it, j + kKStages);
-            if (j == 0 && have_next) {
+            if (kPrefetchNext && j == 0 && have_next) {
               // The first tiles of the next item are wanted soon after this item's last score MMA
               // frees Q, less than a trip to HBM later: ask for them in L2 now.
               const int nkv = nx.head / group;
@@ -418,7 +422,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 #pragma unroll
             for (int ks = 1; ks < 8; ++ks) umma_f16_ts(d, a + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, 1u);
             umma_commit(v_empty + vstage);
-            umma_commit(o_done);
+            umma_commit(o_done + buf);
             if (j == it.n - 1) umma_commit(o_full);
             if (++vstage == kVStages) {
               vstage = 0;
@@ -439,7 +443,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     uint8_t* stage = smem + kOStageOffset;
     const bool store_thread = (warp == 8 && lane == 0);
     auto epi_barrier = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
-    uint32_t ic = 0;
+    uint32_t ic = 0, g0 = 0;  // items so far, KV steps before the current item
     bool ok = true;
     for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
       const Item it = decode_item(idx, p);
@@ -460,7 +464,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       if (!ok) break;
       tc_fence_after();
       if (quarter == 0) ATTN_TRACE(3, 100);
-      const float l = lsum[row_in_tile] + lsum[kTileRows + row_in_tile];
+      // The two warpgroups' partial row sums, each relative to the running max the warpgroup last
+      // used; the accumulator is relative to the larger one.  They are added in the order "the
+      // warpgroup that took the item's even steps first", so that the result does not depend on
+      // what the CTA processed before this item.
+      const int we = g0 & 1, wo = we ^ 1;
+      const float m0 = lsum[(we * 2 + 0) * kTileRows + row_in_tile], l0 = lsum[(we * 2 + 1) * kTileRows + row_in_tile];
+      const float m1 = lsum[(wo * 2 + 0) * kTileRows + row_in_tile], l1 = lsum[(wo * 2 + 1) * kTileRows + row_in_tile];
+      const float mm = fmaxf(m0, m1);
+      const float a0 = (m0 == -INFINITY) ? 0.f : ex2(m0 - mm);
+      const float a1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - mm);
+      const float l = l0 * a0 + l1 * a1;
       const float inv = (l > 0.f) ? 1.0f / l : 0.f;
       const uint32_t t_o = tmem_base + lane_field + kTmemO;
 #pragma unroll
@@ -503,101 +517,103 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
       if (quarter == 0) ATTN_TRACE(3, 200);
       ++ic;
+      g0 += it.n;
     }
     if (store_thread) tma_store_wait<0>();
   } else {
-    // ---------------- softmax / correction: half h of the score columns ----------------
+    // ---------------- softmax / correction: warpgroup w takes the KV steps g with (g & 1) == w ----------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-    const int h = warp >> 2;
+    const int w = warp >> 2;  // also the score buffer and the P buffer this warpgroup works on
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t t_o = tmem_base + lane_field + kTmemO + h * 64;
+    const uint32_t t_s = tmem_base + lane_field + kTmemS + w * 128;
+    const uint32_t t_p = tmem_base + lane_field + kTmemP + w * 64;
+    const uint32_t t_o = tmem_base + lane_field + kTmemO;
+    float* m_mine = xmax + w * kTileRows + row_in_tile;
+    const float* m_theirs = xmax + (w ^ 1) * kTileRows + row_in_tile;
     const float scale_log2 = p.scale_log2;
     const float2 scale2 = make_float2(scale_log2, scale_log2);
-    uint32_t g = 0, ic = 0;  // KV steps and items so far
+    uint32_t g = 0, ic = 0;  // KV steps (of both warpgroups) and items so far
     bool ok = true;
-    // This thread's 64 scores live in registers.  The load of the next tile is issued at the end
-    // of a step, when the registers are dead, so that its latency and the completion of the P
-    // stores overlap.
-    uint32_t sr[64];
-    bool inflight = false;  // the load of tile g has been issued
     for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
       const Item it = decode_item(idx, p);
       if (it.n == 0) continue;
-      bool has_next_item = false;
-      for (int nidx = idx + gridDim.x; nidx < p.num_items && !has_next_item; nidx += gridDim.x)
-        has_next_item = decode_item(nidx, p).n > 0;
       const int tile_r0 = it.qtile * kTileRows;
       const int q_row = tile_r0 + row_in_tile;
-      float m_used = -INFINITY;
+      float m_ref = -INFINITY;  // running max this warpgroup's row sum is relative to
       float2 l2 = make_float2(0.f, 0.f);
       for (int j = 0; j < it.n; ++j, ++g) {
-        const uint32_t buf = g & 1;
-        const uint32_t t_s = tmem_base + lane_field + kTmemS + buf * 128 + h * 64;
-        const uint32_t t_p = tmem_base + lane_field + kTmemP + buf * 64 + h * 32;
-        if (!inflight) {
-          ok = mbar_wait(s_full + buf, (g >> 1) & 1, abort_word);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          tmem_ld_32x32b_x64(t_s, sr);
-        }
-        inflight = false;
+        if ((g & 1u) != static_cast<uint32_t>(w)) continue;
+        const uint32_t ph = (g >> 1) & 1;  // phase of this warpgroup's own barriers in this step
+        ok = mbar_wait(s_full + w, ph, abort_word);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr[128];
+        tmem_ld_32x32b_x64(t_s, sr);
+        tmem_ld_32x32b_x64(t_s + 64, sr + 64);
 
         const int col0 = j * kTileRows;
         const bool need_mask =
             (p.causal && col0 + kTileRows - 1 > tile_r0 + p.causal_offset) || (col0 + kTileRows > p.seq_kv);
-        int limit = 64;  // columns [0, limit) of this thread's half are visible to this row
+        int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
         if (need_mask) {
           int vis = p.seq_kv;
           if (p.causal) vis = min(vis, q_row + p.causal_offset + 1);
-          limit = vis - col0 - h * 64;
+          limit = vis - col0;
         }
-
         tmem_wait_ld();
         // the row is in registers: the tensor core may write the tile two steps ahead over it
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(s_free + buf);
-        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 100 + j);  // S_j in registers
+        if (lane == 0) mbar_arrive(s_free + w);
+        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 100 + j);  // S_j in registers
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
+          for (int i = 0; i < 128; ++i)
             if (i >= limit) sr[i] = 0xff800000u;  // -inf
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
+        for (int i = 0; i < 128; i += 4) {
           mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
           mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
         }
-        // exchange the partial maxima of the two halves of the row
-        const float m_loc = fmaxf(mx0, mx1);
-        xmax[(buf * 2 + h) * kTileRows + row_in_tile] = m_loc;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(x_full + buf);
-        ok = mbar_wait(x_full + buf, (g >> 1) & 1, abort_word);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const float m_oth = xmax[(buf * 2 + (h ^ 1)) * kTileRows + row_in_tile];
-        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 200 + j);  // row max known
-        const float m_new = fmaxf(m_loc, m_oth) * scale_log2;
-        const bool grow = m_new > m_used + kRescaleThreshold;  // also true for the first finite max
-        // Every phase of o_done is observed exactly once, in order, and always before P of this
-        // step is handed over: a parity wait only works within one phase of the barrier's current
-        // one, and the score buffers run ahead of the second MMA.
-        bool seen_prev_pv = (g == 0);
-        if (j > 0 && __any_sync(0xffffffffu, grow)) {
-          float alpha = 1.f;
-          if (grow) alpha = ex2(m_used - m_new);  // m_used = -inf gives 0
-          ok = mbar_wait(o_done, (g - 1) & 1, abort_word);  // O += P V of the previous step is done
+        const float m_new = fmaxf(mx0, mx1) * scale_log2;
+        // The running max after the previous step, published by the other warpgroup early in that
+        // step (half a step ago).  Every phase of x_full is observed, also when the value is not
+        // needed (first step of an item).
+        float m_prev = -INFINITY;
+        if (g > 0) {
+          ok = mbar_wait(x_full + (w ^ 1), ((g - 1) >> 1) & 1, abort_word);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          seen_prev_pv = true;
+          if (j > 0) m_prev = *m_theirs;
+        }
+        const bool grow = m_new > m_prev + kRescaleThreshold;  // also true for the first finite max
+        const float m_cur = grow ? m_new : m_prev;
+        *m_mine = m_cur;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x_full + w);
+        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 200 + j);  // running max published
+        // this warpgroup's partial row sum follows the running max
+        if (m_prev != m_ref) {  // m_prev > m_ref: the other warpgroup raised it
+          const float a = ex2(m_ref - m_prev);  // m_ref = -inf gives 0 (and the sum is 0 then)
+          l2.x *= a;
+          l2.y *= a;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          // Rescale O between "O += P V" of the previous step (the other warpgroup's P) and this
+          // step's.  Rare after the first steps of an item: the max must grow by 2^8.
+          float alpha = 1.f;
+          if (grow) alpha = ex2(m_prev - m_new);  // m_prev = -inf gives 0
+          ok = mbar_wait(o_done + (w ^ 1), ((g - 1) >> 1) & 1, abort_word);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {  // this thread's 64 columns of the accumulator
+          for (int c = 0; c < 8; ++c) {
             uint32_t r[16];
             tmem_ld_32x32b_x16(t_o + c * 16, r);
             tmem_wait_ld();
@@ -608,15 +624,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           l2.x *= alpha;
           l2.y *= alpha;
         }
-        if (grow) m_used = m_new;
-        const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+        m_ref = m_cur;
+        const float m_sub = (m_cur == -INFINITY) ? 0.f : m_cur;
         const float2 negm2 = make_float2(-m_sub, -m_sub);
+        // this warpgroup's P buffer was last read by "O += P V" two steps ago
+        if (g >= 2) {
+          ok = mbar_wait(o_done + w, ph ^ 1, abort_word);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
 
-        // probabilities -> tensor memory (16-bit pairs); masked scores are -inf and give (almost)
-        // exactly 0.  The second MMA that read this P buffer two steps ago was seen complete in
-        // the previous step.
+        // probabilities -> tensor memory (16-bit pairs); masked scores are -inf and give (almost) exactly 0
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -628,34 +648,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           }
           tmem_st_32x32b_x16(t_p + c * 16, pk);
         }
-        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 300 + j);  // exponentials done, P stores issued
-        // Start on the next tile if it is already there (it is, except when the first tile of the
-        // next item has late operands: then P is handed over first and the next step waits).
-        if (j + 1 < it.n || has_next_item) {
-          const uint32_t nbuf = buf ^ 1;
-          if (__all_sync(0xffffffffu, mbar_test_wait(s_full + nbuf, ((g + 1) >> 1) & 1))) {
-            tc_fence_after();
-            tmem_ld_32x32b_x64(tmem_base + lane_field + kTmemS + nbuf * 128 + h * 64, sr);
-            inflight = true;
-          }
-        }
-        if (!seen_prev_pv) {
-          ok = mbar_wait(o_done, (g - 1) & 1, abort_word);  // long complete by now
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
+        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 300 + j);  // exponentials done, P stores issued
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + buf);
-        if (quarter == 0) ATTN_TRACE(2 + 2 * h, 400 + j);  // P signalled
+        if (lane == 0) mbar_arrive(p_full + w);
+        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 400 + j);  // P signalled
       }
       if (!ok) break;
-      // hand the partial row sums to the epilogue warps
+      // hand (max, sum) of this warpgroup's steps to the epilogue warps
       ok = mbar_wait(l_free, (ic & 1) ^ 1, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      lsum[h * kTileRows + row_in_tile] = l2.x + l2.y;
+      lsum[(w * 2 + 0) * kTileRows + row_in_tile] = m_ref;
+      lsum[(w * 2 + 1) * kTileRows + row_in_tile] = l2.x + l2.y;
       __syncwarp();
       if (lane == 0) mbar_arrive(l_full);
       ++ic;
