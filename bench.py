@@ -315,7 +315,7 @@ class PagedDecodeWL(Workload):
 
 
 WORKLOADS = {
-    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 247.0e6),
+    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 246.8e6),
     "attn_causal": lambda: AttentionWL("attn_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
     "gemm_f16": lambda: GemmWL("gemm_f16", 2048, False),
     "gemm_fp8": lambda: GemmWL("gemm_fp8", 8192, True),

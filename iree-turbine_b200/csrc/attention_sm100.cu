@@ -4,8 +4,8 @@
 // takes items blockIdx.x, blockIdx.x + gridDim.x, ... from a list ordered (batch, head)-major with
 // the heaviest query tiles of a head first, so CTAs that run at the same time share K/V in L2.
 //
-//   warps 0..3    softmax + correction, score columns 0..63 of every tile (thread = query row)
-//   warps 4..7    the same for score columns 64..127
+//   warps 0..3    softmax + correction of the even KV steps of the CTA (thread = query row)
+//   warps 4..7    the same for the odd KV steps
 //   warps 8..11   epilogue: O / rowsum -> global, one item behind the others
 //   warp 12       TMA loads: Q of the next item, K_j (3 stages), V_j (2 stages)
 //   warp 13       issues the score MMAs (S = Q K^T) and owns tensor memory
@@ -14,12 +14,16 @@
 //
 // Tensor memory (512 columns x 128 lanes):  S[0] | S[1] (128 fp32 columns each) | P[0] | P[1]
 // (64 columns each: 128 16-bit probabilities per row) | O (128 fp32 columns).
-//   * Two threads share a score row, 64 columns each, and exchange their partial row maximum
-//     through shared memory once per step.  One 128-column softmax step is about 650
-//     instructions on three different pipes (FMA, special function, ALU); one warp per SM
-//     sub-partition runs them nearly back to back (about 2100 cycles per step, measured), two
-//     warps overlap them.
-//   * A softmax thread holds its part of the score row in registers, so a score buffer is free
+//   * Score tile g goes to S[g & 1] and is handled by softmax warpgroup g & 1, which writes P[g & 1].
+//     The two warpgroups are half a step apart: while one is in its latency-bound part (wait,
+//     tensor-memory load, row max, hand-over) the other runs its exponentials.  They share ONE
+//     running row max and ONE accumulator: early in its step a warpgroup reads the running max the
+//     other published half a step before, decides whether this tile raises it (by more than 2^8),
+//     and publishes the result; only when it does raise it is O rescaled, by that warpgroup, after
+//     "O += P V" of the previous step (the other warpgroup's) has completed and before its own P is
+//     handed over.  Each warpgroup keeps a partial row sum relative to the running max it last saw;
+//     the epilogue brings the two to the final max and adds them.
+//   * A softmax thread holds its whole score row in registers, so a score buffer is free
 //     again early in the step, as soon as the row has been loaded: S(j+2) is issued then.  The
 //     probabilities have buffers of their own for that reason.  The tensor core is never what the
 //     softmax waits for: neither the scores of the next step nor "O += P V" of the last one is on
@@ -33,8 +37,8 @@
 //   * P is the A operand of the second MMA straight from tensor memory.
 //
 // Epilogue: accumulator -> registers -> 16-bit -> 128-byte-swizzled staging block (64 columns) in
-// shared memory -> TMA store, twice (rows past the end of the sequence are clipped by the tensor map).  Direct
-// row-per-thread global stores were measured at about 3000 cycles per item and delayed the TMA
+// shared memory -> TMA store, twice (rows past the end of the sequence are clipped by the tensor
+// map).  Direct row-per-thread global stores were measured at about 3000 cycles per item and delayed the TMA
 // loads of the next item; the staged store is a few hundred.
 //
 // Softmax: running max in log2 units (scores are multiplied by scale * log2(e) inside the
@@ -53,7 +57,8 @@ constexpr int kAttnThreads = 512;
 constexpr int kTmaWarp = 12;
 constexpr int kScoreWarp = 13;
 constexpr int kPvWarp = 14;
-// Registers: 4 warps per SM sub-partition x 128 at launch = 512 per lane, redistributed.
+// Registers: 4 warps per SM sub-partition x 128 at launch = 512 per lane, redistributed.  A
+// setmaxnreg.inc beyond what the others gave up never completes.
 constexpr int kRegsSoftmax = 184;
 constexpr int kRegsEpilogue = 80;
 constexpr int kRegsOther = 64;
