@@ -43,8 +43,9 @@
 //
 // Softmax: running max in log2 units (scores are multiplied by scale * log2(e) inside the
 // exponent's FMA); O is only rescaled when a row's max grows by more than 2^8 (stale max used for
-// both P and the running sum, exact after the final division); 3 of every 8 column pairs take a
-// degree-3 polynomial on the FMA pipe instead of ex2.approx to balance the special-function unit.
+// both P and the running sum, exact after the final division).  A degree-3 polynomial on the FMA
+// pipe can replace ex2.approx for a share of the column pairs (B200K_ATTN_POLY_MASK); it is off,
+// see the measurements at kPolyPairMask.
 #include <type_traits>
 
 #include "common.cuh"
@@ -128,7 +129,14 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 }
 
 // Which of every 8 consecutive column pairs take the polynomial instead of ex2.approx (bit i = pair i).
-constexpr uint32_t kPolyPairMask = 0x92u;  // 3 of 8
+// Measured (C2 / C3, TFLOP/s): none 1041 / 1058, 1 of 8 1031 / 1048, 2 of 8 1016 / 1033, 3 of 8 1009 / 1013,
+// 4 of 8 962 / 969.  With two softmax warps per SM sub-partition half a step apart the step is bound by
+// instruction issue, not by the special-function unit, and the polynomial costs more instructions.
+// (With one softmax warp per sub-partition 3 of 8 was the best.)
+#ifndef B200K_ATTN_POLY_MASK
+#define B200K_ATTN_POLY_MASK 0x00u
+#endif
+constexpr uint32_t kPolyPairMask = B200K_ATTN_POLY_MASK;
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
