@@ -250,6 +250,20 @@ int b200k_paged_gather(const void* cache, const int32_t* block_table, const int3
                        int32_t block_table_stride, int32_t max_seq_len, int64_t kv_page_stride,
                        int64_t kv_head_stride, int32_t elem_bytes, void* stream);
 
+/*
+ * KV-cache append (the step before decode; the reference's decode templates assume a cache that
+ * some other kernel has filled, it has no call site of its own for this):
+ *   cache[block_table[s, p / page_size], h, p % page_size, :] = new[s, t, h, :],  p = positions[s] + t
+ * for t in [0, new_tokens), for K and V alike.  k_new / v_new: [num_seqs, new_tokens, kv_heads,
+ * head_dim] contiguous; caches and block table as in b200k_decode_args (paged form).  The address
+ * function is the decode kernel's.  A row whose block-table entry is negative, outside the pool
+ * or beyond the table is not written; B200K status bit 4 is OR-ed into *status (optional).
+ */
+int b200k_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int32_t* block_table,
+                    const int32_t* positions, int32_t num_seqs, int32_t new_tokens, int32_t kv_heads, int32_t head_dim,
+                    int32_t page_size, int32_t num_pages, int32_t block_table_stride, int64_t kv_page_stride,
+                    int64_t kv_head_stride, int32_t elem_bytes, int32_t* status, void* stream);
+
 /* ---- per-tensor fp8 quantisation helper -------------------------------------------- */
 /*
  * scale = max|x| / 448 (1.0 if the tensor is all zero), y = e4m3(x / scale).

@@ -168,6 +168,11 @@ EXPORTED_SYMBOLS = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
          C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p],
     ),
+    "b200k_kv_append": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+         C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p],
+    ),
     "b200k_quantize_e4m3": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "b200k_gemm_nt_host": (C.c_int, [C.POINTER(GemmArgs), C.POINTER(GemmArgs), C.c_void_p]),
     "b200k_attention_fwd_host": (C.c_int, [C.POINTER(AttentionArgs), C.POINTER(AttentionArgs), C.c_void_p]),

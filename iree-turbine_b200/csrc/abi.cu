@@ -236,6 +236,15 @@ int b200k_paged_gather(const void* cache, const int32_t* block_table, const int3
                              static_cast<cudaStream_t>(stream));
 }
 
+int b200k_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int32_t* block_table,
+                    const int32_t* positions, int32_t num_seqs, int32_t new_tokens, int32_t kv_heads, int32_t head_dim,
+                    int32_t page_size, int32_t num_pages, int32_t block_table_stride, int64_t kv_page_stride,
+                    int64_t kv_head_stride, int32_t elem_bytes, int32_t* status, void* stream) {
+  return launch_kv_append(k_new, v_new, k_cache, v_cache, block_table, positions, num_seqs, new_tokens, kv_heads,
+                          head_dim, page_size, num_pages, block_table_stride, kv_page_stride, kv_head_stride, elem_bytes,
+                          status, static_cast<cudaStream_t>(stream));
+}
+
 int b200k_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n, void* stream) {
   return launch_quantize_e4m3(x, y, scale_out, amax_scratch, n, static_cast<cudaStream_t>(stream));
 }

@@ -39,6 +39,10 @@ int launch_paged_gather(const void* cache, const int32_t* block_table, const int
                         int32_t num_seqs, int32_t kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
                         int32_t block_table_stride, int32_t max_seq_len, int64_t kv_page_stride, int64_t kv_head_stride,
                         int32_t elem_bytes, cudaStream_t stream);
+int launch_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int32_t* block_table,
+                     const int32_t* positions, int32_t num_seqs, int32_t new_tokens, int32_t kv_heads, int32_t head_dim,
+                     int32_t page_size, int32_t num_pages, int32_t block_table_stride, int64_t kv_page_stride,
+                     int64_t kv_head_stride, int32_t elem_bytes, int32_t* status, cudaStream_t stream);
 int launch_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n,
                          cudaStream_t stream);
 

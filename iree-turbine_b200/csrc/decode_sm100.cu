@@ -539,6 +539,73 @@ int launch_paged_gather(const void* cache, const int32_t* block_table, const int
 }
 
 // ------------------------------------------------------------------------------------------
+// KV-cache append: the step before decode.  Row t of new_rows[s] goes to token position
+// positions[s] + t of sequence s, through the block table, with kv_row_offset<true> (the address
+// function of the decode kernel).  One warp per (token, head) row; 16-byte stores; rows whose
+// block-table entry is outside the pool are dropped and reported through the status word.
+// ------------------------------------------------------------------------------------------
+__global__ void kv_append_kernel(const uint8_t* __restrict__ k_new, const uint8_t* __restrict__ v_new,
+                                 uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
+                                 const int32_t* __restrict__ block_table, const int32_t* __restrict__ positions,
+                                 int32_t new_tokens, int32_t kv_heads, int32_t head_dim, int32_t page_size,
+                                 int32_t num_pages, int32_t block_table_stride, int64_t kv_page_stride,
+                                 int64_t kv_head_stride, int32_t elem_bytes, int32_t* status) {
+  const int seq = blockIdx.z;
+  const int head = blockIdx.y;
+  const int row_bytes = head_dim * elem_bytes;
+  const int chunks_per_row = row_bytes / 16;
+  const int pos0 = __ldg(positions + seq);
+  const int warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t = blockIdx.x * warps + warp; t < new_tokens; t += gridDim.x * warps) {
+    const int token = pos0 + t;
+    int64_t off = -1;
+    if (pos0 >= 0 && token / page_size < block_table_stride)
+      off = kv_row_offset<true>(block_table, block_table_stride, page_size, num_pages, kv_page_stride, kv_head_stride, 0,
+                                head_dim, seq, head, token);
+    if (off < 0) {
+      if (lane == 0 && status) atomicOr(status, kStatusDecodeBadPage);
+      continue;
+    }
+    const int64_t src = ((static_cast<int64_t>(seq) * new_tokens + t) * kv_heads + head) * row_bytes;
+    const uint4* ks = reinterpret_cast<const uint4*>(k_new + src);
+    const uint4* vs = reinterpret_cast<const uint4*>(v_new + src);
+    uint4* kd = reinterpret_cast<uint4*>(k_cache + off * elem_bytes);
+    uint4* vd = reinterpret_cast<uint4*>(v_cache + off * elem_bytes);
+    for (int c = lane; c < chunks_per_row; c += 32) {
+      kd[c] = __ldg(ks + c);
+      vd[c] = __ldg(vs + c);
+    }
+  }
+}
+
+int launch_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int32_t* block_table,
+                     const int32_t* positions, int32_t num_seqs, int32_t new_tokens, int32_t kv_heads, int32_t head_dim,
+                     int32_t page_size, int32_t num_pages, int32_t block_table_stride, int64_t kv_page_stride,
+                     int64_t kv_head_stride, int32_t elem_bytes, int32_t* status, cudaStream_t stream) {
+  if (!k_new || !v_new || !k_cache || !v_cache || !block_table || !positions)
+    return set_error(B200K_ERR_NULL, "kv_append: NULL pointer");
+  if (num_seqs <= 0 || new_tokens <= 0 || kv_heads <= 0 || head_dim <= 0 || page_size <= 0 || num_pages <= 0 ||
+      block_table_stride <= 0 || num_seqs > 65535 || kv_heads > 65535)
+    return set_error(B200K_ERR_BAD_SHAPE, "kv_append: bad dimensions");
+  if (elem_bytes <= 0 || (head_dim * elem_bytes) % 16 != 0 || (kv_page_stride * elem_bytes) % 16 != 0 ||
+      (kv_head_stride * elem_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(v_cache) & 15) || (reinterpret_cast<uintptr_t>(k_new) & 15) ||
+      (reinterpret_cast<uintptr_t>(v_new) & 15))
+    return set_error(B200K_ERR_BAD_ALIGN, "kv_append: rows, strides and bases must be multiples of 16 bytes");
+  int rc = ensure_sm100();
+  if (rc) return rc;
+  const int warps = 4;
+  int gx = (new_tokens + warps - 1) / warps;
+  if (gx > 1024) gx = 1024;
+  kv_append_kernel<<<dim3(gx, kv_heads, num_seqs), warps * 32, 0, stream>>>(
+      reinterpret_cast<const uint8_t*>(k_new), reinterpret_cast<const uint8_t*>(v_new),
+      reinterpret_cast<uint8_t*>(k_cache), reinterpret_cast<uint8_t*>(v_cache), block_table, positions, new_tokens,
+      kv_heads, head_dim, page_size, num_pages, block_table_stride, kv_page_stride, kv_head_stride, elem_bytes, status);
+  return check_cuda(cudaGetLastError(), "kv_append_kernel launch");
+}
+
+// ------------------------------------------------------------------------------------------
 // Decode with scratch that lives inside the library.
 //
 // Some callers have no way to hand over scratch memory: a host runtime that gives a plug-in

@@ -31,6 +31,7 @@ __all__ = [
     "paged_decode_attention",
     "quantize_e4m3",
     "paged_gather",
+    "kv_append",
     "device_status",
     "reset_device_status",
 ]
@@ -405,3 +406,52 @@ class paged_gather(CustomOp):
             )
         )
         return out
+
+
+@CustomOp.register(library=LIBRARY)
+class kv_append(CustomOp):
+    """Writes new K/V rows into the paged cache through the block table (in place).
+
+    ``k_new`` / ``v_new``: [num_seqs, new_tokens, kv_heads, head_dim]; row ``t`` of sequence ``s``
+    goes to token position ``positions[s] + t``, i.e. to
+    ``cache[block_table[s, p // page], h, p % page, :]``.  The pages must already be in the table.
+    Same address function as the paged decode kernel.
+    """
+
+    signature = ("kv_append(Tensor k_new, Tensor v_new, Tensor(a!) k_cache, Tensor(b!) v_cache, "
+                 "Tensor block_table, Tensor positions) -> ()")
+
+    def select(self, sel: KernelSelection):
+        kn = sel.arg_tensor(0)
+        vn = sel.arg_tensor(1)
+        kc = sel.arg_tensor(2)
+        vc = sel.arg_tensor(3)
+        bt = sel.arg_tensor(4)
+        pos = sel.arg_tensor(5)
+        torch._check(kn.t.dim() == 4 and vn.t.shape == kn.t.shape,
+                     lambda: "kv_append: k_new and v_new must be [num_seqs, new_tokens, kv_heads, head_dim]")
+        torch._check(kc.t.dim() == 4 and vc.t.shape == kc.t.shape,
+                     lambda: "kv_append: caches must be [num_pages, kv_heads, page_size, head_dim]")
+        torch._check(kc.t.dtype == kn.t.dtype and vc.t.dtype == kn.t.dtype and vn.t.dtype == kn.t.dtype,
+                     lambda: "kv_append: dtypes of new rows and caches must match")
+        torch._check(kn.t.size(2) == kc.t.size(1) and kn.t.size(3) == kc.t.size(3),
+                     lambda: "kv_append: heads / head_dim of new rows and caches must match")
+        torch._check(bt.t.dtype == torch.int32 and bt.t.dim() == 2 and bt.t.size(0) == kn.t.size(0),
+                     lambda: "kv_append: block_table must be int32 [num_seqs, max_pages]")
+        torch._check(pos.t.dtype == torch.int32 and pos.t.dim() == 1 and pos.t.size(0) == kn.t.size(0),
+                     lambda: "kv_append: positions must be int32 [num_seqs]")
+
+    def eager_execute(self, k_new, v_new, k_cache, v_cache, block_table, positions):
+        if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise ValueError("kv_append: the caches are written in place and must be contiguous")
+        k_new, v_new = k_new.contiguous(), v_new.contiguous()
+        block_table, positions = block_table.contiguous(), positions.contiguous()
+        L.check(
+            L.lib().b200k_kv_append(
+                k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+                positions.data_ptr(), k_new.size(0), k_new.size(1), k_new.size(2), k_new.size(3), k_cache.size(2),
+                k_cache.size(0), block_table.stride(0), k_cache.stride(0), k_cache.stride(1), k_cache.element_size(),
+                _status_ptr(k_cache.device), _stream(k_cache),
+            )
+        )
+        return None

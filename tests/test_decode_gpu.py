@@ -116,3 +116,43 @@ def test_config_paged_decode_64_seqs():
     assert torch.equal(kg.view(torch.int16), ref_g.view(torch.int16))
     # run-to-run determinism
     assert torch.equal(kern(qd, kcd, vcd, btd, sld), o)
+
+
+# ---- KV-cache append (the step before decode) ----
+@pytest.mark.parametrize("new_tokens", [1, 5, 40])
+def test_kv_append_bit_exact_and_decodes(new_tokens):
+    lens = [17, 64, 300, 1, 129]
+    q, k_cache, v_cache, block_table, seq_lens = oracle.make_paged_decode_inputs(
+        lens=[n + new_tokens for n in lens], seed=21)
+    g = torch.Generator().manual_seed(22)
+    k_new = torch.randn(len(lens), new_tokens, 8, 128, generator=g).half()
+    v_new = torch.randn(len(lens), new_tokens, 8, 128, generator=g).half()
+    positions = torch.tensor(lens, dtype=torch.int32)
+    k_ref, v_ref = oracle.kv_append(k_new, v_new, k_cache, v_cache, block_table, positions)
+    kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+    torch.ops.b200k.kv_append(k_new.to(DEV), v_new.to(DEV), kc, vc, block_table.to(DEV), positions.to(DEV))
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    assert torch.equal(kc.cpu(), k_ref) and torch.equal(vc.cpu(), v_ref)
+    # the appended cache decodes like the oracle's
+    o = torch.ops.b200k.paged_decode_attention(q.to(DEV), kc, vc, block_table.to(DEV), seq_lens.to(DEV), SCALE)
+    torch.cuda.synchronize()
+    oracle.assert_close_half(o.cpu(), oracle.paged_decode_attention(q, k_ref, v_ref, block_table, seq_lens, SCALE))
+
+
+def test_kv_append_outside_pool_is_dropped_and_reported():
+    q, k_cache, v_cache, block_table, seq_lens = oracle.make_paged_decode_inputs(lens=[40, 40], seed=23)
+    bad = block_table.clone()
+    bad[1, 2] = -1  # tokens 32..47 of sequence 1 have no page
+    k_new = torch.ones(2, 4, 8, 128).half()
+    positions = torch.tensor([30, 30], dtype=torch.int32)
+    kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+    tb.reset_device_status()
+    torch.ops.b200k.kv_append(k_new.to(DEV), k_new.to(DEV), kc, vc, bad.to(DEV), positions.to(DEV))
+    torch.cuda.synchronize()
+    assert tb.device_status() == 4
+    tb.reset_device_status()
+    # sequence 0 and tokens 30, 31 of sequence 1 were written; nothing else changed
+    k_ref, _ = oracle.kv_append(k_new[:1], k_new[:1], k_cache, v_cache, block_table[:1], positions[:1])
+    k_ref, _ = oracle.kv_append(k_new[1:, :2], k_new[1:, :2], k_ref, v_cache, block_table[1:], positions[1:])
+    assert torch.equal(kc.cpu(), k_ref)

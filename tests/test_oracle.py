@@ -120,3 +120,18 @@ def test_decode_equals_attention_with_one_query():
         n = int(lens[s])
         ref = oracle.attention(q[s:s + 1], k[s:s + 1, :, :n], v[s:s + 1, :, :n], 0.1, False)
         torch.testing.assert_close(o[s], ref[0, :, 0], rtol=1e-6, atol=1e-6)
+
+
+def test_kv_append_then_gather_round_trip():
+    """Appended rows come back through the gather at their token positions; nothing else moves."""
+    q, kc, vc, bt, sl = oracle.make_paged_decode_inputs(lens=[20, 33], seed=1)
+    kn = torch.randn(2, 3, 8, 128).half()
+    vn = torch.randn(2, 3, 8, 128).half()
+    pos = torch.tensor([17, 30], dtype=torch.int32)
+    k2, v2 = oracle.kv_append(kn, vn, kc, vc, bt, pos)
+    gk, gv = oracle.paged_gather(k2, bt, sl, 48), oracle.paged_gather(v2, bt, sl, 48)
+    assert torch.equal(gk[0, :, 17:20], kn[0].transpose(0, 1)) and torch.equal(gk[1, :, 30:33], kn[1].transpose(0, 1))
+    assert torch.equal(gv[0, :, 17:20], vn[0].transpose(0, 1)) and torch.equal(gv[1, :, 30:33], vn[1].transpose(0, 1))
+    g0 = oracle.paged_gather(kc, bt, sl, 48)
+    assert torch.equal(gk[0, :, :17], g0[0, :, :17]) and torch.equal(gk[1, :, :30], g0[1, :, :30])
+    assert int((k2 != kc).any(dim=-1).sum()) <= 2 * 3 * 8
