@@ -1,0 +1,274 @@
+"""``torch.compile`` backend that routes matmul and SDPA nodes to the b200k kernels.
+
+The reference gets GEMM / SDPA onto its own kernels the same way: an ``aot_autograd`` backend whose
+forward compiler rewrites ATen nodes through a replacement schema and then hands the graph to a
+nested backend (iree/turbine/dynamo/backends/boo.py:55-126; schema of offloaded ops
+iree/turbine/kernel/boo/fusion/schema.py:106-135; the SDPA variants are matched as in
+iree/turbine/kernel/boo/fusion/replacement.py:239-290: a multi-output fused-attention node is only
+replaced when nothing but its first output is used).
+
+What is rewritten (forward graph only; the backward graph, if any, goes to the nested backend as is):
+
+* ``aten.mm(a, t(w))``           -> ``b200k.gemm_nt(a, w, out_dtype=a.dtype)``
+* ``aten.addmm(bias, a, t(w))``  -> ``b200k.gemm_nt(a, w) + bias``   (alpha = beta = 1)
+  for 2-D f16 / bf16 CUDA operands of one dtype, where ``t`` is ``aten.t``, ``aten.transpose(0, 1)``
+  or ``aten.permute([1, 0])`` -- the "activation [M, K] x weight stored [N, K]" form ``nn.Linear``
+  lowers to.
+* ``aten._scaled_dot_product_{flash,efficient,cudnn}_attention`` and
+  ``aten.scaled_dot_product_attention`` -> ``b200k.attention(q, k, v, scale, is_causal)``
+  for [B, H, S, 128] f16 / bf16 CUDA tensors, no mask / bias, dropout 0, q_heads a multiple of
+  kv_heads, and -- when causal -- equal query and key lengths (torch aligns the causal mask to the
+  top-left corner, the kernel to the bottom-right; they coincide only then).
+
+Everything else is left alone.  ``backend()`` returns the compiler; it is also registered under the
+name ``"b200k"``: ``torch.compile(model, backend="b200k")``.
+"""
+
+from __future__ import annotations
+
+import math
+import operator
+from typing import Callable, Dict, Optional
+
+import torch
+from torch import fx
+
+from . import ops as _ops  # noqa: F401  (registers torch.ops.b200k.*)
+
+__all__ = [
+    "ReplacementSchema",
+    "DEFAULT_REPLACEMENTS",
+    "apply_replacements",
+    "backend",
+    "replace_mm",
+    "replace_addmm",
+    "replace_fused_sdpa",
+    "replace_sdpa",
+]
+
+aten = torch.ops.aten
+ReplacementSchema = Dict[object, Callable[[fx.Node], bool]]
+_HALF = (torch.float16, torch.bfloat16)
+
+
+def _val(node) -> Optional[torch.Tensor]:
+    """The fake tensor recorded for a node, if any."""
+    if not isinstance(node, fx.Node):
+        return None
+    v = node.meta.get("val")
+    return v if isinstance(v, torch.Tensor) else None
+
+
+def _is_cuda_half(t: Optional[torch.Tensor], dim: int) -> bool:
+    return t is not None and t.device.type == "cuda" and t.dtype in _HALF and t.dim() == dim
+
+
+def _transposed_source(node) -> Optional[fx.Node]:
+    """If ``node`` is a 2-D transpose of another node, returns that node."""
+    if not isinstance(node, fx.Node) or node.op != "call_function":
+        return None
+    if node.target is aten.t.default:
+        return node.args[0]
+    if node.target is aten.transpose.int and sorted(d % 2 for d in node.args[1:3]) == [0, 1]:
+        return node.args[0]
+    if node.target is aten.permute.default and list(node.args[1]) == [1, 0]:
+        return node.args[0]
+    return None
+
+
+def _match_nt(a, b):
+    """(a, w) if ``mm(a, b)`` is ``a[M, K] @ w[N, K]^T`` on supported operands, else None."""
+    w = _transposed_source(b)
+    if w is None:
+        return None
+    va, vw = _val(a), _val(w)
+    if not (_is_cuda_half(va, 2) and _is_cuda_half(vw, 2)) or va.dtype != vw.dtype or va.size(1) != vw.size(1):
+        return None
+    return a, w
+
+
+def replace_mm(node: fx.Node) -> bool:
+    m = _match_nt(*node.args[:2])
+    if m is None:
+        return False
+    a, w = m
+    with node.graph.inserting_before(node):
+        new = node.graph.call_function(torch.ops.b200k.gemm_nt.default, args=(a, w, _val(a).dtype))
+    new.meta = dict(node.meta)
+    node.replace_all_uses_with(new)
+    node.graph.erase_node(node)
+    return True
+
+
+def replace_addmm(node: fx.Node) -> bool:
+    bias, a, b = node.args[:3]
+    if node.kwargs.get("alpha", 1) != 1 or node.kwargs.get("beta", 1) != 1:
+        return False
+    m = _match_nt(a, b)
+    vb = _val(bias)
+    if m is None or vb is None or vb.dtype != _val(a).dtype:
+        return False
+    a, w = m
+    g = node.graph
+    with g.inserting_before(node):
+        mm = g.call_function(torch.ops.b200k.gemm_nt.default, args=(a, w, _val(a).dtype))
+        mm.meta = dict(node.meta)
+        new = g.call_function(aten.add.Tensor, args=(mm, bias))
+        new.meta = dict(node.meta)
+    node.replace_all_uses_with(new)
+    g.erase_node(node)
+    return True
+
+
+def _sdpa_supported(q, k, v, mask, dropout_p, is_causal) -> bool:
+    vq, vk, vv = _val(q), _val(k), _val(v)
+    if mask is not None or dropout_p not in (0, 0.0):
+        return False
+    if not (_is_cuda_half(vq, 4) and _is_cuda_half(vk, 4) and _is_cuda_half(vv, 4)):
+        return False
+    if not (vq.dtype == vk.dtype == vv.dtype) or vk.shape != vv.shape:
+        return False
+    if vq.size(-1) != 128 or vk.size(-1) != 128 or vq.size(0) != vk.size(0):
+        return False
+    if vk.size(1) == 0 or vq.size(1) % vk.size(1) != 0:
+        return False
+    if is_causal and vq.size(2) != vk.size(2):
+        return False
+    return True
+
+
+def _scale_of(node: fx.Node, q) -> float:
+    s = node.kwargs.get("scale")
+    return float(s) if s is not None else 1.0 / math.sqrt(_val(q).size(-1))
+
+
+def replace_sdpa(node: fx.Node) -> bool:
+    """aten.scaled_dot_product_attention(q, k, v, attn_mask=None, dropout_p=0, is_causal=False, *, scale)"""
+    q, k, v = node.args[:3]
+    mask = _arg(node, 3, "attn_mask", None)
+    dropout_p = _arg(node, 4, "dropout_p", 0.0)
+    is_causal = bool(_arg(node, 5, "is_causal", False))
+    if node.kwargs.get("enable_gqa", False) is False and _val(q) is not None and _val(k) is not None \
+            and _val(q).size(1) != _val(k).size(1):
+        return False  # torch itself would reject this call
+    if not _sdpa_supported(q, k, v, mask, dropout_p, is_causal):
+        return False
+    with node.graph.inserting_before(node):
+        new = node.graph.call_function(torch.ops.b200k.attention.default,
+                                       args=(q, k, v, _scale_of(node, q), is_causal))
+    new.meta = dict(node.meta)
+    node.replace_all_uses_with(new)
+    node.graph.erase_node(node)
+    return True
+
+
+def _arg(node: fx.Node, index: int, name: str, default):
+    if len(node.args) > index:
+        return node.args[index]
+    return node.kwargs.get(name, default)
+
+
+def _fused_args(node: fx.Node):
+    """(q, k, v, mask_or_bias, dropout_p, is_causal) of a fused-attention node."""
+    q, k, v = node.args[:3]
+    if node.target is aten._scaled_dot_product_flash_attention.default:
+        # (q, k, v, dropout_p=0, is_causal=False, return_debug_mask=False, *, scale)
+        return q, k, v, None, _arg(node, 3, "dropout_p", 0.0), bool(_arg(node, 4, "is_causal", False))
+    # efficient / cudnn: (q, k, v, attn_bias, compute_log_sumexp, dropout_p=0, is_causal=False, ..., *, scale)
+    return (q, k, v, _arg(node, 3, "attn_bias", None), _arg(node, 5, "dropout_p", 0.0),
+            bool(_arg(node, 6, "is_causal", False)))
+
+
+def replace_fused_sdpa(node: fx.Node) -> bool:
+    """A fused-attention node returns (output, logsumexp, ...): replaced only when nothing but
+    output is used (so never in a graph whose backward needs the log-sum-exp)."""
+    q, k, v, mask, dropout_p, is_causal = _fused_args(node)
+    if not _sdpa_supported(q, k, v, mask, dropout_p, is_causal):
+        return False
+    getitems = [u for u in node.users if u.op == "call_function" and u.target is operator.getitem]
+    if len(getitems) != len(node.users):
+        return False
+    out_user = None
+    for u in getitems:
+        if u.args[1] == 0:
+            out_user = u
+        elif len(u.users) > 0:
+            return False
+    if out_user is None:
+        return False
+    g = node.graph
+    with g.inserting_before(node):
+        new = g.call_function(torch.ops.b200k.attention.default, args=(q, k, v, _scale_of(node, q), is_causal))
+    new.meta = dict(out_user.meta)
+    out_user.replace_all_uses_with(new)
+    for u in getitems:
+        g.erase_node(u)
+    g.erase_node(node)
+    return True
+
+
+def _default_replacements() -> ReplacementSchema:
+    schema: ReplacementSchema = {
+        aten.mm.default: replace_mm,
+        aten.addmm.default: replace_addmm,
+        aten.scaled_dot_product_attention.default: replace_sdpa,
+    }
+    for name in ("_scaled_dot_product_flash_attention", "_scaled_dot_product_efficient_attention",
+                 "_scaled_dot_product_cudnn_attention"):
+        pkt = getattr(aten, name, None)
+        if pkt is not None:
+            schema[pkt.default] = replace_fused_sdpa
+    return schema
+
+
+DEFAULT_REPLACEMENTS: ReplacementSchema = _default_replacements()
+
+
+def apply_replacements(gm: fx.GraphModule, replacements: ReplacementSchema = DEFAULT_REPLACEMENTS) -> int:
+    """Rewrites ``gm`` in place; returns how many nodes were replaced."""
+    count = 0
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function":
+            continue
+        fn = replacements.get(node.target)
+        if fn is not None and fn(node):
+            count += 1
+    if count:
+        gm.graph.eliminate_dead_code()
+        gm.graph.lint()
+        gm.recompile()
+    return count
+
+
+def backend(*, nested_backend="eager", replacements: ReplacementSchema = DEFAULT_REPLACEMENTS):
+    """A ``torch.compile`` backend: ATen forward graph -> replacements -> ``nested_backend``."""
+    from functorch.compile import make_boxed_func
+    from torch._dynamo.backends.common import aot_autograd
+
+    nested = torch._dynamo.lookup_backend(nested_backend) if isinstance(nested_backend, str) else nested_backend
+
+    def fw_compiler(gm: fx.GraphModule, example_inputs):
+        backend.last_replaced = apply_replacements(gm, replacements)
+        return make_boxed_func(nested(gm, example_inputs))
+
+    def bw_compiler(gm: fx.GraphModule, example_inputs):
+        return make_boxed_func(nested(gm, example_inputs))
+
+    return aot_autograd(fw_compiler=fw_compiler, bw_compiler=bw_compiler)
+
+
+backend.last_replaced = 0  # set by the most recent forward compilation (for tests and diagnostics)
+
+
+def _register():
+    try:
+        from torch._dynamo import register_backend
+    except ImportError:  # pragma: no cover
+        return
+    try:
+        register_backend(name="b200k", compiler_fn=backend())
+    except Exception:  # already registered (module re-import)
+        pass
+
+
+_register()

@@ -227,6 +227,16 @@ def _fill_attention_args(q: Tensor, k: Tensor, v: Tensor, o: Tensor, scale: floa
     return args
 
 
+def _attention_out_like(q: Tensor, device) -> Tensor:
+    """The output takes the memory layout of q when q's rows are contiguous (as
+    aten.scaled_dot_product_attention does: a [B, H, S, D] view of [B, S, H, D] memory stays one),
+    so graphs traced against the ATen op keep their views valid; otherwise it is contiguous.  The
+    kernel writes any layout with contiguous rows."""
+    if q.dim() == 4 and q.stride(-1) == 1:
+        return torch.empty_like(q, device=device)
+    return torch.empty(q.shape, dtype=q.dtype, device=device)
+
+
 @CustomOp.register(library=LIBRARY)
 class attention(CustomOp):
     """O = softmax(scale * Q K^T [causal]) V.  q [B,Hq,Sq,128], k/v [B,Hkv,Skv,128] -> [B,Hq,Sq,128]."""
@@ -247,11 +257,11 @@ class attention(CustomOp):
         torch._check(q.t.size(0) == k.t.size(0), lambda: "attention: batch mismatch")
         torch._check(q.t.size(1) % k.t.size(1) == 0, lambda: "attention: query heads must be a multiple of kv heads")
         q.specialize_dims(3)
-        sel.return_new_tensor(list(q.t.shape), q.t.dtype)
+        sel.return_tensor(_attention_out_like(q.t, "meta"))
 
     def eager_execute(self, q, k, v, scale, is_causal):
+        o = _attention_out_like(q, q.device)
         q, k, v = _bhsd(q), _bhsd(k), _bhsd(v)
-        o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         args = _fill_attention_args(q, k, v, o, scale, is_causal)
         args.status = _status_ptr(q.device)
         L.check(L.lib().b200k_attention_fwd(C.byref(args), _stream(q)))
