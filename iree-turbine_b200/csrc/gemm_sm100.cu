@@ -515,20 +515,33 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   if (rc) return rc;
 
   const int sms = num_sms();
-  // Tile choice: estimated time = waves * tile area / efficiency, where a 128-row tile is limited
-  // by operand delivery (96 bytes per tensor-core cycle) and a 256 x 256 tile is not.
+  // Tile choice: estimated time = waves * tile area / efficiency.  The efficiencies are the
+  // measured throughputs of the three shapes on a many-wave problem (f16 8192^3: 1039 / 1375 /
+  // 1555 TFLOP/s), relative to one another: a 128-row tile is limited by operand delivery (a
+  // 128 x 256 tile needs 96 bytes per tensor-core cycle, a 128 x 128 tile 128), a 256 x 256 tile
+  // is not.  (An earlier model with 0.67 / 0.67 / 0.72 chose 128 x 128 tiles for 4096^3, which
+  // run at 983 TFLOP/s where 256 x 256 tiles reach 1398.)
   auto cost = [&](int bm, int bn) {
     const int64_t tiles = ((a.m + bm - 1) / bm) * ((a.n + bn - 1) / bn);
     const int64_t waves = (tiles + sms - 1) / sms;
-    // measured: 256 x 256 tiles are 4..9% faster per flop than 128 x 256 on large problems
-    const double eff = bm == 256 ? 0.72 : 0.67;
+    const double eff = bm == 256 ? 0.93 : (bn == 256 ? 0.83 : 0.62);
     return static_cast<double>(waves) * bm * bn / eff;
   };
   int bm = a.tile_m, bn = a.tile_n;
   if (bm == 256 && bn == 0) bn = 256;
   if (bn == 0) {
-    bn = (a.n > 128 && cost(128, 256) <= cost(128, 128)) ? 256 : 128;
-    if (bm == 0) bm = (bn == 256 && a.m > 128 && cost(256, 256) < cost(128, 256)) ? 256 : 128;
+    double best = cost(128, 128);
+    bn = 128;
+    int best_bm = 128;
+    if (a.n > 128 && cost(128, 256) <= best) {
+      best = cost(128, 256);
+      bn = 256;
+    }
+    if (bm != 128 && a.n > 128 && a.m > 128 && cost(256, 256) < best) {
+      bn = 256;
+      best_bm = 256;
+    }
+    if (bm == 0) bm = best_bm;
   }
   if (bm == 0) bm = 128;
   if (bm == 256 && bn != 256)
