@@ -161,6 +161,39 @@ typedef struct b200k_attention_args {
 
 int b200k_attention_fwd(const b200k_attention_args* args, void* stream);
 
+/*
+ * Attention forward over a PAGED K/V cache (prefill, or a chunk of it, after its K/V rows have been
+ * appended with b200k_kv_append): same computation as b200k_attention_fwd, with
+ *   K/V of sequence b, token t  =  cache[block_table[b * block_table_stride + t / page_size], h, t % page_size, :]
+ * and seq_lens[b] <= max_seq_kv keys for sequence b.  The seq_q queries of a sequence are its last
+ * seq_q tokens: with causal != 0 query i sees keys j <= i + seq_lens[b] - seq_q.  A sequence with
+ * no visible key yields zeros.  k_cache / v_cache: [num_pages, kv_heads, page_size, head_dim] with
+ * contiguous rows, page_size in {16, 32, 64, 128}.  Whole pages are fetched, so the rows of a
+ * sequence's last page past seq_lens[b] must hold finite values (they are masked, but 0 * NaN is
+ * NaN).  A block-table entry outside the pool reads as zeros and sets status bit 4.
+ * The reference has no call site for this; its layout is the decode path's.
+ */
+typedef struct b200k_paged_attention_args {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  void* o;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  int32_t batch, q_heads, kv_heads, seq_q, max_seq_kv, head_dim;
+  int32_t page_size, num_pages, block_table_stride, reserved;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  int64_t kv_page_stride, kv_head_stride;
+  int32_t dtype; /* F16 | BF16 */
+  int32_t causal;
+  float scale;
+  int32_t reserved2;
+  int32_t* status; /* device status word, may be NULL */
+} b200k_paged_attention_args;
+
+int b200k_paged_attention_fwd(const b200k_paged_attention_args* args, void* stream);
+
 /* ---- decode / paged-decode attention (split-KV + reduction) ------------------------ */
 /*
  * Replaces the Wave decode and paged-decode attention template launches: one query token per

@@ -151,6 +151,21 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class PagedAttentionArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("o", C.c_void_p),
+        ("block_table", C.c_void_p), ("seq_lens", C.c_void_p),
+        ("batch", C.c_int32), ("q_heads", C.c_int32), ("kv_heads", C.c_int32), ("seq_q", C.c_int32),
+        ("max_seq_kv", C.c_int32), ("head_dim", C.c_int32),
+        ("page_size", C.c_int32), ("num_pages", C.c_int32), ("block_table_stride", C.c_int32), ("reserved", C.c_int32),
+        ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("q_stride_s", C.c_int64),
+        ("o_stride_b", C.c_int64), ("o_stride_h", C.c_int64), ("o_stride_s", C.c_int64),
+        ("kv_page_stride", C.c_int64), ("kv_head_stride", C.c_int64),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float), ("reserved2", C.c_int32),
+        ("status", C.c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); this table is also what the symbol-export test walks.
 EXPORTED_SYMBOLS = {
     "b200k_abi_version": (C.c_int, []),
@@ -168,6 +183,7 @@ EXPORTED_SYMBOLS = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
          C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p],
     ),
+    "b200k_paged_attention_fwd": (C.c_int, [C.POINTER(PagedAttentionArgs), C.c_void_p]),
     "b200k_kv_append": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,

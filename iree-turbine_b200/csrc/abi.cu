@@ -236,6 +236,11 @@ int b200k_paged_gather(const void* cache, const int32_t* block_table, const int3
                              static_cast<cudaStream_t>(stream));
 }
 
+int b200k_paged_attention_fwd(const b200k_paged_attention_args* args, void* stream) {
+  if (!args) return set_error(B200K_ERR_NULL, "paged_attention_fwd: args is NULL");
+  return launch_paged_attention_fwd(*args, static_cast<cudaStream_t>(stream));
+}
+
 int b200k_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int32_t* block_table,
                     const int32_t* positions, int32_t num_seqs, int32_t new_tokens, int32_t kv_heads, int32_t head_dim,
                     int32_t page_size, int32_t num_pages, int32_t block_table_stride, int64_t kv_page_stride,

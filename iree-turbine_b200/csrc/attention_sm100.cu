@@ -101,6 +101,13 @@ struct AttnParams {
   int32_t num_items;    // batch * q_heads * num_q_tiles
   float scale_log2;
   int32_t* status;
+  // Paged K/V (block_table != nullptr): the tensor maps of K and V describe the page pool
+  // [num_pages, kv_heads, page_size, 128]; token t of sequence b lives in page
+  // block_table[b * block_table_stride + t / page_size], row t % page_size; sequence b has
+  // seq_lens[b] <= seq_kv keys and its queries are its last seq_q tokens.
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  int32_t block_table_stride, page_size, num_pages;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -174,6 +181,7 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi)
 
 struct Item {
   int qtile, head, batch, n;  // n = number of 128-row KV tiles this item visits
+  int kv_len, causal_offset;  // keys of this item's sequence; key j is visible to query i iff j <= i + causal_offset
 };
 
 __device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
@@ -182,11 +190,14 @@ __device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
   it.qtile = p.num_q_tiles - 1 - (idx - bh * p.num_q_tiles);  // heaviest tiles of a head first
   it.batch = bh / p.q_heads;
   it.head = bh - it.batch * p.q_heads;
-  const int kv_tiles_total = (p.seq_kv + kTileRows - 1) / kTileRows;
+  it.kv_len = p.seq_kv;
+  if (p.seq_lens) it.kv_len = max(0, min(__ldg(p.seq_lens + it.batch), p.seq_kv));
+  it.causal_offset = it.kv_len - p.seq_q;
+  const int kv_tiles_total = (it.kv_len + kTileRows - 1) / kTileRows;
   if (!p.causal) {
     it.n = kv_tiles_total;
   } else {
-    const int last_col = it.qtile * kTileRows + kTileRows - 1 + p.causal_offset;
+    const int last_col = it.qtile * kTileRows + kTileRows - 1 + it.causal_offset;
     it.n = last_col < 0 ? 0 : min(last_col / kTileRows + 1, kv_tiles_total);
   }
   return it;
@@ -280,14 +291,34 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       if (lane == 0) {
         uint32_t qc = 0, kc = 0, vc = 0;  // Q loads, K tiles, V tiles issued so far
         bool ok = true;
+        // One 128-row K or V tile.  Dense: one box per 64-column block.  Paged: one box per page and
+        // block; a page past the sequence's length is replaced by the sequence's first page (those
+        // rows are masked; the data only has to be finite), an entry outside the pool is reported
+        // and reads as zeros (the tensor map clips it).
+        auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, const Item& it, int j) {
+          if (p.block_table == nullptr) {
+#pragma unroll
+            for (int db = 0; db < 2; ++db)
+              tma_load_4d(dst + db * kHalfTileBytes, tm, bar, db * 64, j * kTileRows, it.head / group, it.batch);
+            return;
+          }
+          const int32_t* row = p.block_table + static_cast<int64_t>(it.batch) * p.block_table_stride;
+          const int pages_per_tile = kTileRows / p.page_size;
+          const int valid_pages = (it.kv_len + p.page_size - 1) / p.page_size;
+          for (int pp = 0; pp < pages_per_tile; ++pp) {
+            const int lp = j * pages_per_tile + pp;
+            const int page = __ldg(row + (lp < valid_pages ? lp : 0));
+            if ((page < 0 || page >= p.num_pages) && p.status) atomicOr(p.status, kStatusDecodeBadPage);
+#pragma unroll
+            for (int db = 0; db < 2; ++db)
+              tma_load_4d(dst + db * kHalfTileBytes + pp * p.page_size * 128, tm, bar, db * 64, 0, it.head / group, page);
+          }
+        };
         auto load_k = [&](const Item& it, int j) {
           const int ks = kc % kKStages;
           if (!mbar_wait(k_empty + ks, ((kc / kKStages) & 1) ^ 1, abort_word)) return false;
           mbar_arrive_expect_tx(k_full + ks, kTileBytes);
-#pragma unroll
-          for (int db = 0; db < 2; ++db)
-            tma_load_4d(smem + kKOffset + ks * kTileBytes + db * kHalfTileBytes, &tmap_k, k_full + ks, db * 64,
-                        j * kTileRows, it.head / group, it.batch);
+          load_tile(smem + kKOffset + ks * kTileBytes, &tmap_k, k_full + ks, it, j);
           ++kc;
           return true;
         };
@@ -313,11 +344,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           }
           return p.num_items;
         };
-        Item it = {0, 0, 0, 0};
+        Item it = {};
         int idx = next_item(static_cast<int>(blockIdx.x) - static_cast<int>(gridDim.x), it);
         if (idx < p.num_items) ok = load_head(it);
         while (idx < p.num_items && ok) {
-          Item nx = {0, 0, 0, 0};
+          Item nx = {};
           const int nidx = next_item(idx, nx);
           const bool have_next = nidx < p.num_items;
           // Order within an item: V_j, then K_(j+3); a K stage is released (by the score MMA that
@@ -330,13 +361,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             const int vs = vc % kVStages;
             if (!mbar_wait(v_empty + vs, ((vc / kVStages) & 1) ^ 1, abort_word)) { ok = false; break; }
             mbar_arrive_expect_tx(v_full + vs, kTileBytes);
-#pragma unroll
-            for (int db = 0; db < 2; ++db)
-              tma_load_4d(smem + kVOffset + vs * kTileBytes + db * kHalfTileBytes, &tmap_v, v_full + vs, db * 64,
-                          j * kTileRows, it.head / group, it.batch);
+            load_tile(smem + kVOffset + vs * kTileBytes, &tmap_v, v_full + vs, it, j);
             ++vc;
             if (j + kKStages < it.n) ok = load_k(it, j + kKStages);
-            if (kPrefetchNext && j == 0 && have_next) {
+            if (kPrefetchNext && p.block_table == nullptr && j == 0 && have_next) {
               // The first tiles of the next item are wanted soon after this item's last score MMA
               // frees Q, less than a trip to HBM later: ask for them in L2 now.
               const int nkv = nx.head / group;
@@ -569,11 +597,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
         const int col0 = j * kTileRows;
         const bool need_mask =
-            (p.causal && col0 + kTileRows - 1 > tile_r0 + p.causal_offset) || (col0 + kTileRows > p.seq_kv);
+            (p.causal && col0 + kTileRows - 1 > tile_r0 + it.causal_offset) || (col0 + kTileRows > it.kv_len);
         int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
         if (need_mask) {
-          int vis = p.seq_kv;
-          if (p.causal) vis = min(vis, q_row + p.causal_offset + 1);
+          int vis = it.kv_len;
+          if (p.causal) vis = min(vis, q_row + it.causal_offset + 1);
           limit = vis - col0;
         }
         tmem_wait_ld();
@@ -798,6 +826,89 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   p.num_items = static_cast<int32_t>(items);
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
+  p.block_table = nullptr;
+  p.seq_lens = nullptr;
+  p.block_table_stride = p.page_size = p.num_pages = 0;
+  if (a.dtype == B200K_F16) return launch_typed<__half>(tq, tk, tv, to, p, stream);
+  return launch_typed<__nv_bfloat16>(tq, tk, tv, to, p, stream);
+}
+
+int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t stream) {
+  if (!a.q || !a.k_cache || !a.v_cache || !a.o || !a.block_table || !a.seq_lens)
+    return set_error(B200K_ERR_NULL, "paged_attention_fwd: q, k_cache, v_cache, o, block_table, seq_lens must be non-NULL");
+  if (a.batch <= 0 || a.q_heads <= 0 || a.kv_heads <= 0 || a.seq_q <= 0 || a.max_seq_kv <= 0)
+    return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: all dimensions must be positive");
+  if (a.head_dim != kD) return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: head_dim must be 128");
+  if (a.q_heads % a.kv_heads != 0)
+    return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: q_heads must be a multiple of kv_heads");
+  if (a.dtype != B200K_F16 && a.dtype != B200K_BF16)
+    return set_error(B200K_ERR_BAD_DTYPE, "paged_attention_fwd: dtype must be F16 or BF16");
+  if (a.page_size < 16 || a.page_size > kTileRows || kTileRows % a.page_size != 0 || a.page_size % 8 != 0)
+    return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: page_size must be 16, 32, 64 or 128");
+  if (a.num_pages <= 0 || a.block_table_stride <= 0 ||
+      static_cast<int64_t>(a.block_table_stride) * a.page_size < a.max_seq_kv)
+    return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: the block table does not cover max_seq_kv");
+  const int64_t strides[] = {a.q_stride_b, a.q_stride_h, a.q_stride_s, a.o_stride_b, a.o_stride_h, a.o_stride_s,
+                             a.kv_page_stride, a.kv_head_stride};
+  for (int64_t s : strides)
+    if (s <= 0 || s % 8 != 0)
+      return set_error(B200K_ERR_BAD_ALIGN, "paged_attention_fwd: every stride must be a positive multiple of 8 elements");
+  if ((reinterpret_cast<uintptr_t>(a.q) & 15) || (reinterpret_cast<uintptr_t>(a.k_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(a.v_cache) & 15) || (reinterpret_cast<uintptr_t>(a.o) & 15))
+    return set_error(B200K_ERR_BAD_ALIGN, "paged_attention_fwd: q, caches and o must be 16-byte aligned");
+  if (!(a.scale > 0.f)) return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: scale must be positive");
+  int rc = ensure_sm100();
+  if (rc) return rc;
+
+  CUtensorMap tq, tk, tv, to;
+  const uint32_t box[4] = {64, kTileRows, 1, 1};
+  const uint32_t page_box[4] = {64, static_cast<uint32_t>(a.page_size), 1, 1};
+  {
+    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
+                        static_cast<uint64_t>(a.batch)};
+    uint64_t st[3] = {static_cast<uint64_t>(a.q_stride_s) * 2, static_cast<uint64_t>(a.q_stride_h) * 2,
+                      static_cast<uint64_t>(a.q_stride_b) * 2};
+    rc = encode_tmap(&tq, a.dtype, 4, const_cast<void*>(a.q), dims, st, box);
+    if (rc) return rc;
+    uint64_t so[3] = {static_cast<uint64_t>(a.o_stride_s) * 2, static_cast<uint64_t>(a.o_stride_h) * 2,
+                      static_cast<uint64_t>(a.o_stride_b) * 2};
+    rc = encode_tmap(&to, a.dtype, 4, a.o, dims, so, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.page_size), static_cast<uint64_t>(a.kv_heads),
+                        static_cast<uint64_t>(a.num_pages)};
+    uint64_t st[3] = {static_cast<uint64_t>(kD) * 2, static_cast<uint64_t>(a.kv_head_stride) * 2,
+                      static_cast<uint64_t>(a.kv_page_stride) * 2};
+    rc = encode_tmap(&tk, a.dtype, 4, const_cast<void*>(a.k_cache), dims, st, page_box);
+    if (rc) return rc;
+    rc = encode_tmap(&tv, a.dtype, 4, const_cast<void*>(a.v_cache), dims, st, page_box);
+    if (rc) return rc;
+  }
+
+  AttnParams p;
+  p.o = a.o;
+  p.o_stride_b = a.o_stride_b;
+  p.o_stride_h = a.o_stride_h;
+  p.o_stride_s = a.o_stride_s;
+  p.batch = a.batch;
+  p.q_heads = a.q_heads;
+  p.kv_heads = a.kv_heads;
+  p.seq_q = a.seq_q;
+  p.seq_kv = a.max_seq_kv;
+  p.causal = a.causal ? 1 : 0;
+  p.causal_offset = a.max_seq_kv - a.seq_q;
+  p.num_q_tiles = (a.seq_q + kTileRows - 1) / kTileRows;
+  const int64_t items = static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles;
+  if (items > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: too many query tiles");
+  p.num_items = static_cast<int32_t>(items);
+  p.scale_log2 = a.scale * kLog2e;
+  p.status = a.status;
+  p.block_table = a.block_table;
+  p.seq_lens = a.seq_lens;
+  p.block_table_stride = a.block_table_stride;
+  p.page_size = a.page_size;
+  p.num_pages = a.num_pages;
   if (a.dtype == B200K_F16) return launch_typed<__half>(tq, tk, tv, to, p, stream);
   return launch_typed<__nv_bfloat16>(tq, tk, tv, to, p, stream);
 }

@@ -32,6 +32,7 @@ __all__ = [
     "quantize_e4m3",
     "paged_gather",
     "kv_append",
+    "paged_attention",
     "device_status",
     "reset_device_status",
 ]
@@ -465,3 +466,60 @@ class kv_append(CustomOp):
             )
         )
         return None
+
+
+@CustomOp.register(library=LIBRARY)
+class paged_attention(CustomOp):
+    """Attention forward (prefill) over a paged K/V cache.
+
+    q [B, Hq, Sq, 128]; caches [num_pages, Hkv, page_size, 128]; block_table int32 [B, max_pages];
+    seq_lens int32 [B] = number of keys of each sequence.  The Sq queries of a sequence are its last
+    Sq tokens (append their K/V first, see ``kv_append``); with ``is_causal`` query i sees keys
+    j <= i + seq_lens[b] - Sq.  Rows of a sequence's last page past its length must be finite.
+    """
+
+    signature = ("paged_attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_table, Tensor seq_lens, "
+                 "float scale, bool is_causal) -> Tensor")
+
+    def select(self, sel: KernelSelection):
+        q = sel.arg_tensor(0)
+        kc = sel.arg_tensor(1)
+        vc = sel.arg_tensor(2)
+        bt = sel.arg_tensor(3)
+        lens = sel.arg_tensor(4)
+        sel.attr_float(5)
+        sel.attr_bool(6)
+        torch._check(q.t.dim() == 4 and q.t.size(3) == 128, lambda: "paged_attention: q must be [B, Hq, Sq, 128]")
+        torch._check(q.t.dtype in _HALF_TYPES, lambda: f"paged_attention: dtype must be float16 or bfloat16, got {q.t.dtype}")
+        torch._check(kc.t.dim() == 4 and kc.t.shape == vc.t.shape and kc.t.size(3) == 128,
+                     lambda: "paged_attention: caches must be [num_pages, Hkv, page_size, 128] and equal in shape")
+        torch._check(kc.t.dtype == q.t.dtype and vc.t.dtype == q.t.dtype, lambda: "paged_attention: dtypes must match")
+        torch._check(kc.t.size(2) in (16, 32, 64, 128), lambda: "paged_attention: page_size must be 16, 32, 64 or 128")
+        torch._check(q.t.size(1) % kc.t.size(1) == 0, lambda: "paged_attention: query heads must be a multiple of kv heads")
+        torch._check(bt.t.dtype == torch.int32 and bt.t.dim() == 2 and bt.t.size(0) == q.t.size(0),
+                     lambda: "paged_attention: block_table must be int32 [B, max_pages]")
+        torch._check(lens.t.dtype == torch.int32 and lens.t.dim() == 1 and lens.t.size(0) == q.t.size(0),
+                     lambda: "paged_attention: seq_lens must be int32 [B]")
+        sel.return_tensor(_attention_out_like(q.t, "meta"))
+
+    def eager_execute(self, q, k_cache, v_cache, block_table, seq_lens, scale, is_causal):
+        o = _attention_out_like(q, q.device)
+        q = _bhsd(q)
+        k_cache, v_cache = k_cache.contiguous(), v_cache.contiguous()
+        block_table, seq_lens = block_table.contiguous(), seq_lens.contiguous()
+        a = L.PagedAttentionArgs()
+        a.q, a.k_cache, a.v_cache, a.o = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), o.data_ptr()
+        a.block_table, a.seq_lens = block_table.data_ptr(), seq_lens.data_ptr()
+        a.batch, a.q_heads, a.kv_heads, a.seq_q = q.size(0), q.size(1), k_cache.size(1), q.size(2)
+        a.page_size, a.num_pages, a.block_table_stride = k_cache.size(2), k_cache.size(0), block_table.stride(0)
+        a.max_seq_kv = block_table.size(1) * k_cache.size(2)
+        a.head_dim = 128
+        a.q_stride_b, a.q_stride_h, a.q_stride_s = q.stride(0), q.stride(1), q.stride(2)
+        a.o_stride_b, a.o_stride_h, a.o_stride_s = o.stride(0), o.stride(1), o.stride(2)
+        a.kv_page_stride, a.kv_head_stride = k_cache.stride(0), k_cache.stride(1)
+        a.dtype = L.DTYPE_CODES[q.dtype]
+        a.causal = 1 if is_causal else 0
+        a.scale = float(scale)
+        a.status = _status_ptr(q.device)
+        L.check(L.lib().b200k_paged_attention_fwd(C.byref(a), _stream(q)))
+        return o

@@ -40,6 +40,11 @@ def test_struct_layouts_match_the_header():
                                                    "scale", "status"]),
         "b200k_decode_args": (L.DecodeArgs, ["q", "workspace_bytes", "num_seqs", "max_seq_len", "kv_batch_stride",
                                              "kv_page_stride", "dtype", "scale"]),
+        "b200k_paged_attention_args": (L.PagedAttentionArgs, ["q", "seq_lens", "batch", "head_dim", "page_size",
+                                                              "block_table_stride", "q_stride_b", "o_stride_s",
+                                                              "kv_page_stride", "kv_head_stride", "dtype", "scale",
+                                                              "status"]),
+        "b200k_gemm_allgather_args": (L.GemmAllGatherArgs, ["gemm", "peer_c", "num_peers", "peer_ldc", "col_offset"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for cname, (_, fs) in fields.items():

@@ -111,3 +111,58 @@ def test_config_causal_bf16_b4_h32_s4096():
     # head sharding (what multi-GPU runs do) is bitwise the same as the full call
     o_shard = torch.ops.b200k.attention(q[:, 8:16], k[:, 8:16], v[:, 8:16], SCALE, True)
     assert torch.equal(o_shard, o[:, 8:16])
+
+
+# ---- prefill over a paged K/V cache ----
+def _paged_case(lens, sq, hq=8, hkv=2, page=16, dtype=torch.float16, seed=31):
+    q0, k_cache, v_cache, block_table, seq_lens = oracle.make_paged_decode_inputs(
+        q_heads=hq, kv_heads=hkv, page_size=page, lens=lens, dtype=dtype, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    q = (torch.randn(len(lens), hq, sq, 128, generator=g) * 0.5).to(dtype)
+    return q, k_cache, v_cache, block_table, seq_lens
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("page", [16, 64, 128])
+def test_paged_prefill_matches_oracle_and_dense_call(causal, page):
+    lens = [300, 128, 517, 129, 40]
+    sq = 40 if causal else 130
+    q, kc, vc, bt, sl = _paged_case(lens, sq, page=page)
+    o = torch.ops.b200k.paged_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), SCALE, causal)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(o.cpu(), oracle.paged_attention(q, kc, vc, bt, sl, SCALE, causal))
+    # the same kernel on the gathered, contiguous K/V of each sequence gives the same bits
+    for i, n in enumerate(lens):
+        kg = oracle.paged_gather(kc, bt[i:i + 1], sl[i:i + 1], n)
+        vg = oracle.paged_gather(vc, bt[i:i + 1], sl[i:i + 1], n)
+        od = torch.ops.b200k.attention(q[i:i + 1].to(DEV), kg.to(DEV), vg.to(DEV), SCALE, causal)
+        assert torch.equal(od.cpu(), o[i:i + 1].cpu()), f"sequence {i}"
+
+
+def test_paged_prefill_after_append_chunked():
+    """Chunked prefill: append a chunk's K/V, attend causally over everything so far."""
+    lens0, chunk = [64, 200, 0], 96
+    total = [n + chunk for n in lens0]
+    q, kc, vc, bt, sl = _paged_case(total, chunk, dtype=torch.bfloat16, seed=41)
+    g = torch.Generator().manual_seed(5)
+    k_new = torch.randn(3, chunk, 2, 128, generator=g).bfloat16()
+    v_new = torch.randn(3, chunk, 2, 128, generator=g).bfloat16()
+    pos = torch.tensor(lens0, dtype=torch.int32)
+    k_ref, v_ref = oracle.kv_append(k_new, v_new, kc, vc, bt, pos)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    torch.ops.b200k.kv_append(k_new.to(DEV), v_new.to(DEV), kd, vd, bt.to(DEV), pos.to(DEV))
+    o = torch.ops.b200k.paged_attention(q.to(DEV), kd, vd, bt.to(DEV), sl.to(DEV), SCALE, True)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(o.cpu(), oracle.paged_attention(q, k_ref, v_ref, bt, sl, SCALE, True))
+
+
+def test_paged_prefill_zero_length_and_queries_before_first_key():
+    q, kc, vc, bt, sl = _paged_case([0, 20], 64)
+    o = torch.ops.b200k.paged_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), sl.to(DEV), SCALE, True)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    assert bool((o[0] == 0).all())                 # no keys at all
+    assert bool((o[1, :, :44] == 0).all())         # queries 0..43 precede the first key (64 queries, 20 keys)
+    oracle.assert_close_half(o.cpu(), oracle.paged_attention(q, kc, vc, bt, sl, SCALE, True))
