@@ -184,15 +184,17 @@ struct Item {
   int kv_len, causal_offset;  // keys of this item's sequence; key j is visible to query i iff j <= i + causal_offset
 };
 
+template <bool PAGED>
 __device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
   Item it;
   const int bh = idx / p.num_q_tiles;
   it.qtile = p.num_q_tiles - 1 - (idx - bh * p.num_q_tiles);  // heaviest tiles of a head first
   it.batch = bh / p.q_heads;
   it.head = bh - it.batch * p.q_heads;
+  // (dense: the two are launch constants and the fields fold away)
   it.kv_len = p.seq_kv;
-  if (p.seq_lens) it.kv_len = max(0, min(__ldg(p.seq_lens + it.batch), p.seq_kv));
-  it.causal_offset = it.kv_len - p.seq_q;
+  if (PAGED) it.kv_len = max(0, min(__ldg(p.seq_lens + it.batch), p.seq_kv));
+  it.causal_offset = PAGED ? it.kv_len - p.seq_q : p.causal_offset;
   const int kv_tiles_total = (it.kv_len + kTileRows - 1) / kTileRows;
   if (!p.causal) {
     it.n = kv_tiles_total;
@@ -203,7 +205,7 @@ __device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
   return it;
 }
 
-template <typename T>
+template <typename T, bool PAGED>
 __global__ void __launch_bounds__(kAttnThreads, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         // rows are masked; the data only has to be finite), an entry outside the pool is reported
         // and reads as zeros (the tensor map clips it).
         auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, const Item& it, int j) {
-          if (p.block_table == nullptr) {
+          if (!PAGED) {
 #pragma unroll
             for (int db = 0; db < 2; ++db)
               tma_load_4d(dst + db * kHalfTileBytes, tm, bar, db * 64, j * kTileRows, it.head / group, it.batch);
@@ -339,7 +341,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         };
         auto next_item = [&](int idx, Item& nx) {  // next item of this CTA that has work; num_items if none
           for (idx += gridDim.x; idx < p.num_items; idx += gridDim.x) {
-            nx = decode_item(idx, p);
+            nx = decode_item<PAGED>(idx, p);
             if (nx.n > 0) return idx;
           }
           return p.num_items;
@@ -364,7 +366,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             load_tile(smem + kVOffset + vs * kTileBytes, &tmap_v, v_full + vs, it, j);
             ++vc;
             if (j + kKStages < it.n) ok = load_k(it, j + kKStages);
-            if (kPrefetchNext && p.block_table == nullptr && j == 0 && have_next) {
+            if (kPrefetchNext && !PAGED && j == 0 && have_next) {
               // The first tiles of the next item are wanted soon after this item's last score MMA
               // frees Q, less than a trip to HBM later: ask for them in L2 now.
               const int nkv = nx.head / group;
@@ -405,7 +407,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         uint32_t qpar = 0;
         bool ok = true;
         for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-          const Item it = decode_item(idx, p);
+          const Item it = decode_item<PAGED>(idx, p);
           if (it.n == 0) continue;
           if (!mbar_wait(q_full, qpar, abort_word)) break;
           qpar ^= 1;
@@ -446,7 +448,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         uint32_t vstage = 0, vpar = 0;
         bool ok = true;
         for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-          const Item it = decode_item(idx, p);
+          const Item it = decode_item<PAGED>(idx, p);
           if (it.n == 0) continue;
           for (int j = 0; j < it.n; ++j, ++g) {
             const uint32_t buf = g & 1;
@@ -487,7 +489,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     uint32_t ic = 0, g0 = 0;  // items so far, KV steps before the current item
     bool ok = true;
     for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-      const Item it = decode_item(idx, p);
+      const Item it = decode_item<PAGED>(idx, p);
       if (it.n == 0) {
         // no visible key: zeros (rare; plain stores)
         const int q_row = it.qtile * kTileRows + row_in_tile;
@@ -578,10 +580,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     uint32_t g = 0, ic = 0;  // KV steps (of both warpgroups) and items so far
     bool ok = true;
     for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-      const Item it = decode_item(idx, p);
+      const Item it = decode_item<PAGED>(idx, p);
       if (it.n == 0) continue;
       const int tile_r0 = it.qtile * kTileRows;
       const int q_row = tile_r0 + row_in_tile;
+      const int kv_len = PAGED ? it.kv_len : p.seq_kv;
+      const int causal_offset = PAGED ? it.causal_offset : p.causal_offset;
       float m_ref = -INFINITY;  // running max this warpgroup's row sum is relative to
       float2 l2 = make_float2(0.f, 0.f);
       for (int j = 0; j < it.n; ++j, ++g) {
@@ -597,11 +601,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
         const int col0 = j * kTileRows;
         const bool need_mask =
-            (p.causal && col0 + kTileRows - 1 > tile_r0 + it.causal_offset) || (col0 + kTileRows > it.kv_len);
+            (p.causal && col0 + kTileRows - 1 > tile_r0 + causal_offset) || (col0 + kTileRows > kv_len);
         int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
         if (need_mask) {
-          int vis = it.kv_len;
-          if (p.causal) vis = min(vis, q_row + it.causal_offset + 1);
+          int vis = kv_len;
+          if (p.causal) vis = min(vis, q_row + causal_offset + 1);
           limit = vis - col0;
         }
         tmem_wait_ld();
@@ -736,10 +740,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   }
 }
 
-template <typename T>
+template <typename T, bool PAGED>
 int launch_typed(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                  const AttnParams& p, cudaStream_t stream) {
-  auto kfn = attn_fwd_kernel<T>;
+  auto kfn = attn_fwd_kernel<T, PAGED>;
   static bool configured = false;
   if (!configured) {
     int rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem),
@@ -829,8 +833,8 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   p.block_table = nullptr;
   p.seq_lens = nullptr;
   p.block_table_stride = p.page_size = p.num_pages = 0;
-  if (a.dtype == B200K_F16) return launch_typed<__half>(tq, tk, tv, to, p, stream);
-  return launch_typed<__nv_bfloat16>(tq, tk, tv, to, p, stream);
+  if (a.dtype == B200K_F16) return launch_typed<__half, false>(tq, tk, tv, to, p, stream);
+  return launch_typed<__nv_bfloat16, false>(tq, tk, tv, to, p, stream);
 }
 
 int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t stream) {
@@ -909,8 +913,8 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
   p.block_table_stride = a.block_table_stride;
   p.page_size = a.page_size;
   p.num_pages = a.num_pages;
-  if (a.dtype == B200K_F16) return launch_typed<__half>(tq, tk, tv, to, p, stream);
-  return launch_typed<__nv_bfloat16>(tq, tk, tv, to, p, stream);
+  if (a.dtype == B200K_F16) return launch_typed<__half, true>(tq, tk, tv, to, p, stream);
+  return launch_typed<__nv_bfloat16, true>(tq, tk, tv, to, p, stream);
 }
 
 }  // namespace b200k
