@@ -84,6 +84,8 @@ const char* b200k_status_string(int status);
  * multiple of 16 bytes.  C: base aligned to 16 bytes, ldc * sizeof(out) a multiple of 16.
  * K tails, M tails and N tails are handled (out-of-range operand elements read as zero).
  */
+enum { B200K_ACT_NONE = 0, B200K_ACT_RELU = 1, B200K_ACT_GELU = 2 /* erf form */, B200K_ACT_SILU = 3 };
+
 typedef struct b200k_gemm_args {
   const void* a;
   const void* b;
@@ -97,6 +99,12 @@ typedef struct b200k_gemm_args {
   int32_t* status;      /* device status word, may be NULL */
   int32_t tile_n;       /* 0 = choose; else 128 or 256 */
   int32_t tile_m;       /* 0 = choose; else 128 or 256 (256 needs tile_n 256 or 0) */
+  /* Optional fused epilogue (the bias / activation tail of a linear layer, cf. the reference's
+   * ops/templates/test_linear_trailing_optional_biased.mlir):  C = act(A B^T * scales + bias[n]).
+   * bias: device vector of n elements, NULL = none; activation: B200K_ACT_*. */
+  const void* bias;
+  int32_t bias_dtype; /* F32 | F16 | BF16 */
+  int32_t activation;
 } b200k_gemm_args;
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);

@@ -78,6 +78,9 @@ class GemmArgs(C.Structure):
         ("status", C.c_void_p),
         ("tile_n", C.c_int32),
         ("tile_m", C.c_int32),
+        ("bias", C.c_void_p),
+        ("bias_dtype", C.c_int32),
+        ("activation", C.c_int32),
     ]
 
 
@@ -165,6 +168,8 @@ class PagedAttentionArgs(C.Structure):
         ("status", C.c_void_p),
     ]
 
+
+ACTIVATION_CODES = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
 
 # name -> (restype, argtypes); this table is also what the symbol-export test walks.
 EXPORTED_SYMBOLS = {

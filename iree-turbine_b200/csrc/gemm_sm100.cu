@@ -36,6 +36,11 @@ struct GemmParams {
   int64_t ldc;
   int32_t m, n;
   int32_t tiles_m, tiles_n, num_kb;  // tiles_m counts MT * 128-row tiles
+  // Optional fused epilogue: y = act(acc * scale + bias[col]); bias == nullptr and act == 0 leave
+  // the plain path untouched.
+  const void* bias;
+  int32_t bias_dtype;  // B200K_F32 | B200K_F16 | B200K_BF16
+  int32_t act;         // B200K_ACT_*
   int32_t vec_store_ok;
   int32_t tma_store_ok;  // C is 16-byte aligned with a 16-byte-multiple row pitch: epilogue uses TMA stores
   // Fused all-gather of a column shard: when num_peers > 0 every output tile is written with plain
@@ -84,6 +89,39 @@ __device__ __forceinline__ __half to_out<__half>(float v) {
 template <>
 __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case B200K_ACT_RELU:
+      return fmaxf(x, 0.f);
+    case B200K_ACT_GELU:  // exact (erf) form, the default of aten::gelu
+      return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case B200K_ACT_SILU:
+      return x / (1.f + __expf(-x));
+    default:
+      return x;
+  }
+}
+
+__device__ __forceinline__ float load_bias(const void* bias, int dtype, int col) {
+  if (dtype == B200K_F32) return __ldg(reinterpret_cast<const float*>(bias) + col);
+  if (dtype == B200K_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(bias) + col));
+  return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(bias) + col));
+}
+
+// Fused epilogue on N accumulator values of one row (columns col0 .. col0 + N - 1), in place:
+// r = act(r * scale + bias).  Every lane of a warp reads the same bias element (one broadcast
+// load per column).  Afterwards the caller's own scaling must be 1.
+template <int N>
+__device__ __forceinline__ void fused_epilogue(uint32_t (&r)[N], float scale, const void* bias, int bias_dtype, int act,
+                                               int col0, int n) {
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    float x = __uint_as_float(r[j]) * scale;
+    if (bias != nullptr && col0 + j < n) x += load_bias(bias, bias_dtype, col0 + j);
+    r[j] = __float_as_uint(apply_act(x, act));
+  }
 }
 
 // Stores 32 consecutive columns of one output row.
@@ -258,6 +296,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const float sb = p.scale_b ? *p.scale_b : 1.0f;
       scale = sa * sb;
     }
+    const bool fused = p.bias != nullptr || p.act != 0;  // uniform over the grid
     OutT* cbase = reinterpret_cast<OutT*>(p.c);
     uint8_t* staging = smem + S::kStagingOffset + (warp - 2) * (2 * 4096);
     uint32_t stg_count = 0;
@@ -290,16 +329,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               uint32_t r[32];
               tmem_ld_32x32b_x32(taddr + c * 32, r);
               tmem_wait_ld();
+              float sc = scale;
+              if (fused) {
+                fused_epilogue<32>(r, scale, p.bias, p.bias_dtype, p.act, tn * BN + c * 32, p.n);
+                sc = 1.f;
+              }
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                v[i] = make_uint4(__float_as_uint(__uint_as_float(r[4 * i]) * scale),
-                                  __float_as_uint(__uint_as_float(r[4 * i + 1]) * scale),
-                                  __float_as_uint(__uint_as_float(r[4 * i + 2]) * scale),
-                                  __float_as_uint(__uint_as_float(r[4 * i + 3]) * scale));
+                v[i] = make_uint4(__float_as_uint(__uint_as_float(r[4 * i]) * sc),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 1]) * sc),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 2]) * sc),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 3]) * sc));
             } else {
               uint32_t r[64];
               tmem_ld_32x32b_x64(taddr + c * 64, r);
               tmem_wait_ld();
+              float sc = scale;
+              if (fused) {
+                fused_epilogue<64>(r, scale, p.bias, p.bias_dtype, p.act, tn * BN + c * 64, p.n);
+                sc = 1.f;
+              }
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 union {
@@ -307,7 +356,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   OutT e[8];
                 } pk;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * scale);
+                for (int j = 0; j < 8; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * sc);
                 v[i] = pk.u;
               }
             }
@@ -347,16 +396,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               uint32_t r[32];
               tmem_ld_32x32b_x32(taddr + c * 32, r);
               tmem_wait_ld();
+              float sc = scale;
+              if (fused) {
+                fused_epilogue<32>(r, scale, p.bias, p.bias_dtype, p.act, tn * BN + c * 32, p.n);
+                sc = 1.f;
+              }
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                v[i] = make_uint4(__float_as_uint(__uint_as_float(r[4 * i]) * scale),
-                                  __float_as_uint(__uint_as_float(r[4 * i + 1]) * scale),
-                                  __float_as_uint(__uint_as_float(r[4 * i + 2]) * scale),
-                                  __float_as_uint(__uint_as_float(r[4 * i + 3]) * scale));
+                v[i] = make_uint4(__float_as_uint(__uint_as_float(r[4 * i]) * sc),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 1]) * sc),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 2]) * sc),
+                                  __float_as_uint(__uint_as_float(r[4 * i + 3]) * sc));
             } else {
               uint32_t r[64];
               tmem_ld_32x32b_x64(taddr + c * 64, r);
               tmem_wait_ld();
+              float sc = scale;
+              if (fused) {
+                fused_epilogue<64>(r, scale, p.bias, p.bias_dtype, p.act, tn * BN + c * 64, p.n);
+                sc = 1.f;
+              }
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 union {
@@ -364,7 +423,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   OutT e[8];
                 } pk;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * scale);
+                for (int j = 0; j < 8; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * sc);
                 v[i] = pk.u;
               }
             }
@@ -386,8 +445,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tmem_ld_32x32b_x32(taddr + c * 32, r);
             tmem_wait_ld();
             const int col = tn * BN + c * 32;
+            float sc = scale;
+            if (fused) {
+              fused_epilogue<32>(r, scale, p.bias, p.bias_dtype, p.act, col, p.n);
+              sc = 1.f;
+            }
             if (row < p.m && col < p.n) {
-              store_chunk<OutT>(cbase + static_cast<int64_t>(row) * p.ldc + col, r, scale, p.n - col,
+              store_chunk<OutT>(cbase + static_cast<int64_t>(row) * p.ldc + col, r, sc, p.n - col,
                                 p.vec_store_ok != 0);
             }
           }
@@ -507,6 +571,10 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
     return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt: A/B base and row stride must be multiples of 16 bytes");
   if (peers.num == 0 && reinterpret_cast<uintptr_t>(a.c) % out_es != 0)
     return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt: C is not aligned to its element size");
+  if (a.activation < B200K_ACT_NONE || a.activation > B200K_ACT_SILU)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: unknown activation %d", a.activation);
+  if (a.bias && a.bias_dtype != B200K_F32 && a.bias_dtype != B200K_F16 && a.bias_dtype != B200K_BF16)
+    return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: bias must be F32, F16 or BF16");
   if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_n must be 0, 128 or 256");
   if (a.tile_m != 0 && a.tile_m != 128 && a.tile_m != 256)
@@ -571,6 +639,9 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   p.scale_a = a.scale_a;
   p.scale_b = a.scale_b;
   p.status = a.status;
+  p.bias = a.bias;
+  p.bias_dtype = a.bias_dtype;
+  p.act = a.activation;
   p.ldc = a.ldc;
   p.m = static_cast<int32_t>(a.m);
   p.n = static_cast<int32_t>(a.n);

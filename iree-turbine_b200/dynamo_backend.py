@@ -10,7 +10,8 @@ replaced when nothing but its first output is used).
 What is rewritten (forward graph only; the backward graph, if any, goes to the nested backend as is):
 
 * ``aten.mm(a, t(w))``           -> ``b200k.gemm_nt(a, w, out_dtype=a.dtype)``
-* ``aten.addmm(bias, a, t(w))``  -> ``b200k.gemm_nt(a, w) + bias``   (alpha = beta = 1)
+* ``aten.addmm(bias, a, t(w))``  -> ``b200k.linear_act(a, w, bias)`` (bias [N] added in the GEMM's
+  epilogue; alpha = beta = 1)
   for 2-D f16 / bf16 CUDA operands of one dtype, where ``t`` is ``aten.t``, ``aten.transpose(0, 1)``
   or ``aten.permute([1, 0])`` -- the "activation [M, K] x weight stored [N, K]" form ``nn.Linear``
   lowers to.
@@ -109,11 +110,11 @@ def replace_addmm(node: fx.Node) -> bool:
     if m is None or vb is None or vb.dtype != _val(a).dtype:
         return False
     a, w = m
+    if vb.dim() != 1 or vb.size(0) != _val(w).size(0):
+        return False  # only the per-output-feature bias of a linear layer fuses into the epilogue
     g = node.graph
     with g.inserting_before(node):
-        mm = g.call_function(torch.ops.b200k.gemm_nt.default, args=(a, w, _val(a).dtype))
-        mm.meta = dict(node.meta)
-        new = g.call_function(aten.add.Tensor, args=(mm, bias))
+        new = g.call_function(torch.ops.b200k.linear_act.default, args=(a, w, bias, "none", _val(a).dtype))
         new.meta = dict(node.meta)
     node.replace_all_uses_with(new)
     g.erase_node(node)

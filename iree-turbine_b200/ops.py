@@ -15,6 +15,7 @@ same rules.
 from __future__ import annotations
 
 import ctypes as C
+from typing import Optional
 
 import torch
 from torch import Tensor
@@ -26,6 +27,7 @@ __all__ = [
     "LIBRARY",
     "gemm_nt",
     "gemm_fp8_nt",
+    "linear_act",
     "attention",
     "decode_attention",
     "paged_decode_attention",
@@ -94,7 +96,8 @@ def _gemm_out_dtype(in_dtype: torch.dtype, out_dtype) -> torch.dtype:
     return od
 
 
-def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: int = 0, tile_m: int = 0) -> None:
+def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: int = 0, tile_m: int = 0,
+                 bias: Optional[Tensor] = None, activation: str = "none") -> None:
     a = _row_major_2d(a)
     b = _row_major_2d(b)
     args = L.GemmArgs()
@@ -108,6 +111,13 @@ def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: in
     args.status = _status_ptr(a.device)
     args.tile_n = tile_n
     args.tile_m = tile_m
+    if activation not in L.ACTIVATION_CODES:
+        raise ValueError(f"unknown activation {activation!r}; expected one of {sorted(L.ACTIVATION_CODES)}")
+    args.activation = L.ACTIVATION_CODES[activation]
+    if bias is not None:
+        bias = bias.contiguous()
+        args.bias = bias.data_ptr()
+        args.bias_dtype = L.DTYPE_CODES[bias.dtype]
     L.check(L.lib().b200k_gemm_nt(C.byref(args), _stream(a)))
 
 
@@ -136,6 +146,39 @@ class gemm_nt(CustomOp):
     def eager_execute(self, a, b, out_dtype=None):
         out = torch.empty((a.size(0), b.size(0)), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
         _launch_gemm(a, b, out, None, None)
+        return out
+
+
+@CustomOp.register(library=LIBRARY)
+class linear_act(CustomOp):
+    """act(A[M,K] @ W[N,K]^T + bias[N]) in one kernel: the GEMM with bias and activation applied in
+    its epilogue (the shape of a linear layer with trailing optional bias).  ``activation`` is
+    "none", "relu", "gelu" (erf form) or "silu"; output dtype as for ``gemm_nt``."""
+
+    signature = ("linear_act(Tensor a, Tensor w, Tensor? bias=None, str activation=\"none\", "
+                 "ScalarType? out_dtype=None) -> Tensor")
+
+    def select(self, sel: KernelSelection):
+        a = sel.arg_tensor(0)
+        w = sel.arg_tensor(1)
+        bias = sel.arg_optional_tensor(2)
+        act = sel.attr_str(3)
+        od = sel.attr_optional(4)
+        torch._check(a.t.dim() == 2 and w.t.dim() == 2, lambda: "linear_act: a and w must be 2-D")
+        torch._check(a.t.dtype in _HALF_TYPES and a.t.dtype == w.t.dtype,
+                     lambda: f"linear_act: a and w must both be float16 or bfloat16, got {a.t.dtype}, {w.t.dtype}")
+        torch._check(a.t.size(1) == w.t.size(1) and a.t.size(1) % 8 == 0,
+                     lambda: "linear_act: K must match and be a multiple of 8")
+        torch._check(act.v in L.ACTIVATION_CODES, lambda: f"linear_act: unknown activation {act.v!r}")
+        bt = bias.t if bias is not None else None
+        if bt is not None:
+            torch._check(bt.dim() == 1 and bt.size(0) == w.t.size(0), lambda: "linear_act: bias must be [N]")
+            torch._check(bt.dtype in (torch.float32,) + _HALF_TYPES, lambda: "linear_act: bias must be float32 / float16 / bfloat16")
+        sel.return_new_tensor([a.t.size(0), w.t.size(0)], _gemm_out_dtype(a.t.dtype, od.v))
+
+    def eager_execute(self, a, w, bias=None, activation="none", out_dtype=None):
+        out = torch.empty((a.size(0), w.size(0)), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
+        _launch_gemm(a, w, out, None, None, bias=bias, activation=activation)
         return out
 
 

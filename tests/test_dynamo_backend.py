@@ -59,7 +59,7 @@ def test_mm_nt_is_routed(transpose):
     assert node.args[2] == torch.float16 and [a.name for a in node.args[:2]] == ["a", "w"]
 
 
-def test_addmm_becomes_gemm_plus_add():
+def test_addmm_becomes_fused_linear():
     def build(g):
         bias = _ph(g, "bias", _fake((512,)))
         a = _ph(g, "a", _fake((64, 256)))
@@ -73,7 +73,9 @@ def test_addmm_becomes_gemm_plus_add():
     gm = _graph(build)
     assert db.apply_replacements(gm) == 1
     t = _targets(gm)
-    assert torch.ops.b200k.gemm_nt.default in t and aten.add.Tensor in t and aten.addmm.default not in t
+    assert torch.ops.b200k.linear_act.default in t and aten.addmm.default not in t
+    node = next(n for n in gm.graph.nodes if n.target is torch.ops.b200k.linear_act.default)
+    assert [a.name for a in node.args[:3]] == ["a", "w", "bias"] and node.args[3] == "none"
 
 
 @pytest.mark.parametrize("case", ["nn_form", "float32", "cpu", "three_d"])

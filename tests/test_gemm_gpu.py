@@ -166,3 +166,45 @@ def test_quantize_matches_oracle_bitwise():
     yo, so = oracle.quantize_e4m3(x)
     assert torch.equal(s.cpu(), so)
     assert torch.equal(y.cpu().view(torch.uint8), yo.view(torch.uint8))
+
+
+# ---- fused bias / activation epilogue ----
+@pytest.mark.parametrize("activation", ["none", "relu", "gelu", "silu"])
+@pytest.mark.parametrize("bias_dtype", [None, torch.float32, torch.float16])
+def test_linear_act_matches_oracle(activation, bias_dtype):
+    m, n, k = 300, 520, 256   # ragged M and N: edge tiles take the bias guard
+    a, w = oracle.make_gemm_inputs(m, n, k, torch.float16, seed=7)
+    a, w = a * 0.25, w * 0.25
+    bias = None if bias_dtype is None else torch.randn(n, generator=torch.Generator().manual_seed(8)).to(bias_dtype)
+    ref = oracle.linear_act(a, w, bias, activation)
+    for out_dtype in (None, torch.float16):
+        y = torch.ops.b200k.linear_act(a.to(DEV), w.to(DEV), None if bias is None else bias.to(DEV), activation, out_dtype)
+        torch.cuda.synchronize()
+        assert tb.device_status() == 0
+        assert y.dtype == (torch.float32 if out_dtype is None else torch.float16)
+        oracle.assert_close_half(y, ref)
+
+
+@pytest.mark.parametrize("tile", [(128, 128), (128, 256), (256, 256)])
+def test_linear_act_all_tile_shapes_and_unaligned_output(tile):
+    m, n, k = 512, 512, 128
+    a, w = oracle.make_gemm_inputs(m, n, k, torch.bfloat16, seed=9)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(10))
+    ref = oracle.linear_act(a, w, bias, "silu")
+    # TMA-store epilogue
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops._launch_gemm(a.to(DEV), w.to(DEV), out, None, None, tile_n=tile[1], tile_m=tile[0], bias=bias.to(DEV), activation="silu")
+    # predicated-store epilogue: a view whose rows are not 16-byte aligned
+    wide = torch.empty(m, n + 3, dtype=torch.bfloat16, device=DEV)
+    out2 = wide[:, 1:n + 1]
+    ops._launch_gemm(a.to(DEV), w.to(DEV), out2, None, None, tile_n=tile[1], tile_m=tile[0], bias=bias.to(DEV), activation="silu")
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(out, ref)
+    assert torch.equal(out, out2)
+
+
+def test_linear_act_rejects_unknown_activation():
+    a, w = oracle.make_gemm_inputs(128, 128, 64, torch.float16, seed=1)
+    with pytest.raises((RuntimeError, ValueError)):
+        torch.ops.b200k.linear_act(a.to(DEV), w.to(DEV), None, "tanh", None)
