@@ -105,6 +105,13 @@ typedef struct b200k_gemm_args {
   const void* bias;
   int32_t bias_dtype; /* F32 | F16 | BF16 */
   int32_t activation;
+  /* Operand storage, F16 / BF16 only (0, 0 = the NT form above).  a_km != 0: A is stored [K, M]
+   * (lda = its row stride >= M), i.e. the product uses A^T of the stored matrix; b_kn != 0: B is
+   * stored [K, N] (ldb >= N).  With these the four BLAS forms and the two backward products of
+   * the NT form (dA = dC B: b_kn; dB = dC^T A: a_km and b_kn; kernel/boo/op_exports/gemm.py:233-270)
+   * run without repacking an operand. */
+  int32_t a_km;
+  int32_t b_kn;
 } b200k_gemm_args;
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);

@@ -81,6 +81,8 @@ class GemmArgs(C.Structure):
         ("bias", C.c_void_p),
         ("bias_dtype", C.c_int32),
         ("activation", C.c_int32),
+        ("a_km", C.c_int32),
+        ("b_kn", C.c_int32),
     ]
 
 

@@ -41,6 +41,9 @@ struct GemmParams {
   const void* bias;
   int32_t bias_dtype;  // B200K_F32 | B200K_F16 | B200K_BF16
   int32_t act;         // B200K_ACT_*
+  // Operand storage (generic kernel only): a_mn = A is stored [K, M] (M contiguous), b_mn = B is
+  // stored [K, N] (N contiguous); 0 = the contraction dimension K is the contiguous one.
+  int32_t a_mn, b_mn;
   int32_t vec_store_ok;
   int32_t tma_store_ok;  // C is 16-byte aligned with a 16-byte-multiple row pitch: epilogue uses TMA stores
   // Fused all-gather of a column shard: when num_peers > 0 every output tile is written with plain
@@ -155,7 +158,13 @@ __device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t (&r)[32], 
   }
 }
 
-template <int BN, int MT, int KIND, typename OutT>
+// GEN = false: both operands K-major (A [M, K], B [N, K]); the issue path is all compile-time
+// offsets.  GEN = true (16-bit types only): either operand may be MN-major, chosen at run time
+// (p.a_mn, p.b_mn).  An MN-major operand is stored [K, R] with R contiguous; a pipeline stage holds
+// it as R / 64 blocks of 64 K-rows x 128 bytes (128-byte swizzle), one TMA box each; the UMMA
+// descriptor has LBO = 8 KB between the 64-element blocks, SBO = 1 KB between 8-row groups, and a
+// k-step of 16 rows advances 2 KB.  A stage has the same size either way.
+template <int BN, int MT, int KIND, typename OutT, bool GEN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
@@ -224,8 +233,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           uint8_t* sa = smem + stage * S::kStageBytes;
           mbar_arrive_expect_tx(full + stage, S::kStageBytes);
-          tma_load_2d(sa, &tmap_a, full + stage, kb * kElemsPerStage, tm * kTileM);
-          tma_load_2d(sa + S::kABytes, &tmap_b, full + stage, kb * kElemsPerStage, tn * BN);
+          if (GEN && p.a_mn) {
+#pragma unroll
+            for (int b = 0; b < kTileM / 64; ++b)
+              tma_load_2d(sa + b * 8192, &tmap_a, full + stage, tm * kTileM + b * 64, kb * kElemsPerStage);
+          } else {
+            tma_load_2d(sa, &tmap_a, full + stage, kb * kElemsPerStage, tm * kTileM);
+          }
+          if (GEN && p.b_mn) {
+#pragma unroll
+            for (int b = 0; b < BN / 64; ++b)
+              tma_load_2d(sa + S::kABytes + b * 8192, &tmap_b, full + stage, tn * BN + b * 64, kb * kElemsPerStage);
+          } else {
+            tma_load_2d(sa + S::kABytes, &tmap_b, full + stage, kb * kElemsPerStage, tn * BN);
+          }
           if (++stage == S::kStages) {
             stage = 0;
             phase ^= 1;
@@ -246,6 +267,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t hi = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
       const uint32_t lo0 = static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem)));
       auto desc = [](uint32_t lo, uint32_t h) { return (static_cast<uint64_t>(h) << 32) | lo; };
+      // generic kernel: per-operand high word, k-step and instruction descriptor chosen once
+      // (the block stride of an MN-major operand, LBO, sits in the LOW word next to the address)
+      const uint32_t hi_mn = static_cast<uint32_t>(make_desc_mnmajor_sw128(0, 8192) >> 32);
+      const uint32_t lo0_mn = static_cast<uint32_t>(make_desc_mnmajor_sw128(smem_u32(smem), 8192));
+      const uint32_t lo0_a = (GEN && p.a_mn) ? lo0_mn : lo0;
+      const uint32_t lo0_b = (GEN && p.b_mn) ? lo0_mn : lo0;
+      const uint32_t hi_a = (GEN && p.a_mn) ? hi_mn : hi;
+      const uint32_t hi_b = (GEN && p.b_mn) ? hi_mn : hi;
+      const uint32_t step_a = (GEN && p.a_mn) ? (2048u >> 4) : 2u;
+      const uint32_t step_b = (GEN && p.b_mn) ? (2048u >> 4) : 2u;
+      const uint32_t idesc = GEN ? (kIdesc | (p.a_mn ? 1u << 15 : 0u) | (p.b_mn ? 1u << 16 : 0u)) : kIdesc;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int acc = it % kAccBufs;
         const uint32_t acc_phase = (it / kAccBufs) & 1;
@@ -261,20 +293,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           tc_fence_after();
-          const uint32_t a_lo = lo0 + stage * (S::kStageBytes >> 4);
-          const uint32_t b_lo = a_lo + (S::kABytes >> 4);
+          const uint32_t a_lo = (GEN ? lo0_a : lo0) + stage * (S::kStageBytes >> 4);
+          const uint32_t b_lo = (GEN ? lo0_b + stage * (S::kStageBytes >> 4) : a_lo) + (S::kABytes >> 4);
           const uint32_t accum0 = kb != 0 ? 1u : 0u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t accum = k == 0 ? accum0 : 1u;
 #pragma unroll
             for (int h = 0; h < MT; ++h) {
-              const uint64_t a_desc = desc(a_lo + h * ((kBM * kBKBytes) >> 4) + 2 * k, hi);
-              const uint64_t b_desc = desc(b_lo + 2 * k, hi);
-              if constexpr (KIND == kKindE4M3)
-                umma_f8_ss(d_tmem + h * BN, a_desc, b_desc, kIdesc, accum);
-              else
-                umma_f16_ss(d_tmem + h * BN, a_desc, b_desc, kIdesc, accum);
+              if constexpr (GEN) {
+                const uint64_t a_desc = desc(a_lo + h * ((kBM * kBKBytes) >> 4) + step_a * k, hi_a);
+                const uint64_t b_desc = desc(b_lo + step_b * k, hi_b);
+                umma_f16_ss(d_tmem + h * BN, a_desc, b_desc, idesc, accum);
+              } else {
+                const uint64_t a_desc = desc(a_lo + h * ((kBM * kBKBytes) >> 4) + 2 * k, hi);
+                const uint64_t b_desc = desc(b_lo + 2 * k, hi);
+                if constexpr (KIND == kKindE4M3)
+                  umma_f8_ss(d_tmem + h * BN, a_desc, b_desc, kIdesc, accum);
+                else
+                  umma_f16_ss(d_tmem + h * BN, a_desc, b_desc, kIdesc, accum);
+              }
             }
           }
           umma_commit(empty + stage);  // frees the stage once these MMAs have read it
@@ -483,11 +521,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-template <int BN, int MT, int KIND, typename OutT>
+template <int BN, int MT, int KIND, typename OutT, bool GEN = false>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
                cudaStream_t stream) {
   using S = GemmSmem<BN, MT>;
-  auto kfn = gemm_nt_kernel<BN, MT, KIND, OutT>;
+  auto kfn = gemm_nt_kernel<BN, MT, KIND, OutT, GEN>;
   static bool configured = false;  // per instantiation; benign race (idempotent attribute set)
   if (!configured) {
     int rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
@@ -502,6 +540,18 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
 template <int BN, int MT>
 int dispatch_dtype(int in_dtype, int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                    const GemmParams& p, int grid, cudaStream_t stream) {
+  if (p.a_mn || p.b_mn) {  // generic operand storage: 16-bit types
+    if (in_dtype == B200K_F16 && out_dtype == B200K_F32)
+      return launch_one<BN, MT, kKindF16, float, true>(ta, tb, tc, p, grid, stream);
+    if (in_dtype == B200K_F16 && out_dtype == B200K_F16)
+      return launch_one<BN, MT, kKindF16, __half, true>(ta, tb, tc, p, grid, stream);
+    if (in_dtype == B200K_BF16 && out_dtype == B200K_F32)
+      return launch_one<BN, MT, kKindBF16, float, true>(ta, tb, tc, p, grid, stream);
+    if (in_dtype == B200K_BF16 && out_dtype == B200K_BF16)
+      return launch_one<BN, MT, kKindBF16, __nv_bfloat16, true>(ta, tb, tc, p, grid, stream);
+    return set_error(B200K_ERR_BAD_DTYPE, "gemm: operands stored [K, M] / [K, N] need F16 or BF16 (in=%d out=%d)",
+                     in_dtype, out_dtype);
+  }
   if (in_dtype == B200K_F16 && out_dtype == B200K_F32)
     return launch_one<BN, MT, kKindF16, float>(ta, tb, tc, p, grid, stream);
   if (in_dtype == B200K_F16 && out_dtype == B200K_F16)
@@ -564,7 +614,10 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   const size_t out_es = dtype_size(a.out_dtype);
   if (in_es == 0 || out_es == 0 || a.in_dtype == B200K_F32)
     return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: unsupported dtype in=%d out=%d", a.in_dtype, a.out_dtype);
-  if (a.lda < a.k || a.ldb < a.k || (peers.num == 0 && a.ldc < a.n))
+  const bool a_mn = a.a_km != 0, b_mn = a.b_kn != 0;
+  if ((a_mn || b_mn) && a.in_dtype == B200K_E4M3)
+    return set_error(B200K_ERR_BAD_DTYPE, "gemm: a_km / b_kn operand storage is for F16 / BF16 only");
+  if (a.lda < (a_mn ? a.m : a.k) || a.ldb < (b_mn ? a.n : a.k) || (peers.num == 0 && a.ldc < a.n))
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: leading dimensions smaller than the row length");
   if ((reinterpret_cast<uintptr_t>(a.a) & 15) || (reinterpret_cast<uintptr_t>(a.b) & 15) ||
       (a.lda * in_es) % 16 != 0 || (a.ldb * in_es) % 16 != 0)
@@ -620,16 +673,18 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
 
   CUtensorMap ta, tb;
   {
-    uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m)};
+    // K-major: rows of the stored matrix are rows of the tile; MN-major ([K, M] storage): one box
+    // is 64 contiguous M-elements x 64 K-rows
+    uint64_t dims[2] = {static_cast<uint64_t>(a_mn ? a.m : a.k), static_cast<uint64_t>(a_mn ? a.k : a.m)};
     uint64_t strides[1] = {static_cast<uint64_t>(a.lda) * in_es};
-    uint32_t box[2] = {static_cast<uint32_t>(k_per_stage), static_cast<uint32_t>(bm)};
+    uint32_t box[2] = {static_cast<uint32_t>(a_mn ? 64 : k_per_stage), static_cast<uint32_t>(a_mn ? 64 : bm)};
     rc = encode_tmap(&ta, a.in_dtype, 2, const_cast<void*>(a.a), dims, strides, box);
     if (rc) return rc;
   }
   {
-    uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n)};
+    uint64_t dims[2] = {static_cast<uint64_t>(b_mn ? a.n : a.k), static_cast<uint64_t>(b_mn ? a.k : a.n)};
     uint64_t strides[1] = {static_cast<uint64_t>(a.ldb) * in_es};
-    uint32_t box[2] = {static_cast<uint32_t>(k_per_stage), static_cast<uint32_t>(bn)};
+    uint32_t box[2] = {static_cast<uint32_t>(b_mn ? 64 : k_per_stage), static_cast<uint32_t>(b_mn ? 64 : bn)};
     rc = encode_tmap(&tb, a.in_dtype, 2, const_cast<void*>(a.b), dims, strides, box);
     if (rc) return rc;
   }
@@ -642,6 +697,8 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   p.bias = a.bias;
   p.bias_dtype = a.bias_dtype;
   p.act = a.activation;
+  p.a_mn = a_mn ? 1 : 0;
+  p.b_mn = b_mn ? 1 : 0;
   p.ldc = a.ldc;
   p.m = static_cast<int32_t>(a.m);
   p.n = static_cast<int32_t>(a.n);

@@ -19,8 +19,9 @@ Commands:
   driver/sample_commands.txt:22,26): operands are created with exactly the given strides.
 
 Backends: ``b200k`` (default; this library's kernels) and ``torch`` (the ATen op on the same
-device).  The kernels take ``A[M, K] x B[N, K]^T`` with contiguous rows; an operand given in
-another layout is repacked once before timing, and the line printed for the command says so.
+device).  The GEMM kernel reads either storage order of each operand ([M, K] or [K, M]; [K, N] or
+[N, K]), so the four transA / transB forms run as given; an operand with no contiguous dimension is
+repacked once before timing, and the line printed for the command says so.
 A command or backend that cannot run (float32 GEMM, head dim other than 128, a mask, ...) gets
 ``N.A.`` in its columns, as in the reference.  Times are microseconds per call, measured with CUDA
 events on the current stream after 3 untimed calls.  There is no CPU path.
@@ -159,14 +160,20 @@ def _mm_callable(backend: str, a: torch.Tensor, b: torch.Tensor, notes: List[str
         return lambda: torch.mm(a, b)
     if a.dtype not in (torch.float16, torch.bfloat16) or a.dtype != b.dtype:
         raise Unsupported(f"b200k GEMM takes float16 / bfloat16 operands, not {a.dtype}")
-    a_nt, b_nk = a, b.t()
-    if not _rows_contiguous(a_nt):
-        a_nt = a_nt.contiguous()
-        notes.append("A repacked to row-major [M, K] before timing")
-    if not _rows_contiguous(b_nk):
-        b_nk = b_nk.contiguous()
-        notes.append("B repacked to [N, K] before timing")
-    return lambda: torch.ops.b200k.gemm_nt(a_nt, b_nk, a.dtype)
+    # the kernel reads either storage order of each operand; only a layout with no contiguous
+    # dimension (or rows that are not 16-byte multiples) is repacked, once, before timing
+    def pick(t: torch.Tensor, what: str):
+        if _rows_contiguous(t) and t.stride(0) % 8 == 0 and t.size(1) % 8 == 0:
+            return t, False
+        tt = t.t()
+        if _rows_contiguous(tt) and tt.stride(0) % 8 == 0 and tt.size(1) % 8 == 0:
+            return tt, True
+        notes.append(f"{what} repacked to contiguous rows before timing")
+        return t.contiguous(), False
+
+    a_s, ta = pick(a, "A")
+    b_s, tb_ = pick(b, "B")
+    return lambda: torch.ops.b200k.gemm(a_s, b_s, ta, tb_, a.dtype)
 
 
 def build_callable(cmd, backend: str, device, notes: List[str]) -> Callable[[], torch.Tensor]:

@@ -10,6 +10,8 @@ replaced when nothing but its first output is used).
 What is rewritten (forward graph only; the backward graph, if any, goes to the nested backend as is):
 
 * ``aten.mm(a, t(w))``           -> ``b200k.gemm_nt(a, w, out_dtype=a.dtype)``
+* ``aten.mm`` in the other three storage forms (``mm(a, b)``, ``mm(t(a), b)``, ``mm(t(a), t(b))``)
+                                 -> ``b200k.gemm(a, b, trans_a, trans_b)`` (no operand is repacked)
 * ``aten.addmm(bias, a, t(w))``  -> ``b200k.linear_act(a, w, bias)`` (bias [N] added in the GEMM's
   epilogue; alpha = beta = 1)
   for 2-D f16 / bf16 CUDA operands of one dtype, where ``t`` is ``aten.t``, ``aten.transpose(0, 1)``
@@ -77,24 +79,44 @@ def _transposed_source(node) -> Optional[fx.Node]:
     return None
 
 
+def _storage(node):
+    """(source node, transposed?) with the source's rows contiguous, or None."""
+    src = _transposed_source(node)
+    trans = src is not None
+    if src is None:
+        src = node
+    v = _val(src)
+    if not _is_cuda_half(v, 2) or v.stride(1) != 1 or v.size(1) % 8 != 0 or v.stride(0) % 8 != 0:
+        return None
+    return src, trans
+
+
+def _match_mm(a, b):
+    """(a_src, b_src, trans_a, trans_b) if ``mm(a, b)`` can run on the kernel as it is stored."""
+    sa, sb = _storage(a), _storage(b)
+    if sa is None or sb is None or _val(sa[0]).dtype != _val(sb[0]).dtype:
+        return None
+    return sa[0], sb[0], sa[1], sb[1]
+
+
 def _match_nt(a, b):
     """(a, w) if ``mm(a, b)`` is ``a[M, K] @ w[N, K]^T`` on supported operands, else None."""
-    w = _transposed_source(b)
-    if w is None:
+    m = _match_mm(a, b)
+    if m is None or m[2] or not m[3]:
         return None
-    va, vw = _val(a), _val(w)
-    if not (_is_cuda_half(va, 2) and _is_cuda_half(vw, 2)) or va.dtype != vw.dtype or va.size(1) != vw.size(1):
-        return None
-    return a, w
+    return m[0], m[1]
 
 
 def replace_mm(node: fx.Node) -> bool:
-    m = _match_nt(*node.args[:2])
+    m = _match_mm(*node.args[:2])
     if m is None:
         return False
-    a, w = m
+    a, b, ta, tb_ = m
     with node.graph.inserting_before(node):
-        new = node.graph.call_function(torch.ops.b200k.gemm_nt.default, args=(a, w, _val(a).dtype))
+        if not ta and tb_:
+            new = node.graph.call_function(torch.ops.b200k.gemm_nt.default, args=(a, b, _val(a).dtype))
+        else:
+            new = node.graph.call_function(torch.ops.b200k.gemm.default, args=(a, b, ta, tb_, _val(a).dtype))
     new.meta = dict(node.meta)
     node.replace_all_uses_with(new)
     node.graph.erase_node(node)

@@ -27,6 +27,8 @@ __all__ = [
     "LIBRARY",
     "gemm_nt",
     "gemm_fp8_nt",
+    "gemm",
+    "linear",
     "linear_act",
     "attention",
     "decode_attention",
@@ -97,12 +99,16 @@ def _gemm_out_dtype(in_dtype: torch.dtype, out_dtype) -> torch.dtype:
 
 
 def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: int = 0, tile_m: int = 0,
-                 bias: Optional[Tensor] = None, activation: str = "none") -> None:
+                 bias: Optional[Tensor] = None, activation: str = "none", a_km: bool = False,
+                 b_kn: bool = False) -> None:
+    """a is stored [M, K] ([K, M] with a_km); b is stored [N, K] ([K, N] with b_kn)."""
     a = _row_major_2d(a)
     b = _row_major_2d(b)
     args = L.GemmArgs()
     args.a, args.b, args.c = a.data_ptr(), b.data_ptr(), out.data_ptr()
-    args.m, args.n, args.k = a.size(0), b.size(0), a.size(1)
+    args.m, args.k = (a.size(1), a.size(0)) if a_km else (a.size(0), a.size(1))
+    args.n = b.size(1) if b_kn else b.size(0)
+    args.a_km, args.b_kn = int(a_km), int(b_kn)
     args.lda, args.ldb, args.ldc = a.stride(0), b.stride(0), out.stride(0)
     args.in_dtype = L.DTYPE_CODES[a.dtype]
     args.out_dtype = L.DTYPE_CODES[out.dtype]
@@ -147,6 +153,73 @@ class gemm_nt(CustomOp):
         out = torch.empty((a.size(0), b.size(0)), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
         _launch_gemm(a, b, out, None, None)
         return out
+
+
+@CustomOp.register(library=LIBRARY)
+class gemm(CustomOp):
+    """C = op(a) @ op(b) with BLAS-style flags: ``a`` is [M, K] ([K, M] with ``trans_a``), ``b`` is
+    [K, N] ([N, K] with ``trans_b``); f16 / bf16, fp32 accumulation.  No operand is repacked: the
+    kernel reads either storage order.  ``gemm_nt(a, b)`` is ``gemm(a, b, trans_b=True)``."""
+
+    signature = ("gemm(Tensor a, Tensor b, bool trans_a=False, bool trans_b=False, "
+                 "ScalarType? out_dtype=None) -> Tensor")
+
+    @staticmethod
+    def _mnk(a, b, trans_a, trans_b):
+        m, k = (a.size(1), a.size(0)) if trans_a else (a.size(0), a.size(1))
+        kb, n = (b.size(1), b.size(0)) if trans_b else (b.size(0), b.size(1))
+        return m, n, k, kb
+
+    def select(self, sel: KernelSelection):
+        a = sel.arg_tensor(0)
+        b = sel.arg_tensor(1)
+        ta = sel.attr_bool(2)
+        tb_ = sel.attr_bool(3)
+        od = sel.attr_optional(4)
+        torch._check(a.t.dim() == 2 and b.t.dim() == 2, lambda: "gemm: a and b must be 2-D")
+        torch._check(a.t.dtype in _HALF_TYPES and a.t.dtype == b.t.dtype,
+                     lambda: f"gemm: a and b must both be float16 or bfloat16, got {a.t.dtype}, {b.t.dtype}")
+        m, n, k, kb = self._mnk(a.t, b.t, bool(ta.v), bool(tb_.v))
+        torch._check(k == kb, lambda: f"gemm: contraction sizes differ ({k} vs {kb})")
+        torch._check(a.t.size(1) % 8 == 0 and b.t.size(1) % 8 == 0,
+                     lambda: "gemm: the contiguous dimension of each operand must be a multiple of 8")
+        sel.return_new_tensor([m, n], _gemm_out_dtype(a.t.dtype, od.v))
+
+    def eager_execute(self, a, b, trans_a=False, trans_b=False, out_dtype=None):
+        m, n, _, _ = self._mnk(a, b, trans_a, trans_b)
+        out = torch.empty((m, n), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
+        _launch_gemm(a, b, out, None, None, a_km=bool(trans_a), b_kn=not trans_b)
+        return out
+
+
+class _LinearFunction(torch.autograd.Function):
+    """y = x @ w^T (+ bias) with both backward products on the same kernel (the reference wraps its
+    own op the same way, kernel/boo/ops/conv.py:313-372; the products are those of
+    kernel/boo/op_exports/gemm.py:233-270): dx = dy @ w, dw = dy^T @ x, db = sum(dy)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return torch.ops.b200k.linear_act(x, w, bias, "none", x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.ops.b200k.gemm(dy, w, False, False, x.dtype)       # [M, N] @ [N, K]
+        if ctx.needs_input_grad[1]:
+            dw = torch.ops.b200k.gemm(dy, x, True, False, w.dtype)        # [M, N]^T @ [M, K]
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: Tensor, w: Tensor, bias: Optional[Tensor] = None) -> Tensor:
+    """Differentiable ``x[M, K] @ w[N, K]^T + bias`` (f16 / bf16 CUDA tensors) on the b200k GEMM."""
+    return _LinearFunction.apply(x, w, bias)
 
 
 @CustomOp.register(library=LIBRARY)

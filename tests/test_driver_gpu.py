@@ -28,7 +28,7 @@ def test_commands_file_round_trip(tmp_path):
     rows = list(csv.DictReader(out.read_text().splitlines()))
     assert [r["arguments"] for r in rows] == [shlex.join(shlex.split(c)) for c in commands]
     assert rows[0]["b200k num_dispatches"] == "5" and float(rows[0]["b200k min"]) > 0
-    assert rows[1]["b200k num_dispatches"] == "5"          # B repacked before timing
+    assert rows[1]["b200k num_dispatches"] == "5"          # B stored [K, N]: read as it is
     assert rows[2]["b200k min"] == "N.A." and rows[2]["torch num_dispatches"] == "3"   # float32: torch only
     assert rows[3]["b200k num_dispatches"] == "4" and rows[4]["b200k num_dispatches"] == "4"
     for r in rows:

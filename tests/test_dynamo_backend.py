@@ -78,14 +78,28 @@ def test_addmm_becomes_fused_linear():
     assert [a.name for a in node.args[:3]] == ["a", "w", "bias"] and node.args[3] == "none"
 
 
-@pytest.mark.parametrize("case", ["nn_form", "float32", "cpu", "three_d"])
+def test_mm_nn_form_is_routed_to_the_general_op():
+    def build(g):
+        a = _ph(g, "a", _fake((64, 256)))
+        b = _ph(g, "b", _fake((256, 512)))
+        mm = g.call_function(aten.mm.default, (a, b))
+        mm.meta["val"] = _fake((64, 512))
+        return mm
+
+    gm = _graph(build)
+    assert db.apply_replacements(gm) == 1
+    node = next(n for n in gm.graph.nodes if n.target is torch.ops.b200k.gemm.default)
+    assert node.args[2] is False and node.args[3] is False
+
+
+@pytest.mark.parametrize("case", ["odd_rows", "float32", "cpu", "three_d"])
 def test_mm_left_alone(case):
     def build(g):
         dtype = torch.float32 if case == "float32" else torch.float16
         dev = "cpu" if case == "cpu" else "cuda"
         a = _ph(g, "a", _fake((4, 64, 256) if case == "three_d" else (64, 256), dtype, dev))
-        if case == "nn_form":
-            b = _ph(g, "b", _fake((256, 512), dtype, dev))
+        if case == "odd_rows":
+            b = _ph(g, "b", _fake((256, 516), dtype, dev))   # rows of 516 halves are not 16-byte multiples
         else:
             w = _ph(g, "w", _fake((512, 256), dtype, dev))
             b = g.call_function(aten.t.default, (w,))

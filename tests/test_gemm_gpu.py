@@ -208,3 +208,57 @@ def test_linear_act_rejects_unknown_activation():
     a, w = oracle.make_gemm_inputs(128, 128, 64, torch.float16, seed=1)
     with pytest.raises((RuntimeError, ValueError)):
         torch.ops.b200k.linear_act(a.to(DEV), w.to(DEV), None, "tanh", None)
+
+
+# ---- operand storage orders (the four BLAS forms) and the backward products ----
+@pytest.mark.parametrize("trans_a", [False, True])
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("mnk", [(256, 256, 128), (296, 200, 136), (512, 768, 1024)])
+def test_gemm_all_forms(trans_a, trans_b, mnk):
+    m, n, k = mnk
+    g = torch.Generator().manual_seed(12)
+    a = torch.randn((k, m) if trans_a else (m, k), generator=g).half()
+    b = torch.randn((n, k) if trans_b else (k, n), generator=g).half()
+    c = torch.ops.b200k.gemm(a.to(DEV), b.to(DEV), trans_a, trans_b, None)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(c, oracle.gemm(a, b, trans_a, trans_b))
+
+
+@pytest.mark.parametrize("tile", [(128, 128), (128, 256), (256, 256)])
+def test_gemm_mn_major_operands_every_tile_shape(tile):
+    m, n, k = 512, 512, 320
+    g = torch.Generator().manual_seed(13)
+    a = torch.randn(k, m, generator=g).bfloat16()   # stored [K, M]
+    b = torch.randn(k, n, generator=g).bfloat16()   # stored [K, N]
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops._launch_gemm(a.to(DEV), b.to(DEV), out, None, None, tile_n=tile[1], tile_m=tile[0], a_km=True, b_kn=True)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(out, oracle.gemm(a, b, True, False))
+
+
+def test_linear_autograd_matches_torch():
+    g = torch.Generator().manual_seed(14)
+    x = (torch.randn(384, 256, generator=g) * 0.5).half()
+    w = (torch.randn(512, 256, generator=g) * 0.5).half()
+    bias = torch.randn(512, generator=g).half()
+    dy = (torch.randn(384, 512, generator=g) * 0.5).half()
+    xr, wr, br = (t.float().requires_grad_() for t in (x, w, bias))
+    (torch.nn.functional.linear(xr, wr, br) * dy.float()).sum().backward()
+    xd, wd, bd = (t.to(DEV).requires_grad_() for t in (x, w, bias))
+    y = ops.linear(xd, wd, bd)
+    (y.float() * dy.to(DEV).float()).sum().backward()
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(y.detach(), torch.nn.functional.linear(x.float(), w.float(), bias.float()))
+    for got, ref in ((xd.grad, xr.grad), (wd.grad, wr.grad), (bd.grad, br.grad)):
+        scale = ref.abs().max().item()
+        assert (got.float().cpu() - ref).abs().max().item() <= 1e-2 * max(scale, 1.0)
+
+
+def test_gemm_rejects_rows_that_are_not_16_byte_multiples():
+    a = torch.zeros(136, 300, dtype=torch.float16, device=DEV)   # stored [K, M] with M = 300
+    b = torch.zeros(136, 200, dtype=torch.float16, device=DEV)
+    with pytest.raises((RuntimeError, ValueError)):
+        torch.ops.b200k.gemm(a, b, True, False, None)
