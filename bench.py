@@ -145,7 +145,7 @@ class GemmWL(Workload):
 
     def __init__(self, name, n, fp8):
         self.name, self.n, self.fp8 = name, n, fp8
-        self.traffic_bytes = 409.6e6 if (fp8 and n == 8192) else (16.8e6 if (not fp8 and n == 2048) else None)
+        self.traffic_bytes = 417.1e6 if (fp8 and n == 8192) else (16.9e6 if (not fp8 and n == 2048) else None)
         # the measured peak is a bf16 GEMM; e4m3 runs the tensor pipe at twice that rate
         self.peak_scale = 2.0 if fp8 else 1.0
         self.dtype = "e4m3" if fp8 else "f16"
@@ -315,7 +315,7 @@ class PagedDecodeWL(Workload):
 
 
 WORKLOADS = {
-    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 246.8e6),
+    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 249.1e6),
     "attn_causal": lambda: AttentionWL("attn_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
     "gemm_f16": lambda: GemmWL("gemm_f16", 2048, False),
     "gemm_fp8": lambda: GemmWL("gemm_fp8", 8192, True),
