@@ -16,7 +16,9 @@ from .templates import (  # noqa: F401
     get_decode_attention_kernel,
     get_fp8_gemm_kernel,
     get_gemm_kernel,
+    get_kv_append_kernel,
     get_paged_decode_attention_kernel,
+    get_paged_prefill_attention_kernel,
     get_vanilla_attention_kernel,
 )
 

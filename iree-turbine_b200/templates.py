@@ -27,6 +27,8 @@ __all__ = [
     "get_causal_attention_kernel",
     "get_decode_attention_kernel",
     "get_paged_decode_attention_kernel",
+    "get_paged_prefill_attention_kernel",
+    "get_kv_append_kernel",
 ]
 
 _HALF = (torch.float16, torch.bfloat16)
@@ -146,3 +148,39 @@ def get_paged_decode_attention_kernel(shape: AttentionShape, dtype: torch.dtype 
         return torch.ops.b200k.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, sc, chunk_tokens)
 
     return LaunchableKernel("paged_decode_attention", shape, dtype, run)
+
+
+def get_paged_prefill_attention_kernel(shape: AttentionShape, dtype: torch.dtype = torch.bfloat16,
+                                       causal: bool = True, scale: Optional[float] = None) -> LaunchableKernel:
+    """Prefill (or one chunk of it) over the paged cache: kernel(q, k_cache, v_cache, block_table, seq_lens)
+    with q [num_seqs, heads, query_seq_len, 128]; the queries of a sequence are its last query_seq_len tokens."""
+    if shape.head_size != 128:
+        raise ValueError("paged prefill attention: head_size must be 128")
+    if shape.block_size not in (16, 32, 64, 128):
+        raise ValueError("paged prefill attention: block_size must be 16, 32, 64 or 128")
+    sc = shape.head_size ** -0.5 if scale is None else float(scale)
+
+    def run(q, k_cache, v_cache, block_table, seq_lens):
+        _expect(q, (shape.num_seqs, shape.num_query_heads, shape.query_seq_len, shape.head_size), dtype, "q")
+        if tuple(k_cache.shape[1:]) != (shape.num_kv_heads, shape.block_size, shape.head_size):
+            raise ValueError(
+                f"k_cache: expected [pages, {shape.num_kv_heads}, {shape.block_size}, {shape.head_size}], "
+                f"got {tuple(k_cache.shape)}"
+            )
+        return torch.ops.b200k.paged_attention(q, k_cache, v_cache, block_table, seq_lens, sc, causal)
+
+    return LaunchableKernel("paged_prefill_attention", shape, dtype, run)
+
+
+def get_kv_append_kernel(shape: AttentionShape, dtype: torch.dtype = torch.bfloat16) -> LaunchableKernel:
+    """kernel(k_new, v_new, k_cache, v_cache, block_table, positions): writes query_seq_len new rows per
+    sequence into the paged cache at token positions positions[s] + t (in place)."""
+    if shape.block_size is None or shape.block_size <= 0:
+        raise ValueError("kv append: block_size is required")
+
+    def run(k_new, v_new, k_cache, v_cache, block_table, positions):
+        _expect(k_new, (shape.num_seqs, shape.query_seq_len, shape.num_kv_heads, shape.head_size), dtype, "k_new")
+        torch.ops.b200k.kv_append(k_new, v_new, k_cache, v_cache, block_table, positions)
+        return None
+
+    return LaunchableKernel("kv_append", shape, dtype, run)

@@ -166,3 +166,22 @@ def test_paged_prefill_zero_length_and_queries_before_first_key():
     assert bool((o[0] == 0).all())                 # no keys at all
     assert bool((o[1, :, :44] == 0).all())         # queries 0..43 precede the first key (64 queries, 20 keys)
     oracle.assert_close_half(o.cpu(), oracle.paged_attention(q, kc, vc, bt, sl, SCALE, True))
+
+
+def test_template_constructors_for_append_and_paged_prefill():
+    lens0, chunk = [100, 37], 32
+    total = [n + chunk for n in lens0]
+    q, kc, vc, bt, sl = _paged_case(total, chunk, hq=8, hkv=2, dtype=torch.bfloat16, seed=51)
+    shape = tb.AttentionShape(num_query_heads=8, num_kv_heads=2, head_size=128, query_seq_len=chunk,
+                              num_seqs=2, block_size=16)
+    g = torch.Generator().manual_seed(6)
+    k_new = torch.randn(2, chunk, 2, 128, generator=g).bfloat16()
+    v_new = torch.randn(2, chunk, 2, 128, generator=g).bfloat16()
+    pos = torch.tensor(lens0, dtype=torch.int32)
+    k_ref, v_ref = oracle.kv_append(k_new, v_new, kc, vc, bt, pos)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    tb.get_kv_append_kernel(shape, torch.bfloat16)(k_new.to(DEV), v_new.to(DEV), kd, vd, bt.to(DEV), pos.to(DEV))
+    o = tb.get_paged_prefill_attention_kernel(shape, torch.bfloat16)(q.to(DEV), kd, vd, bt.to(DEV), sl.to(DEV))
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(o.cpu(), oracle.paged_attention(q, k_ref, v_ref, bt, sl, SCALE, True))
