@@ -135,3 +135,61 @@ def test_kv_append_then_gather_round_trip():
     g0 = oracle.paged_gather(kc, bt, sl, 48)
     assert torch.equal(gk[0, :, :17], g0[0, :, :17]) and torch.equal(gk[1, :, :30], g0[1, :, :30])
     assert int((k2 != kc).any(dim=-1).sum()) <= 2 * 3 * 8
+
+
+@pytest.mark.parametrize("trans_a", [False, True])
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_gemm_forms_match_torch_mm(trans_a, trans_b):
+    g = torch.Generator().manual_seed(2)
+    m, n, k = 24, 40, 16
+    a = torch.randn((k, m) if trans_a else (m, k), generator=g, dtype=torch.float64)
+    b = torch.randn((n, k) if trans_b else (k, n), generator=g, dtype=torch.float64)
+    ref = torch.mm(a.t() if trans_a else a, b.t() if trans_b else b)
+    torch.testing.assert_close(oracle.gemm(a, b, trans_a, trans_b).double(), ref, rtol=1e-5, atol=1e-5)
+    # the backward products of the NT form are two of these forms (gemm.py:233-270 of the reference)
+    if not trans_a and trans_b:
+        x = a.clone().requires_grad_()
+        w = b.clone().requires_grad_()
+        dy = torch.randn(m, n, generator=g, dtype=torch.float64)
+        (torch.mm(x, w.t()) * dy).sum().backward()
+        torch.testing.assert_close(oracle.gemm(dy, b, False, False).double(), x.grad, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(oracle.gemm(dy, a, True, False).double(), w.grad, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("activation", ["none", "relu", "gelu", "silu"])
+def test_linear_act_matches_torch_functional(activation):
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(12, 32, generator=g)
+    w = torch.randn(20, 32, generator=g)
+    bias = torch.randn(20, generator=g)
+    y = torch.nn.functional.linear(a, w, bias)
+    ref = {"none": lambda t: t, "relu": torch.relu, "gelu": torch.nn.functional.gelu,
+           "silu": torch.nn.functional.silu}[activation](y)
+    torch.testing.assert_close(oracle.linear_act(a, w, bias, activation), ref, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(oracle.linear_act(a, w, None, "none"), torch.mm(a, w.t()), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_paged_attention_matches_sdpa_per_sequence(causal):
+    lens, sq = [40, 23, 0], 8
+    q0, kc, vc, bt, sl = oracle.make_paged_decode_inputs(q_heads=4, kv_heads=2, lens=lens, seed=4)
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(3, 4, sq, 128, generator=g).half()
+    out = oracle.paged_attention(q, kc, vc, bt, sl, 128 ** -0.5, causal)
+    for i, n in enumerate(lens):
+        if n == 0:
+            assert bool((out[i] == 0).all())
+            continue
+        # explicit per-token gather, independent of oracle.paged_gather
+        rows_k = torch.stack([kc[int(bt[i, t // 16]), :, t % 16] for t in range(n)], dim=1)   # [Hkv, n, D]
+        rows_v = torch.stack([vc[int(bt[i, t // 16]), :, t % 16] for t in range(n)], dim=1)
+        kk = rows_k.float().repeat_interleave(2, dim=0).unsqueeze(0)
+        vv = rows_v.float().repeat_interleave(2, dim=0).unsqueeze(0)
+        mask = None
+        if causal:
+            ii = torch.arange(sq).unsqueeze(1)
+            jj = torch.arange(n).unsqueeze(0)
+            mask = jj <= ii + (n - sq)
+        ref = torch.nn.functional.scaled_dot_product_attention(q[i:i + 1].float(), kk, vv, attn_mask=mask,
+                                                               scale=128 ** -0.5)
+        torch.testing.assert_close(out[i:i + 1], ref, rtol=1e-4, atol=1e-5)
