@@ -80,11 +80,62 @@ def paged_case():
                         gathered_k=bits16(gathered_k), scale=np.array(scale, dtype=np.float64))
 
 
+def linear_cases():
+    """Linear layer with bias and activation, and the two backward products of the NT form (from
+    torch autograd)."""
+    g = torch.Generator().manual_seed(13)
+    x = (torch.randn(72, 64, generator=g) * 0.5).half()
+    w = (torch.randn(88, 64, generator=g) * 0.5).half()
+    bias = torch.randn(88, generator=g).half()
+    dy = (torch.randn(72, 88, generator=g) * 0.5).half()
+    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
+    y = F.linear(xr, wr, bias.float())
+    (y * dy.float()).sum().backward()
+    np.savez_compressed(os.path.join(HERE, "linear_f16_72x88x64.npz"), x=bits16(x), w=bits16(w), bias=bits16(bias),
+                        dy=bits16(dy), y_gelu=F.gelu(y.detach()).numpy(), y_silu=F.silu(y.detach()).numpy(),
+                        y=y.detach().numpy(), dx=xr.grad.numpy(), dw=wr.grad.numpy())
+
+
+def paged_prefill_case():
+    """Append a chunk of K/V rows to a paged cache, then attend causally over everything: expected
+    cache from a per-token loop, expected output from SDPA with an explicit mask per sequence."""
+    lens0, chunk, hq, hkv = [50, 0, 129], 24, 4, 2
+    total = [n + chunk for n in lens0]
+    _, kc, vc, bt, sl = oracle.make_paged_decode_inputs(q_heads=hq, kv_heads=hkv, page_size=16, dtype=torch.bfloat16,
+                                                        seed=14, lens=total)
+    g = torch.Generator().manual_seed(15)
+    q = (torch.randn(3, hq, chunk, 128, generator=g) * 0.5).bfloat16()
+    k_new = torch.randn(3, chunk, hkv, 128, generator=g).bfloat16()
+    v_new = torch.randn(3, chunk, hkv, 128, generator=g).bfloat16()
+    k_after, v_after = kc.clone(), vc.clone()
+    for s, n0 in enumerate(lens0):
+        for t in range(chunk):
+            p = n0 + t
+            k_after[int(bt[s, p // 16]), :, p % 16] = k_new[s, t]
+            v_after[int(bt[s, p // 16]), :, p % 16] = v_new[s, t]
+    scale = 128 ** -0.5
+    out = torch.zeros(3, hq, chunk, 128)
+    for s, n in enumerate(total):
+        kk = torch.stack([k_after[int(bt[s, t // 16]), :, t % 16] for t in range(n)], dim=1).float()
+        vv = torch.stack([v_after[int(bt[s, t // 16]), :, t % 16] for t in range(n)], dim=1).float()
+        kk = kk.repeat_interleave(hq // hkv, dim=0).unsqueeze(0)
+        vv = vv.repeat_interleave(hq // hkv, dim=0).unsqueeze(0)
+        i = torch.arange(chunk).unsqueeze(1)
+        j = torch.arange(n).unsqueeze(0)
+        out[s] = F.scaled_dot_product_attention(q[s:s + 1].float(), kk, vv, attn_mask=j <= i + (n - chunk), scale=scale)[0]
+    np.savez_compressed(os.path.join(HERE, "paged_prefill_bf16.npz"), q=bits16(q), k_cache=bits16(kc), v_cache=bits16(vc),
+                        k_new=bits16(k_new), v_new=bits16(v_new), block_table=bt.numpy(),
+                        positions=np.array(lens0, dtype=np.int32), seq_lens=sl.numpy(), k_after=bits16(k_after),
+                        v_after=bits16(v_after), o=out.numpy(), scale=np.array(scale, dtype=np.float64))
+
+
 if __name__ == "__main__":
     torch.set_num_threads(1)  # deterministic reduction order for the stored fp32 values
     gemm_case()
     attention_cases()
     paged_case()
+    linear_cases()
+    paged_prefill_case()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -185,3 +185,17 @@ def test_template_constructors_for_append_and_paged_prefill():
     torch.cuda.synchronize()
     assert tb.device_status() == 0
     oracle.assert_close_half(o.cpu(), oracle.paged_attention(q, k_ref, v_ref, bt, sl, SCALE, True))
+
+
+def test_paged_prefill_golden_fixture():
+    z = np.load(os.path.join(GOLDEN, "paged_prefill_bf16.npz"))
+    h = lambda n: torch.from_numpy(z[n].copy()).view(torch.bfloat16).to(DEV)  # noqa: E731
+    bt, sl, pos = (torch.from_numpy(z[n]).to(DEV) for n in ("block_table", "seq_lens", "positions"))
+    kc, vc = h("k_cache"), h("v_cache")
+    torch.ops.b200k.kv_append(h("k_new"), h("v_new"), kc, vc, bt, pos)
+    o = torch.ops.b200k.paged_attention(h("q"), kc, vc, bt, sl, float(z["scale"]), True)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    assert torch.equal(kc.cpu().view(torch.int16), torch.from_numpy(z["k_after"]))
+    assert torch.equal(vc.cpu().view(torch.int16), torch.from_numpy(z["v_after"]))
+    oracle.assert_close_half(o.cpu(), torch.from_numpy(z["o"]))

@@ -262,3 +262,14 @@ def test_gemm_rejects_rows_that_are_not_16_byte_multiples():
     b = torch.zeros(136, 200, dtype=torch.float16, device=DEV)
     with pytest.raises((RuntimeError, ValueError)):
         torch.ops.b200k.gemm(a, b, True, False, None)
+
+
+def test_linear_golden_fixture_forward_and_backward_products():
+    z = np.load(os.path.join(GOLDEN, "linear_f16_72x88x64.npz"))
+    h = lambda n: torch.from_numpy(z[n].copy()).view(torch.float16).to(DEV)  # noqa: E731
+    x, w, bias, dy = h("x"), h("w"), h("bias"), h("dy")
+    for act, key in (("none", "y"), ("gelu", "y_gelu"), ("silu", "y_silu")):
+        oracle.assert_close_half(torch.ops.b200k.linear_act(x, w, bias, act, None), torch.from_numpy(z[key]))
+    oracle.assert_close_half(torch.ops.b200k.gemm(dy, w, False, False, None), torch.from_numpy(z["dx"]))
+    oracle.assert_close_half(torch.ops.b200k.gemm(dy, x, True, False, None), torch.from_numpy(z["dw"]))
+    assert tb.device_status() == 0

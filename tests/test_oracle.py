@@ -193,3 +193,24 @@ def test_paged_attention_matches_sdpa_per_sequence(causal):
         ref = torch.nn.functional.scaled_dot_product_attention(q[i:i + 1].float(), kk, vv, attn_mask=mask,
                                                                scale=128 ** -0.5)
         torch.testing.assert_close(out[i:i + 1], ref, rtol=1e-4, atol=1e-5)
+
+
+def test_linear_golden_fixture():
+    z = np.load(os.path.join(GOLDEN, "linear_f16_72x88x64.npz"))
+    h = lambda n: torch.from_numpy(z[n].copy()).view(torch.float16)  # noqa: E731
+    x, w, bias, dy = h("x"), h("w"), h("bias"), h("dy")
+    for act, key in (("none", "y"), ("gelu", "y_gelu"), ("silu", "y_silu")):
+        torch.testing.assert_close(oracle.linear_act(x, w, bias, act), torch.from_numpy(z[key]), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(oracle.gemm(dy, w, False, False), torch.from_numpy(z["dx"]), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(oracle.gemm(dy, x, True, False), torch.from_numpy(z["dw"]), rtol=1e-5, atol=1e-5)
+
+
+def test_paged_prefill_golden_fixture():
+    z = np.load(os.path.join(GOLDEN, "paged_prefill_bf16.npz"))
+    h = lambda n: torch.from_numpy(z[n].copy()).view(torch.bfloat16)  # noqa: E731
+    bt, sl, pos = (torch.from_numpy(z[n]) for n in ("block_table", "seq_lens", "positions"))
+    k2, v2 = oracle.kv_append(h("k_new"), h("v_new"), h("k_cache"), h("v_cache"), bt, pos)
+    assert torch.equal(k2.view(torch.int16), torch.from_numpy(z["k_after"]))
+    assert torch.equal(v2.view(torch.int16), torch.from_numpy(z["v_after"]))
+    out = oracle.paged_attention(h("q"), k2, v2, bt, sl, float(z["scale"]), True)
+    torch.testing.assert_close(out, torch.from_numpy(z["o"]), rtol=1e-4, atol=1e-5)
