@@ -503,7 +503,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
       const uint32_t par = ic & 1;
       ok = mbar_wait(o_full, par, abort_word) && mbar_wait(l_full, par, abort_word);
-      ok = __all_sync(0xffffffffu, ok);
+      // the four warps meet at named barriers below: they give up together or not at all
+      ok = bar_red_and(1, 128, ok);
       if (!ok) break;
       tc_fence_after();
       if (quarter == 0) ATTN_TRACE(3, 100);

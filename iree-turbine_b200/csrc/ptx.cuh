@@ -88,6 +88,22 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Named barrier over `nthreads` threads that also ANDs a predicate over them: every participant
+// gets the same answer, so a group of warps can agree to give up together instead of leaving some
+// of them waiting at a later barrier.
+__device__ __forceinline__ bool bar_red_and(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
+
 // Wall-clock limit for any single wait, in nanoseconds.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
