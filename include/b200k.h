@@ -84,6 +84,7 @@ const char* b200k_status_string(int status);
  * multiple of 16 bytes.  C: base aligned to 16 bytes, ldc * sizeof(out) a multiple of 16.
  * K tails, M tails and N tails are handled (out-of-range operand elements read as zero).
  */
+enum { B200K_TILE_SM_PAIR = -2 };
 enum { B200K_ACT_NONE = 0, B200K_ACT_RELU = 1, B200K_ACT_GELU = 2 /* erf form */, B200K_ACT_SILU = 3 };
 
 typedef struct b200k_gemm_args {
@@ -98,7 +99,9 @@ typedef struct b200k_gemm_args {
   const float* scale_b; /* device scalar, E4M3 only, may be NULL (= 1.0) */
   int32_t* status;      /* device status word, may be NULL */
   int32_t tile_n;       /* 0 = choose; else 128 or 256 */
-  int32_t tile_m;       /* 0 = choose; else 128 or 256 (256 needs tile_n 256 or 0) */
+  int32_t tile_m;       /* 0 = choose; else 128 or 256 (256 needs tile_n 256 or 0), or
+                           B200K_TILE_SM_PAIR: 256 x 256 tiles, each computed by a pair of SMs
+                           (F16 / BF16, NT storage, no fused epilogue) */
   /* Optional fused epilogue (the bias / activation tail of a linear layer, cf. the reference's
    * ops/templates/test_linear_trailing_optional_biased.mlir):  C = act(A B^T * scales + bias[n]).
    * bias: device vector of n elements, NULL = none; activation: B200K_ACT_*. */

@@ -173,6 +173,10 @@ class PagedAttentionArgs(C.Structure):
 
 ACTIVATION_CODES = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
 
+# GemmArgs.tile_m value that asks b200k_gemm_nt for 256 x 256 tiles computed by pairs of SMs
+# (B200K_TILE_SM_PAIR).
+TILE_SM_PAIR = -2
+
 # name -> (restype, argtypes); this table is also what the symbol-export test walks.
 EXPORTED_SYMBOLS = {
     "b200k_abi_version": (C.c_int, []),

@@ -159,6 +159,12 @@ int get_side_stream(SideStream* out) {
 
 }  // namespace b200k
 
+namespace b200k {
+// gemm_pair_sm100.cu: 256 x 256 tiles computed by pairs of SMs
+int launch_gemm_pair(const b200k_gemm_args& a, cudaStream_t stream);
+bool gemm_pair_eligible(const b200k_gemm_args& a);
+}  // namespace b200k
+
 using namespace b200k;
 
 extern "C" {
@@ -194,6 +200,7 @@ const char* b200k_status_string(int status) {
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream) {
   if (!args) return set_error(B200K_ERR_NULL, "gemm_nt: args is NULL");
+  if (args->tile_m == B200K_TILE_SM_PAIR) return launch_gemm_pair(*args, static_cast<cudaStream_t>(stream));
   return launch_gemm_nt(*args, static_cast<cudaStream_t>(stream));
 }
 

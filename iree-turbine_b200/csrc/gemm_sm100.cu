@@ -631,7 +631,7 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_n must be 0, 128 or 256");
   if (a.tile_m != 0 && a.tile_m != 128 && a.tile_m != 256)
-    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_m must be 0, 128 or 256");
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_m must be 0, 128 or 256 (the SM-pair tile is taken by b200k_gemm_nt only)");
   int rc = ensure_sm100();
   if (rc) return rc;
 

@@ -55,6 +55,33 @@ def test_256x256_tiles(m, n, k, dtype):
     assert torch.equal(c, _run(a, b, tile_m=256))
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 320), (300, 520, 136), (1, 8, 8), (2560, 2304, 512),
+                                   (5120, 4096, 192)])
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.float16, torch.float32), (torch.float16, torch.float16),
+                                             (torch.bfloat16, torch.bfloat16)])
+def test_sm_pair_tiles(m, n, k, dtype, out_dtype):
+    """256 x 256 tiles computed by pairs of SMs (clusters of two CTAs, one MMA spanning both).
+    Exact and ragged shapes; 2560 x 2304 gives 90 tiles and 5120 x 4096 gives 320 for the 74 pairs,
+    so pairs run several tiles through both accumulator buffers.  The same tile decomposition in
+    one CTA (tile_m=256) must give the same bits: both accumulate each element over k in one order."""
+    from iree_turbine_b200 import _launcher
+
+    a, b = oracle.make_gemm_inputs(m, n, k, dtype, seed=12)
+    c = _run(a, b, out_dtype=out_dtype, tile_m=_launcher.TILE_SM_PAIR)
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b))
+    assert torch.equal(c, _run(a, b, out_dtype=out_dtype, tile_m=_launcher.TILE_SM_PAIR))
+    assert torch.equal(c, _run(a, b, out_dtype=out_dtype, tile_m=256))
+
+
+def test_sm_pair_tiles_reject_what_they_do_not_cover():
+    from iree_turbine_b200 import _launcher
+
+    a, w, bias = oracle.make_gemm_inputs(256, 256, 64, torch.float16, seed=1) + (torch.zeros(256, dtype=torch.float16),)
+    out = torch.empty(256, 256, dtype=torch.float16, device=DEV)
+    with pytest.raises((RuntimeError, ValueError)):
+        ops._launch_gemm(a.to(DEV), w.to(DEV), out, None, None, tile_m=_launcher.TILE_SM_PAIR, bias=bias.to(DEV))
+
+
 @pytest.mark.parametrize("m,n,k", [(200, 136, 72), (1, 8, 8), (130, 260, 1032), (1000, 24, 4096)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_ragged_shapes(m, n, k, dtype):
