@@ -180,6 +180,49 @@ typedef struct b200k_attention_args {
 int b200k_attention_fwd(const b200k_attention_args* args, void* stream);
 
 /*
+ * Attention backward: given q, k, v, the forward output o and its gradient d_o (layouts, head
+ * grouping, causal alignment and scale as in b200k_attention_fwd), writes
+ *   d_q [batch, q_heads, seq_q, 128],  d_k and d_v [batch, kv_heads, seq_kv, 128]
+ * (for grouped-query heads d_k / d_v are summed over the query heads of a group).  Nothing but o is
+ * needed from the forward call: the row statistics are recomputed.  No atomics are used; results
+ * do not depend on the grid.  workspace: device memory, 16-byte aligned, at least
+ * b200k_attention_bwd_workspace_bytes(args) bytes (two fp32 values per query row); contents need
+ * not be preserved between calls.
+ * The reference lists attention backward beside its GEMM backward (kernel/boo/op_exports/gemm.py:233-270,
+ * wrapped as in kernel/boo/ops/conv.py:313-372) without a kernel of its own; the formulas are the
+ * ones torch.autograd derives for softmax(scale * q k^T) v.
+ */
+typedef struct b200k_attention_bwd_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  void* d_q;
+  void* d_k;
+  void* d_v;
+  void* workspace;
+  uint64_t workspace_bytes;
+  int32_t batch, q_heads, kv_heads, seq_q, seq_kv, head_dim;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  int64_t v_stride_b, v_stride_h, v_stride_s;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  int64_t do_stride_b, do_stride_h, do_stride_s;
+  int64_t dq_stride_b, dq_stride_h, dq_stride_s;
+  int64_t dk_stride_b, dk_stride_h, dk_stride_s;
+  int64_t dv_stride_b, dv_stride_h, dv_stride_s;
+  int32_t dtype; /* F16 | BF16 */
+  int32_t causal;
+  float scale;
+  int32_t reserved;
+  int32_t* status; /* device status word, may be NULL; bit 6 = a bounded wait ran out */
+} b200k_attention_bwd_args;
+
+uint64_t b200k_attention_bwd_workspace_bytes(const b200k_attention_bwd_args* args);
+int b200k_attention_bwd(const b200k_attention_bwd_args* args, void* stream);
+
+/*
  * Attention forward over a PAGED K/V cache (prefill, or a chunk of it, after its K/V rows have been
  * appended with b200k_kv_append): same computation as b200k_attention_fwd, with
  *   K/V of sequence b, token t  =  cache[block_table[b * block_table_stride + t / page_size], h, t % page_size, :]

@@ -23,6 +23,7 @@ __all__ = [
     "GemmArgs",
     "GemmAllGatherArgs",
     "AttentionArgs",
+    "AttentionBwdArgs",
     "DecodeArgs",
     "lib",
     "lib_path",
@@ -128,6 +129,17 @@ class AttentionArgs(C.Structure):
     ]
 
 
+class AttentionBwdArgs(C.Structure):
+    _fields_ = (
+        [(n, C.c_void_p) for n in ("q", "k", "v", "o", "d_o", "d_q", "d_k", "d_v", "workspace")]
+        + [("workspace_bytes", C.c_uint64)]
+        + [(n, C.c_int32) for n in ("batch", "q_heads", "kv_heads", "seq_q", "seq_kv", "head_dim")]
+        + [(f"{t}_stride_{d}", C.c_int64) for t in ("q", "k", "v", "o", "do", "dq", "dk", "dv") for d in "bhs"]
+        + [("dtype", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float), ("reserved", C.c_int32),
+           ("status", C.c_void_p)]
+    )
+
+
 class DecodeArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p),
@@ -185,6 +197,8 @@ EXPORTED_SYMBOLS = {
     "b200k_gemm_nt": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "b200k_gemm_nt_allgather": (C.c_int, [C.POINTER(GemmAllGatherArgs), C.c_void_p]),
     "b200k_attention_fwd": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p]),
+    "b200k_attention_bwd_workspace_bytes": (C.c_uint64, [C.POINTER(AttentionBwdArgs)]),
+    "b200k_attention_bwd": (C.c_int, [C.POINTER(AttentionBwdArgs), C.c_void_p]),
     "b200k_decode_workspace_bytes": (C.c_uint64, [C.POINTER(DecodeArgs)]),
     "b200k_decode_default_chunk": (C.c_int32, [C.POINTER(DecodeArgs)]),
     "b200k_decode_attention": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),

@@ -114,9 +114,18 @@ int encode_tmap(CUtensorMap* out, int dtype, int rank, void* base, const uint64_
     estr[i] = 1;
     if (i > 0) gstrides[i - 1] = strides_bytes[i - 1];
   }
-  CUresult r = fn(out, dt, static_cast<cuuint32_t>(rank), base, gdims, gstrides, gbox, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&]() {
+    return fn(out, dt, static_cast<cuuint32_t>(rank), base, gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // A thread that has made no runtime call that needs the device yet (an autograd worker thread
+    // running a backward op first thing) has no current driver context: bind the primary one.
+    cudaFree(nullptr);
+    r = encode();
+  }
   if (r != CUDA_SUCCESS)
     return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu)",
                      static_cast<int>(r), rank, static_cast<unsigned long long>(dims[0]),
@@ -163,6 +172,9 @@ namespace b200k {
 // gemm_pair_sm100.cu: 256 x 256 tiles computed by pairs of SMs
 int launch_gemm_pair(const b200k_gemm_args& a, cudaStream_t stream);
 bool gemm_pair_eligible(const b200k_gemm_args& a);
+// attention_bwd_sm100.cu
+int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream);
+uint64_t attention_bwd_workspace_bytes(const b200k_attention_bwd_args& a);
 }  // namespace b200k
 
 using namespace b200k;
@@ -207,6 +219,15 @@ int b200k_gemm_nt(const b200k_gemm_args* args, void* stream) {
 int b200k_gemm_nt_allgather(const b200k_gemm_allgather_args* args, void* stream) {
   if (!args) return set_error(B200K_ERR_NULL, "gemm_nt_allgather: args is NULL");
   return launch_gemm_nt_allgather(*args, static_cast<cudaStream_t>(stream));
+}
+
+uint64_t b200k_attention_bwd_workspace_bytes(const b200k_attention_bwd_args* args) {
+  return args ? attention_bwd_workspace_bytes(*args) : 0;
+}
+
+int b200k_attention_bwd(const b200k_attention_bwd_args* args, void* stream) {
+  if (!args) return set_error(B200K_ERR_NULL, "attention_bwd: args is NULL");
+  return launch_attention_bwd(*args, static_cast<cudaStream_t>(stream));
 }
 
 int b200k_attention_fwd(const b200k_attention_args* args, void* stream) {

@@ -1,0 +1,531 @@
+// Attention backward (head dim 128, f16 / bf16, grouped-query heads, optional causal mask aligned
+// to the bottom-right corner as in the forward kernel):
+//   P  = exp(scale * Q K^T - LSE)          dV = P^T dO
+//   dP = dO V^T                            dS = P o (dP - delta),  delta[i] = sum_d dO[i, d] O[i, d]
+//   dQ = scale * dS K                      dK = scale * dS^T Q
+//
+// Three launches, none of which needs anything from the forward call but its output O:
+//   1. attn_bwd_delta_kernel: delta (one warp per query row).
+//   2. attn_bwd_kernel<T, kModeDQ>: one CTA per (batch, query head, tile of 128 queries).  It holds
+//      Q and dO and sweeps the visible K/V tiles twice: a statistics sweep (S = Q K^T only, running
+//      row maximum and sum -> LSE, kept in registers and written to the workspace) and a gradient
+//      sweep (S, dP -> dS in shared memory -> dQ += dS K).
+//   3. attn_bwd_kernel<T, kModeDKV>: one CTA per (batch, K/V head, tile of 128 keys).  It holds K
+//      and V and sweeps the query tiles of every query head of the group that see these keys:
+//      S, dP -> P, dS in shared memory -> dV += P^T dO, dK += dS^T Q.
+// No atomics: every output element is accumulated by one CTA in a fixed order, so results do not
+// depend on the grid or on how heads are sharded over devices.
+//
+// All five products are tcgen05 MMAs (M = N = K = 128, fp32 accumulators in tensor memory).  Every
+// operand tile is 128 rows x 128 16-bit columns stored as two 64-column blocks of 16 KB with the
+// 128-byte swizzle -- what TMA writes for Q, K, V, dO and what the softmax threads write for P and
+// dS -- and is described to the tensor core as K-major (contraction along the 128-byte rows) or
+// MN-major (contraction along the row index) as the product needs:
+//   S  = Q K^T    A = Q  K-major    B = K  K-major       dV += P^T dO   A = P   MN-major  B = dO MN-major
+//   dP = dO V^T   A = dO K-major    B = V  K-major       dK += dS^T Q   A = dS  MN-major  B = Q  MN-major
+//                                                        dQ += dS K     A = dS  K-major   B = K  MN-major
+//
+// Roles (6 warps): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 2..5 one
+// query row (lane of tensor memory) per thread for the softmax algebra, then the epilogue.
+// The stages of one iteration run one after the other (load -> S, dP -> P, dS -> gradient MMAs):
+// a first, unpipelined version.  Every wait is bounded.
+#include <type_traits>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200k {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kRows = 128;
+constexpr int kBwdThreads = 192;
+constexpr int kTileBytes = kRows * kD * 2;  // 32 KB
+constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column block
+constexpr int kModeDQ = 0, kModeDKV = 1;
+
+constexpr int kOffQ = 0, kOffDO = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 3 * kTileBytes;
+constexpr int kOffP = 4 * kTileBytes, kOffDS = 5 * kTileBytes;
+constexpr int kOffBars = 6 * kTileBytes;
+// fix_full, ld_full, s_full, pds_full, it_done
+constexpr int kNumBwdBars = 5;
+constexpr int kBwdSmem = kOffBars + kNumBwdBars * 8 + 16 + 1024;
+constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384;
+constexpr float kLog2eBwd = 1.4426950408889634f;
+constexpr int kStatusBwdTimeout = 64;
+
+struct BwdParams {
+  int32_t batch, q_heads, kv_heads, seq_q, seq_kv;
+  int32_t causal, causal_offset;  // query i sees keys j <= i + causal_offset
+  int32_t num_q_tiles, num_kv_tiles;
+  float scale, scale_log2;
+  float* lse2;   // [batch, q_heads, seq_q], log2 domain: log2(sum_j exp2(scale_log2 * s_ij))
+  float* delta;  // [batch, q_heads, seq_q]
+  int32_t* status;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Writes 32 consecutive columns [c0, c0 + 32) of row `r` of a 128 x 128 16-bit tile (two 64-column
+// blocks, 128-byte rows, 16-byte chunks XOR-swizzled with the row index as TMA does).
+__device__ __forceinline__ void store_row_chunk(uint8_t* tile, int r, int c0, const uint32_t (&w)[16]) {
+  uint8_t* row = tile + (c0 >> 6) * kHalfBytes + r * 128;
+  const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(row + (((chunk0 + i) ^ (r & 7)) << 4)) =
+        make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
+// D[128 x 128] (+)= A * B with both operands in shared memory; eight K = 16 steps.
+// K-major operand: step = 32 bytes inside a 64-column block, second block 16 KB further.
+// MN-major operand: step = 16 rows = 2 KB.
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void mma_128x128x128(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
+                                                bool accumulate) {
+  const uint64_t a0 = A_MN ? make_desc_mnmajor_sw128(a_addr, kHalfBytes) : make_desc_kmajor_sw128(a_addr);
+  const uint64_t b0 = B_MN ? make_desc_mnmajor_sw128(b_addr, kHalfBytes) : make_desc_kmajor_sw128(b_addr);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    const uint32_t a_off = A_MN ? ks * (2048 >> 4) : (ks >> 2) * (kHalfBytes >> 4) + (ks & 3) * 2;
+    const uint32_t b_off = B_MN ? ks * (2048 >> 4) : (ks >> 2) * (kHalfBytes >> 4) + (ks & 3) * 2;
+    umma_f16_ss(d_tmem, a0 + a_off, b0 + b_off, idesc, (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+
+__device__ __forceinline__ void load_tile_4d(uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, int row0, int head,
+                                             int batch) {
+  tma_load_4d(dst, tmap, bar, 0, row0, head, batch);
+  tma_load_4d(dst + kHalfBytes, tmap, bar, 64, row0, head, batch);
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                    const __grid_constant__ CUtensorMap tmap_out0,  // dQ (kModeDQ) or dV (kModeDKV)
+                    const __grid_constant__ CUtensorMap tmap_out1,  // dK (kModeDKV)
+                    const BwdParams p) {
+  constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
+  constexpr uint32_t kIdKK = make_idesc(kFmt, kFmt, 128, 128, 0, 0);
+  constexpr uint32_t kIdKM = make_idesc(kFmt, kFmt, 128, 128, 0, 1);
+  constexpr uint32_t kIdMM = make_idesc(kFmt, kFmt, 128, 128, 1, 1);
+  constexpr bool DQ = MODE == kModeDQ;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  uint64_t* fix_full = bars;      // the tiles held for the whole item have landed
+  uint64_t* ld_full = bars + 1;   // the streamed tiles of this iteration have landed
+  uint64_t* s_full = bars + 2;    // S (and dP) are in tensor memory
+  uint64_t* pds_full = bars + 3;  // 128 rows of P / dS written (and S / dP read)
+  uint64_t* it_done = bars + 4;   // the iteration's last MMAs have completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBwdBars);
+  volatile uint32_t* abort_word = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int group = p.q_heads / p.kv_heads;
+
+  // ---- work item ----
+  int batch, kvh, row0;          // row0: first query (DQ) / first key (DKV) of the held tile
+  int head = 0;                  // DQ: the query head
+  int n = 0;                     // DQ: visible K/V tiles;  DKV: query tiles per head that see these keys
+  int qt_lo = 0;                 // DKV: first such query tile
+  if (DQ) {
+    const int bh = blockIdx.x / p.num_q_tiles;
+    const int tile = p.num_q_tiles - 1 - (blockIdx.x - bh * p.num_q_tiles);  // heaviest tiles first
+    batch = bh / p.q_heads;
+    head = bh - batch * p.q_heads;
+    kvh = head / group;
+    row0 = tile * kRows;
+    n = p.num_kv_tiles;
+    if (p.causal) {
+      const int last_col = row0 + kRows - 1 + p.causal_offset;
+      n = last_col < 0 ? 0 : min(last_col / kRows + 1, p.num_kv_tiles);
+    }
+  } else {
+    const int bh = blockIdx.x / p.num_kv_tiles;
+    const int tile = blockIdx.x - bh * p.num_kv_tiles;
+    batch = bh / p.kv_heads;
+    kvh = bh - batch * p.kv_heads;
+    row0 = tile * kRows;
+    if (p.causal) qt_lo = max(0, row0 - p.causal_offset) / kRows;
+    n = max(0, p.num_q_tiles - qt_lo);
+  }
+  const int total = DQ ? 2 * n : group * n;  // iterations
+
+  if (threadIdx.x == 0) {
+    mbar_init(fix_full, 1);
+    mbar_init(ld_full, 1);
+    mbar_init(s_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(it_done, 1);
+    *abort_word = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_do);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0 && total > 0) {
+      mbar_arrive_expect_tx(fix_full, 2 * kTileBytes);
+      if (DQ) {
+        load_tile_4d(smem + kOffQ, &tmap_q, fix_full, row0, head, batch);
+        load_tile_4d(smem + kOffDO, &tmap_do, fix_full, row0, head, batch);
+      } else {
+        load_tile_4d(smem + kOffK, &tmap_k, fix_full, row0, kvh, batch);
+        load_tile_4d(smem + kOffV, &tmap_v, fix_full, row0, kvh, batch);
+      }
+      for (int i = 0; i < total; ++i) {
+        // the previous iteration's MMAs have finished reading the streamed tiles
+        if (i > 0 && !mbar_wait(it_done, (i - 1) & 1, abort_word)) break;
+        if (DQ) {
+          const bool stats = i < n;
+          const int j = stats ? i : i - n;
+          mbar_arrive_expect_tx(ld_full, stats ? kTileBytes : 2 * kTileBytes);
+          load_tile_4d(smem + kOffK, &tmap_k, ld_full, j * kRows, kvh, batch);
+          if (!stats) load_tile_4d(smem + kOffV, &tmap_v, ld_full, j * kRows, kvh, batch);
+        } else {
+          const int g = i / n;
+          const int qt = qt_lo + (i - g * n);
+          mbar_arrive_expect_tx(ld_full, 2 * kTileBytes);
+          load_tile_4d(smem + kOffQ, &tmap_q, ld_full, qt * kRows, kvh * group + g, batch);
+          load_tile_4d(smem + kOffDO, &tmap_do, ld_full, qt * kRows, kvh * group + g, batch);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && total > 0) {
+      const uint32_t sq = smem_u32(smem + kOffQ), sdo = smem_u32(smem + kOffDO), sk = smem_u32(smem + kOffK),
+                     sv = smem_u32(smem + kOffV), sp = smem_u32(smem + kOffP), sds = smem_u32(smem + kOffDS);
+      bool ok = mbar_wait(fix_full, 0, abort_word);
+      for (int i = 0; i < total && ok; ++i) {
+        if (!mbar_wait(ld_full, i & 1, abort_word)) break;
+        tc_fence_after();
+        const bool stats = DQ && i < n;
+        mma_128x128x128<false, false>(tmem_base + kTmS, sq, sk, kIdKK, false);
+        if (!stats) mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
+        umma_commit(s_full);
+        if (!mbar_wait(pds_full, i & 1, abort_word)) break;
+        tc_fence_after();
+        if (!stats) {
+          const bool first = DQ ? i == n : i == 0;
+          if (DQ) {
+            mma_128x128x128<false, true>(tmem_base + kTmAcc0, sds, sk, kIdKM, !first);  // dQ += dS K
+          } else {
+            mma_128x128x128<true, true>(tmem_base + kTmAcc0, sp, sdo, kIdMM, !first);  // dV += P^T dO
+            mma_128x128x128<true, true>(tmem_base + kTmAcc1, sds, sq, kIdMM, !first);  // dK += dS^T Q
+          }
+        }
+        umma_commit(it_done);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- softmax algebra, one query row per thread; then the epilogue ----------------
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const float ninf = -INFINITY;
+    float m = ninf, l = 0.f, lse2 = INFINITY, dl = 0.f;
+    int q_g = row0 + r;  // DQ: fixed; DKV: set per iteration
+    int64_t stat_idx = 0;
+    if (DQ) {
+      stat_idx = (static_cast<int64_t>(batch) * p.q_heads + head) * p.seq_q + q_g;
+      if (q_g < p.seq_q) dl = __ldg(p.delta + stat_idx);
+    }
+    bool ok = true;
+    for (int i = 0; i < total; ++i) {
+      const bool stats = DQ && i < n;
+      int kv_base;
+      if (DQ) {
+        kv_base = (stats ? i : i - n) * kRows;
+      } else {
+        const int g = i / n;
+        const int qt = qt_lo + (i - g * n);
+        q_g = qt * kRows + r;
+        kv_base = row0;
+        stat_idx = (static_cast<int64_t>(batch) * p.q_heads + kvh * group + g) * p.seq_q + q_g;
+        lse2 = INFINITY;
+        dl = 0.f;
+        if (q_g < p.seq_q) {
+          lse2 = __ldg(p.lse2 + stat_idx);
+          dl = __ldg(p.delta + stat_idx);
+        }
+      }
+      // key j (global index) is visible to this row iff j <= col_hi
+      int col_hi = -1;
+      if (q_g < p.seq_q) {
+        col_hi = p.seq_kv - 1;
+        if (p.causal) col_hi = min(col_hi, q_g + p.causal_offset);
+      }
+      if (!mbar_wait(s_full, i & 1, abort_word)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t s[32];
+        tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
+        const int kv0 = kv_base + c4 * 32;
+        if (stats) {
+          tmem_wait_ld();
+          float cm = ninf;
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const float x = (kv0 + k <= col_hi) ? __uint_as_float(s[k]) * p.scale_log2 : ninf;
+            s[k] = __float_as_uint(x);
+            cm = fmaxf(cm, x);
+          }
+          const float m_new = fmaxf(m, cm);
+          if (m_new > ninf) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) acc += exp2f(__uint_as_float(s[k]) - m_new);
+            l = l * exp2f(m - m_new) + acc;
+            m = m_new;
+          }
+        } else {
+          uint32_t dp[32];
+          tmem_ld_32x32b_x32(lane_base + kTmDP + c4 * 32, dp);
+          tmem_wait_ld();
+          uint32_t pw[16], dsw[16];
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            float p0 = 0.f, p1 = 0.f;
+            if (kv0 + k <= col_hi) p0 = exp2f(__uint_as_float(s[k]) * p.scale_log2 - lse2);
+            if (kv0 + k + 1 <= col_hi) p1 = exp2f(__uint_as_float(s[k + 1]) * p.scale_log2 - lse2);
+            const float d0 = p0 * (__uint_as_float(dp[k]) - dl);
+            const float d1 = p1 * (__uint_as_float(dp[k + 1]) - dl);
+            pw[k >> 1] = pack2<T>(p0, p1);
+            dsw[k >> 1] = pack2<T>(d0, d1);
+          }
+          if (!DQ) store_row_chunk(smem + kOffP, r, c4 * 32, pw);
+          store_row_chunk(smem + kOffDS, r, c4 * 32, dsw);
+        }
+      }
+      if (DQ && stats && i == n - 1) {
+        lse2 = l > 0.f ? m + log2f(l) : INFINITY;
+        if (q_g < p.seq_q) p.lse2[stat_idx] = lse2;
+      }
+      tc_fence_before();
+      if (!stats) fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+    }
+    if (ok && total > 0) ok = mbar_wait(it_done, (total - 1) & 1, abort_word);
+    // every thread of the four warps must agree before the named barrier below
+    ok = bar_red_and(1, 128, ok);
+    if (ok) {
+      tc_fence_after();
+      // accumulators -> 16-bit tiles in the (now unused) P / dS buffers -> TMA stores
+      constexpr int kOuts = DQ ? 1 : 2;
+#pragma unroll
+      for (int o = 0; o < kOuts; ++o) {
+        uint8_t* stage = smem + (DQ || o == 1 ? kOffDS : kOffP);
+        const uint32_t acc = lane_base + (o == 0 ? kTmAcc0 : kTmAcc1);
+        const float f = (DQ || o == 1) ? p.scale : 1.f;  // dQ and dK carry the softmax scale
+#pragma unroll 1
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t v[32], w[16];
+          if (total > 0) {
+            tmem_ld_32x32b_x32(acc + c4 * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = 0u;  // no query sees these keys / no key is visible
+          }
+#pragma unroll
+          for (int k = 0; k < 32; k += 2)
+            w[k >> 1] = pack2<T>(__uint_as_float(v[k]) * f, __uint_as_float(v[k + 1]) * f);
+          store_row_chunk(stage, r, c4 * 32, w);
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (r == 0) {
+        if (DQ) {
+          tma_store_4d(&tmap_out0, smem + kOffDS, 0, row0, head, batch);
+          tma_store_4d(&tmap_out0, smem + kOffDS + kHalfBytes, 64, row0, head, batch);
+        } else {
+          tma_store_4d(&tmap_out0, smem + kOffP, 0, row0, kvh, batch);
+          tma_store_4d(&tmap_out0, smem + kOffP + kHalfBytes, 64, row0, kvh, batch);
+          tma_store_4d(&tmap_out1, smem + kOffDS, 0, row0, kvh, batch);
+          tma_store_4d(&tmap_out1, smem + kOffDS + kHalfBytes, 64, row0, kvh, batch);
+        }
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0 && threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusBwdTimeout);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, i] = sum_d dO[b, h, i, d] * O[b, h, i, d]; one warp per row, four columns per lane.
+template <typename T>
+__global__ void attn_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta,
+                                      int64_t rows, int q_heads, int seq_q, int64_t o_sb, int64_t o_sh, int64_t o_ss,
+                                      int64_t do_sb, int64_t do_sh, int64_t do_ss) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t bh = row / seq_q;
+  const int i = static_cast<int>(row - bh * seq_q);
+  const int64_t b = bh / q_heads, h = bh - b * q_heads;
+  const uint2 ov = *reinterpret_cast<const uint2*>(o + b * o_sb + h * o_sh + i * o_ss + lane * 4);
+  const uint2 dv = *reinterpret_cast<const uint2*>(d_o + b * do_sb + h * do_sh + i * do_ss + lane * 4);
+  const T* oe = reinterpret_cast<const T*>(&ov);
+  const T* de = reinterpret_cast<const T*>(&dv);
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) acc += static_cast<float>(oe[k]) * static_cast<float>(de[k]);
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[row] = acc;
+}
+
+struct BwdMaps {
+  CUtensorMap q, d_o, k, v, dq, dk, dv;
+};
+
+int encode_bshd(CUtensorMap* out, int dtype, const void* base, int seq, int heads, int batch, int64_t sb, int64_t sh,
+                int64_t ss) {
+  const uint32_t box[4] = {64, kRows, 1, 1};
+  uint64_t dims[4] = {kD, static_cast<uint64_t>(seq), static_cast<uint64_t>(heads), static_cast<uint64_t>(batch)};
+  uint64_t st[3] = {static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(sb) * 2};
+  return encode_tmap(out, dtype, 4, const_cast<void*>(base), dims, st, box);
+}
+
+template <typename T>
+int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const BwdParams& p, cudaStream_t stream) {
+  auto k_dq = attn_bwd_kernel<T, kModeDQ>;
+  auto k_dkv = attn_bwd_kernel<T, kModeDKV>;
+  static bool configured = false;
+  if (!configured) {
+    int rc = check_cuda(cudaFuncSetAttribute(k_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem),
+                        "cudaFuncSetAttribute(attention bwd dq smem)");
+    if (rc) return rc;
+    rc = check_cuda(cudaFuncSetAttribute(k_dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem),
+                    "cudaFuncSetAttribute(attention bwd dkv smem)");
+    if (rc) return rc;
+    configured = true;
+  }
+  const int64_t rows = static_cast<int64_t>(a.batch) * a.q_heads * a.seq_q;
+  const int warps_per_block = 8;
+  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block),
+                             warps_per_block * 32, 0, stream>>>(
+      static_cast<const T*>(a.o), static_cast<const T*>(a.d_o), p.delta, rows, a.q_heads, a.seq_q, a.o_stride_b,
+      a.o_stride_h, a.o_stride_s, a.do_stride_b, a.do_stride_h, a.do_stride_s);
+  int rc = check_cuda(cudaGetLastError(), "attn_bwd_delta_kernel launch");
+  if (rc) return rc;
+  const int grid_dq = a.batch * a.q_heads * p.num_q_tiles;
+  k_dq<<<grid_dq, kBwdThreads, kBwdSmem, stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dq, tm.dq, p);
+  rc = check_cuda(cudaGetLastError(), "attn_bwd_kernel (dQ) launch");
+  if (rc) return rc;
+  const int grid_dkv = a.batch * a.kv_heads * p.num_kv_tiles;
+  k_dkv<<<grid_dkv, kBwdThreads, kBwdSmem, stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dv, tm.dk, p);
+  return check_cuda(cudaGetLastError(), "attn_bwd_kernel (dK, dV) launch");
+}
+
+}  // namespace
+
+uint64_t attention_bwd_workspace_bytes(const b200k_attention_bwd_args& a) {
+  if (a.batch <= 0 || a.q_heads <= 0 || a.seq_q <= 0) return 0;
+  return 2ull * sizeof(float) * static_cast<uint64_t>(a.batch) * a.q_heads * a.seq_q;
+}
+
+int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream) {
+  if (!a.q || !a.k || !a.v || !a.o || !a.d_o || !a.d_q || !a.d_k || !a.d_v)
+    return set_error(B200K_ERR_NULL, "attention_bwd: q, k, v, o, d_o, d_q, d_k, d_v must be non-NULL");
+  if (a.batch <= 0 || a.q_heads <= 0 || a.kv_heads <= 0 || a.seq_q <= 0 || a.seq_kv <= 0)
+    return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: all dimensions must be positive");
+  if (a.head_dim != kD) return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: head_dim must be 128");
+  if (a.q_heads % a.kv_heads != 0)
+    return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: q_heads must be a multiple of kv_heads");
+  if (a.dtype != B200K_F16 && a.dtype != B200K_BF16)
+    return set_error(B200K_ERR_BAD_DTYPE, "attention_bwd: dtype must be F16 or BF16");
+  const int64_t strides[] = {a.q_stride_b,  a.q_stride_h,  a.q_stride_s,  a.k_stride_b,  a.k_stride_h,  a.k_stride_s,
+                             a.v_stride_b,  a.v_stride_h,  a.v_stride_s,  a.o_stride_b,  a.o_stride_h,  a.o_stride_s,
+                             a.do_stride_b, a.do_stride_h, a.do_stride_s, a.dq_stride_b, a.dq_stride_h, a.dq_stride_s,
+                             a.dk_stride_b, a.dk_stride_h, a.dk_stride_s, a.dv_stride_b, a.dv_stride_h, a.dv_stride_s};
+  for (int64_t s : strides)
+    if (s <= 0 || s % 8 != 0)
+      return set_error(B200K_ERR_BAD_ALIGN, "attention_bwd: every stride must be a positive multiple of 8 elements");
+  const void* ptrs[] = {a.q, a.k, a.v, a.o, a.d_o, a.d_q, a.d_k, a.d_v};
+  for (const void* ptr : ptrs)
+    if (reinterpret_cast<uintptr_t>(ptr) & 15)
+      return set_error(B200K_ERR_BAD_ALIGN, "attention_bwd: every tensor must be 16-byte aligned");
+  if (!(a.scale > 0.f)) return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: scale must be positive");
+  const uint64_t need = attention_bwd_workspace_bytes(a);
+  if (!a.workspace || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 15))
+    return set_error(B200K_ERR_WORKSPACE, "attention_bwd: workspace must be 16-byte aligned and hold %llu bytes",
+                     static_cast<unsigned long long>(need));
+  int rc = ensure_sm100();
+  if (rc) return rc;
+
+  BwdMaps tm;
+  rc = encode_bshd(&tm.q, a.dtype, a.q, a.seq_q, a.q_heads, a.batch, a.q_stride_b, a.q_stride_h, a.q_stride_s);
+  if (!rc) rc = encode_bshd(&tm.d_o, a.dtype, a.d_o, a.seq_q, a.q_heads, a.batch, a.do_stride_b, a.do_stride_h, a.do_stride_s);
+  if (!rc) rc = encode_bshd(&tm.k, a.dtype, a.k, a.seq_kv, a.kv_heads, a.batch, a.k_stride_b, a.k_stride_h, a.k_stride_s);
+  if (!rc) rc = encode_bshd(&tm.v, a.dtype, a.v, a.seq_kv, a.kv_heads, a.batch, a.v_stride_b, a.v_stride_h, a.v_stride_s);
+  if (!rc) rc = encode_bshd(&tm.dq, a.dtype, a.d_q, a.seq_q, a.q_heads, a.batch, a.dq_stride_b, a.dq_stride_h, a.dq_stride_s);
+  if (!rc) rc = encode_bshd(&tm.dk, a.dtype, a.d_k, a.seq_kv, a.kv_heads, a.batch, a.dk_stride_b, a.dk_stride_h, a.dk_stride_s);
+  if (!rc) rc = encode_bshd(&tm.dv, a.dtype, a.d_v, a.seq_kv, a.kv_heads, a.batch, a.dv_stride_b, a.dv_stride_h, a.dv_stride_s);
+  if (rc) return rc;
+
+  BwdParams p;
+  p.batch = a.batch;
+  p.q_heads = a.q_heads;
+  p.kv_heads = a.kv_heads;
+  p.seq_q = a.seq_q;
+  p.seq_kv = a.seq_kv;
+  p.causal = a.causal ? 1 : 0;
+  p.causal_offset = a.seq_kv - a.seq_q;
+  p.num_q_tiles = (a.seq_q + kRows - 1) / kRows;
+  p.num_kv_tiles = (a.seq_kv + kRows - 1) / kRows;
+  if (static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles > INT32_MAX ||
+      static_cast<int64_t>(a.batch) * a.kv_heads * p.num_kv_tiles > INT32_MAX)
+    return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: too many tiles");
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * kLog2eBwd;
+  p.lse2 = static_cast<float*>(a.workspace);
+  p.delta = p.lse2 + static_cast<int64_t>(a.batch) * a.q_heads * a.seq_q;
+  p.status = a.status;
+  if (a.dtype == B200K_F16) return launch_bwd_typed<__half>(a, tm, p, stream);
+  return launch_bwd_typed<__nv_bfloat16>(a, tm, p, stream);
+}
+
+}  // namespace b200k

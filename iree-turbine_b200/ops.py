@@ -31,6 +31,8 @@ __all__ = [
     "linear",
     "linear_act",
     "attention",
+    "attention_bwd",
+    "sdpa",
     "decode_attention",
     "paged_decode_attention",
     "quantize_e4m3",
@@ -383,6 +385,86 @@ class attention(CustomOp):
         args.status = _status_ptr(q.device)
         L.check(L.lib().b200k_attention_fwd(C.byref(args), _stream(q)))
         return o
+
+
+def _attention_bwd_checks(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor) -> None:
+    for t in (q, k, v, o, d_o):
+        torch._check(t.dim() == 4 and t.size(3) == 128, lambda: "attention_bwd: tensors must be [B,H,S,128]")
+        torch._check(t.dtype == q.dtype, lambda: "attention_bwd: all tensors must share a dtype")
+    torch._check(q.dtype in _HALF_TYPES, lambda: f"attention_bwd: dtype must be float16 or bfloat16, got {q.dtype}")
+    torch._check(k.shape == v.shape, lambda: "attention_bwd: k and v must have the same shape")
+    torch._check(o.shape == q.shape and d_o.shape == q.shape, lambda: "attention_bwd: o and d_o must have q's shape")
+    torch._check(q.size(0) == k.size(0), lambda: "attention_bwd: batch mismatch")
+    torch._check(k.size(1) > 0 and q.size(1) % k.size(1) == 0,
+                 lambda: "attention_bwd: query heads must be a multiple of kv heads")
+
+
+@CustomOp.register(library=LIBRARY)
+class attention_bwd(CustomOp):
+    """Gradients of ``attention``: (q, k, v, o, d_o) -> (d_q, d_k, d_v).  d_k / d_v are summed over
+    the query heads of a group.  Only the forward OUTPUT is needed; row statistics are recomputed."""
+
+    signature = ("attention_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, float scale, bool is_causal)"
+                 " -> (Tensor, Tensor, Tensor)")
+
+    def select(self, sel: KernelSelection):
+        q, k, v, o, d_o = (sel.arg_tensor(i) for i in range(5))
+        sel.attr_float(5)
+        sel.attr_bool(6)
+        _attention_bwd_checks(q.t, k.t, v.t, o.t, d_o.t)
+        sel.return_new_tensor(list(q.t.shape), q.t.dtype)
+        sel.return_new_tensor(list(k.t.shape), q.t.dtype)
+        sel.return_new_tensor(list(k.t.shape), q.t.dtype)
+
+    def eager_execute(self, q, k, v, o, d_o, scale, is_causal):
+        _attention_bwd_checks(q, k, v, o, d_o)
+        q, k, v, o, d_o = (_bhsd(t) for t in (q, k, v, o, d_o))
+        d_q, d_k, d_v = torch.empty_like(q, memory_format=torch.contiguous_format), \
+            torch.empty_like(k, memory_format=torch.contiguous_format), \
+            torch.empty_like(v, memory_format=torch.contiguous_format)
+        a = L.AttentionBwdArgs()
+        for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", d_o), ("dq", d_q), ("dk", d_k), ("dv", d_v)):
+            setattr(a, {"do": "d_o", "dq": "d_q", "dk": "d_k", "dv": "d_v"}.get(name, name), t.data_ptr())
+            for d, i in (("b", 0), ("h", 1), ("s", 2)):
+                setattr(a, f"{name}_stride_{d}", t.stride(i))
+        a.batch, a.q_heads, a.seq_q, a.head_dim = q.size(0), q.size(1), q.size(2), 128
+        a.kv_heads, a.seq_kv = k.size(1), k.size(2)
+        a.dtype = L.DTYPE_CODES[q.dtype]
+        a.causal = 1 if is_causal else 0
+        a.scale = float(scale)
+        a.status = _status_ptr(q.device)
+        lib = L.lib()
+        need = lib.b200k_attention_bwd_workspace_bytes(C.byref(a))
+        ws = torch.empty(max(int(need), 16), dtype=torch.uint8, device=q.device)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        L.check(lib.b200k_attention_bwd(C.byref(a), _stream(q)))
+        return d_q, d_k, d_v
+
+
+class _AttentionFunction(torch.autograd.Function):
+    """``attention`` with its gradient on the backward kernels (wrapped the way the reference wraps
+    its own forward / backward ops, kernel/boo/ops/conv.py:313-372)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, is_causal):
+        o = torch.ops.b200k.attention(q, k, v, scale, is_causal)
+        ctx.save_for_backward(q, k, v, o)
+        ctx.scale, ctx.is_causal = scale, is_causal
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o = ctx.saved_tensors
+        d_q, d_k, d_v = torch.ops.b200k.attention_bwd(q, k, v, o, d_o, ctx.scale, ctx.is_causal)
+        return d_q, d_k, d_v, None, None
+
+
+def sdpa(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, is_causal: bool = False) -> Tensor:
+    """Differentiable scaled-dot-product attention on the b200k kernels ([B, H, S, 128] f16 / bf16
+    CUDA tensors; grouped-query heads; causal mask aligned to the bottom-right corner)."""
+    if scale is None:
+        scale = 1.0 / (q.size(-1) ** 0.5)
+    return _AttentionFunction.apply(q, k, v, float(scale), bool(is_causal))
 
 
 # ---------------------------------------------------------------------------------------------

@@ -44,6 +44,9 @@ def test_struct_layouts_match_the_header():
                                                               "block_table_stride", "q_stride_b", "o_stride_s",
                                                               "kv_page_stride", "kv_head_stride", "dtype", "scale",
                                                               "status"]),
+        "b200k_attention_bwd_args": (L.AttentionBwdArgs, ["q", "d_o", "d_v", "workspace", "workspace_bytes", "batch",
+                                                          "head_dim", "q_stride_b", "do_stride_h", "dv_stride_s",
+                                                          "dtype", "scale", "status"]),
         "b200k_gemm_allgather_args": (L.GemmAllGatherArgs, ["gemm", "peer_c", "num_peers", "peer_ldc", "col_offset"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
@@ -94,6 +97,23 @@ def test_argument_errors_are_status_codes(kernel_lib):
     a.head_dim = 64
     assert lib.b200k_attention_fwd(C.byref(a), None) == L.ERR_BAD_SHAPE
     assert b"head_dim" in lib.b200k_last_error()
+
+    w = L.AttentionBwdArgs()
+    assert lib.b200k_attention_bwd(None, None) == L.ERR_NULL
+    assert lib.b200k_attention_bwd(C.byref(w), None) == L.ERR_NULL
+    w.q = w.k = w.v = w.o = w.d_o = w.d_q = w.d_k = w.d_v = 0x1000
+    w.batch, w.q_heads, w.kv_heads, w.seq_q, w.seq_kv, w.head_dim = 2, 6, 4, 100, 128, 128
+    assert lib.b200k_attention_bwd(C.byref(w), None) == L.ERR_BAD_SHAPE  # 6 % 4 != 0
+    w.q_heads = 8
+    w.dtype = L.F32
+    assert lib.b200k_attention_bwd(C.byref(w), None) == L.ERR_BAD_DTYPE
+    w.dtype = L.BF16
+    assert lib.b200k_attention_bwd(C.byref(w), None) == L.ERR_BAD_ALIGN  # strides are still zero
+    for t in ("q", "k", "v", "o", "do", "dq", "dk", "dv"):
+        setattr(w, f"{t}_stride_s", 128), setattr(w, f"{t}_stride_h", 128 * 128), setattr(w, f"{t}_stride_b", 8 * 128 * 128)
+    w.scale = 0.1
+    assert lib.b200k_attention_bwd_workspace_bytes(C.byref(w)) == 2 * 4 * 2 * 8 * 100
+    assert lib.b200k_attention_bwd(C.byref(w), None) == L.ERR_WORKSPACE
 
     d = L.DecodeArgs()
     assert lib.b200k_decode_attention(C.byref(d), None) == L.ERR_NULL
