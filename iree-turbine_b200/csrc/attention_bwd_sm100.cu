@@ -25,10 +25,11 @@
 //   dP = dO V^T   A = dO K-major    B = V  K-major       dK += dS^T Q   A = dS  MN-major  B = Q  MN-major
 //                                                        dQ += dS K     A = dS  K-major   B = K  MN-major
 //
-// Roles (6 warps): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 2..5 one
-// query row (lane of tensor memory) per thread for the softmax algebra, then the epilogue.
-// The stages of one iteration run one after the other (load -> S, dP -> P, dS -> gradient MMAs):
-// a first, unpipelined version.  Every wait is bounded.
+// Roles (10 warps): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 2..9 the
+// softmax algebra (two threads per query row = lane of tensor memory, 64 columns each), then the
+// epilogue.  Within an iteration the stages run one after the other (S, dP -> P, dS -> gradient
+// MMAs); the dQ kernel loads the next K / V tiles meanwhile (two buffers), the dK/dV kernel has
+// no shared memory left for that.  Every wait is bounded.
 #include <type_traits>
 
 #include "common.cuh"
@@ -39,17 +40,21 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kRows = 128;
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;      // TMA warp, MMA warp, eight softmax / epilogue warps
+constexpr int kSoftmaxThreads = 256;  // two threads per query row, 64 columns each
 constexpr int kTileBytes = kRows * kD * 2;  // 32 KB
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column block
 constexpr int kModeDQ = 0, kModeDKV = 1;
 
+// Shared-memory tiles.  dK/dV kernel: Q, dO (streamed), K, V (held), P, dS.  dQ kernel: Q, dO (held),
+// two K and two V buffers (streamed, the next tiles load while the current ones are used), dS.
 constexpr int kOffQ = 0, kOffDO = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 3 * kTileBytes;
 constexpr int kOffP = 4 * kTileBytes, kOffDS = 5 * kTileBytes;
-constexpr int kOffBars = 6 * kTileBytes;
-// fix_full, ld_full, s_full, pds_full, it_done
-constexpr int kNumBwdBars = 5;
-constexpr int kBwdSmem = kOffBars + kNumBwdBars * 8 + 16 + 1024;
+constexpr int kOffK1 = kOffP, kOffV1 = 6 * kTileBytes;  // dQ kernel only (it has no P tile)
+constexpr int kNumTiles[2] = {7, 6};                    // by mode
+// fix_full, ld_full[2], s_full, pds_full, it_done[2]
+constexpr int kNumBwdBars = 7;
+constexpr int bwd_smem_bytes(int mode) { return kNumTiles[mode] * kTileBytes + kNumBwdBars * 8 + 16 + 1024; }
 constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384;
 constexpr float kLog2eBwd = 1.4426950408889634f;
 constexpr int kStatusBwdTimeout = 64;
@@ -125,12 +130,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  constexpr int kBufs = DQ ? 2 : 1;  // buffers for the streamed tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kNumTiles[MODE] * kTileBytes);
   uint64_t* fix_full = bars;      // the tiles held for the whole item have landed
-  uint64_t* ld_full = bars + 1;   // the streamed tiles of this iteration have landed
-  uint64_t* s_full = bars + 2;    // S (and dP) are in tensor memory
-  uint64_t* pds_full = bars + 3;  // 128 rows of P / dS written (and S / dP read)
-  uint64_t* it_done = bars + 4;   // the iteration's last MMAs have completed
+  uint64_t* ld_full = bars + 1;   // [buffer] the streamed tiles of an iteration have landed
+  uint64_t* s_full = bars + 3;    // S (and dP) are in tensor memory
+  uint64_t* pds_full = bars + 4;  // all rows of P / dS written (and S / dP read)
+  uint64_t* it_done = bars + 5;   // [buffer] the last MMAs of an iteration that used it have completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBwdBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -169,9 +175,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   if (threadIdx.x == 0) {
     mbar_init(fix_full, 1);
     mbar_init(ld_full, 1);
+    mbar_init(ld_full + 1, 1);
     mbar_init(s_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, kSoftmaxThreads);
     mbar_init(it_done, 1);
+    mbar_init(it_done + 1, 1);
     *abort_word = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -201,20 +209,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         load_tile_4d(smem + kOffV, &tmap_v, fix_full, row0, kvh, batch);
       }
       for (int i = 0; i < total; ++i) {
-        // the previous iteration's MMAs have finished reading the streamed tiles
-        if (i > 0 && !mbar_wait(it_done, (i - 1) & 1, abort_word)) break;
+        const int buf = i % kBufs;
+        // the MMAs of the iteration that last used this buffer have finished reading it
+        if (i >= kBufs && !mbar_wait(it_done + buf, ((i - kBufs) / kBufs) & 1, abort_word)) break;
+        uint64_t* full = ld_full + buf;
         if (DQ) {
           const bool stats = i < n;
           const int j = stats ? i : i - n;
-          mbar_arrive_expect_tx(ld_full, stats ? kTileBytes : 2 * kTileBytes);
-          load_tile_4d(smem + kOffK, &tmap_k, ld_full, j * kRows, kvh, batch);
-          if (!stats) load_tile_4d(smem + kOffV, &tmap_v, ld_full, j * kRows, kvh, batch);
+          mbar_arrive_expect_tx(full, stats ? kTileBytes : 2 * kTileBytes);
+          load_tile_4d(smem + (buf ? kOffK1 : kOffK), &tmap_k, full, j * kRows, kvh, batch);
+          if (!stats) load_tile_4d(smem + (buf ? kOffV1 : kOffV), &tmap_v, full, j * kRows, kvh, batch);
         } else {
           const int g = i / n;
           const int qt = qt_lo + (i - g * n);
-          mbar_arrive_expect_tx(ld_full, 2 * kTileBytes);
-          load_tile_4d(smem + kOffQ, &tmap_q, ld_full, qt * kRows, kvh * group + g, batch);
-          load_tile_4d(smem + kOffDO, &tmap_do, ld_full, qt * kRows, kvh * group + g, batch);
+          mbar_arrive_expect_tx(full, 2 * kTileBytes);
+          load_tile_4d(smem + kOffQ, &tmap_q, full, qt * kRows, kvh * group + g, batch);
+          load_tile_4d(smem + kOffDO, &tmap_do, full, qt * kRows, kvh * group + g, batch);
         }
       }
     }
@@ -222,13 +232,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && total > 0) {
-      const uint32_t sq = smem_u32(smem + kOffQ), sdo = smem_u32(smem + kOffDO), sk = smem_u32(smem + kOffK),
-                     sv = smem_u32(smem + kOffV), sp = smem_u32(smem + kOffP), sds = smem_u32(smem + kOffDS);
+      const uint32_t sq = smem_u32(smem + kOffQ), sdo = smem_u32(smem + kOffDO), sp = smem_u32(smem + kOffP),
+                     sds = smem_u32(smem + kOffDS);
       bool ok = mbar_wait(fix_full, 0, abort_word);
       for (int i = 0; i < total && ok; ++i) {
-        if (!mbar_wait(ld_full, i & 1, abort_word)) break;
+        const int buf = i % kBufs;
+        if (!mbar_wait(ld_full + buf, (i / kBufs) & 1, abort_word)) break;
         tc_fence_after();
         const bool stats = DQ && i < n;
+        const uint32_t sk = smem_u32(smem + (buf ? kOffK1 : kOffK)), sv = smem_u32(smem + (buf ? kOffV1 : kOffV));
         mma_128x128x128<false, false>(tmem_base + kTmS, sq, sk, kIdKK, false);
         if (!stats) mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
         umma_commit(s_full);
@@ -243,14 +255,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             mma_128x128x128<true, true>(tmem_base + kTmAcc1, sds, sq, kIdMM, !first);  // dK += dS^T Q
           }
         }
-        umma_commit(it_done);
+        umma_commit(it_done + buf);
       }
     }
     __syncwarp();
   } else {
-    // ---------------- softmax algebra, one query row per thread; then the epilogue ----------------
-    const int r = (warp & 3) * 32 + lane;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    // ---------------- softmax algebra, then the epilogue: two threads per query row ----------------
+    // Warp w may touch tensor-memory lanes 32 (w % 4) ..: warps 2..5 take columns 0..63 of their
+    // rows, warps 6..9 columns 64..127.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float ninf = -INFINITY;
     float m = ninf, l = 0.f, lse2 = INFINITY, dl = 0.f;
     int q_g = row0 + r;  // DQ: fixed; DKV: set per iteration
@@ -259,6 +275,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       stat_idx = (static_cast<int64_t>(batch) * p.q_heads + head) * p.seq_q + q_g;
       if (q_g < p.seq_q) dl = __ldg(p.delta + stat_idx);
     }
+    // After a wait has given up the loop keeps its shape (arrivals and named barriers) but skips the work.
     bool ok = true;
     for (int i = 0; i < total; ++i) {
       const bool stats = DQ && i < n;
@@ -284,63 +301,73 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         col_hi = p.seq_kv - 1;
         if (p.causal) col_hi = min(col_hi, q_g + p.causal_offset);
       }
-      if (!mbar_wait(s_full, i & 1, abort_word)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
+      if (ok && !mbar_wait(s_full, i & 1, abort_word)) ok = false;
+      if (ok) {
+        tc_fence_after();
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t s[32];
-        tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
-        const int kv0 = kv_base + c4 * 32;
-        if (stats) {
-          tmem_wait_ld();
-          float cm = ninf;
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c4 = half * 2 + cc;
+          uint32_t s[32];
+          tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
+          const int kv0 = kv_base + c4 * 32;
+          if (stats) {
+            tmem_wait_ld();
+            float cm = ninf;
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const float x = (kv0 + k <= col_hi) ? __uint_as_float(s[k]) * p.scale_log2 : ninf;
-            s[k] = __float_as_uint(x);
-            cm = fmaxf(cm, x);
-          }
-          const float m_new = fmaxf(m, cm);
-          if (m_new > ninf) {
-            float acc = 0.f;
+            for (int k = 0; k < 32; ++k) {
+              const float x = (kv0 + k <= col_hi) ? __uint_as_float(s[k]) * p.scale_log2 : ninf;
+              s[k] = __float_as_uint(x);
+              cm = fmaxf(cm, x);
+            }
+            const float m_new = fmaxf(m, cm);
+            if (m_new > ninf) {
+              float acc = 0.f;
 #pragma unroll
-            for (int k = 0; k < 32; ++k) acc += exp2f(__uint_as_float(s[k]) - m_new);
-            l = l * exp2f(m - m_new) + acc;
-            m = m_new;
-          }
-        } else {
-          uint32_t dp[32];
-          tmem_ld_32x32b_x32(lane_base + kTmDP + c4 * 32, dp);
-          tmem_wait_ld();
-          uint32_t pw[16], dsw[16];
+              for (int k = 0; k < 32; ++k) acc += exp2f(__uint_as_float(s[k]) - m_new);
+              l = l * exp2f(m - m_new) + acc;
+              m = m_new;
+            }
+          } else {
+            uint32_t dp[32];
+            tmem_ld_32x32b_x32(lane_base + kTmDP + c4 * 32, dp);
+            tmem_wait_ld();
+            uint32_t pw[16], dsw[16];
 #pragma unroll
-          for (int k = 0; k < 32; k += 2) {
-            float p0 = 0.f, p1 = 0.f;
-            if (kv0 + k <= col_hi) p0 = exp2f(__uint_as_float(s[k]) * p.scale_log2 - lse2);
-            if (kv0 + k + 1 <= col_hi) p1 = exp2f(__uint_as_float(s[k + 1]) * p.scale_log2 - lse2);
-            const float d0 = p0 * (__uint_as_float(dp[k]) - dl);
-            const float d1 = p1 * (__uint_as_float(dp[k + 1]) - dl);
-            pw[k >> 1] = pack2<T>(p0, p1);
-            dsw[k >> 1] = pack2<T>(d0, d1);
+            for (int k = 0; k < 32; k += 2) {
+              float p0 = 0.f, p1 = 0.f;
+              if (kv0 + k <= col_hi) p0 = exp2f(__uint_as_float(s[k]) * p.scale_log2 - lse2);
+              if (kv0 + k + 1 <= col_hi) p1 = exp2f(__uint_as_float(s[k + 1]) * p.scale_log2 - lse2);
+              const float d0 = p0 * (__uint_as_float(dp[k]) - dl);
+              const float d1 = p1 * (__uint_as_float(dp[k + 1]) - dl);
+              pw[k >> 1] = pack2<T>(p0, p1);
+              dsw[k >> 1] = pack2<T>(d0, d1);
+            }
+            if (!DQ) store_row_chunk(smem + kOffP, r, c4 * 32, pw);
+            store_row_chunk(smem + kOffDS, r, c4 * 32, dsw);
           }
-          if (!DQ) store_row_chunk(smem + kOffP, r, c4 * 32, pw);
-          store_row_chunk(smem + kOffDS, r, c4 * 32, dsw);
         }
       }
       if (DQ && stats && i == n - 1) {
-        lse2 = l > 0.f ? m + log2f(l) : INFINITY;
-        if (q_g < p.seq_q) p.lse2[stat_idx] = lse2;
+        // The two threads of a row combine their (max, sum) over the dS tile, which nothing uses
+        // before the gradient sweep; both evaluate the same expression, so they agree bitwise.
+        float2* xchg = reinterpret_cast<float2*>(smem + kOffDS);
+        xchg[half * kRows + r] = make_float2(m, l);
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        const float2 a0 = xchg[r], a1 = xchg[kRows + r];
+        asm volatile("bar.sync 3, 256;" ::: "memory");  // all have read before the tile is written again
+        const float mt = fmaxf(a0.x, a1.x);
+        const float lt = mt > ninf ? a0.y * exp2f(a0.x - mt) + a1.y * exp2f(a1.x - mt) : 0.f;
+        lse2 = lt > 0.f ? mt + log2f(lt) : INFINITY;
+        if (half == 0 && q_g < p.seq_q) p.lse2[stat_idx] = lse2;
       }
       tc_fence_before();
       if (!stats) fence_proxy_async_smem();
       mbar_arrive(pds_full);
     }
-    if (ok && total > 0) ok = mbar_wait(it_done, (total - 1) & 1, abort_word);
-    // every thread of the four warps must agree before the named barrier below
-    ok = bar_red_and(1, 128, ok);
+    if (ok && total > 0)
+      ok = mbar_wait(it_done + (total - 1) % kBufs, ((total - 1) / kBufs) & 1, abort_word);
+    // every thread of the eight warps must agree before the named barrier below
+    ok = bar_red_and(1, kSoftmaxThreads, ok);
     if (ok) {
       tc_fence_after();
       // accumulators -> 16-bit tiles in the (now unused) P / dS buffers -> TMA stores
@@ -351,7 +378,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         const uint32_t acc = lane_base + (o == 0 ? kTmAcc0 : kTmAcc1);
         const float f = (DQ || o == 1) ? p.scale : 1.f;  // dQ and dK carry the softmax scale
 #pragma unroll 1
-        for (int c4 = 0; c4 < 4; ++c4) {
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c4 = half * 2 + cc;
           uint32_t v[32], w[16];
           if (total > 0) {
             tmem_ld_32x32b_x32(acc + c4 * 32, v);
@@ -367,8 +395,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (r == 0) {
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (r == 0 && half == 0) {
         if (DQ) {
           tma_store_4d(&tmap_out0, smem + kOffDS, 0, row0, head, batch);
           tma_store_4d(&tmap_out0, smem + kOffDS + kHalfBytes, 64, row0, head, batch);
@@ -435,10 +463,10 @@ int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const
   auto k_dkv = attn_bwd_kernel<T, kModeDKV>;
   static bool configured = false;
   if (!configured) {
-    int rc = check_cuda(cudaFuncSetAttribute(k_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem),
+    int rc = check_cuda(cudaFuncSetAttribute(k_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem_bytes(kModeDQ)),
                         "cudaFuncSetAttribute(attention bwd dq smem)");
     if (rc) return rc;
-    rc = check_cuda(cudaFuncSetAttribute(k_dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem),
+    rc = check_cuda(cudaFuncSetAttribute(k_dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem_bytes(kModeDKV)),
                     "cudaFuncSetAttribute(attention bwd dkv smem)");
     if (rc) return rc;
     configured = true;
@@ -452,11 +480,11 @@ int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const
   int rc = check_cuda(cudaGetLastError(), "attn_bwd_delta_kernel launch");
   if (rc) return rc;
   const int grid_dq = a.batch * a.q_heads * p.num_q_tiles;
-  k_dq<<<grid_dq, kBwdThreads, kBwdSmem, stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dq, tm.dq, p);
+  k_dq<<<grid_dq, kBwdThreads, bwd_smem_bytes(kModeDQ), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dq, tm.dq, p);
   rc = check_cuda(cudaGetLastError(), "attn_bwd_kernel (dQ) launch");
   if (rc) return rc;
   const int grid_dkv = a.batch * a.kv_heads * p.num_kv_tiles;
-  k_dkv<<<grid_dkv, kBwdThreads, kBwdSmem, stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dv, tm.dk, p);
+  k_dkv<<<grid_dkv, kBwdThreads, bwd_smem_bytes(kModeDKV), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dv, tm.dk, p);
   return check_cuda(cudaGetLastError(), "attn_bwd_kernel (dK, dV) launch");
 }
 
