@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 Default workload: non-causal attention f16, batch 8, 32 heads, Sq = Skv = 1024, head dim 128.
-Other workloads (same JSON line): gemm_f16, attn_causal, paged_decode, gemm_fp8.
+Other workloads (same JSON line): gemm_f16, attn_causal, attn_bwd_causal, paged_decode, gemm_fp8.
 
 A step is one pass of the kernel over one batch of synthetic inputs.  Each step is timed with
 CUDA events on the launching stream; between steps either the inputs are larger than L2 or L2 is
@@ -138,6 +138,64 @@ class AttentionWL(Workload):
         f = 4.0 * bs * hs * self.s * self.s * 128
         f = f / 2 if self.causal else f
         return f, best, f"oracle.attention on batch {bs} x {hs} heads of the same shape, best of 2"
+
+
+class AttentionBwdWL(AttentionWL):
+    """Attention backward (dQ, dK, dV from q, k, v, o, dO).  Work is counted as five 128-deep
+    products per score element (2.5 x the forward count), the usual convention; the kernels
+    execute eight (row statistics and the scores are recomputed in both passes)."""
+
+    launches_per_step = 3  # delta, dQ (+ statistics), dK/dV
+
+    def __init__(self, name, batch, heads, seq, dtype, causal, std):
+        super().__init__(name, batch, heads, seq, dtype, causal, std)
+        kind = "causal" if causal else "non-causal"
+        self.metric = f"attention bwd TFLOP/s ({kind} {self.dtype} B{batch} H{heads} S{seq} D128)"
+
+    def _make_do(self, dev, seed=11):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        return torch.randn(self.b, self.h, self.s, 128, generator=g, device=dev).to(self.tdtype)
+
+    def setup(self, dev):
+        self.q, self.k, self.v = self._make(dev)
+        self.d_o = self._make_do(dev)
+        self.o = torch.ops.b200k.attention(self.q, self.k, self.v, SCALE, self.causal)
+
+    def step(self):
+        self.grads = torch.ops.b200k.attention_bwd(self.q, self.k, self.v, self.o, self.d_o, SCALE, self.causal)
+
+    def units_per_step(self):
+        return 2.5 * super().units_per_step()
+
+    def setup_e2e(self, dev):
+        self.host_in = [t.cpu().pin_memory() for t in (self.q, self.k, self.v, self.o, self.d_o)]
+        self.host_out = [torch.empty_like(self.host_in[0]).pin_memory() for _ in range(3)]
+
+    def step_e2e(self):
+        dev_in = [t.to(self.q.device, non_blocking=True) for t in self.host_in]
+        grads = torch.ops.b200k.attention_bwd(*dev_in, SCALE, self.causal)
+        for h, g in zip(self.host_out, grads):
+            h.copy_(g, non_blocking=True)
+
+    def e2e_bytes(self):
+        n = self.b * self.h * self.s * 128 * 2
+        return 5 * n, 3 * n
+
+    def cpu_sample(self):
+        from oracle import oracle
+
+        bs, hs = 1, min(self.h, 4 if self.s > 2048 else 16)
+        q, k, v = oracle.make_attention_inputs(bs, hs, hs, self.s, self.s, 128, self.tdtype, seed=10, std=self.std)
+        d_o = torch.randn(q.shape, generator=torch.Generator().manual_seed(11)).to(self.tdtype)
+        best = None
+        for _ in range(2):
+            t0 = time.perf_counter()
+            oracle.attention_bwd(q, k, v, d_o, SCALE, self.causal)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        f = 2.5 * 4.0 * bs * hs * self.s * self.s * 128
+        f = f / 2 if self.causal else f
+        return f, best, f"oracle.attention_bwd on batch {bs} x {hs} heads of the same shape, best of 2"
 
 
 class GemmWL(Workload):
@@ -317,6 +375,7 @@ class PagedDecodeWL(Workload):
 WORKLOADS = {
     "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 249.1e6),
     "attn_causal": lambda: AttentionWL("attn_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
+    "attn_bwd_causal": lambda: AttentionBwdWL("attn_bwd_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
     "gemm_f16": lambda: GemmWL("gemm_f16", 2048, False),
     "gemm_fp8": lambda: GemmWL("gemm_fp8", 8192, True),
     "paged_decode": lambda: PagedDecodeWL("paged_decode"),
