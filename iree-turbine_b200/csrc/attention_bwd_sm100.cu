@@ -27,9 +27,9 @@
 //
 // Roles (10 warps): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 2..9 the
 // softmax algebra (two threads per query row = lane of tensor memory, 64 columns each), then the
-// epilogue.  Within an iteration the stages run one after the other (S, dP -> P, dS -> gradient
-// MMAs); the dQ kernel loads the next K / V tiles meanwhile (two buffers), the dK/dV kernel has
-// no shared memory left for that.  Every wait is bounded.
+// epilogue.  Within an iteration: S -> (P while dP is computed) -> (dS while dV accumulates) ->
+// dK or dQ; the dQ kernel loads the next K / V tiles meanwhile (two buffers), the dK/dV kernel
+// has no shared memory left for that.  Every wait is bounded.
 #include <type_traits>
 
 #include "common.cuh"
@@ -52,8 +52,8 @@ constexpr int kOffQ = 0, kOffDO = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 3 
 constexpr int kOffP = 4 * kTileBytes, kOffDS = 5 * kTileBytes;
 constexpr int kOffK1 = kOffP, kOffV1 = 6 * kTileBytes;  // dQ kernel only (it has no P tile)
 constexpr int kNumTiles[2] = {7, 6};                    // by mode
-// fix_full, ld_full[2], s_full, pds_full, it_done[2]
-constexpr int kNumBwdBars = 7;
+// fix_full, ld_full[2], s_full, pds_full, it_done[2], dp_full, p_full
+constexpr int kNumBwdBars = 9;
 constexpr int bwd_smem_bytes(int mode) { return kNumTiles[mode] * kTileBytes + kNumBwdBars * 8 + 16 + 1024; }
 constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384;
 constexpr float kLog2eBwd = 1.4426950408889634f;
@@ -137,6 +137,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   uint64_t* s_full = bars + 3;    // S (and dP) are in tensor memory
   uint64_t* pds_full = bars + 4;  // all rows of P / dS written (and S / dP read)
   uint64_t* it_done = bars + 5;   // [buffer] the last MMAs of an iteration that used it have completed
+  uint64_t* dp_full = bars + 7;   // dP is in tensor memory (gradient iterations)
+  uint64_t* p_full = bars + 8;    // all rows of P written (dK/dV kernel)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBwdBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -180,6 +182,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     mbar_init(pds_full, kSoftmaxThreads);
     mbar_init(it_done, 1);
     mbar_init(it_done + 1, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_full, kSoftmaxThreads);
     *abort_word = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -241,18 +245,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         tc_fence_after();
         const bool stats = DQ && i < n;
         const uint32_t sk = smem_u32(smem + (buf ? kOffK1 : kOffK)), sv = smem_u32(smem + (buf ? kOffV1 : kOffV));
+        // The algebra on S starts while dP is still being computed, and dV is issued as soon as P
+        // is in shared memory, while dS is still being computed.
         mma_128x128x128<false, false>(tmem_base + kTmS, sq, sk, kIdKK, false);
-        if (!stats) mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
         umma_commit(s_full);
+        const int gi = DQ ? i - n : i;  // index among the gradient iterations
+        if (!stats) {
+          mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
+          umma_commit(dp_full);
+          if (!DQ) {
+            if (!mbar_wait(p_full, gi & 1, abort_word)) break;
+            tc_fence_after();
+            mma_128x128x128<true, true>(tmem_base + kTmAcc0, sp, sdo, kIdMM, gi > 0);  // dV += P^T dO
+          }
+        }
         if (!mbar_wait(pds_full, i & 1, abort_word)) break;
         tc_fence_after();
         if (!stats) {
-          const bool first = DQ ? i == n : i == 0;
           if (DQ) {
-            mma_128x128x128<false, true>(tmem_base + kTmAcc0, sds, sk, kIdKM, !first);  // dQ += dS K
+            mma_128x128x128<false, true>(tmem_base + kTmAcc0, sds, sk, kIdKM, gi > 0);  // dQ += dS K
           } else {
-            mma_128x128x128<true, true>(tmem_base + kTmAcc0, sp, sdo, kIdMM, !first);  // dV += P^T dO
-            mma_128x128x128<true, true>(tmem_base + kTmAcc1, sds, sq, kIdMM, !first);  // dK += dS^T Q
+            mma_128x128x128<true, true>(tmem_base + kTmAcc1, sds, sq, kIdMM, gi > 0);  // dK += dS^T Q
           }
         }
         umma_commit(it_done + buf);
@@ -302,15 +315,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if (p.causal) col_hi = min(col_hi, q_g + p.causal_offset);
       }
       if (ok && !mbar_wait(s_full, i & 1, abort_word)) ok = false;
-      if (ok) {
-        tc_fence_after();
+      const int gi = DQ ? i - n : i;  // index among the gradient iterations
+      if (stats) {
+        if (ok) {
+          tc_fence_after();
 #pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c4 = half * 2 + cc;
-          uint32_t s[32];
-          tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
-          const int kv0 = kv_base + c4 * 32;
-          if (stats) {
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c4 = half * 2 + cc;
+            uint32_t s[32];
+            tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
+            const int kv0 = kv_base + c4 * 32;
             tmem_wait_ld();
             float cm = ninf;
 #pragma unroll
@@ -327,22 +341,48 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
               l = l * exp2f(m - m_new) + acc;
               m = m_new;
             }
-          } else {
-            uint32_t dp[32];
+          }
+        }
+      } else {
+        // P from S while the tensor core still computes dP; then dS = P o (dP - delta)
+        float pf[64];
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c4 = half * 2 + cc;
+            uint32_t s[32];
+            tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
+            const int kv0 = kv_base + c4 * 32;
+            tmem_wait_ld();
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              pf[cc * 32 + k] = (kv0 + k <= col_hi) ? exp2f(__uint_as_float(s[k]) * p.scale_log2 - lse2) : 0.f;
+            if (!DQ) {
+              uint32_t pw[16];
+#pragma unroll
+              for (int k = 0; k < 32; k += 2) pw[k >> 1] = pack2<T>(pf[cc * 32 + k], pf[cc * 32 + k + 1]);
+              store_row_chunk(smem + kOffP, r, c4 * 32, pw);
+            }
+          }
+        }
+        if (!DQ) {
+          fence_proxy_async_smem();
+          mbar_arrive(p_full);
+        }
+        if (ok && !mbar_wait(dp_full, gi & 1, abort_word)) ok = false;
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c4 = half * 2 + cc;
+            uint32_t dp[32], dsw[16];
             tmem_ld_32x32b_x32(lane_base + kTmDP + c4 * 32, dp);
             tmem_wait_ld();
-            uint32_t pw[16], dsw[16];
 #pragma unroll
-            for (int k = 0; k < 32; k += 2) {
-              float p0 = 0.f, p1 = 0.f;
-              if (kv0 + k <= col_hi) p0 = exp2f(__uint_as_float(s[k]) * p.scale_log2 - lse2);
-              if (kv0 + k + 1 <= col_hi) p1 = exp2f(__uint_as_float(s[k + 1]) * p.scale_log2 - lse2);
-              const float d0 = p0 * (__uint_as_float(dp[k]) - dl);
-              const float d1 = p1 * (__uint_as_float(dp[k + 1]) - dl);
-              pw[k >> 1] = pack2<T>(p0, p1);
-              dsw[k >> 1] = pack2<T>(d0, d1);
-            }
-            if (!DQ) store_row_chunk(smem + kOffP, r, c4 * 32, pw);
+            for (int k = 0; k < 32; k += 2)
+              dsw[k >> 1] = pack2<T>(pf[cc * 32 + k] * (__uint_as_float(dp[k]) - dl),
+                                     pf[cc * 32 + k + 1] * (__uint_as_float(dp[k + 1]) - dl));
             store_row_chunk(smem + kOffDS, r, c4 * 32, dsw);
           }
         }
