@@ -52,10 +52,12 @@ constexpr int kOffQ = 0, kOffDO = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 3 
 constexpr int kOffP = 4 * kTileBytes, kOffDS = 5 * kTileBytes;
 constexpr int kOffK1 = kOffP, kOffV1 = 6 * kTileBytes;  // dQ kernel only (it has no P tile)
 constexpr int kNumTiles[2] = {7, 6};                    // by mode
-// fix_full, ld_full[2], s_full, pds_full, it_done[2], dp_full, p_full
-constexpr int kNumBwdBars = 9;
+// fix_full, ld_full[2], s_full[2], pds_full, it_done[2], dp_full, p_full
+constexpr int kNumBwdBars = 10;
 constexpr int bwd_smem_bytes(int mode) { return kNumTiles[mode] * kTileBytes + kNumBwdBars * 8 + 16 + 1024; }
-constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384;
+// Tensor-memory columns.  The dQ kernel has one accumulator and uses the fourth quarter as a second
+// S buffer, so that the next score product runs while the algebra reads the current one.
+constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384, kTmS1 = 384;
 constexpr float kLog2eBwd = 1.4426950408889634f;
 constexpr int kStatusBwdTimeout = 64;
 
@@ -134,11 +136,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kNumTiles[MODE] * kTileBytes);
   uint64_t* fix_full = bars;      // the tiles held for the whole item have landed
   uint64_t* ld_full = bars + 1;   // [buffer] the streamed tiles of an iteration have landed
-  uint64_t* s_full = bars + 3;    // S (and dP) are in tensor memory
-  uint64_t* pds_full = bars + 4;  // all rows of P / dS written (and S / dP read)
-  uint64_t* it_done = bars + 5;   // [buffer] the last MMAs of an iteration that used it have completed
-  uint64_t* dp_full = bars + 7;   // dP is in tensor memory (gradient iterations)
-  uint64_t* p_full = bars + 8;    // all rows of P written (dK/dV kernel)
+  uint64_t* s_full = bars + 3;    // [S buffer] S is in tensor memory
+  uint64_t* pds_full = bars + 5;  // all rows of P / dS written (and S / dP read)
+  uint64_t* it_done = bars + 6;   // [buffer] the last MMAs of an iteration that used it have completed
+  uint64_t* dp_full = bars + 8;   // dP is in tensor memory (gradient iterations)
+  uint64_t* p_full = bars + 9;    // all rows of P written (dK/dV kernel)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBwdBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -179,6 +181,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     mbar_init(ld_full, 1);
     mbar_init(ld_full + 1, 1);
     mbar_init(s_full, 1);
+    mbar_init(s_full + 1, 1);
     mbar_init(pds_full, kSoftmaxThreads);
     mbar_init(it_done, 1);
     mbar_init(it_done + 1, 1);
@@ -239,20 +242,33 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       const uint32_t sq = smem_u32(smem + kOffQ), sdo = smem_u32(smem + kOffDO), sp = smem_u32(smem + kOffP),
                      sds = smem_u32(smem + kOffDS);
       bool ok = mbar_wait(fix_full, 0, abort_word);
+      // S of iteration `it`, once its streamed tiles have landed.  dQ kernel: into S buffer it & 1.
+      auto issue_s = [&](int it) -> bool {
+        const int b = it % kBufs;
+        if (!mbar_wait(ld_full + b, (it / kBufs) & 1, abort_word)) return false;
+        tc_fence_after();
+        const int sb = DQ ? (it & 1) : 0;
+        mma_128x128x128<false, false>(tmem_base + (sb ? kTmS1 : kTmS), sq, smem_u32(smem + (b ? kOffK1 : kOffK)), kIdKK,
+                                      false);
+        umma_commit(s_full + sb);
+        return true;
+      };
+      if (ok && DQ) ok = issue_s(0);
       for (int i = 0; i < total && ok; ++i) {
         const int buf = i % kBufs;
-        if (!mbar_wait(ld_full + buf, (i / kBufs) & 1, abort_word)) break;
-        tc_fence_after();
         const bool stats = DQ && i < n;
         const uint32_t sk = smem_u32(smem + (buf ? kOffK1 : kOffK)), sv = smem_u32(smem + (buf ? kOffV1 : kOffV));
         // The algebra on S starts while dP is still being computed, and dV is issued as soon as P
-        // is in shared memory, while dS is still being computed.
-        mma_128x128x128<false, false>(tmem_base + kTmS, sq, sk, kIdKK, false);
-        umma_commit(s_full);
+        // is in shared memory, while dS is still being computed.  The dQ kernel also issues the
+        // next iteration's S now (its S buffer was released by the previous iteration's algebra).
+        if (!DQ && !issue_s(i)) break;
         const int gi = DQ ? i - n : i;  // index among the gradient iterations
         if (!stats) {
           mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
           umma_commit(dp_full);
+        }
+        if (DQ && i + 1 < total && !issue_s(i + 1)) break;
+        if (!stats) {
           if (!DQ) {
             if (!mbar_wait(p_full, gi & 1, abort_word)) break;
             tc_fence_after();
@@ -314,7 +330,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         col_hi = p.seq_kv - 1;
         if (p.causal) col_hi = min(col_hi, q_g + p.causal_offset);
       }
-      if (ok && !mbar_wait(s_full, i & 1, abort_word)) ok = false;
+      const int sb = DQ ? (i & 1) : 0;  // S buffer of this iteration
+      const uint32_t s_base = lane_base + (sb ? kTmS1 : kTmS);
+      if (ok && !mbar_wait(s_full + sb, (DQ ? (i >> 1) : i) & 1, abort_word)) ok = false;
       const int gi = DQ ? i - n : i;  // index among the gradient iterations
       if (stats) {
         if (ok) {
@@ -323,7 +341,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
           for (int cc = 0; cc < 2; ++cc) {
             const int c4 = half * 2 + cc;
             uint32_t s[32];
-            tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
+            tmem_ld_32x32b_x32(s_base + c4 * 32, s);
             const int kv0 = kv_base + c4 * 32;
             tmem_wait_ld();
             float cm = ninf;
@@ -352,7 +370,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
           for (int cc = 0; cc < 2; ++cc) {
             const int c4 = half * 2 + cc;
             uint32_t s[32];
-            tmem_ld_32x32b_x32(lane_base + kTmS + c4 * 32, s);
+            tmem_ld_32x32b_x32(s_base + c4 * 32, s);
             const int kv0 = kv_base + c4 * 32;
             tmem_wait_ld();
 #pragma unroll

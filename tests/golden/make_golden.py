@@ -129,6 +129,26 @@ def paged_prefill_case():
                         v_after=bits16(v_after), o=out.numpy(), scale=np.array(scale, dtype=np.float64))
 
 
+def attention_bwd_case():
+    """Gradients from torch autograd through scaled_dot_product_attention on fp32-upcast inputs
+    (grouped heads expanded with repeat_interleave, so autograd sums dK / dV over the group)."""
+    sq, skv, hq, hkv, dtype = 72, 136, 4, 2, torch.bfloat16
+    q, k, v = oracle.make_attention_inputs(1, hq, hkv, sq, skv, 128, dtype, seed=13, std=0.5)
+    d_o = torch.randn(1, hq, sq, 128, generator=torch.Generator().manual_seed(14)).to(dtype)
+    scale = 128 ** -0.5
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    i = torch.arange(sq).unsqueeze(1)
+    j = torch.arange(skv).unsqueeze(0)
+    mask = j <= i + (skv - sq)
+    g = hq // hkv
+    o = F.scaled_dot_product_attention(qf, kf.repeat_interleave(g, dim=1), vf.repeat_interleave(g, dim=1),
+                                       attn_mask=mask, scale=scale)
+    o.backward(d_o.float())
+    np.savez_compressed(os.path.join(HERE, "attn_bwd_bf16_causal_gqa.npz"), q=bits16(q), k=bits16(k), v=bits16(v),
+                        d_o=bits16(d_o), dq=qf.grad.numpy(), dk=kf.grad.numpy(), dv=vf.grad.numpy(),
+                        scale=np.array(scale, dtype=np.float64))
+
+
 if __name__ == "__main__":
     torch.set_num_threads(1)  # deterministic reduction order for the stored fp32 values
     gemm_case()
@@ -136,6 +156,7 @@ if __name__ == "__main__":
     paged_case()
     linear_cases()
     paged_prefill_case()
+    attention_bwd_case()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -236,3 +236,20 @@ def test_attention_bwd_matches_torch_autograd(shape):
     got = oracle.attention_bwd(q.detach().float(), k.detach().float(), v.detach().float(), d_o.float(), 0.1, causal)
     for g, ref in zip(got, (q.grad, k.grad, v.grad)):
         assert (g.double() - ref).abs().max().item() < 1e-4
+
+
+def _load_bwd_fixture():
+    z = np.load(os.path.join(GOLDEN, "attn_bwd_bf16_causal_gqa.npz"))
+    ins = [torch.from_numpy(z[n].copy()).view(torch.bfloat16) for n in ("q", "k", "v", "d_o")]
+    refs = [torch.from_numpy(z[n]) for n in ("dq", "dk", "dv")]
+    return ins, refs, float(z["scale"])
+
+
+def test_attention_bwd_golden_fixture():
+    """Expected gradients in the fixture come from torch autograd through
+    scaled_dot_product_attention, not from the oracle."""
+    (q, k, v, d_o), refs, scale = _load_bwd_fixture()
+    got = oracle.attention_bwd(q, k, v, d_o, scale, True)
+    for g, r in zip(got, refs):
+        assert g.shape == r.shape
+        assert (g - r).abs().max().item() < 1e-4
