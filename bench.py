@@ -143,7 +143,8 @@ class AttentionWL(Workload):
 class AttentionBwdWL(AttentionWL):
     """Attention backward (dQ, dK, dV from q, k, v, o, dO).  Work is counted as five 128-deep
     products per score element (2.5 x the forward count), the usual convention; the kernels
-    execute eight (row statistics and the scores are recomputed in both passes)."""
+    execute seven (the scores and dP are recomputed in both passes).  The forward's row statistic
+    (lse) is an input, as in a training step."""
 
     launches_per_step = 3  # delta, dQ (+ statistics), dK/dV
 
@@ -159,27 +160,30 @@ class AttentionBwdWL(AttentionWL):
     def setup(self, dev):
         self.q, self.k, self.v = self._make(dev)
         self.d_o = self._make_do(dev)
-        self.o = torch.ops.b200k.attention(self.q, self.k, self.v, SCALE, self.causal)
+        self.o, self.lse = torch.ops.b200k.attention_lse(self.q, self.k, self.v, SCALE, self.causal)
 
     def step(self):
-        self.grads = torch.ops.b200k.attention_bwd(self.q, self.k, self.v, self.o, self.d_o, SCALE, self.causal)
+        self.grads = torch.ops.b200k.attention_bwd(self.q, self.k, self.v, self.o, self.d_o, SCALE, self.causal,
+                                                   self.lse)
 
     def units_per_step(self):
         return 2.5 * super().units_per_step()
 
     def setup_e2e(self, dev):
         self.host_in = [t.cpu().pin_memory() for t in (self.q, self.k, self.v, self.o, self.d_o)]
+        self.host_lse = self.lse.cpu().pin_memory()
         self.host_out = [torch.empty_like(self.host_in[0]).pin_memory() for _ in range(3)]
 
     def step_e2e(self):
         dev_in = [t.to(self.q.device, non_blocking=True) for t in self.host_in]
-        grads = torch.ops.b200k.attention_bwd(*dev_in, SCALE, self.causal)
+        grads = torch.ops.b200k.attention_bwd(*dev_in, SCALE, self.causal,
+                                              self.host_lse.to(self.q.device, non_blocking=True))
         for h, g in zip(self.host_out, grads):
             h.copy_(g, non_blocking=True)
 
     def e2e_bytes(self):
         n = self.b * self.h * self.s * 128 * 2
-        return 5 * n, 3 * n
+        return 5 * n + self.b * self.h * self.s * 4, 3 * n
 
     def cpu_sample(self):
         from oracle import oracle

@@ -175,6 +175,9 @@ typedef struct b200k_attention_args {
   int32_t causal;
   float scale;
   int32_t* status; /* device status word, may be NULL */
+  float* lse;      /* optional output [batch, q_heads, seq_q] (contiguous fp32), may be NULL:
+                      ln sum_j exp(scale * q_i . k_j) over the visible keys, -inf for a row that sees
+                      none; b200k_attention_bwd takes it to skip recomputing the row statistics */
 } b200k_attention_args;
 
 int b200k_attention_fwd(const b200k_attention_args* args, void* stream);
@@ -216,7 +219,9 @@ typedef struct b200k_attention_bwd_args {
   int32_t causal;
   float scale;
   int32_t reserved;
-  int32_t* status; /* device status word, may be NULL; bit 6 = a bounded wait ran out */
+  int32_t* status;  /* device status word, may be NULL; bit 6 = a bounded wait ran out */
+  const float* lse; /* optional: the lse output of b200k_attention_fwd for the same q, k, v; NULL =
+                       recompute the row statistics (one more pass over K in the dQ kernel) */
 } b200k_attention_bwd_args;
 
 uint64_t b200k_attention_bwd_workspace_bytes(const b200k_attention_bwd_args* args);

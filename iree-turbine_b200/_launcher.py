@@ -126,6 +126,7 @@ class AttentionArgs(C.Structure):
         ("causal", C.c_int32),
         ("scale", C.c_float),
         ("status", C.c_void_p),
+        ("lse", C.c_void_p),
     ]
 
 
@@ -136,7 +137,7 @@ class AttentionBwdArgs(C.Structure):
         + [(n, C.c_int32) for n in ("batch", "q_heads", "kv_heads", "seq_q", "seq_kv", "head_dim")]
         + [(f"{t}_stride_{d}", C.c_int64) for t in ("q", "k", "v", "o", "do", "dq", "dk", "dv") for d in "bhs"]
         + [("dtype", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float), ("reserved", C.c_int32),
-           ("status", C.c_void_p)]
+           ("status", C.c_void_p), ("lse", C.c_void_p)]
     )
 
 

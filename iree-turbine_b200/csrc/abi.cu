@@ -365,6 +365,7 @@ int b200k_attention_fwd_host(const b200k_attention_args* host, const b200k_atten
     one.k = static_cast<const char*>(dev->k) + b * k1;
     one.v = static_cast<const char*>(dev->v) + b * k1;
     one.o = static_cast<char*>(dev->o) + b * q1;
+    if (dev->lse) one.lse = dev->lse + static_cast<size_t>(b) * dev->q_heads * dev->seq_q;  // stays on the device
     rc = check_cuda(cudaMemcpyAsync(const_cast<void*>(one.q), static_cast<const char*>(host->q) + b * q1, q1,
                                     cudaMemcpyHostToDevice, s), "copy Q");
     if (rc) return rc;

@@ -68,8 +68,13 @@ struct BwdParams {
   float scale, scale_log2;
   float* lse2;   // [batch, q_heads, seq_q], log2 domain: log2(sum_j exp2(scale_log2 * s_ij))
   float* delta;  // [batch, q_heads, seq_q]
+  const float* lse_in;  // optional: the forward's ln-sum-exp per row (then lse2 is not used)
   int32_t* status;
 };
+
+// The forward's row statistic (natural log, -inf for a row without keys) in the form used here:
+// log2 domain, +inf for such a row so that exp2(x - lse2) is 0.
+__device__ __forceinline__ float lse_to_log2(float lse) { return lse == -INFINITY ? INFINITY : lse * kLog2eBwd; }
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -174,7 +179,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     if (p.causal) qt_lo = max(0, row0 - p.causal_offset) / kRows;
     n = max(0, p.num_q_tiles - qt_lo);
   }
-  const int total = DQ ? 2 * n : group * n;  // iterations
+  // dQ kernel: a statistics sweep over the n tiles first, unless the caller supplied the forward's LSE
+  const int n_stats = (DQ && p.lse_in == nullptr) ? n : 0;
+  const int total = DQ ? n_stats + n : group * n;  // iterations
 
   if (threadIdx.x == 0) {
     mbar_init(fix_full, 1);
@@ -221,8 +228,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if (i >= kBufs && !mbar_wait(it_done + buf, ((i - kBufs) / kBufs) & 1, abort_word)) break;
         uint64_t* full = ld_full + buf;
         if (DQ) {
-          const bool stats = i < n;
-          const int j = stats ? i : i - n;
+          const bool stats = i < n_stats;
+          const int j = stats ? i : i - n_stats;
           mbar_arrive_expect_tx(full, stats ? kTileBytes : 2 * kTileBytes);
           load_tile_4d(smem + (buf ? kOffK1 : kOffK), &tmap_k, full, j * kRows, kvh, batch);
           if (!stats) load_tile_4d(smem + (buf ? kOffV1 : kOffV), &tmap_v, full, j * kRows, kvh, batch);
@@ -256,13 +263,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       if (ok && DQ) ok = issue_s(0);
       for (int i = 0; i < total && ok; ++i) {
         const int buf = i % kBufs;
-        const bool stats = DQ && i < n;
+        const bool stats = DQ && i < n_stats;
         const uint32_t sk = smem_u32(smem + (buf ? kOffK1 : kOffK)), sv = smem_u32(smem + (buf ? kOffV1 : kOffV));
         // The algebra on S starts while dP is still being computed, and dV is issued as soon as P
         // is in shared memory, while dS is still being computed.  The dQ kernel also issues the
         // next iteration's S now (its S buffer was released by the previous iteration's algebra).
         if (!DQ && !issue_s(i)) break;
-        const int gi = DQ ? i - n : i;  // index among the gradient iterations
+        const int gi = DQ ? i - n_stats : i;  // index among the gradient iterations
         if (!stats) {
           mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
           umma_commit(dp_full);
@@ -302,15 +309,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     int64_t stat_idx = 0;
     if (DQ) {
       stat_idx = (static_cast<int64_t>(batch) * p.q_heads + head) * p.seq_q + q_g;
-      if (q_g < p.seq_q) dl = __ldg(p.delta + stat_idx);
+      if (q_g < p.seq_q) {
+        dl = __ldg(p.delta + stat_idx);
+        if (p.lse_in) lse2 = lse_to_log2(__ldg(p.lse_in + stat_idx));
+      }
     }
     // After a wait has given up the loop keeps its shape (arrivals and named barriers) but skips the work.
     bool ok = true;
     for (int i = 0; i < total; ++i) {
-      const bool stats = DQ && i < n;
+      const bool stats = DQ && i < n_stats;
       int kv_base;
       if (DQ) {
-        kv_base = (stats ? i : i - n) * kRows;
+        kv_base = (stats ? i : i - n_stats) * kRows;
       } else {
         const int g = i / n;
         const int qt = qt_lo + (i - g * n);
@@ -320,7 +330,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         lse2 = INFINITY;
         dl = 0.f;
         if (q_g < p.seq_q) {
-          lse2 = __ldg(p.lse2 + stat_idx);
+          lse2 = p.lse_in ? lse_to_log2(__ldg(p.lse_in + stat_idx)) : __ldg(p.lse2 + stat_idx);
           dl = __ldg(p.delta + stat_idx);
         }
       }
@@ -333,7 +343,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       const int sb = DQ ? (i & 1) : 0;  // S buffer of this iteration
       const uint32_t s_base = lane_base + (sb ? kTmS1 : kTmS);
       if (ok && !mbar_wait(s_full + sb, (DQ ? (i >> 1) : i) & 1, abort_word)) ok = false;
-      const int gi = DQ ? i - n : i;  // index among the gradient iterations
+      const int gi = DQ ? i - n_stats : i;  // index among the gradient iterations
       if (stats) {
         if (ok) {
           tc_fence_after();
@@ -405,7 +415,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
           }
         }
       }
-      if (DQ && stats && i == n - 1) {
+      if (DQ && stats && i == n_stats - 1) {
         // The two threads of a row combine their (max, sum) over the dS tile, which nothing uses
         // before the gradient sweep; both evaluate the same expression, so they agree bitwise.
         float2* xchg = reinterpret_cast<float2*>(smem + kOffDS);
@@ -575,6 +585,8 @@ int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream)
     if (reinterpret_cast<uintptr_t>(ptr) & 15)
       return set_error(B200K_ERR_BAD_ALIGN, "attention_bwd: every tensor must be 16-byte aligned");
   if (!(a.scale > 0.f)) return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: scale must be positive");
+  if (reinterpret_cast<uintptr_t>(a.lse) & 3)
+    return set_error(B200K_ERR_BAD_ALIGN, "attention_bwd: lse must be 4-byte aligned");
   const uint64_t need = attention_bwd_workspace_bytes(a);
   if (!a.workspace || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 15))
     return set_error(B200K_ERR_WORKSPACE, "attention_bwd: workspace must be 16-byte aligned and hold %llu bytes",
@@ -607,6 +619,7 @@ int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream)
     return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: too many tiles");
   p.scale = a.scale;
   p.scale_log2 = a.scale * kLog2eBwd;
+  p.lse_in = a.lse;
   p.lse2 = static_cast<float*>(a.workspace);
   p.delta = p.lse2 + static_cast<int64_t>(a.batch) * a.q_heads * a.seq_q;
   p.status = a.status;

@@ -101,6 +101,7 @@ struct AttnParams {
   int32_t num_items;    // batch * q_heads * num_q_tiles
   float scale_log2;
   int32_t* status;
+  float* lse;  // optional [batch, q_heads, seq_q]: ln sum_j exp(scale * s_ij), -inf for a row without keys
   // Paged K/V (block_table != nullptr): the tensor maps of K and V describe the page pool
   // [num_pages, kv_heads, page_size, 128]; token t of sequence b lives in page
   // block_table[b * block_table_stride + t / page_size], row t % page_size; sequence b has
@@ -498,6 +499,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
                     static_cast<int64_t>(q_row) * p.o_stride_s;
 #pragma unroll
           for (int v = 0; v < 16; ++v) reinterpret_cast<uint4*>(orow)[v] = make_uint4(0u, 0u, 0u, 0u);
+          if (p.lse) p.lse[(static_cast<int64_t>(it.batch) * p.q_heads + it.head) * p.seq_q + q_row] = -INFINITY;
         }
         continue;
       }
@@ -520,6 +522,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       const float a1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - mm);
       const float l = l0 * a0 + l1 * a1;
       const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+      if (p.lse) {
+        // mm is in the log2 domain (scores times scale * log2 e), l is relative to it
+        const int q_row = it.qtile * kTileRows + row_in_tile;
+        if (q_row < p.seq_q)
+          p.lse[(static_cast<int64_t>(it.batch) * p.q_heads + it.head) * p.seq_q + q_row] =
+              (l > 0.f) ? (mm + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
       const uint32_t t_o = tmem_base + lane_field + kTmemO;
 #pragma unroll
       for (int c2 = 0; c2 < 2; ++c2) {  // one 64-column block at a time
@@ -778,6 +787,7 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
       (reinterpret_cast<uintptr_t>(a.v) & 15) || (reinterpret_cast<uintptr_t>(a.o) & 15))
     return set_error(B200K_ERR_BAD_ALIGN, "attention_fwd: q, k, v, o must be 16-byte aligned");
   if (!(a.scale > 0.f)) return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: scale must be positive");
+  if (reinterpret_cast<uintptr_t>(a.lse) & 3) return set_error(B200K_ERR_BAD_ALIGN, "attention_fwd: lse must be 4-byte aligned");
   int rc = ensure_sm100();
   if (rc) return rc;
 
@@ -831,6 +841,7 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   p.num_items = static_cast<int32_t>(items);
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
+  p.lse = a.lse;
   p.block_table = nullptr;
   p.seq_lens = nullptr;
   p.block_table_stride = p.page_size = p.num_pages = 0;
@@ -909,6 +920,7 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
   p.num_items = static_cast<int32_t>(items);
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
+  p.lse = nullptr;
   p.block_table = a.block_table;
   p.seq_lens = a.seq_lens;
   p.block_table_stride = a.block_table_stride;

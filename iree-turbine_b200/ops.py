@@ -31,6 +31,7 @@ __all__ = [
     "linear",
     "linear_act",
     "attention",
+    "attention_lse",
     "attention_bwd",
     "sdpa",
     "decode_attention",
@@ -356,6 +357,24 @@ def _attention_out_like(q: Tensor, device) -> Tensor:
     return torch.empty(q.shape, dtype=q.dtype, device=device)
 
 
+def _attention_select(sel: KernelSelection):
+    q = sel.arg_tensor(0)
+    k = sel.arg_tensor(1)
+    v = sel.arg_tensor(2)
+    sel.attr_float(3)
+    sel.attr_bool(4)
+    torch._check(q.t.dim() == 4 and k.t.dim() == 4 and v.t.dim() == 4, lambda: "attention: q, k, v must be 4-D [B,H,S,D]")
+    torch._check(q.t.dtype in _HALF_TYPES, lambda: f"attention: dtype must be float16 or bfloat16, got {q.t.dtype}")
+    torch._check(q.t.dtype == k.t.dtype == v.t.dtype, lambda: "attention: q, k, v must share a dtype")
+    torch._check(q.t.size(3) == 128 and k.t.size(3) == 128 and v.t.size(3) == 128, lambda: "attention: head dim must be 128")
+    torch._check(k.t.shape == v.t.shape, lambda: "attention: k and v must have the same shape")
+    torch._check(q.t.size(0) == k.t.size(0), lambda: "attention: batch mismatch")
+    torch._check(q.t.size(1) % k.t.size(1) == 0, lambda: "attention: query heads must be a multiple of kv heads")
+    q.specialize_dims(3)
+    sel.return_tensor(_attention_out_like(q.t, "meta"))
+    return q
+
+
 @CustomOp.register(library=LIBRARY)
 class attention(CustomOp):
     """O = softmax(scale * Q K^T [causal]) V.  q [B,Hq,Sq,128], k/v [B,Hkv,Skv,128] -> [B,Hq,Sq,128]."""
@@ -363,20 +382,7 @@ class attention(CustomOp):
     signature = "attention(Tensor q, Tensor k, Tensor v, float scale, bool is_causal) -> Tensor"
 
     def select(self, sel: KernelSelection):
-        q = sel.arg_tensor(0)
-        k = sel.arg_tensor(1)
-        v = sel.arg_tensor(2)
-        sel.attr_float(3)
-        sel.attr_bool(4)
-        torch._check(q.t.dim() == 4 and k.t.dim() == 4 and v.t.dim() == 4, lambda: "attention: q, k, v must be 4-D [B,H,S,D]")
-        torch._check(q.t.dtype in _HALF_TYPES, lambda: f"attention: dtype must be float16 or bfloat16, got {q.t.dtype}")
-        torch._check(q.t.dtype == k.t.dtype == v.t.dtype, lambda: "attention: q, k, v must share a dtype")
-        torch._check(q.t.size(3) == 128 and k.t.size(3) == 128 and v.t.size(3) == 128, lambda: "attention: head dim must be 128")
-        torch._check(k.t.shape == v.t.shape, lambda: "attention: k and v must have the same shape")
-        torch._check(q.t.size(0) == k.t.size(0), lambda: "attention: batch mismatch")
-        torch._check(q.t.size(1) % k.t.size(1) == 0, lambda: "attention: query heads must be a multiple of kv heads")
-        q.specialize_dims(3)
-        sel.return_tensor(_attention_out_like(q.t, "meta"))
+        _attention_select(sel)
 
     def eager_execute(self, q, k, v, scale, is_causal):
         o = _attention_out_like(q, q.device)
@@ -387,7 +393,33 @@ class attention(CustomOp):
         return o
 
 
-def _attention_bwd_checks(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor) -> None:
+@CustomOp.register(library=LIBRARY)
+class attention_lse(CustomOp):
+    """``attention`` that also returns the row statistic the backward needs:
+    lse[b, h, i] = ln sum_j exp(scale * q_i . k_j) over the visible keys (float32, -inf for a row
+    that sees none)."""
+
+    signature = "attention_lse(Tensor q, Tensor k, Tensor v, float scale, bool is_causal) -> (Tensor, Tensor)"
+
+    def select(self, sel: KernelSelection):
+        q = _attention_select(sel)
+        sel.return_new_tensor(list(q.t.shape[:3]), torch.float32)
+
+    def eager_execute(self, q, k, v, scale, is_causal):
+        o = _attention_out_like(q, q.device)
+        lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+        q, k, v = _bhsd(q), _bhsd(k), _bhsd(v)
+        args = _fill_attention_args(q, k, v, o, scale, is_causal)
+        args.status = _status_ptr(q.device)
+        args.lse = lse.data_ptr()
+        L.check(L.lib().b200k_attention_fwd(C.byref(args), _stream(q)))
+        return o, lse
+
+
+def _attention_bwd_checks(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tensor, lse: Optional[Tensor] = None) -> None:
+    if lse is not None:
+        torch._check(lse.dtype == torch.float32 and tuple(lse.shape) == tuple(q.shape[:3]),
+                     lambda: "attention_bwd: lse must be float32 [B, Hq, Sq]")
     for t in (q, k, v, o, d_o):
         torch._check(t.dim() == 4 and t.size(3) == 128, lambda: "attention_bwd: tensors must be [B,H,S,128]")
         torch._check(t.dtype == q.dtype, lambda: "attention_bwd: all tensors must share a dtype")
@@ -404,20 +436,23 @@ class attention_bwd(CustomOp):
     """Gradients of ``attention``: (q, k, v, o, d_o) -> (d_q, d_k, d_v).  d_k / d_v are summed over
     the query heads of a group.  Only the forward OUTPUT is needed; row statistics are recomputed."""
 
-    signature = ("attention_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, float scale, bool is_causal)"
-                 " -> (Tensor, Tensor, Tensor)")
+    signature = ("attention_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, float scale, bool is_causal, "
+                 "Tensor? lse=None) -> (Tensor, Tensor, Tensor)")
 
     def select(self, sel: KernelSelection):
         q, k, v, o, d_o = (sel.arg_tensor(i) for i in range(5))
         sel.attr_float(5)
         sel.attr_bool(6)
-        _attention_bwd_checks(q.t, k.t, v.t, o.t, d_o.t)
+        lse = sel.arg_optional_tensor(7)
+        _attention_bwd_checks(q.t, k.t, v.t, o.t, d_o.t, lse.t if lse is not None else None)
         sel.return_new_tensor(list(q.t.shape), q.t.dtype)
         sel.return_new_tensor(list(k.t.shape), q.t.dtype)
         sel.return_new_tensor(list(k.t.shape), q.t.dtype)
 
-    def eager_execute(self, q, k, v, o, d_o, scale, is_causal):
-        _attention_bwd_checks(q, k, v, o, d_o)
+    def eager_execute(self, q, k, v, o, d_o, scale, is_causal, lse=None):
+        _attention_bwd_checks(q, k, v, o, d_o, lse)
+        if lse is not None:
+            lse = lse.contiguous()
         q, k, v, o, d_o = (_bhsd(t) for t in (q, k, v, o, d_o))
         d_q, d_k, d_v = torch.empty_like(q, memory_format=torch.contiguous_format), \
             torch.empty_like(k, memory_format=torch.contiguous_format), \
@@ -433,6 +468,7 @@ class attention_bwd(CustomOp):
         a.causal = 1 if is_causal else 0
         a.scale = float(scale)
         a.status = _status_ptr(q.device)
+        a.lse = lse.data_ptr() if lse is not None else None
         lib = L.lib()
         need = lib.b200k_attention_bwd_workspace_bytes(C.byref(a))
         ws = torch.empty(max(int(need), 16), dtype=torch.uint8, device=q.device)
@@ -447,15 +483,15 @@ class _AttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, scale, is_causal):
-        o = torch.ops.b200k.attention(q, k, v, scale, is_causal)
-        ctx.save_for_backward(q, k, v, o)
+        o, lse = torch.ops.b200k.attention_lse(q, k, v, scale, is_causal)
+        ctx.save_for_backward(q, k, v, o, lse)
         ctx.scale, ctx.is_causal = scale, is_causal
         return o
 
     @staticmethod
     def backward(ctx, d_o):
-        q, k, v, o = ctx.saved_tensors
-        d_q, d_k, d_v = torch.ops.b200k.attention_bwd(q, k, v, o, d_o, ctx.scale, ctx.is_causal)
+        q, k, v, o, lse = ctx.saved_tensors
+        d_q, d_k, d_v = torch.ops.b200k.attention_bwd(q, k, v, o, d_o, ctx.scale, ctx.is_causal, lse)
         return d_q, d_k, d_v, None, None
 
 

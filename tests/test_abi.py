@@ -37,7 +37,7 @@ def test_struct_layouts_match_the_header():
     fields = {
         "b200k_gemm_args": (L.GemmArgs, ["a", "ldc", "in_dtype", "scale_a", "status", "tile_n"]),
         "b200k_attention_args": (L.AttentionArgs, ["q", "batch", "head_dim", "q_stride_b", "o_stride_s", "dtype",
-                                                   "scale", "status"]),
+                                                   "scale", "status", "lse"]),
         "b200k_decode_args": (L.DecodeArgs, ["q", "workspace_bytes", "num_seqs", "max_seq_len", "kv_batch_stride",
                                              "kv_page_stride", "dtype", "scale"]),
         "b200k_paged_attention_args": (L.PagedAttentionArgs, ["q", "seq_lens", "batch", "head_dim", "page_size",
@@ -46,7 +46,7 @@ def test_struct_layouts_match_the_header():
                                                               "status"]),
         "b200k_attention_bwd_args": (L.AttentionBwdArgs, ["q", "d_o", "d_v", "workspace", "workspace_bytes", "batch",
                                                           "head_dim", "q_stride_b", "do_stride_h", "dv_stride_s",
-                                                          "dtype", "scale", "status"]),
+                                                          "dtype", "scale", "status", "lse"]),
         "b200k_gemm_allgather_args": (L.GemmAllGatherArgs, ["gemm", "peer_c", "num_peers", "peer_ldc", "col_offset"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]

@@ -106,6 +106,35 @@ def test_gradient_against_torch_sdpa_autograd_on_the_same_device():
         _assert_close(g, r.cpu())
 
 
+@pytest.mark.parametrize("b,hq,hkv,sq,skv,causal", [(1, 2, 1, 200, 300, True), (1, 1, 1, 300, 200, True),
+                                                    (2, 4, 2, 256, 384, False)])
+def test_forward_lse_and_backward_from_it(b, hq, hkv, sq, skv, causal):
+    """The forward's optional row statistic is ln sum exp(scale * s) (-inf where a row sees no key);
+    given to the backward it replaces the statistics sweep: same gradients within tolerance of
+    the oracle, and the forward output is bitwise the one of the plain op."""
+    q, k, v = oracle.make_attention_inputs(b, hq, hkv, sq, skv, dtype=torch.bfloat16, seed=15)
+    d_o = _d_o((b, hq, sq, 128), torch.bfloat16)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, d_o))
+    o, lse = torch.ops.b200k.attention_lse(qd, kd, vd, SCALE, causal)
+    assert torch.equal(o, torch.ops.b200k.attention(qd, kd, vd, SCALE, causal))
+    s = torch.matmul(q.float(), k.float().repeat_interleave(hq // hkv, 1).transpose(-1, -2)) * SCALE
+    if causal:
+        i, j = torch.arange(sq).unsqueeze(1), torch.arange(skv).unsqueeze(0)
+        s = s.masked_fill(j > i + (skv - sq), float("-inf"))
+    ref_lse = torch.logsumexp(s, dim=-1)
+    dead = torch.isinf(ref_lse)
+    assert torch.equal(torch.isinf(lse.cpu()), dead) and (lse.cpu()[dead] < 0).all()
+    assert (lse.cpu()[~dead] - ref_lse[~dead]).abs().max().item() < 1e-3
+    got = torch.ops.b200k.attention_bwd(qd, kd, vd, o, dod, SCALE, causal, lse)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    for g, r in zip(got, oracle.attention_bwd(q, k, v, d_o, SCALE, causal)):
+        _assert_close(g, r)
+    again = torch.ops.b200k.attention_bwd(qd, kd, vd, o, dod, SCALE, causal, lse)
+    for a, b_ in zip(got, again):
+        assert torch.equal(a, b_)
+
+
 def test_golden_fixture():
     """Inputs and torch-autograd gradients committed under tests/golden/ (generated by make_golden.py)."""
     import os
