@@ -46,14 +46,17 @@ constexpr int kTileBytes = kRows * kD * 2;  // 32 KB
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column block
 constexpr int kModeDQ = 0, kModeDKV = 1;
 
-// Shared-memory tiles.  dK/dV kernel: Q, dO (streamed), K, V (held), P, dS.  dQ kernel: Q, dO (held),
-// two K and two V buffers (streamed, the next tiles load while the current ones are used), dS.
+// Shared-memory tiles.  dQ kernel: Q, dO (held), two K and two V buffers (streamed, the next tiles
+// load while the current ones are used), dS.  dK/dV kernel: K, V (held), two Q buffers and one dO
+// buffer (streamed: the next Q loads during the iteration, the next dO as soon as dV += P^T dO has
+// read the current one), P, dS.
 constexpr int kOffQ = 0, kOffDO = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 3 * kTileBytes;
 constexpr int kOffP = 4 * kTileBytes, kOffDS = 5 * kTileBytes;
 constexpr int kOffK1 = kOffP, kOffV1 = 6 * kTileBytes;  // dQ kernel only (it has no P tile)
-constexpr int kNumTiles[2] = {7, 6};                    // by mode
-// fix_full, ld_full[2], s_full[2], pds_full, it_done[2], dp_full, p_full
-constexpr int kNumBwdBars = 10;
+constexpr int kOffQ1 = 6 * kTileBytes;                  // dK/dV kernel: second Q buffer
+constexpr int kNumTiles[2] = {7, 7};                    // by mode
+// fix_full, ld_full[2], s_full[2], pds_full, it_done[2], dp_full, p_full, do_full, do_free
+constexpr int kNumBwdBars = 12;
 constexpr int bwd_smem_bytes(int mode) { return kNumTiles[mode] * kTileBytes + kNumBwdBars * 8 + 16 + 1024; }
 // Tensor-memory columns.  The dQ kernel has one accumulator and uses the fourth quarter as a second
 // S buffer, so that the next score product runs while the algebra reads the current one.
@@ -137,7 +140,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  constexpr int kBufs = DQ ? 2 : 1;  // buffers for the streamed tiles
+  constexpr int kBufs = 2;  // buffers for the streamed tiles (dQ kernel: K and V; dK/dV kernel: Q)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kNumTiles[MODE] * kTileBytes);
   uint64_t* fix_full = bars;      // the tiles held for the whole item have landed
   uint64_t* ld_full = bars + 1;   // [buffer] the streamed tiles of an iteration have landed
@@ -146,6 +149,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   uint64_t* it_done = bars + 6;   // [buffer] the last MMAs of an iteration that used it have completed
   uint64_t* dp_full = bars + 8;   // dP is in tensor memory (gradient iterations)
   uint64_t* p_full = bars + 9;    // all rows of P written (dK/dV kernel)
+  uint64_t* do_full = bars + 10;  // (dK/dV kernel) the iteration's dO tile has landed
+  uint64_t* do_free = bars + 11;  // (dK/dV kernel) dV += P^T dO, the last reader of the dO tile, has completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBwdBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -194,6 +199,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     mbar_init(it_done + 1, 1);
     mbar_init(dp_full, 1);
     mbar_init(p_full, kSoftmaxThreads);
+    mbar_init(do_full, 1);
+    mbar_init(do_free, 1);
     *abort_word = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -236,9 +243,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         } else {
           const int g = i / n;
           const int qt = qt_lo + (i - g * n);
-          mbar_arrive_expect_tx(full, 2 * kTileBytes);
-          load_tile_4d(smem + kOffQ, &tmap_q, full, qt * kRows, kvh * group + g, batch);
-          load_tile_4d(smem + kOffDO, &tmap_do, full, qt * kRows, kvh * group + g, batch);
+          mbar_arrive_expect_tx(full, kTileBytes);
+          load_tile_4d(smem + (buf ? kOffQ1 : kOffQ), &tmap_q, full, qt * kRows, kvh * group + g, batch);
+          // one dO buffer: free once the previous iteration's dV product has read it
+          if (i > 0 && !mbar_wait(do_free, (i - 1) & 1, abort_word)) break;
+          mbar_arrive_expect_tx(do_full, kTileBytes);
+          load_tile_4d(smem + kOffDO, &tmap_do, do_full, qt * kRows, kvh * group + g, batch);
         }
       }
     }
@@ -255,8 +265,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if (!mbar_wait(ld_full + b, (it / kBufs) & 1, abort_word)) return false;
         tc_fence_after();
         const int sb = DQ ? (it & 1) : 0;
-        mma_128x128x128<false, false>(tmem_base + (sb ? kTmS1 : kTmS), sq, smem_u32(smem + (b ? kOffK1 : kOffK)), kIdKK,
-                                      false);
+        if (DQ)
+          mma_128x128x128<false, false>(tmem_base + (sb ? kTmS1 : kTmS), sq, smem_u32(smem + (b ? kOffK1 : kOffK)),
+                                        kIdKK, false);
+        else
+          mma_128x128x128<false, false>(tmem_base + kTmS, smem_u32(smem + (b ? kOffQ1 : kOffQ)),
+                                        smem_u32(smem + kOffK), kIdKK, false);
         umma_commit(s_full + sb);
         return true;
       };
@@ -264,13 +278,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       for (int i = 0; i < total && ok; ++i) {
         const int buf = i % kBufs;
         const bool stats = DQ && i < n_stats;
-        const uint32_t sk = smem_u32(smem + (buf ? kOffK1 : kOffK)), sv = smem_u32(smem + (buf ? kOffV1 : kOffV));
+        const uint32_t sk = smem_u32(smem + ((DQ && buf) ? kOffK1 : kOffK)),
+                       sv = smem_u32(smem + ((DQ && buf) ? kOffV1 : kOffV));
         // The algebra on S starts while dP is still being computed, and dV is issued as soon as P
         // is in shared memory, while dS is still being computed.  The dQ kernel also issues the
         // next iteration's S now (its S buffer was released by the previous iteration's algebra).
         if (!DQ && !issue_s(i)) break;
         const int gi = DQ ? i - n_stats : i;  // index among the gradient iterations
         if (!stats) {
+          if (!DQ) {
+            if (!mbar_wait(do_full, i & 1, abort_word)) break;
+            tc_fence_after();
+          }
           mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
           umma_commit(dp_full);
         }
@@ -280,6 +299,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             if (!mbar_wait(p_full, gi & 1, abort_word)) break;
             tc_fence_after();
             mma_128x128x128<true, true>(tmem_base + kTmAcc0, sp, sdo, kIdMM, gi > 0);  // dV += P^T dO
+            umma_commit(do_free);
           }
         }
         if (!mbar_wait(pds_full, i & 1, abort_word)) break;
@@ -288,7 +308,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
           if (DQ) {
             mma_128x128x128<false, true>(tmem_base + kTmAcc0, sds, sk, kIdKM, gi > 0);  // dQ += dS K
           } else {
-            mma_128x128x128<true, true>(tmem_base + kTmAcc1, sds, sq, kIdMM, gi > 0);  // dK += dS^T Q
+            mma_128x128x128<true, true>(tmem_base + kTmAcc1, sds, smem_u32(smem + (buf ? kOffQ1 : kOffQ)), kIdMM,
+                                        gi > 0);  // dK += dS^T Q
           }
         }
         umma_commit(it_done + buf);
