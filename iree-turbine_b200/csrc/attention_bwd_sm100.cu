@@ -4,12 +4,13 @@
 //   dP = dO V^T                            dS = P o (dP - delta),  delta[i] = sum_d dO[i, d] O[i, d]
 //   dQ = scale * dS K                      dK = scale * dS^T Q
 //
-// Three launches, none of which needs anything from the forward call but its output O:
+// Three launches.  Only the forward's output O is required from the forward call; its row
+// log-sum-exp, if the caller kept it, spares the statistics sweep of the second launch:
 //   1. attn_bwd_delta_kernel: delta (one warp per query row).
 //   2. attn_bwd_kernel<T, kModeDQ>: one CTA per (batch, query head, tile of 128 queries).  It holds
-//      Q and dO and sweeps the visible K/V tiles twice: a statistics sweep (S = Q K^T only, running
-//      row maximum and sum -> LSE, kept in registers and written to the workspace) and a gradient
-//      sweep (S, dP -> dS in shared memory -> dQ += dS K).
+//      Q and dO and sweeps the visible K/V tiles: first a statistics sweep when no LSE was given
+//      (S = Q K^T only, running row maximum and sum -> LSE, kept in registers and written to the
+//      workspace), then the gradient sweep (S, dP -> dS in shared memory -> dQ += dS K).
 //   3. attn_bwd_kernel<T, kModeDKV>: one CTA per (batch, K/V head, tile of 128 keys).  It holds K
 //      and V and sweeps the query tiles of every query head of the group that see these keys:
 //      S, dP -> P, dS in shared memory -> dV += P^T dO, dK += dS^T Q.
