@@ -80,6 +80,12 @@ struct BwdParams {
 // log2 domain, +inf for such a row so that exp2(x - lse2) is 0.
 __device__ __forceinline__ float lse_to_log2(float lse) { return lse == -INFINITY ? INFINITY : lse * kLog2eBwd; }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <>
@@ -405,9 +411,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             tmem_ld_32x32b_x32(s_base + c4 * 32, s);
             const int kv0 = kv_base + c4 * 32;
             tmem_wait_ld();
+            if (kv0 + 31 <= col_hi) {  // the whole chunk is visible to this row: no per-element test
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
-              pf[cc * 32 + k] = (kv0 + k <= col_hi) ? exp2f(__uint_as_float(s[k]) * p.scale_log2 - lse2) : 0.f;
+              for (int k = 0; k < 32; ++k)
+                pf[cc * 32 + k] = ex2_approx(fmaf(__uint_as_float(s[k]), p.scale_log2, -lse2));
+            } else {
+#pragma unroll
+              for (int k = 0; k < 32; ++k)
+                pf[cc * 32 + k] =
+                    (kv0 + k <= col_hi) ? ex2_approx(fmaf(__uint_as_float(s[k]), p.scale_log2, -lse2)) : 0.f;
+            }
             if (!DQ) {
               uint32_t pw[16];
 #pragma unroll
