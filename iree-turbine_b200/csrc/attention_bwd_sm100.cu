@@ -404,13 +404,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         float pf[64];
         if (ok) {
           tc_fence_after();
+          uint32_t s64[64];  // this thread's 64 columns in one load
+          tmem_ld_32x32b_x64(s_base + half * 64, s64);
+          tmem_wait_ld();
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const int c4 = half * 2 + cc;
-            uint32_t s[32];
-            tmem_ld_32x32b_x32(s_base + c4 * 32, s);
+            const uint32_t* s = s64 + cc * 32;
             const int kv0 = kv_base + c4 * 32;
-            tmem_wait_ld();
             if (kv0 + 31 <= col_hi) {  // the whole chunk is visible to this row: no per-element test
 #pragma unroll
               for (int k = 0; k < 32; ++k)
@@ -436,12 +437,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if (ok && !mbar_wait(dp_full, gi & 1, abort_word)) ok = false;
         if (ok) {
           tc_fence_after();
+          uint32_t dp64[64];
+          tmem_ld_32x32b_x64(lane_base + kTmDP + half * 64, dp64);
+          tmem_wait_ld();
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const int c4 = half * 2 + cc;
-            uint32_t dp[32], dsw[16];
-            tmem_ld_32x32b_x32(lane_base + kTmDP + c4 * 32, dp);
-            tmem_wait_ld();
+            const uint32_t* dp = dp64 + cc * 32;
+            uint32_t dsw[16];
 #pragma unroll
             for (int k = 0; k < 32; k += 2)
               dsw[k >> 1] = pack2<T>(pf[cc * 32 + k] * (__uint_as_float(dp[k]) - dl),
