@@ -383,9 +383,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             const int kv0 = kv_base + c4 * 32;
             tmem_wait_ld();
             float cm = ninf;
+            const bool all_visible = kv0 + 31 <= col_hi;  // no per-element test then
 #pragma unroll
             for (int k = 0; k < 32; ++k) {
-              const float x = (kv0 + k <= col_hi) ? __uint_as_float(s[k]) * p.scale_log2 : ninf;
+              const float x = (all_visible || kv0 + k <= col_hi) ? __uint_as_float(s[k]) * p.scale_log2 : ninf;
               s[k] = __float_as_uint(x);
               cm = fmaxf(cm, x);
             }
@@ -393,8 +394,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             if (m_new > ninf) {
               float acc = 0.f;
 #pragma unroll
-              for (int k = 0; k < 32; ++k) acc += exp2f(__uint_as_float(s[k]) - m_new);
-              l = l * exp2f(m - m_new) + acc;
+              for (int k = 0; k < 32; ++k) acc += ex2_approx(__uint_as_float(s[k]) - m_new);
+              l = l * ex2_approx(m - m_new) + acc;
               m = m_new;
             }
           }
