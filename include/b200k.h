@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define B200K_ABI_VERSION 1
+#define B200K_ABI_VERSION 2
 
 typedef enum b200k_status {
   B200K_OK = 0,
@@ -268,7 +268,9 @@ int b200k_paged_attention_fwd(const b200k_paged_attention_args* args, void* stre
  *
  * q            [num_seqs, q_heads, head_dim]                       (contiguous)
  * o            [num_seqs, q_heads, head_dim]                       (contiguous, dtype of q)
- * seq_lens     int32 [num_seqs], 0 <= len; a zero-length sequence yields zeros
+ * seq_lens     int32 [num_seqs]; a zero-length sequence yields zeros.  The lengths are device data,
+ *              so the kernels bound them themselves: an entry above max_seq_len is treated as
+ *              max_seq_len (status bit 3 is set), a negative one as 0.
  *
  * block_table != NULL  (paged):
  *   k_cache/v_cache [num_pages, kv_heads, page_size, head_dim]; token t of sequence s lives in
@@ -302,6 +304,8 @@ typedef struct b200k_decode_args {
   int32_t chunk_tokens;       /* KV tokens per split; 0 = choose */
   float scale;
   int32_t reserved;
+  int32_t* status;            /* device status word, may be NULL; bit 3 (value 8) = a seq_lens entry was
+                                 larger than max_seq_len and was cut to it */
 } b200k_decode_args;
 
 /* Bytes of scratch the call needs for the given problem (depends on num_seqs, q_heads,
@@ -377,6 +381,11 @@ int b200k_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* ama
  * `dev` (same struct, device pointers, caller-allocated), launches, and copies the output back
  * to the host pointer, all on `stream`, then returns without synchronizing.  Host buffers
  * should be pinned for the copies to be asynchronous.
+ * The copy-back runs on a stream the library keeps per device, ordered with two events that all
+ * calls on that device share: call these two functions from ONE host thread per device at a time
+ * (calls on different devices are independent).  b200k_gemm_nt_host takes the [M, K] x [N, K]
+ * storage with single-SM tiles only (a_km, b_kn and B200K_TILE_SM_PAIR are rejected); the row
+ * pitches of both images are checked against the row lengths before any copy.
  */
 int b200k_gemm_nt_host(const b200k_gemm_args* host, const b200k_gemm_args* dev, void* stream);
 int b200k_attention_fwd_host(const b200k_attention_args* host, const b200k_attention_args* dev, void* stream);

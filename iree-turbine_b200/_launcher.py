@@ -34,6 +34,8 @@ __all__ = [
 _PKG_DIR = Path(__file__).resolve().parent
 _LIB_NAME = "libb200kern.so"
 
+ABI_VERSION = 2  # B200K_ABI_VERSION this binding was written against
+
 # Status codes (b200k_status).
 OK = 0
 ERR_BAD_SHAPE = -1
@@ -166,6 +168,7 @@ class DecodeArgs(C.Structure):
         ("chunk_tokens", C.c_int32),
         ("scale", C.c_float),
         ("reserved", C.c_int32),
+        ("status", C.c_void_p),
     ]
 
 
@@ -250,8 +253,8 @@ def lib() -> C.CDLL:
             fn.restype = restype
             fn.argtypes = argtypes
         version = handle.b200k_abi_version()
-        if version != 1:
-            raise RuntimeError(f"{path}: ABI version {version}, this binding expects 1")
+        if version != ABI_VERSION:
+            raise RuntimeError(f"{path}: ABI version {version}, this binding expects {ABI_VERSION}")
         _lib = handle
     return _lib
 

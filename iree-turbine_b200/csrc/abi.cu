@@ -290,6 +290,14 @@ int b200k_gemm_nt_host(const b200k_gemm_args* host, const b200k_gemm_args* dev, 
   const size_t in_es = dtype_size(dev->in_dtype), out_es = dtype_size(dev->out_dtype);
   if (in_es == 0 || out_es == 0) return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt_host: bad dtype");
   if (dev->m <= 0 || dev->n <= 0 || dev->k <= 0) return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: bad shape");
+  // The row-block slicing below assumes A stored [M, K] and B stored [N, K], single-CTA tiles.
+  if (dev->a_km || dev->b_kn || host->a_km || host->b_kn)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: operands stored [K, M] / [K, N] are not supported on the host-buffer path");
+  if (dev->tile_m == B200K_TILE_SM_PAIR)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: the SM-pair tile is not supported on the host-buffer path");
+  if (dev->lda < dev->k || dev->ldb < dev->k || dev->ldc < dev->n || host->lda < dev->k || host->ldb < dev->k ||
+      host->ldc < dev->n)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: a row pitch of the host or device image is smaller than the row");
   // Row pitches may differ between the host and device images.  B goes up first; then A is
   // uploaded, multiplied and C copied back in row blocks, the copy-back of one block (on the
   // library's copy-back stream) overlapping the upload of the next.

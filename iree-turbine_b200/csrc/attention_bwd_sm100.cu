@@ -601,23 +601,18 @@ template <typename T>
 int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const BwdParams& p, cudaStream_t stream) {
   auto k_dq = attn_bwd_kernel<T, kModeDQ>;
   auto k_dkv = attn_bwd_kernel<T, kModeDKV>;
-  static bool configured = false;
-  if (!configured) {
-    int rc = check_cuda(cudaFuncSetAttribute(k_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem_bytes(kModeDQ)),
-                        "cudaFuncSetAttribute(attention bwd dq smem)");
-    if (rc) return rc;
-    rc = check_cuda(cudaFuncSetAttribute(k_dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem_bytes(kModeDKV)),
-                    "cudaFuncSetAttribute(attention bwd dkv smem)");
-    if (rc) return rc;
-    configured = true;
-  }
+  static bool configured_dq[64] = {}, configured_dkv[64] = {};  // per instantiation and device ordinal
+  int rc = ensure_dynamic_smem(k_dq, bwd_smem_bytes(kModeDQ), configured_dq, "cudaFuncSetAttribute(attention bwd dq smem)");
+  if (rc) return rc;
+  rc = ensure_dynamic_smem(k_dkv, bwd_smem_bytes(kModeDKV), configured_dkv, "cudaFuncSetAttribute(attention bwd dkv smem)");
+  if (rc) return rc;
   const int64_t rows = static_cast<int64_t>(a.batch) * a.q_heads * a.seq_q;
   const int warps_per_block = 8;
   attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block),
                              warps_per_block * 32, 0, stream>>>(
       static_cast<const T*>(a.o), static_cast<const T*>(a.d_o), p.delta, rows, a.q_heads, a.seq_q, a.o_stride_b,
       a.o_stride_h, a.o_stride_s, a.do_stride_b, a.do_stride_h, a.do_stride_s);
-  int rc = check_cuda(cudaGetLastError(), "attn_bwd_delta_kernel launch");
+  rc = check_cuda(cudaGetLastError(), "attn_bwd_delta_kernel launch");
   if (rc) return rc;
   const int grid_dq = a.batch * a.q_heads * p.num_q_tiles;
   k_dq<<<grid_dq, kBwdThreads, bwd_smem_bytes(kModeDQ), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dq, tm.dq, p);

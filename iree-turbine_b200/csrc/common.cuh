@@ -14,6 +14,7 @@ enum : int32_t {
   kStatusGemmTimeout = 1,
   kStatusAttnTimeout = 2,
   kStatusDecodeBadPage = 4,
+  kStatusDecodeLenClamped = 8,
 };
 
 // ---- host-side error plumbing (abi.cu) ----
@@ -46,6 +47,22 @@ int launch_kv_append(const void* k_new, const void* v_new, void* k_cache, void* 
                      int64_t kv_head_stride, int32_t elem_bytes, int32_t* status, cudaStream_t stream);
 int launch_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n,
                          cudaStream_t stream);
+
+// Opts a kernel into more than 48 KB of dynamic shared memory.  The attribute belongs to the
+// (function, device) pair, so it is set once per device ordinal: `done` is the caller's table, one
+// per kernel instantiation.  Setting it twice is harmless, which is why the table needs no lock.
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kfn, int bytes, bool (&done)[64], const char* what) {
+  int dev = -1;
+  int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) return set_error(B200K_ERR_CUDA, "%s: device ordinal %d out of range", what, dev);
+  if (done[dev]) return B200K_OK;
+  rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), what);
+  if (rc) return rc;
+  done[dev] = true;
+  return B200K_OK;
+}
 
 inline size_t dtype_size(int dt) {
   switch (dt) {

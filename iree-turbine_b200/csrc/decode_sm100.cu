@@ -45,6 +45,8 @@ struct DecodeParams {
   int32_t num_seqs, q_heads, kv_heads, group;
   int32_t page_size, num_pages, block_table_stride;
   int32_t chunk_tokens, max_chunks;
+  int32_t max_seq_len;  // seq_lens entries are clamped to [0, max_seq_len]
+  int32_t* status;      // optional device status word
   int64_t kv_batch_stride, kv_head_stride, kv_page_stride;
   float scale_log2;
 };
@@ -138,7 +140,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
   const int chunk = blockIdx.x;
   const int kvh = blockIdx.y;
   const int seq = blockIdx.z;
-  const int len = __ldg(p.seq_lens + seq);
+  // seq_lens is device data the host cannot validate: a length beyond what the grid, the workspace
+  // and the block table were sized for is cut to max_seq_len (and reported), a negative one to 0.
+  const int len_given = __ldg(p.seq_lens + seq);
+  const int len = max(0, min(len_given, p.max_seq_len));
+  if (len_given > p.max_seq_len && chunk == 0 && kvh == 0 && threadIdx.x == 0 && p.status)
+    atomicOr(p.status, kStatusDecodeLenClamped);
   const int chunk_start = chunk * p.chunk_tokens;
   if (chunk_start >= len) return;
   const int chunk_end = min(len, chunk_start + p.chunk_tokens);
@@ -354,8 +361,8 @@ __global__ void __launch_bounds__(kHeadDim) decode_reduce_kernel(const DecodePar
   const int qh = blockIdx.x;
   const int seq = blockIdx.y;
   const int d = threadIdx.x;
-  const int len = __ldg(p.seq_lens + seq);
-  const int n_chunks = (len + p.chunk_tokens - 1) / p.chunk_tokens;
+  const int len = max(0, min(__ldg(p.seq_lens + seq), p.max_seq_len));  // same clamp as phase 1
+  const int n_chunks = (len + p.chunk_tokens - 1) / p.chunk_tokens;      // <= max_chunks
   const int64_t slot0 = (static_cast<int64_t>(seq) * p.q_heads + qh) * p.max_chunks;
   float M = -INFINITY;
   for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, p.ws_ml[slot0 + c].x);
@@ -504,6 +511,8 @@ int launch_decode(const b200k_decode_args& a, cudaStream_t stream) {
   p.block_table_stride = a.block_table_stride;
   p.chunk_tokens = decode_default_chunk(a);
   p.max_chunks = (a.max_seq_len + p.chunk_tokens - 1) / p.chunk_tokens;
+  p.max_seq_len = a.max_seq_len;
+  p.status = a.status;
   p.kv_batch_stride = a.kv_batch_stride;
   p.kv_head_stride = a.kv_head_stride;
   p.kv_page_stride = a.kv_page_stride;
@@ -511,8 +520,8 @@ int launch_decode(const b200k_decode_args& a, cudaStream_t stream) {
   const uint64_t slots = static_cast<uint64_t>(a.num_seqs) * a.q_heads * p.max_chunks;
   p.ws_o = reinterpret_cast<float*>(a.workspace);
   p.ws_ml = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(a.workspace) + slots * kHeadDim * sizeof(float));
-  if (p.max_chunks > 2147483647 / 1)
-    return set_error(B200K_ERR_BAD_SHAPE, "decode_attention: too many chunks");
+  if (p.max_chunks > 65535 * 32)
+    return set_error(B200K_ERR_BAD_SHAPE, "decode_attention: too many chunks (raise chunk_tokens)");
   if (a.dtype == B200K_F16) return launch_decode_typed<__half>(p, a.block_table != nullptr, a.num_seqs, stream);
   return launch_decode_typed<__nv_bfloat16>(p, a.block_table != nullptr, a.num_seqs, stream);
 }

@@ -378,13 +378,9 @@ template <bool BF16, typename OutT>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const PairParams& p, int grid,
                 cudaStream_t stream) {
   auto kfn = gemm_pair_kernel<BF16, OutT>;
-  static bool configured = false;
-  if (!configured) {
-    int rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem),
-                        "cudaFuncSetAttribute(pair gemm smem)");
-    if (rc) return rc;
-    configured = true;
-  }
+  static bool configured[64] = {};  // per instantiation and device ordinal
+  int rc = ensure_dynamic_smem(kfn, kSmem, configured, "cudaFuncSetAttribute(pair gemm smem)");
+  if (rc) return rc;
   kfn<<<grid, kThreads, kSmem, stream>>>(ta, tb, tc, p);
   return check_cuda(cudaGetLastError(), "gemm_pair_kernel launch");
 }

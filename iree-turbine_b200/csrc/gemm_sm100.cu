@@ -526,13 +526,9 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
                cudaStream_t stream) {
   using S = GemmSmem<BN, MT>;
   auto kfn = gemm_nt_kernel<BN, MT, KIND, OutT, GEN>;
-  static bool configured = false;  // per instantiation; benign race (idempotent attribute set)
-  if (!configured) {
-    int rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
-                        "cudaFuncSetAttribute(gemm smem)");
-    if (rc) return rc;
-    configured = true;
-  }
+  static bool configured[64] = {};  // per instantiation and device ordinal
+  int rc = ensure_dynamic_smem(kfn, S::kDynamic, configured, "cudaFuncSetAttribute(gemm smem)");
+  if (rc) return rc;
   kfn<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tb, tc, p);
   return check_cuda(cudaGetLastError(), "gemm_nt_kernel launch");
 }

@@ -16,7 +16,8 @@ from typing import Callable, Optional
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "head_shard", "column_parallel_gemm", "gather_columns", "FusedColumnParallelGemm"]
+__all__ = ["shard_range", "head_shard", "column_parallel_gemm", "gather_columns", "ResultTurn",
+           "FusedColumnParallelGemm"]
 
 
 def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
@@ -55,7 +56,7 @@ def gather_columns(c_local: torch.Tensor, group: Optional[dist.ProcessGroup] = N
     return stage.view(world, m, nl).permute(1, 0, 2).reshape(m, world * nl)
 
 
-def column_parallel_gemm(gemm: Callable[[torch.Tensor], torch.Tensor], b_full_rows: int, world: int, rank: int,
+def column_parallel_gemm(gemm: Callable[[int, int], torch.Tensor], b_full_rows: int, world: int, rank: int,
                          gather: bool, group: Optional[dist.ProcessGroup] = None):
     """Runs ``gemm(b_rows_slice)`` for this rank's rows of B (= columns of C).
 
@@ -68,6 +69,37 @@ def column_parallel_gemm(gemm: Callable[[torch.Tensor], torch.Tensor], b_full_ro
     return gather_columns(c_local, group) if gather else c_local
 
 
+class ResultTurn:
+    """Which of `n` result buffers a call uses: ``begin()`` hands out the next one, ``end()`` closes the
+    call and names the buffer that now holds a finished result.  Every ``begin()`` must be closed by
+    an ``end()`` before the next one, because the barrier in between is what makes the reuse safe."""
+
+    def __init__(self, n: int = 2):
+        if n < 2:
+            raise ValueError("at least two buffers are needed for a result to outlive the next call")
+        self.n = n
+        self.calls = 0
+        self.open = False
+
+    @property
+    def current(self) -> int:
+        return (self.calls - 1) % self.n if self.calls else 0
+
+    def begin(self) -> int:
+        if self.open:
+            raise RuntimeError("finish() of the previous call is missing: its barrier is what lets the "
+                               "buffers alternate safely")
+        self.open = True
+        self.calls += 1
+        return (self.calls - 1) % self.n
+
+    def end(self) -> int:
+        if not self.open:
+            raise RuntimeError("finish() without a call")
+        self.open = False
+        return (self.calls - 1) % self.n
+
+
 class FusedColumnParallelGemm:
     """Column-parallel C = A @ B^T whose all-gather is done by the GEMM kernel itself.
 
@@ -76,6 +108,14 @@ class FusedColumnParallelGemm:
     every rank's copy (``b200k_gemm_nt_allgather``), so the transfer over NVLink overlaps the math
     and there is no separate collective.  ``finish()`` is the cross-rank barrier after which every
     rank may read the full matrix.
+
+    Reuse across calls.  ``finish()`` orders writes before reads; nothing orders a rank's reads of
+    result i before a faster peer's stores of result i + 1.  The class therefore owns TWO result
+    matrices and alternates between them: call i + 1 stores into the other matrix, and call i + 2
+    (which reuses the first) cannot start on any rank before every rank has passed the barrier of
+    call i + 1, which each rank enqueues after its own reads of result i.  So a result stays valid
+    until the ``finish()`` of the NEXT call, provided it is read on the stream that made the calls;
+    a caller that reads it from another stream must order that stream before its next ``finish()``.
     """
 
     def __init__(self, m: int, n: int, out_dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None):
@@ -87,9 +127,15 @@ class FusedColumnParallelGemm:
         if n % self.world:
             raise ValueError(f"N = {n} is not divisible by {self.world} ranks")
         self.m, self.n = m, n
-        self.c = symm_mem.empty((m, n), dtype=out_dtype, device=torch.device("cuda", torch.cuda.current_device()))
-        self.handle = symm_mem.rendezvous(self.c, self.group)
-        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.bufs = [symm_mem.empty((m, n), dtype=out_dtype, device=dev) for _ in range(2)]
+        self.handles = [symm_mem.rendezvous(c, self.group) for c in self.bufs]
+        self.turn = ResultTurn(2)
+
+    @property
+    def c(self) -> torch.Tensor:
+        """The result matrix of the current (or, before the first call, the next) call."""
+        return self.bufs[self.turn.current]
 
     def __call__(self, a: torch.Tensor, b_local: torch.Tensor, scale_a=None, scale_b=None) -> torch.Tensor:
         import ctypes as C
@@ -106,20 +152,25 @@ class FusedColumnParallelGemm:
         g.gemm.m, g.gemm.n, g.gemm.k = self.m, hi - lo, a.size(1)
         g.gemm.lda, g.gemm.ldb, g.gemm.ldc = a.stride(0), b_local.stride(0), 0
         g.gemm.in_dtype = L.DTYPE_CODES[a.dtype]
-        g.gemm.out_dtype = L.DTYPE_CODES[self.c.dtype]
+        idx = self.turn.begin()
+        c = self.bufs[idx]
+        g.gemm.out_dtype = L.DTYPE_CODES[c.dtype]
         g.gemm.scale_a = scale_a.data_ptr() if scale_a is not None else None
         g.gemm.scale_b = scale_b.data_ptr() if scale_b is not None else None
         g.gemm.status = _status_ptr(a.device)
-        for i, ptr in enumerate(self.peer_ptrs):
-            g.peer_c[i] = ptr
+        for i, ptr in enumerate(self.handles[idx].buffer_ptrs):
+            g.peer_c[i] = int(ptr)
         g.num_peers = self.world
-        g.peer_ldc = self.c.stride(0)
+        g.peer_ldc = c.stride(0)
         g.col_offset = lo
         stream = C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)
-        L.check(L.lib().b200k_gemm_nt_allgather(C.byref(g), stream))
-        return self.c
+        with torch.cuda.device(a.device):
+            L.check(L.lib().b200k_gemm_nt_allgather(C.byref(g), stream))
+        return c
 
     def finish(self) -> torch.Tensor:
-        """Cross-rank barrier on the current stream; afterwards ``self.c`` is complete on every rank."""
-        self.handle.barrier()
-        return self.c
+        """Cross-rank barrier on the current stream; afterwards the result of the last call is complete
+        on every rank and stays valid until the ``finish()`` of the next call."""
+        idx = self.turn.end()
+        self.handles[idx].barrier()
+        return self.bufs[idx]

@@ -72,7 +72,7 @@ class GemmCommand:
     transpose_a: bool
     transpose_b: bool
     dtype: torch.dtype
-    mode: int  # 1 forward; 2 / 3 are the reference's backward modes, not covered here
+    mode: int  # 1 forward; 2 / 3 the reference's backward products (dA, dB)
 
     @property
     def func_name(self) -> str:
@@ -179,15 +179,24 @@ def _mm_callable(backend: str, a: torch.Tensor, b: torch.Tensor, notes: List[str
 def build_callable(cmd, backend: str, device, notes: List[str]) -> Callable[[], torch.Tensor]:
     gen = torch.Generator(device=device).manual_seed(SEED)
     if isinstance(cmd, GemmCommand):
-        if cmd.mode != 1:
-            raise Unsupported("only the forward GEMM (-F 1) is covered")
-        a_store = torch.randn((cmd.k, cmd.m) if cmd.transpose_a else (cmd.m, cmd.k), generator=gen, device=device,
-                              dtype=torch.float32).to(cmd.dtype)
-        b_store = torch.randn((cmd.n, cmd.k) if cmd.transpose_b else (cmd.k, cmd.n), generator=gen, device=device,
-                              dtype=torch.float32).to(cmd.dtype)
-        a = a_store.t() if cmd.transpose_a else a_store
-        b = b_store.t() if cmd.transpose_b else b_store
-        return _mm_callable(backend, a, b, notes)
+        def stored(rows, cols):
+            return torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32).to(cmd.dtype)
+
+        if cmd.mode == 1:
+            a_store = stored(*((cmd.k, cmd.m) if cmd.transpose_a else (cmd.m, cmd.k)))
+            b_store = stored(*((cmd.n, cmd.k) if cmd.transpose_b else (cmd.k, cmd.n)))
+            a = a_store.t() if cmd.transpose_a else a_store
+            b = b_store.t() if cmd.transpose_b else b_store
+            return _mm_callable(backend, a, b, notes)
+        # The reference's backward modes (kernel/boo/op_exports/gemm.py:233-270) take the output
+        # gradient and the OTHER operand as stored; a final transpose for a transposed operand is a
+        # view there and costs nothing, so only the product is timed.
+        d_c = stored(cmd.m, cmd.n)
+        if cmd.mode == 2:  # dA = dC @ B^T
+            b_store = stored(*((cmd.n, cmd.k) if cmd.transpose_b else (cmd.k, cmd.n)))
+            return _mm_callable(backend, d_c, b_store if cmd.transpose_b else b_store.t(), notes)
+        a_store = stored(*((cmd.k, cmd.m) if cmd.transpose_a else (cmd.m, cmd.k)))  # dB = A^T @ dC
+        return _mm_callable(backend, a_store if cmd.transpose_a else a_store.t(), d_c, notes)
     name = cmd.name.removeprefix("aten::")
     tensors = []
     for dims, ty, strides, concrete in zip(cmd.input_dims, cmd.input_type, cmd.input_strides, cmd.concrete_inputs):

@@ -47,7 +47,8 @@ class AttentionHost:
         dev.status = _status_ptr(self.device)
         host = _fill_attention_args(q, k, v, out, scale, causal)
         stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        L.check(L.lib().b200k_attention_fwd_host(C.byref(host), C.byref(dev), stream))
+        with torch.cuda.device(self.device):
+            L.check(L.lib().b200k_attention_fwd_host(C.byref(host), C.byref(dev), stream))
         return out
 
 
@@ -80,5 +81,6 @@ class GemmHost:
         dev.status = _status_ptr(self.device)
         host = self._args(a, b, out, None, None)
         stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        L.check(L.lib().b200k_gemm_nt_host(C.byref(host), C.byref(dev), stream))
+        with torch.cuda.device(self.device):
+            L.check(L.lib().b200k_gemm_nt_host(C.byref(host), C.byref(dev), stream))
         return out

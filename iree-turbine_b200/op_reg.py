@@ -386,8 +386,36 @@ def _schema_arguments(op: CustomOp) -> list:
         return []
 
 
+def _tensor_args(args) -> list:
+    out = []
+    for a in args:
+        if isinstance(a, torch.Tensor):
+            out.append(a)
+        elif isinstance(a, (list, tuple)):
+            out.extend(t for t in a if isinstance(t, torch.Tensor))
+    return out
+
+
+def _check_one_device(op: CustomOp, args) -> Optional[torch.device]:
+    """Every tensor argument (auxiliary ones included: lengths, tables, scales, bias) must live on
+    the device of the first one.  The dispatcher picks the CUDA implementation as soon as ONE
+    argument is a CUDA tensor, so without this check a host tensor's pointer, or a pointer into
+    another GPU's memory, would reach a kernel.  Returns that device (None if there is no tensor)."""
+    tensors = _tensor_args(args)
+    if not tensors:
+        return None
+    dev = tensors[0].device
+    for t in tensors[1:]:
+        torch._check(
+            t.device == dev,
+            lambda: f"{op.library.ns}.{op.name}: all tensor arguments must be on one device, got {dev} and {t.device}",
+        )
+    return dev
+
+
 def _meta_impl(op: CustomOp):
     def meta(*args):
+        _check_one_device(op, args)
         sel = EagerKernelSelection(op, args)
         op.select(sel)
         return sel.generate_meta_returns()
@@ -397,7 +425,14 @@ def _meta_impl(op: CustomOp):
 
 def _impl_trampoline(op: CustomOp):
     def handler(*args):
-        result = op.eager_execute(*args)
+        dev = _check_one_device(op, args)
+        if dev is not None and dev.type == "cuda":
+            # launch on the tensors' device, whatever device happens to be current (the reference
+            # takes the device from the tensors as well, runtime/op_reg/eager.py:71-100)
+            with torch.cuda.device(dev):
+                result = op.eager_execute(*args)
+        else:
+            result = op.eager_execute(*args)
         if result is NotImplemented:
             raise NotImplementedError(
                 f"{op.library.ns}.{op.name} has no device implementation (eager_execute returned "

@@ -525,6 +525,7 @@ def _launch_decode(args: L.DecodeArgs, q: Tensor) -> None:
     ws = torch.empty(need, dtype=torch.uint8, device=q.device)
     args.workspace = ws.data_ptr()
     args.workspace_bytes = need
+    args.status = _status_ptr(q.device)
     L.check(lib.b200k_decode_attention(C.byref(args), _stream(q)))
 
 
@@ -552,7 +553,7 @@ class decode_attention(CustomOp):
         sel.return_new_tensor(list(q.t.shape), q.t.dtype)
 
     def eager_execute(self, q, k, v, seq_lens, scale, chunk_tokens=0):
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        q, k, v, seq_lens = q.contiguous(), k.contiguous(), v.contiguous(), seq_lens.contiguous()
         o = torch.empty_like(q)
         args = L.DecodeArgs()
         args.q, args.k_cache, args.v_cache, args.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
@@ -599,7 +600,7 @@ class paged_decode_attention(CustomOp):
 
     def eager_execute(self, q, k_cache, v_cache, block_table, seq_lens, scale, chunk_tokens=0):
         q, k_cache, v_cache = q.contiguous(), k_cache.contiguous(), v_cache.contiguous()
-        block_table = block_table.contiguous()
+        block_table, seq_lens = block_table.contiguous(), seq_lens.contiguous()
         o = torch.empty_like(q)
         args = L.DecodeArgs()
         args.q, args.k_cache, args.v_cache, args.o = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), o.data_ptr()
@@ -640,7 +641,7 @@ class paged_gather(CustomOp):
 
     def eager_execute(self, cache, block_table, seq_lens, max_seq_len):
         cache = cache.contiguous()
-        block_table = block_table.contiguous()
+        block_table, seq_lens = block_table.contiguous(), seq_lens.contiguous()
         out = torch.zeros((block_table.size(0), cache.size(1), max_seq_len, cache.size(3)), dtype=cache.dtype,
                           device=cache.device)
         L.check(

@@ -29,7 +29,7 @@ def test_every_declared_symbol_is_exported_and_bound(kernel_lib):
         assert hasattr(kernel_lib, name), f"{name} is declared in include/b200k.h but not exported"
         assert name in L.EXPORTED_SYMBOLS, f"{name} has no ctypes prototype"
     assert sorted(L.EXPORTED_SYMBOLS) == declared
-    assert kernel_lib.b200k_abi_version() == 1
+    assert kernel_lib.b200k_abi_version() == L.ABI_VERSION == 2
 
 
 def test_struct_layouts_match_the_header():
@@ -39,7 +39,7 @@ def test_struct_layouts_match_the_header():
         "b200k_attention_args": (L.AttentionArgs, ["q", "batch", "head_dim", "q_stride_b", "o_stride_s", "dtype",
                                                    "scale", "status", "lse"]),
         "b200k_decode_args": (L.DecodeArgs, ["q", "workspace_bytes", "num_seqs", "max_seq_len", "kv_batch_stride",
-                                             "kv_page_stride", "dtype", "scale"]),
+                                             "kv_page_stride", "dtype", "scale", "status"]),
         "b200k_paged_attention_args": (L.PagedAttentionArgs, ["q", "seq_lens", "batch", "head_dim", "page_size",
                                                               "block_table_stride", "q_stride_b", "o_stride_s",
                                                               "kv_page_stride", "kv_head_stride", "dtype", "scale",

@@ -97,6 +97,33 @@ def test_out_of_range_page_is_ignored_not_dereferenced():
     assert bool(torch.isfinite(o[1].float()).all())
 
 
+def test_length_above_the_table_capacity_is_cut_and_reported():
+    """seq_lens is device data: an entry beyond what the block table (paged) or the history buffer
+    (contiguous) holds is treated as that capacity and status bit 3 is raised; nothing is read past
+    the table row and the reduction stays inside the sequence's own partials."""
+    q, kc, vc, bt, sl = oracle.make_paged_decode_inputs(num_seqs=3, q_heads=8, kv_heads=2, lens=[40, 100, 7], seed=8)
+    cap = bt.shape[1] * 16  # 112 tokens: the last page of sequence 1 is full of (random) rows
+    too_long = sl.clone()
+    too_long[1] = 5000
+    cut = sl.clone()
+    cut[1] = cap
+    tb.reset_device_status()
+    o = _paged(q, kc, vc, bt, too_long, chunk=64)
+    assert tb.device_status() == 8
+    tb.reset_device_status()
+    oracle.assert_close_half(o, oracle.paged_decode_attention(q, kc, vc, bt, cut, SCALE))
+    assert torch.equal(o, _paged(q, kc, vc, bt, cut, chunk=64)), "the cut length must behave exactly like the capacity"
+    assert tb.device_status() == 0
+    # contiguous form: capacity = rows of the history buffer; a negative length counts as zero
+    qc, k, v = oracle.make_attention_inputs(3, 8, 2, 1, 200, 128, torch.float16, seed=9)
+    lens = torch.tensor([100000, 17, -5], dtype=torch.int32)
+    oc = torch.ops.b200k.decode_attention(qc[:, :, 0].to(DEV), k.to(DEV), v.to(DEV), lens.to(DEV), SCALE)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 8
+    tb.reset_device_status()
+    oracle.assert_close_half(oc, oracle.decode_attention(qc[:, :, 0], k, v, torch.tensor([200, 17, 0], dtype=torch.int32), SCALE))
+
+
 def test_config_paged_decode_64_seqs():
     """64 sequences, 32 q-heads / 8 kv-heads, lengths U[512, 8192], page 16, permuted pool."""
     q, kc, vc, bt, sl = oracle.make_paged_decode_inputs(seed=10)

@@ -34,6 +34,24 @@ def test_head_shard_keeps_groups_together():
         tdist.head_shard(q, k, k, 4, 0)
 
 
+def test_result_buffers_alternate_and_need_the_barrier_in_between():
+    turn = tdist.ResultTurn(2)
+    assert turn.current == 0
+    seen = []
+    for _ in range(5):
+        b = turn.begin()
+        assert turn.current == b
+        with pytest.raises(RuntimeError, match="finish"):
+            turn.begin()  # the barrier of the open call has not been enqueued yet
+        assert turn.end() == b and turn.current == b
+        seen.append(b)
+    assert seen == [0, 1, 0, 1, 0]  # a result is overwritten two calls later, never by the next one
+    with pytest.raises(RuntimeError):
+        turn.end()
+    with pytest.raises(ValueError):
+        tdist.ResultTurn(1)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -105,6 +105,25 @@ def test_shipped_ops_reject_bad_arguments():
         torch.ops.b200k.attention(m(1, 3, 8, 128), m(1, 2, 8, 128), m(1, 2, 8, 128), 1.0, False)
 
 
+def test_tensor_arguments_on_different_devices_are_rejected_before_any_launch():
+    """A host-resident seq_lens / scale next to device tensors would hand a host pointer to a kernel:
+    both the Meta path and the device trampoline refuse it."""
+    from iree_turbine_b200.op_reg import _impl_trampoline
+
+    m = lambda *s, dtype=torch.float16: torch.empty(*s, dtype=dtype, device="meta")  # noqa: E731
+    qd, kv = m(5, 8, 128), m(5, 2, 64, 128)
+    with pytest.raises(RuntimeError, match="one device"):
+        torch.ops.b200k.decode_attention(qd, kv, kv, torch.zeros(5, dtype=torch.int32), 0.1)
+    a8 = m(128, 64, dtype=torch.float8_e4m3fn)
+    with pytest.raises(RuntimeError, match="one device"):
+        torch.ops.b200k.gemm_fp8_nt(a8, a8, torch.ones(1), m(1, dtype=torch.float32))
+    # the device implementation's trampoline, called directly: rejected before eager_execute runs
+    op = ALL_CUSTOM_OP_REGS["b200k.paged_decode_attention"]
+    pool, bt = m(40, 2, 16, 128), m(5, 7, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="one device"):
+        _impl_trampoline(op)(qd, pool, pool, bt, torch.zeros(5, dtype=torch.int32), 0.1, 0)
+
+
 def test_cpu_tensors_have_no_implementation():
     a = torch.zeros(8, 8, dtype=torch.float16)
     with pytest.raises(NotImplementedError, match="CPU"):

@@ -76,6 +76,33 @@ def test_static_scratch_decode_matches_the_workspace_entry_point(kernel_lib):
         oracle.assert_close_half(o_new, oracle.paged_decode_attention(q, kc, vc, bt, sl, SCALE))
 
 
+def test_static_scratch_decode_cuts_a_length_beyond_the_table(kernel_lib):
+    """A seq_lens entry above the block table's capacity must not make the reduction walk into the
+    next head's slots of the shared array: it is cut to the capacity and reported (status bit 3)."""
+    lib = kernel_lib
+    host = oracle.make_paged_decode_inputs(num_seqs=3, q_heads=16, kv_heads=4, lens=[33, 90, 5], seed=23)
+    q, kc, vc, bt, sl = (t.to(DEV) for t in host)
+    cap = bt.size(1) * kc.size(2)
+    bad = host[4].clone()
+    bad[1] = 10 ** 6
+    cut = host[4].clone()
+    cut[1] = cap
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    outs = []
+    for lens in (bad, cut):
+        o = torch.full_like(q, float("nan"))
+        a = _args(q, kc, vc, bt, lens.to(DEV), o, 64)
+        a.status = status.data_ptr()
+        L.check(lib.b200k_decode_attention_static(C.byref(a), stream))
+        torch.cuda.synchronize()
+        outs.append((o, int(status.item())))
+        status.zero_()
+    assert outs[0][1] == 8 and outs[1][1] == 0
+    assert torch.equal(outs[0][0], outs[1][0])
+    oracle.assert_close_half(outs[0][0], oracle.paged_decode_attention(host[0], host[1], host[2], host[3], cut, SCALE))
+
+
 def test_static_scratch_decode_rejects_oversized_problems(kernel_lib):
     lib = kernel_lib
     # 4096 sequences x 32 heads x 16 chunks of 64 tokens needs ~1 GB of partials: far over the limit.
