@@ -1,18 +1,26 @@
 """Throughput benchmark for the GEMM / attention / decode kernels.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--no-extras] [--impl reference]
 
-Default workload: non-causal attention f16, batch 8, 32 heads, Sq = Skv = 1024, head dim 128.
-Other workloads (same JSON line): gemm_f16, attn_causal, attn_bwd_causal, paged_decode, gemm_fp8.
+The headline workload (``--workload``, default ``attn_causal``) is causal prefill attention bf16,
+batch 4, 32 heads, S = 4096, head dim 128.  With N > 1 it is ONE problem sharded by heads (32 / N
+heads of every batch element per GPU, no data-path collective): strong scaling.  The other
+workloads of the metric -- ``gemm_f16`` (2048^3, fp32 out), ``attn_noncausal`` (f16 B8 H32 S1024),
+``paged_decode`` (64 sequences, GQA 32/8, page 16) and ``gemm_fp8`` (8192^3 e4m3, bf16 out;
+column-parallel over N with N > 1) -- are measured in the same run and reported under
+``"workloads"`` in the same JSON line, each with its own roofline, end-to-end figure, CPU baseline
+(N = 1) and a parity figure against the CPU oracle on a sampled slice (computed after the timed
+region).  ``--no-extras`` measures the headline workload only.
 
 A step is one pass of the kernel over one batch of synthetic inputs.  Each step is timed with
 CUDA events on the launching stream; between steps either the inputs are larger than L2 or L2 is
-flushed by writing a 256 MB buffer (stated in ``config.l2``).  With N > 1 every rank runs the
-same workload on its own GPU (independent units: batch x head shards; no data-path collective),
-the timed region is bracketed by barrier + synchronize and the maximum over ranks is used.
+flushed by writing a 256 MB buffer (stated in ``config.l2``).  Timed regions are bracketed by
+barrier + synchronize and the maximum over ranks is used.  Besides the per-step (burst) figure
+a sustained leg runs the headline kernel back to back for at least a second, with the SM clock
+sampled meanwhile, and is compared with the sustained cuBLAS figure of MEASURED_PEAKS.json.
 
-``--impl reference`` times the CPU restatement of the reference path (the oracle) on the host
-cores on a bounded sample of the same workload; rank 0 only.
+``--impl reference`` times the CPU statement of the reference path on the host cores on a bounded
+sample of the same workload (the faster of the oracle and torch's own CPU operator); rank 0 only.
 """
 
 from __future__ import annotations
@@ -45,6 +53,16 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def best_of(fn, n):
+    best = None
+    for _ in range(n):
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
 # ---------------------------------------------------------------------------------------------
 # workloads
 # ---------------------------------------------------------------------------------------------
@@ -59,21 +77,38 @@ class Workload:
     bound = "tensor"
     launches_per_step = 1
     needs_flush = False
+    peak_scale = 1.0
+    scaling = "strong"
+    world, rank = 1, 0
 
-    scaling = "weak"  # per-GPU work fixed as N grows, unless a workload says otherwise
+    def shard(self, world: int, rank: int):
+        self.world, self.rank = world, rank
 
     def config(self) -> dict: ...
     def setup(self, dev): ...
-    def shard(self, world: int, rank: int):
-        """Called before setup() when N > 1; default: every rank runs the whole workload (independent units)."""
     def step(self): ...
     def units_per_step(self) -> float:
-        """flops (tensor-bound) or bytes (hbm-bound) per step."""
+        """flops (tensor-bound) or bytes (hbm-bound) THIS RANK processes per step."""
     def setup_e2e(self, dev): ...
     def step_e2e(self): ...
     def e2e_bytes(self) -> tuple: ...
     def cpu_sample(self) -> tuple:
-        """Runs the oracle on a bounded sample; returns (units processed, seconds, description)."""
+        """Runs the CPU statement on a bounded sample; returns (units processed, seconds, description)."""
+    def parity(self) -> dict:
+        """Compares the last step's result with the CPU oracle on a sampled slice (untimed)."""
+
+    def release(self):
+        for k in list(self.__dict__):
+            if isinstance(self.__dict__[k], torch.Tensor) or k in ("e2e", "fused", "host", "grads"):
+                del self.__dict__[k]
+
+
+def _close(got: torch.Tensor, ref: torch.Tensor, rtol=1e-2, atol=1e-2) -> dict:
+    """max |got - ref| and the worst ratio to the allclose bound atol + rtol |ref| (<= 1 passes)."""
+    d = (got.float().cpu() - ref.float()).abs()
+    bound = atol + rtol * ref.float().abs()
+    return {"max_abs_err": float(d.max()), "worst_over_bound": float((d / bound).max()), "rtol": rtol, "atol": atol,
+            "ok": bool((d <= bound).all())}
 
 
 class AttentionWL(Workload):
@@ -81,6 +116,7 @@ class AttentionWL(Workload):
         self.name = name
         self.traffic_bytes = traffic
         self.b, self.h, self.s = batch, heads, seq
+        self.h_local, self.h0 = heads, 0
         self.tdtype = dtype
         self.dtype = "f16" if dtype == torch.float16 else "bf16"
         self.causal = causal
@@ -88,16 +124,39 @@ class AttentionWL(Workload):
         kind = "causal" if causal else "non-causal"
         self.metric = f"attention fwd TFLOP/s ({kind} {self.dtype} B{batch} H{heads} S{seq} D128)"
 
+    def shard(self, world, rank):
+        from iree_turbine_b200 import dist as tdist
+
+        super().shard(world, rank)
+        if self.h % world:
+            raise SystemExit(f"bench.py: {self.h} heads cannot be split evenly over {world} GPUs")
+        self.h0, h1 = tdist.shard_range(self.h, world, rank)
+        self.h_local = h1 - self.h0
+
     def config(self):
-        nbytes = 4 * self.b * self.h * self.s * 128 * 2
-        return {"workload": self.name, "batch": self.b, "heads": self.h, "seq_q": self.s, "seq_kv": self.s,
-                "head_dim": 128, "causal": self.causal, "scale": SCALE,
-                "l2": f"inputs larger than L2 ({nbytes / 1e6:.0f} MB touched per step)"}
+        nbytes = 4 * self.b * self.h_local * self.s * 128 * 2
+        cfg = {"workload": self.name, "batch": self.b, "heads": self.h, "seq_q": self.s, "seq_kv": self.s,
+               "head_dim": 128, "causal": self.causal, "scale": SCALE,
+               "l2": f"inputs larger than L2 ({nbytes / 1e6:.0f} MB touched per step and GPU)"}
+        if self.world > 1:
+            cfg["parallelism"] = (f"one problem, heads sharded over {self.world} GPUs ({self.h_local} heads of every "
+                                  "batch element per GPU), no collective")
+            if nbytes < 200e6:
+                cfg["l2"] = f"L2 flushed between steps (256 MB write); {nbytes / 1e6:.0f} MB touched per step and GPU"
+        return cfg
+
+    @property
+    def needs_flush(self):
+        return 4 * self.b * self.h_local * self.s * 128 * 2 < 200e6
 
     def _make(self, dev, seed=10):
+        """The whole problem from one seed (identical on every rank), then this rank's heads."""
         g = torch.Generator(device=dev).manual_seed(seed)
-        return [(torch.randn(self.b, self.h, self.s, 128, generator=g, device=dev) * self.std).to(self.tdtype)
-                for _ in range(3)]
+        out = []
+        for _ in range(3):
+            t = (torch.randn(self.b, self.h, self.s, 128, generator=g, device=dev) * self.std).to(self.tdtype)
+            out.append(t[:, self.h0:self.h0 + self.h_local].contiguous())
+        return out
 
     def setup(self, dev):
         self.q, self.k, self.v = self._make(dev)
@@ -106,38 +165,54 @@ class AttentionWL(Workload):
         self.o = torch.ops.b200k.attention(self.q, self.k, self.v, SCALE, self.causal)
 
     def units_per_step(self):
-        f = 4.0 * self.b * self.h * self.s * self.s * 128
+        f = 4.0 * self.b * self.h_local * self.s * self.s * 128
         return f / 2 if self.causal else f
 
     def setup_e2e(self, dev):
         from iree_turbine_b200 import host_api
 
-        q, k, v = self._make(dev)
-        self.hq, self.hk, self.hv = (t.cpu().pin_memory() for t in (q, k, v))
+        self.hq, self.hk, self.hv = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
         self.ho = torch.empty_like(self.hq).pin_memory()
-        self.e2e = host_api.AttentionHost(self.b, self.h, self.h, self.s, self.s, self.tdtype, dev)
+        self.e2e = host_api.AttentionHost(self.b, self.h_local, self.h_local, self.s, self.s, self.tdtype, dev)
 
     def step_e2e(self):
         self.e2e(self.hq, self.hk, self.hv, self.ho, SCALE, self.causal)
 
     def e2e_bytes(self):
-        n = self.b * self.h * self.s * 128 * 2
+        n = self.b * self.h_local * self.s * 128 * 2
         return 3 * n, n
 
-    def cpu_sample(self):
+    def cpu_sample(self, heads=None):
+        """The faster of the two CPU statements of the same math: the oracle (scores materialised)
+        and torch's fused CPU operator on fp32 upcasts."""
         from oracle import oracle
 
-        bs, hs = 1, min(self.h, 8 if self.s > 2048 else 32)
+        bs = 1
+        hs = heads if heads is not None else min(self.h, 16 if self.s > 2048 else 32)
         q, k, v = oracle.make_attention_inputs(bs, hs, hs, self.s, self.s, 128, self.tdtype, seed=10, std=self.std)
-        best = None
-        for _ in range(2):
-            t0 = time.perf_counter()
-            oracle.attention(q, k, v, SCALE, self.causal)
-            dt = time.perf_counter() - t0
-            best = dt if best is None else min(best, dt)
+        qf, kf, vf = q.float(), k.float(), v.float()
+        t_sdpa = best_of(lambda: torch.nn.functional.scaled_dot_product_attention(
+            qf, kf, vf, is_causal=self.causal, scale=SCALE), 2)
+        t_oracle = best_of(lambda: oracle.attention(q, k, v, SCALE, self.causal), 1)
         f = 4.0 * bs * hs * self.s * self.s * 128
         f = f / 2 if self.causal else f
-        return f, best, f"oracle.attention on batch {bs} x {hs} heads of the same shape, best of 2"
+        which = "torch CPU scaled_dot_product_attention on fp32 upcasts" if t_sdpa <= t_oracle else "oracle.attention"
+        return f, min(t_sdpa, t_oracle), (f"{which} (the faster of the two; the other took "
+                                          f"{max(t_sdpa, t_oracle):.2f} s) on batch {bs} x {hs} heads of the same shape")
+
+    def parity(self):
+        from oracle import oracle
+
+        picks = [(0, 0), (self.b - 1, self.h_local - 1)]
+        worst = None
+        for b, h in picks:
+            ref = oracle.attention(self.q[b:b + 1, h:h + 1].cpu(), self.k[b:b + 1, h:h + 1].cpu(),
+                                   self.v[b:b + 1, h:h + 1].cpu(), SCALE, self.causal)
+            r = _close(self.o[b:b + 1, h:h + 1], ref)
+            if worst is None or r["worst_over_bound"] > worst["worst_over_bound"]:
+                worst = r
+        worst["sample"] = f"(batch, local head) {picks} of this rank's output against oracle.attention"
+        return worst
 
 
 class AttentionBwdWL(AttentionWL):
@@ -155,7 +230,8 @@ class AttentionBwdWL(AttentionWL):
 
     def _make_do(self, dev, seed=11):
         g = torch.Generator(device=dev).manual_seed(seed)
-        return torch.randn(self.b, self.h, self.s, 128, generator=g, device=dev).to(self.tdtype)
+        t = torch.randn(self.b, self.h, self.s, 128, generator=g, device=dev).to(self.tdtype)
+        return t[:, self.h0:self.h0 + self.h_local].contiguous()
 
     def setup(self, dev):
         self.q, self.k, self.v = self._make(dev)
@@ -182,8 +258,8 @@ class AttentionBwdWL(AttentionWL):
             h.copy_(g, non_blocking=True)
 
     def e2e_bytes(self):
-        n = self.b * self.h * self.s * 128 * 2
-        return 5 * n + self.b * self.h * self.s * 4, 3 * n
+        n = self.b * self.h_local * self.s * 128 * 2
+        return 5 * n + self.b * self.h_local * self.s * 4, 3 * n
 
     def cpu_sample(self):
         from oracle import oracle
@@ -191,22 +267,29 @@ class AttentionBwdWL(AttentionWL):
         bs, hs = 1, min(self.h, 4 if self.s > 2048 else 16)
         q, k, v = oracle.make_attention_inputs(bs, hs, hs, self.s, self.s, 128, self.tdtype, seed=10, std=self.std)
         d_o = torch.randn(q.shape, generator=torch.Generator().manual_seed(11)).to(self.tdtype)
-        best = None
-        for _ in range(2):
-            t0 = time.perf_counter()
-            oracle.attention_bwd(q, k, v, d_o, SCALE, self.causal)
-            dt = time.perf_counter() - t0
-            best = dt if best is None else min(best, dt)
+        best = best_of(lambda: oracle.attention_bwd(q, k, v, d_o, SCALE, self.causal), 2)
         f = 2.5 * 4.0 * bs * hs * self.s * self.s * 128
         f = f / 2 if self.causal else f
         return f, best, f"oracle.attention_bwd on batch {bs} x {hs} heads of the same shape, best of 2"
 
+    def parity(self):
+        from oracle import oracle
+
+        b, h = self.b - 1, self.h_local - 1
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        refs = oracle.attention_bwd(self.q[sl].cpu(), self.k[sl].cpu(), self.v[sl].cpu(), self.d_o[sl].cpu(), SCALE,
+                                    self.causal)
+        worst = 0.0
+        for got, ref in zip(self.grads, refs):
+            worst = max(worst, float((got[sl].float().cpu() - ref).abs().max() / max(float(ref.abs().max()), 1.0)))
+        return {"max_err_over_max_ref": worst, "tol": 1e-2, "ok": worst <= 1e-2,
+                "sample": f"(batch, local head) ({b}, {h}): dQ, dK, dV against oracle.attention_bwd"}
+
 
 class GemmWL(Workload):
-    needs_flush = True
-
-    def __init__(self, name, n, fp8):
+    def __init__(self, name, n, fp8, mode="fused_gather"):
         self.name, self.n, self.fp8 = name, n, fp8
+        self.mode = mode  # N > 1, fp8 only: "shard_only" | "fused_gather" | "nccl_gather"
         self.traffic_bytes = 417.1e6 if (fp8 and n == 8192) else (16.9e6 if (not fp8 and n == 2048) else None)
         # the measured peak is a bf16 GEMM; e4m3 runs the tensor pipe at twice that rate
         self.peak_scale = 2.0 if fp8 else 1.0
@@ -215,22 +298,29 @@ class GemmWL(Workload):
         self.metric = f"GEMM TFLOP/s ({self.dtype} NT M=N=K={n}, fp32 accumulate, {out} out)"
         self.needs_flush = (2 * n * n * (1 if fp8 else 2) + n * n * (2 if fp8 else 4)) < 200e6
 
+    def shard(self, world, rank):
+        # fp8 GEMM: column-parallel over N (strong scaling).  f16 2048^3 is too small to shard:
+        # independent replicas (weak scaling), every rank the whole problem.
+        super().shard(world, rank)
+        if not self.fp8:
+            self.scaling = "weak"
+
+    @property
+    def sharded(self):
+        return self.fp8 and self.world > 1
+
     def config(self):
         cfg = {"workload": self.name, "m": self.n, "n": self.n, "k": self.n,
                "l2": "L2 flushed between steps (256 MB write)" if self.needs_flush else "operands larger than L2"}
-        if self.world > 1:
-            cfg["parallelism"] = (f"column-parallel over N on {self.world} GPUs, all-gather of C fused into the "
-                                  "GEMM epilogue (peer stores) + cross-rank barrier inside the timed step")
+        if self.sharded:
+            how = {"shard_only": "column shards of C left in place (no exchange)",
+                   "fused_gather": "all-gather of C fused into the GEMM epilogue (peer stores) + cross-rank barrier "
+                                   "inside the timed step",
+                   "nccl_gather": "local GEMM, then NCCL all-gather of C + de-interleaving copy inside the timed step"}
+            cfg["parallelism"] = f"column-parallel over N on {self.world} GPUs, {how[self.mode]}"
+        elif self.world > 1:
+            cfg["parallelism"] = f"{self.world} independent replicas of the whole problem"
         return cfg
-
-    world, rank = 1, 0
-
-    def shard(self, world, rank):
-        # fp8 GEMM: column-parallel over N, all-gather of C fused into the epilogue (strong scaling).
-        # f16 2048^3 is too small to shard: independent replicas.
-        if self.fp8:
-            self.world, self.rank = world, rank
-            self.scaling = "strong"
 
     def setup(self, dev):
         g = torch.Generator(device=dev).manual_seed(10)
@@ -241,46 +331,53 @@ class GemmWL(Workload):
             self.b, self.sb = torch.ops.b200k.quantize_e4m3(b)
         else:
             self.a, self.b = a.half(), b.half()
-        if self.world > 1:
+        del a, b
+        self.col0 = 0
+        if self.sharded:
             from iree_turbine_b200 import dist as tdist
 
             lo, hi = tdist.shard_range(self.n, self.world, self.rank)
+            self.col0 = lo
             self.b = self.b[lo:hi].contiguous()
-            self.fused = tdist.FusedColumnParallelGemm(self.n, self.n, torch.bfloat16)
+            if self.mode == "fused_gather":
+                self.fused = tdist.FusedColumnParallelGemm(self.n, self.n, torch.bfloat16)
 
     def step(self):
-        if self.world > 1:
+        if self.sharded and self.mode == "fused_gather":
             self.fused(self.a, self.b, self.sa, self.sb)
             self.c = self.fused.finish()
+        elif self.sharded and self.mode == "nccl_gather":
+            from iree_turbine_b200 import dist as tdist
+
+            self.c = tdist.gather_columns(torch.ops.b200k.gemm_fp8_nt(self.a, self.b, self.sa, self.sb))
         elif self.fp8:
             self.c = torch.ops.b200k.gemm_fp8_nt(self.a, self.b, self.sa, self.sb)
         else:
             self.c = torch.ops.b200k.gemm_nt(self.a, self.b)
 
     def units_per_step(self):
-        return 2.0 * self.n ** 3 / self.world
+        return 2.0 * self.n ** 3 / (self.world if self.sharded else 1)
 
     def setup_e2e(self, dev):
         from iree_turbine_b200 import host_api
 
-        if self.world > 1:
-            # sharded run: the rank's operands come from pinned host memory each step, the full C
-            # is read back by every rank
-            self.ha, self.hb = self.a.cpu().pin_memory(), self.b.cpu().pin_memory()
-            self.hc = torch.empty(self.n, self.n, dtype=torch.bfloat16).pin_memory()
-            return
-        self.setup(dev)
         self.ha, self.hb = self.a.cpu().pin_memory(), self.b.cpu().pin_memory()
+        if self.sharded:
+            # sharded run: the rank's operands come from pinned host memory each step, the full C
+            # (or the rank's shard, when it stays in place) is read back by every rank
+            cols = self.b.size(0) if self.mode == "shard_only" else self.n
+            self.hc = torch.empty(self.n, cols, dtype=torch.bfloat16).pin_memory()
+            return
         out_dtype = torch.bfloat16 if self.fp8 else torch.float32
         self.hc = torch.empty(self.n, self.n, dtype=out_dtype).pin_memory()
         self.e2e = host_api.GemmHost(self.n, self.n, self.n, self.a.dtype, out_dtype, dev)
 
     def step_e2e(self):
-        if self.world > 1:
+        if self.sharded:
             self.a.copy_(self.ha, non_blocking=True)
             self.b.copy_(self.hb, non_blocking=True)
-            self.fused(self.a, self.b, self.sa, self.sb)
-            self.hc.copy_(self.fused.finish(), non_blocking=True)
+            self.step()
+            self.hc.copy_(self.c, non_blocking=True)
         elif self.fp8:
             self.e2e(self.ha, self.hb, self.hc, self.sa, self.sb)
         else:
@@ -288,8 +385,8 @@ class GemmWL(Workload):
 
     def e2e_bytes(self):
         es = 1 if self.fp8 else 2
-        if self.world > 1:
-            return self.n * self.n * es + self.b.numel() * es, self.n * self.n * 2
+        if self.sharded:
+            return self.n * self.n * es + self.b.numel() * es, self.hc.numel() * 2
         return 2 * self.n * self.n * es, self.n * self.n * (2 if self.fp8 else 4)
 
     def cpu_sample(self):
@@ -302,13 +399,44 @@ class GemmWL(Workload):
         else:
             a, b = oracle.make_gemm_inputs(rows, self.n, self.n, torch.float16, seed=10)
             fn = lambda: oracle.gemm_nt(a, b)  # noqa: E731
-        best = None
-        for _ in range(3):
-            t0 = time.perf_counter()
-            fn()
-            dt = time.perf_counter() - t0
-            best = dt if best is None else min(best, dt)
+        best = best_of(fn, 3)
         return 2.0 * rows * self.n * self.n, best, f"oracle GEMM on {rows} rows of A against all of B, best of 3"
+
+    def parity(self):
+        from oracle import oracle
+
+        rows = 128
+        r0 = self.n - rows
+        a, b = self.a[r0:].cpu(), self.b.cpu()
+        if not self.fp8:
+            r = _close(self.c[r0:], oracle.gemm_nt(a, b))
+            r["sample"] = f"last {rows} rows of C against oracle.gemm_nt"
+            return r
+        ref = oracle.gemm_fp8_nt(a, b, self.sa.cpu(), self.sb.cpu())  # this rank's columns
+        got = self.c[r0:]
+        what = "this rank's column shard"
+        if self.sharded and self.mode != "shard_only":
+            # the gathered matrix: this rank's own columns against the oracle, and every column
+            # against the rank that computed it (all ranks must hold identical bits)
+            import torch.distributed as dist
+
+            mine = got[:, self.col0:self.col0 + self.b.size(0)]
+            digest = got.view(torch.int16).to(torch.int64).sum().reshape(1)
+            lo, hi = digest.clone(), digest.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            same = bool((lo == hi).item())
+            got = mine
+            what = "this rank's columns of the GATHERED matrix"
+        else:
+            same = None
+        fro, mx = oracle.fp8_errors(got, ref)
+        out = {"rel_frobenius": fro, "max_abs_over_rms": mx, "tol": 3e-2, "ok": fro <= 3e-2 and mx <= 3e-2,
+               "sample": f"last {rows} rows, {what}, against oracle.gemm_fp8_nt"}
+        if same is not None:
+            out["gathered_rows_identical_on_all_ranks"] = same
+            out["ok"] = out["ok"] and same
+        return out
 
 
 class PagedDecodeWL(Workload):
@@ -323,9 +451,18 @@ class PagedDecodeWL(Workload):
         self.name = name
 
     def config(self):
-        return {"workload": self.name, "num_seqs": 64, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "page_size": 16,
-                "len_range": [512, 8192], "sum_len": int(self.sum_len) if hasattr(self, "sum_len") else None,
-                "l2": "KV pool larger than L2 (about 1.1 GB read per step)"}
+        cfg = {"workload": self.name, "num_seqs": 64, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "page_size": 16,
+               "len_range": [512, 8192], "sum_len": int(self.sum_len) if hasattr(self, "sum_len") else None,
+               "l2": "KV pool larger than L2 (about 1.1 GB read per step)"}
+        if self.world > 1:
+            cfg["parallelism"] = (f"one problem, sequences sharded over {self.world} GPUs ({64 // self.world} per GPU, "
+                                  "each with the whole page pool resident), no collective")
+            cfg["l2"] = "L2 flushed between steps (256 MB write)"
+        return cfg
+
+    @property
+    def needs_flush(self):
+        return self.world > 1
 
     def _host_inputs(self):
         from oracle import oracle
@@ -333,7 +470,11 @@ class PagedDecodeWL(Workload):
         return oracle.make_paged_decode_inputs(seed=10)
 
     def setup(self, dev):
+        from iree_turbine_b200 import dist as tdist
+
         q, kc, vc, bt, sl = self._host_inputs()
+        lo, hi = tdist.shard_range(64, self.world, self.rank)
+        q, bt, sl = q[lo:hi].contiguous(), bt[lo:hi].contiguous(), sl[lo:hi].contiguous()
         self.sum_len = int(sl.sum())
         self.pages = int(((sl + 15) // 16).sum())
         self.host = (q, kc, vc, bt, sl)
@@ -344,12 +485,11 @@ class PagedDecodeWL(Workload):
 
     def units_per_step(self):
         # K and V rows actually read + Q and O + block-table entries + seq_lens
-        return self.sum_len * 8 * 128 * 2 * 2 + 2 * 64 * 32 * 128 * 2 + 4 * self.pages + 4 * 64
+        return self.sum_len * 8 * 128 * 2 * 2 + 2 * self.q.numel() * 2 + 4 * self.pages + 4 * self.sl.numel()
 
     def setup_e2e(self, dev):
         # The KV pool is state that lives on the device across decode steps; per step the host
         # provides the query, the block table and the lengths and reads the output back.
-        self.setup(dev)
         q, kc, vc, bt, sl = self.host
         self.hq, self.hbt, self.hsl = q.pin_memory(), bt.pin_memory(), sl.pin_memory()
         self.ho = torch.empty_like(q).pin_memory()
@@ -375,15 +515,32 @@ class PagedDecodeWL(Workload):
         nbytes = int(sl[sub].sum()) * 8 * 128 * 2 * 2
         return float(nbytes), dt, "oracle.paged_decode_attention on the first 8 of the 64 sequences, one run"
 
+    def parity(self):
+        from oracle import oracle
+
+        q, kc, vc, bt, sl = self.host
+        n = q.size(0)
+        picks = sorted({0, n - 1, int(sl.argmax()), int(sl.argmin())})
+        sub = torch.tensor(picks)
+        ref = oracle.paged_decode_attention(q[sub], kc, vc, bt[sub], sl[sub], SCALE)
+        r = _close(self.o[sub.to(self.o.device)], ref)
+        r["sample"] = f"sequences {picks} of this rank (first, last, longest, shortest) against the oracle"
+        return r
+
 
 WORKLOADS = {
-    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 249.1e6),
     "attn_causal": lambda: AttentionWL("attn_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
+    "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 249.1e6),
     "attn_bwd_causal": lambda: AttentionBwdWL("attn_bwd_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
     "gemm_f16": lambda: GemmWL("gemm_f16", 2048, False),
     "gemm_fp8": lambda: GemmWL("gemm_fp8", 8192, True),
+    "gemm_fp8_shard_only": lambda: GemmWL("gemm_fp8_shard_only", 8192, True, "shard_only"),
+    "gemm_fp8_nccl_gather": lambda: GemmWL("gemm_fp8_nccl_gather", 8192, True, "nccl_gather"),
     "paged_decode": lambda: PagedDecodeWL("paged_decode"),
 }
+DEFAULT = "attn_causal"
+# the other configurations of the metric, measured in the same run
+EXTRAS = ["gemm_f16", "attn_noncausal", "paged_decode", "gemm_fp8"]
 
 
 # ---------------------------------------------------------------------------------------------
@@ -391,10 +548,11 @@ WORKLOADS = {
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_ms: int = 50):
         self.index = index
+        self.period_ms = period_ms
         self.samples = []
         self.proc = None
 
@@ -402,16 +560,17 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6:
+            if len(parts) == 7:
                 self.samples.append(parts)
 
     def stop(self) -> dict:
@@ -422,12 +581,16 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm = [int(s[0]) for s in self.samples if s[0].isdigit()]
-        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        rows = [s for s in self.samples if s[0].isdigit()]
+        # "under load" = the utilisation counter saw kernels running in the sample window
+        busy = [s for s in rows if s[6].isdigit() and int(s[6]) >= 50]
+        use = busy if busy else rows
+        sm = [int(s[0]) for s in use]
+        mx = [int(s[1]) for s in rows if s[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(rows), "samples_under_load": len(busy)}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -452,7 +615,7 @@ def run_reference(wl: Workload, args) -> dict:
     return {
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+        "scaling": wl.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": value, "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port",
                          "sample": desc},
         "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -480,92 +643,160 @@ def timed_steps(step_fn, steps, warmup, flush_buf, stream):
     return [a.elapsed_time(b) for a, b in evs]
 
 
-def run_ours(wl: Workload, args) -> dict:
-    import torch.distributed as dist
+class Ctx:
+    """Process-wide state of one bench run: ranks, device, peaks, the L2-flush buffer."""
 
-    import iree_turbine_b200 as tb
+    def __init__(self):
+        import torch.distributed as dist
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        self.dist = dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dev = torch.device("cuda", self.local)
+        torch.cuda.set_device(self.dev)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.peaks = load_peaks()
+        self.stream = torch.cuda.current_stream()
+        self.flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=self.dev)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
-    peaks = load_peaks()
-    stream = torch.cuda.current_stream()
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if wl.needs_flush else None
-    if world > 1:
-        wl.shard(world, rank)
-    wl.setup(dev)
-    units = wl.units_per_step()
-    scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
+    def max_over_ranks(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        t = torch.tensor([x], device=self.dev, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    barrier()
-    if sampler:
-        sampler.start()
-    ms = timed_steps(wl.step, args.steps, max(args.warmup, 3), flush, stream)
-    barrier()
-    total_ms = sum(ms)
+    def all_ok(self, ok: bool) -> bool:
+        if self.world == 1:
+            return ok
+        t = torch.tensor([1 if ok else 0], device=self.dev, dtype=torch.int32)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(t.item())
+
+
+def measure(wl: Workload, ctx: Ctx, steps: int, warmup: int, with_cpu: bool, sustained_s: float = 0.0) -> dict:
+    """One workload: device-timed steps, parity against the oracle, the end-to-end leg, the CPU
+    baseline (N = 1 only) and, for the headline workload, the sustained leg.  Rank 0's dictionary is
+    complete; timings are the maximum over ranks."""
+    import iree_turbine_b200 as tb
+
+    world = ctx.world
     if world > 1:
-        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+        wl.shard(world, ctx.rank)
+    wl.setup(ctx.dev)
+    units = wl.units_per_step()
+    all_units = units * world  # whole-job units per step: every rank does `units`
+    scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
+    flush = ctx.flush if wl.needs_flush else None
+
+    sampler = ClockSampler(ctx.local).start() if ctx.rank == 0 else None
+    ctx.barrier()
+    ms = timed_steps(wl.step, steps, warmup, flush, ctx.stream)
+    ctx.barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = ctx.max_over_ranks(sum(ms))
     status = tb.device_status()
 
+    par = wl.parity()
+    par["ok_on_all_ranks"] = ctx.all_ok(bool(par.get("ok")))
+
+    sustained = None
+    if sustained_s > 0:
+        # back-to-back launches for >= sustained_s seconds, one event pair around the whole loop
+        n = max(steps, int(sustained_s * 1e3 / max(statistics.median(ms), 1e-3)) + 1)
+        s2 = ClockSampler(ctx.local).start() if ctx.rank == 0 else None
+        ctx.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ctx.stream)
+        for _ in range(n):
+            wl.step()
+        e1.record(ctx.stream)
+        ctx.barrier()
+        loop_ms = ctx.max_over_ranks(e0.elapsed_time(e1))
+        c2 = s2.stop() if s2 else None
+        val = all_units * n / (loop_ms * 1e-3) / scale
+        peak_s = ctx.peaks["tflops_sustained"] * wl.peak_scale if wl.bound == "tensor" else ctx.peaks["hbm_gbs"]
+        sustained = {"value": val, "unit": wl.unit, "launches": n, "seconds": loop_ms * 1e-3,
+                     "ms_per_step": loop_ms / n, "clocks": c2,
+                     "frac_of_sustained_peak": val / world / peak_s,
+                     "sustained_peak": peak_s, "peak_source": ctx.peaks["source"] + " (sustained)",
+                     "note": "back-to-back launches, no L2 flush in between; one CUDA-event pair around the loop"}
+
     # end-to-end through the host-buffer API (copies inside the timed region)
-    wl.setup_e2e(dev)
-    barrier()
-    e2e_ms = timed_steps(wl.step_e2e, args.steps, max(args.warmup, 3), None, stream)
-    barrier()
-    e2e_total = sum(e2e_ms)
-    if world > 1:
-        t = torch.tensor([e2e_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_total = float(t.item())
-    clocks = sampler.stop() if sampler else None
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return {}
-
-    per_step_ms = total_ms / args.steps
-    value = world * units / (per_step_ms * 1e-3) / scale
-    kernel_ms = statistics.mean(ms)
-    achieved = units / (kernel_ms * 1e-3) / scale
-    peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops"] * getattr(wl, "peak_scale", 1.0)
+    wl.setup_e2e(ctx.dev)
+    ctx.barrier()
+    e2e_ms = timed_steps(wl.step_e2e, steps, warmup, None, ctx.stream)
+    ctx.barrier()
+    e2e_total = ctx.max_over_ranks(sum(e2e_ms))
     h2d, d2h = wl.e2e_bytes()
-    e2e_value = world * units / (e2e_total / args.steps * 1e-3) / scale
 
-    cu, cdt, cdesc = wl.cpu_sample() if world == 1 else (None, None, None)
     cpu_baseline = None
-    if cu is not None:
+    if with_cpu and world == 1:
+        cu, cdt, cdesc = wl.cpu_sample()
         cpu_baseline = {"value": cu / cdt / scale, "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port",
                         "sample": cdesc}
+
+    per_step_ms = total_ms / steps
+    kernel_ms = statistics.mean(ms)
+    achieved = units / (kernel_ms * 1e-3) / scale
+    peak = ctx.peaks["hbm_gbs"] if wl.bound == "hbm" else ctx.peaks["tflops"] * wl.peak_scale
     out = {
-        "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": per_step_ms, "higher_is_better": True, "scaling": wl.scaling,
-        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(),
+        "metric": wl.metric, "value": all_units / (per_step_ms * 1e-3) / scale, "unit": wl.unit, "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
+        "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(),
         "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": wl.unit,
-                     "frac": achieved / peak, "traffic": wl.traffic_bytes, "peak_source": peaks["source"] + (" (burst)" if getattr(wl, "peak_scale", 1.0) == 1.0 else " (burst) bf16 GEMM x 2 for e4m3"),
-                     "min_ms": min(ms), "median_ms": statistics.median(ms)},
+                     "frac": achieved / peak, "traffic": wl.traffic_bytes,
+                     "peak_source": ctx.peaks["source"] + (" (burst)" if wl.peak_scale == 1.0 else
+                                                            " (burst) bf16 GEMM x 2 for e4m3"),
+                     "min_ms": min(ms), "median_ms": statistics.median(ms),
+                     "note": "per rank: this rank's units / its mean step time"},
+        "parity": par,
         "cpu_baseline": cpu_baseline,
-        "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": all_units / (e2e_total / steps * 1e-3) / scale, "unit": wl.unit,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "clocks": clocks,
-        "gpu_launches": wl.launches_per_step * args.steps,
+        "gpu_launches": wl.launches_per_step * steps,
         "device_status": status,
     }
-    if world > 1:
-        dist.destroy_process_group()
+    if wl.scaling == "weak" and world > 1:
+        out["note"] = "independent replicas: value = N x one rank's units / max time"
+    if sustained:
+        out["sustained"] = sustained
+    wl.release()
+    torch.cuda.empty_cache()
     return out
+
+
+def run_ours(args) -> dict:
+    ctx = Ctx()
+    torch.set_num_threads(os.cpu_count() or 1)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    main = measure(WORKLOADS[args.workload](), ctx, steps, warmup, with_cpu=True, sustained_s=args.sustained)
+    if not args.no_extras:
+        extras = {}
+        names = [n for n in EXTRAS if n != args.workload]
+        if args.workload != DEFAULT:
+            names.insert(0, DEFAULT)
+        for name in names:
+            if name == "gemm_fp8" and ctx.world > 1:
+                # the one workload with an exchange step: three legs
+                legs = {}
+                for leg in ("gemm_fp8_shard_only", "gemm_fp8", "gemm_fp8_nccl_gather"):
+                    legs[WORKLOADS[leg]().mode] = measure(WORKLOADS[leg](), ctx, steps, warmup, with_cpu=False)
+                extras[name] = {"legs": legs}
+            else:
+                extras[name] = measure(WORKLOADS[name](), ctx, steps, warmup, with_cpu=True)
+        main["workloads"] = extras
+    if ctx.world > 1:
+        ctx.dist.destroy_process_group()
+    return main if ctx.rank == 0 else {}
 
 
 def main():
@@ -573,16 +804,18 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="attn_noncausal", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="measure the headline workload only")
+    ap.add_argument("--sustained", type=float, default=1.0,
+                    help="seconds of back-to-back launches for the sustained leg (0 = skip)")
     ap.add_argument("--impl", default="b200k", choices=["b200k", "reference"])
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]()
     if args.impl == "reference":
-        out = run_reference(wl, args)
+        out = run_reference(WORKLOADS[args.workload](), args)
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device; the kernels have no CPU path (use --impl reference for the CPU arm)")
-        out = run_ours(wl, args)
+        out = run_ours(args)
     if out:
         print(json.dumps(out))
 
