@@ -547,50 +547,88 @@ EXTRAS = ["gemm_f16", "attn_noncausal", "paged_decode", "gemm_fp8"]
 # clocks sampler
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
+    """Samples SM clock and clock-event reasons of one GPU every `period_ms` through NVML (read-only
+    queries) on a background thread, from start() to close(); window(t0, t1) summarises the samples
+    taken between two time.monotonic() stamps.  "Under load" = samples while the GPU-idle reason
+    was not set.  Falls back to an nvidia-smi query loop if NVML cannot be loaded."""
 
-    def __init__(self, index: int, period_ms: int = 50):
-        self.index = index
-        self.period_ms = period_ms
-        self.samples = []
-        self.proc = None
+    REASONS = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4}
+    IDLE = 0x1
+
+    def __init__(self, index: int, period_ms: float = 2.0):
+        self.index, self.period = index, period_ms * 1e-3
+        self.samples = []  # (monotonic time, sm MHz, reason bits)
+        self.max_mhz = None
+        self.how = None
+        self._stop = threading.Event()
+        self.thread = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = int(vis.split(",")[self.index]) if vis and vis.split(",")[self.index].isdigit() else self.index
+            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                        bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                        self.samples.append((time.monotonic(), mhz, bits))
+                    except Exception:  # noqa: BLE001 - a failed read is a missing sample
+                        pass
+                    time.sleep(self.period)
+
+            self.how = "nvml"
+            self.thread = threading.Thread(target=loop, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception:  # noqa: BLE001
+            self._start_smi()
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 7:
-                self.samples.append(parts)
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+    def _start_smi(self):
+        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.gpu_idle,clocks_event_reasons.sw_power_cap,"
+                  "clocks_event_reasons.hw_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                  "clocks_event_reasons.hw_thermal_slowdown")
         try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        rows = [s for s in self.samples if s[0].isdigit()]
-        # "under load" = the utilisation counter saw kernels running in the sample window
-        busy = [s for s in rows if s[6].isdigit() and int(s[6]) >= 50]
+            proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={fields}",
+                                     "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
+                                    stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.how = "nvidia-smi"
+
+        def loop():
+            bit = [self.IDLE, 0x4, 0x8, 0x20, 0x40]
+            for line in proc.stdout:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) == 7 and parts[0].isdigit():
+                    self.max_mhz = int(parts[1]) if parts[1].isdigit() else self.max_mhz
+                    bits = sum(b for b, v in zip(bit, parts[2:]) if v == "Active")
+                    self.samples.append((time.monotonic(), int(parts[0]), bits))
+                if self._stop.is_set():
+                    break
+            proc.terminate()
+
+        self.thread = threading.Thread(target=loop, daemon=True)
+        self.thread.start()
+
+    def window(self, t0: float, t1: float) -> dict:
+        if self.how is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable"]}
+        rows = [s for s in self.samples if t0 <= s[0] <= t1]
+        busy = [s for s in rows if not (s[2] & self.IDLE)]
         use = busy if busy else rows
-        sm = [int(s[0]) for s in use]
-        mx = [int(s[1]) for s in rows if s[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in rows)]
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(rows), "samples_under_load": len(busy)}
+        reasons = [n for n, b in self.REASONS.items() if any(s[2] & b for s in rows)]
+        return {"sm_mhz": statistics.median(s[1] for s in use) if use else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(rows), "samples_under_load": len(busy), "how": self.how}
+
+    def close(self):
+        self._stop.set()
 
 
 # ---------------------------------------------------------------------------------------------
@@ -660,6 +698,7 @@ class Ctx:
         self.peaks = load_peaks()
         self.stream = torch.cuda.current_stream()
         self.flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=self.dev)
+        self.sampler = ClockSampler(self.local).start() if self.rank == 0 else None
 
     def barrier(self):
         if self.world > 1:
@@ -696,11 +735,11 @@ def measure(wl: Workload, ctx: Ctx, steps: int, warmup: int, with_cpu: bool, sus
     scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
     flush = ctx.flush if wl.needs_flush else None
 
-    sampler = ClockSampler(ctx.local).start() if ctx.rank == 0 else None
     ctx.barrier()
+    t_begin = time.monotonic()
     ms = timed_steps(wl.step, steps, warmup, flush, ctx.stream)
     ctx.barrier()
-    clocks = sampler.stop() if sampler else None
+    clocks = ctx.sampler.window(t_begin, time.monotonic()) if ctx.sampler else None
     total_ms = ctx.max_over_ranks(sum(ms))
     status = tb.device_status()
 
@@ -711,8 +750,8 @@ def measure(wl: Workload, ctx: Ctx, steps: int, warmup: int, with_cpu: bool, sus
     if sustained_s > 0:
         # back-to-back launches for >= sustained_s seconds, one event pair around the whole loop
         n = max(steps, int(sustained_s * 1e3 / max(statistics.median(ms), 1e-3)) + 1)
-        s2 = ClockSampler(ctx.local).start() if ctx.rank == 0 else None
         ctx.barrier()
+        t_begin = time.monotonic()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(ctx.stream)
         for _ in range(n):
@@ -720,7 +759,7 @@ def measure(wl: Workload, ctx: Ctx, steps: int, warmup: int, with_cpu: bool, sus
         e1.record(ctx.stream)
         ctx.barrier()
         loop_ms = ctx.max_over_ranks(e0.elapsed_time(e1))
-        c2 = s2.stop() if s2 else None
+        c2 = ctx.sampler.window(t_begin, time.monotonic()) if ctx.sampler else None
         val = all_units * n / (loop_ms * 1e-3) / scale
         peak_s = ctx.peaks["tflops_sustained"] * wl.peak_scale if wl.bound == "tensor" else ctx.peaks["hbm_gbs"]
         sustained = {"value": val, "unit": wl.unit, "launches": n, "seconds": loop_ms * 1e-3,
@@ -794,6 +833,8 @@ def run_ours(args) -> dict:
             else:
                 extras[name] = measure(WORKLOADS[name](), ctx, steps, warmup, with_cpu=True)
         main["workloads"] = extras
+    if ctx.sampler:
+        ctx.sampler.close()
     if ctx.world > 1:
         ctx.dist.destroy_process_group()
     return main if ctx.rank == 0 else {}

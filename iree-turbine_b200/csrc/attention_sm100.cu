@@ -1,51 +1,49 @@
-// Attention forward (vanilla and causal) on sm_100a.
+// Attention forward (vanilla and causal, dense or paged K/V, head dim 128 or 64) on sm_100a.
 //
-// Persistent CTAs, one per SM.  A work item is one 128-row query tile of one (batch, head); a CTA
-// takes items blockIdx.x, blockIdx.x + gridDim.x, ... from a list ordered (batch, head)-major with
-// the heaviest query tiles of a head first, so CTAs that run at the same time share K/V in L2.
+// Persistent CTAs, one per SM.  A work item is one PAIR of 128-row query tiles (256 consecutive
+// query rows) of one (batch, head).  The two tiles of a pair are independent problems that share
+// every K/V tile: each has its own score buffer, its own probabilities, its own running max / sum
+// and its own output accumulator, and each is served by its own softmax warpgroup.  Nothing is
+// exchanged between the two warpgroups; while one of them is busy with its exponentials the
+// tensor core works for the other one.
 //
-//   warps 0..3    softmax + correction of the even KV steps of the CTA (thread = query row)
-//   warps 4..7    the same for the odd KV steps
-//   warps 8..11   epilogue: O / rowsum -> global, one item behind the others
-//   warp 12       TMA loads: Q of the next item, K_j (3 stages), V_j (2 stages)
-//   warp 13       issues the score MMAs (S = Q K^T) and owns tensor memory
-//   warp 14       issues the second MMAs (O += P V)
-//   warp 15       idle (completes the fourth warpgroup for the setmaxnreg register hand-off)
+//   warps 0..3    softmax of query tile 0 (thread = one query row, the whole score row in registers)
+//   warps 4..7    softmax of query tile 1
+//   warps 8..11   epilogue: O / rowsum -> global for both tiles, one item behind the others
+//   warp 12       TMA loads of K and V: one ring of kKvStages tiles, filled K_0 V_0 K_1 V_1 ...
+//   warp 13       issues the MMAs of query tile 0 (one thread) and owns tensor memory
+//   warp 14       TMA loads of Q (a thread of its own, so that waiting for a free Q buffer never
+//                 holds up K/V loads)
+//   warp 15       issues the MMAs of query tile 1 (one thread)
 //
-// Tensor memory (512 columns x 128 lanes):  S[0] | S[1] (128 fp32 columns each) | P[0] | P[1]
-// (64 columns each: 128 16-bit probabilities per row) | O (128 fp32 columns).
-//   * Score tile g goes to S[g & 1] and is handled by softmax warpgroup g & 1, which writes P[g & 1].
-//     The two warpgroups are half a step apart: while one is in its latency-bound part (wait,
-//     tensor-memory load, row max, hand-over) the other runs its exponentials.  They share ONE
-//     running row max and ONE accumulator: early in its step a warpgroup reads the running max the
-//     other published half a step before, decides whether this tile raises it (by more than 2^8),
-//     and publishes the result; only when it does raise it is O rescaled, by that warpgroup, after
-//     "O += P V" of the previous step (the other warpgroup's) has completed and before its own P is
-//     handed over.  Each warpgroup keeps a partial row sum relative to the running max it last saw;
-//     the epilogue brings the two to the final max and adds them.
-//   * A softmax thread holds its whole score row in registers, so a score buffer is free
-//     again early in the step, as soon as the row has been loaded: S(j+2) is issued then.  The
-//     probabilities have buffers of their own for that reason.  The tensor core is never what the
-//     softmax waits for: neither the scores of the next step nor "O += P V" of the last one is on
-//     its critical path.
-//   * Two threads issue MMAs.  A tcgen05.mma does not return until the tensor pipe has room for
-//     it, so a group of eight blocks its thread for about as long as it executes (plus some 300
-//     cycles when the pipe was idle); with one issuing thread every wait of one kind of MMA
-//     delayed the other.
-//   * One output accumulator is enough: the first "O = P V" of an item is needed a whole softmax
-//     step after the last one of the previous item, and the epilogue reads O in less than that.
-//   * P is the A operand of the second MMA straight from tensor memory.
+// Tensor memory (512 columns x 128 lanes):  S[0] | S[1] (128 fp32 columns each) | O[0] | O[1]
+// (head-dim fp32 columns each).  The probabilities P[t] (16-bit, 64 columns) are written over the
+// first half of S[t] by the thread that has just read that row into registers, and are the A
+// operand of the second MMA straight from tensor memory.
 //
-// Epilogue: accumulator -> registers -> 16-bit -> 128-byte-swizzled staging block (64 columns) in
-// shared memory -> TMA store, twice (rows past the end of the sequence are clipped by the tensor
-// map).  Direct row-per-thread global stores were measured at about 3000 cycles per item and delayed the TMA
-// loads of the next item; the staged store is a few hundred.
+// Order of the MMAs of query tile t (one in-order stream per tile, issued by its own thread), KV tile j:
+//     wait P[t](j) : O[t] += P[t] V_j : S[t] = Q_t K_(j+1)^T : wait P[t](j+1) : ...
+// so the tensor core computes "PV, next S" of one query tile while the other tile's softmax runs.
+// Because S[t](j+1) is issued behind O[t] += P[t](j) V_j by the same thread, S may overwrite P
+// without a barrier; and when the softmax of tile t sees S[t](j) complete, every earlier MMA of the
+// tile is complete as well, so it may rescale O[t] in place with no further wait.  A stream does
+// not stop at item boundaries: a tile that has issued its last PV of an item goes on with the first
+// score tile of its next item as soon as Q and K are there.
+//
+// Causal items: the two tiles of a pair need a different number of KV tiles (n[0] <= n[1]); tile 0
+// simply stops taking part once it is past its diagonal.  Work is dealt to CTAs in units that pair
+// the heaviest remaining pair of a head with the lightest, so every unit of a causal problem costs
+// the same.
 //
 // Softmax: running max in log2 units (scores are multiplied by scale * log2(e) inside the
-// exponent's FMA); O is only rescaled when a row's max grows by more than 2^8 (stale max used for
-// both P and the running sum, exact after the final division).  A degree-3 polynomial on the FMA
-// pipe can replace ex2.approx for a share of the column pairs (B200K_ATTN_POLY_MASK); it is off,
-// see the measurements at kPolyPairMask.
+// exponent's FMA); O is only rescaled when a row's max grows by more than 2^8 (the stale max is
+// used for both P and the running sum, which is exact after the final division).
+//
+// Epilogue: accumulator -> registers -> 16-bit -> 128-byte-swizzled staging block (64 columns) in
+// shared memory -> TMA store (rows past the end of the sequence are clipped by the tensor map).
+//
+// Every wait is bounded; when one gives up all roles drain to the common teardown, tensor memory
+// is freed and the kernel ORs a code into the caller's status word.
 #include <type_traits>
 
 #include "common.cuh"
@@ -55,55 +53,72 @@ namespace b200k {
 namespace {
 
 constexpr int kAttnThreads = 512;
-constexpr int kTmaWarp = 12;
-constexpr int kScoreWarp = 13;
-constexpr int kPvWarp = 14;
+constexpr int kKvWarp = 12;
+constexpr int kMmaWarp = 13;
+constexpr int kQWarp = 14;
+constexpr int kMmaWarp2 = 15;
 // Registers: 4 warps per SM sub-partition x 128 at launch = 512 per lane, redistributed.  A
 // setmaxnreg.inc beyond what the others gave up never completes.
 constexpr int kRegsSoftmax = 184;
 constexpr int kRegsEpilogue = 80;
 constexpr int kRegsOther = 64;
 static_assert(2 * kRegsSoftmax + kRegsEpilogue + kRegsOther <= 512, "setmaxnreg.inc would never complete");
-constexpr int kTileRows = 128;  // query rows per item, KV rows per tile
-constexpr int kD = 128;
-constexpr int kHalfTileBytes = kTileRows * 128;  // one 64-element column block: 16 KB
-constexpr int kTileBytes = 2 * kHalfTileBytes;   // 32 KB
-constexpr int kKStages = 3;
-constexpr int kVStages = 2;
-constexpr int kQOffset = 0;
-constexpr int kKOffset = kTileBytes;
-constexpr int kVOffset = kKOffset + kKStages * kTileBytes;
-constexpr int kOStageOffset = kVOffset + kVStages * kTileBytes;  // epilogue staging: one 64-column block
-constexpr int kMaxOffset = kOStageOffset + kHalfTileBytes;   // float [warpgroup][128 rows]: running max it published
-constexpr int kLsumOffset = kMaxOffset + 2 * kTileRows * 4;  // float [warpgroup][max, sum][128 rows] for the epilogue
-constexpr int kBarOffset = kLsumOffset + 2 * 2 * kTileRows * 4;
-// q_full q_empty | k_full[3] k_empty[3] v_full[2] v_empty[2] | s_full[2] s_free[2] p_full[2] x_full[2] |
-// o_done[2] | o_full o_free l_full l_free
-constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 8 + 2 + 4;
-// tensor memory columns
-constexpr uint32_t kTmemS = 0;    // + 128 * buffer
-constexpr uint32_t kTmemP = 256;  // + 64 * buffer
-constexpr uint32_t kTmemO = 384;
-constexpr int kAttnSmem = kBarOffset + kNumBars * 8 + 16 + 1024;
+constexpr int kTileRows = 128;           // query rows per tile, KV rows per tile
+constexpr int kPairRows = 2 * kTileRows;  // query rows per work item
+constexpr int kHalfTileBytes = kTileRows * 128;  // one 64-element column block of a tile: 16 KB
+constexpr int kKvStages = 4;
+#ifndef VAR_NOPREFETCH
+#define VAR_NOPREFETCH 0
+#endif
+#ifndef VAR_NOLOOKAHEAD
+#define VAR_NOLOOKAHEAD 0
+#endif
+#ifndef VAR_BLOCKLA
+#define VAR_BLOCKLA 0
+#endif
+#ifndef VAR_MAX2
+#define VAR_MAX2 0
+#endif
+#ifndef VAR_STALE
+#define VAR_STALE 0
+#endif
+#ifndef VAR_SWEEP2
+#define VAR_SWEEP2 0
+#endif
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
-#ifndef B200K_ATTN_PREFETCH
-#define B200K_ATTN_PREFETCH 0
-#endif
-constexpr bool kPrefetchNext = B200K_ATTN_PREFETCH != 0;
+
+template <int HD>
+struct AttnSmem {
+  static constexpr int kBlocks = HD / 64;                       // 64-column blocks per tile row
+  static constexpr int kTileBytes = kBlocks * kHalfTileBytes;   // 32 KB (HD 128) or 16 KB (HD 64)
+  static constexpr int kQOffset = 0;                             // two query tiles
+  static constexpr int kKvOffset = 2 * kTileBytes;
+  static constexpr int kStageOffset = kKvOffset + kKvStages * kTileBytes;  // epilogue staging: one 64-column block
+  static constexpr int kLsumOffset = kStageOffset + kHalfTileBytes;        // float [tile][max, sum][128 rows]
+  static constexpr int kBarOffset = kLsumOffset + 2 * 2 * kTileRows * 4;
+  // q_full[2] q_empty[2] | kv_full[4] kv_empty[4] | s_full[2] p_full[2] | o_full[2] o_free[2] | l_full[2] l_free[2] | turn[2]
+  static constexpr int kNumBars = 4 + 2 * kKvStages + 4 + 4 + 4 + 2;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16 + 1024;  // + slack for 1024-byte alignment
+  // tensor memory columns
+  static constexpr uint32_t kTmemS = 0;    // + 128 * tile; P over the first 64 columns
+  static constexpr uint32_t kTmemO = 256;  // + HD * tile
+};
+static_assert(AttnSmem<128>::kTotal <= 232448, "shared memory budget");
 
 struct AttnParams {
   void* o;
   int64_t o_stride_b, o_stride_h, o_stride_s;
   int32_t batch, q_heads, kv_heads, seq_q, seq_kv;
   int32_t causal, causal_offset;
-  int32_t num_q_tiles;  // ceil(seq_q / 128)
-  int32_t num_items;    // batch * q_heads * num_q_tiles
+  int32_t num_pairs;       // ceil(seq_q / 256)
+  int32_t units_per_head;  // work units per (batch, head): pairs, or (heavy, light) couples of pairs when causal
+  int32_t num_units;       // batch * q_heads * units_per_head
   float scale_log2;
   int32_t* status;
   float* lse;  // optional [batch, q_heads, seq_q]: ln sum_j exp(scale * s_ij), -inf for a row without keys
   // Paged K/V (block_table != nullptr): the tensor maps of K and V describe the page pool
-  // [num_pages, kv_heads, page_size, 128]; token t of sequence b lives in page
+  // [num_pages, kv_heads, page_size, head_dim]; token t of sequence b lives in page
   // block_table[b * block_table_stride + t / page_size], row t % page_size; sequence b has
   // seq_lens[b] <= seq_kv keys and its queries are its last seq_q tokens.
   const int32_t* block_table;
@@ -137,14 +152,13 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 }
 
 // Which of every 8 consecutive column pairs take the polynomial instead of ex2.approx (bit i = pair i).
-// Measured (C2 / C3, TFLOP/s): none 1041 / 1058, 1 of 8 1031 / 1048, 2 of 8 1016 / 1033, 3 of 8 1009 / 1013,
-// 4 of 8 962 / 969.  With two softmax warps per SM sub-partition half a step apart the step is bound by
-// instruction issue, not by the special-function unit, and the polynomial costs more instructions.
-// (With one softmax warp per sub-partition 3 of 8 was the best.)
-#ifndef B200K_ATTN_POLY_MASK
-#define B200K_ATTN_POLY_MASK 0x00u
+// The special-function unit delivers 16 results per cycle and SM: 128 x 128 exponentials are 1024
+// cycles, as long as the two MMAs of the same tile, so whatever share of them moves to the FMA
+// pipe comes off the softmax's critical resource.
+#ifndef VAR_POLY
+#define VAR_POLY 0x00u
 #endif
-constexpr uint32_t kPolyPairMask = B200K_ATTN_POLY_MASK;
+constexpr uint32_t kPolyPairMask = VAR_POLY;
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
@@ -159,37 +173,17 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi)
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Optional timeline capture (compile with -DB200K_ATTN_TRACE): block (0,0,0) records
-// (tag, clock64) pairs per role into the buffer passed as the status pointer, 256 events per role:
-// role 0 = TMA thread, 1 = score MMA thread, 2 = softmax warp 0, 3 = epilogue (first warp), 4 = softmax warp 4.
-#ifdef B200K_ATTN_TRACE
-#define ATTN_TRACE(role, tag)                                                                        \
-  do {                                                                                               \
-    if (trace_on && trace_n < 256) {                                                                 \
-      longlong2 ev;                                                                                  \
-      ev.x = (tag);                                                                                  \
-      ev.y = clock64();                                                                              \
-      *reinterpret_cast<longlong2*>(reinterpret_cast<long long*>(p.status) + ((role)*256 + trace_n) * 2) = ev; \
-      ++trace_n;                                                                                     \
-    }                                                                                                \
-  } while (0)
-#else
-#define ATTN_TRACE(role, tag) \
-  do {                        \
-  } while (0)
-#endif
-
-
 struct Item {
-  int qtile, head, batch, n;  // n = number of 128-row KV tiles this item visits
+  int pair, head, batch;
+  int n[2];   // KV tiles query tile t visits (0: the tile has no rows or sees no key)
+  int nmax;   // max(n[0], n[1]): KV tiles loaded for the item
   int kv_len, causal_offset;  // keys of this item's sequence; key j is visible to query i iff j <= i + causal_offset
 };
 
 template <bool PAGED>
-__device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
+__device__ __forceinline__ Item make_item(int bh, int pair, const AttnParams& p) {
   Item it;
-  const int bh = idx / p.num_q_tiles;
-  it.qtile = p.num_q_tiles - 1 - (idx - bh * p.num_q_tiles);  // heaviest tiles of a head first
+  it.pair = pair;
   it.batch = bh / p.q_heads;
   it.head = bh - it.batch * p.q_heads;
   // (dense: the two are launch constants and the fields fold away)
@@ -197,78 +191,109 @@ __device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
   if (PAGED) it.kv_len = max(0, min(__ldg(p.seq_lens + it.batch), p.seq_kv));
   it.causal_offset = PAGED ? it.kv_len - p.seq_q : p.causal_offset;
   const int kv_tiles_total = (it.kv_len + kTileRows - 1) / kTileRows;
-  if (!p.causal) {
-    it.n = kv_tiles_total;
-  } else {
-    const int last_col = it.qtile * kTileRows + kTileRows - 1 + it.causal_offset;
-    it.n = last_col < 0 ? 0 : min(last_col / kTileRows + 1, kv_tiles_total);
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = pair * kPairRows + t * kTileRows;
+    int n = 0;
+    if (r0 < p.seq_q) {
+      if (!p.causal) {
+        n = kv_tiles_total;
+      } else {
+        const int last_col = r0 + kTileRows - 1 + it.causal_offset;
+        n = last_col < 0 ? 0 : min(last_col / kTileRows + 1, kv_tiles_total);
+      }
+    }
+    it.n[t] = n;
   }
+  it.nmax = max(it.n[0], it.n[1]);
   return it;
 }
 
-template <typename T, bool PAGED>
+// The CTA's items, in the order every role walks them: units blockIdx.x, blockIdx.x + gridDim.x, ...;
+// a unit is one pair of a (batch, head), heaviest first, or -- causal -- the k-th heaviest pair
+// followed by the k-th lightest of the same head.
+template <bool PAGED>
+struct ItemWalk {
+  const AttnParams& p;
+  int unit, part;
+  __device__ ItemWalk(const AttnParams& params) : p(params), unit(blockIdx.x), part(0) {}
+  // Next item, empty ones (nmax == 0) included; false when the CTA has no more.
+  __device__ __forceinline__ bool next(Item& it) {
+    while (unit < p.num_units) {
+      const int bh = unit / p.units_per_head;
+      const int s = unit - bh * p.units_per_head;
+      const int heavy = p.num_pairs - 1 - s;
+      if (part == 0) {
+        part = 1;
+        it = make_item<PAGED>(bh, heavy, p);
+        return true;
+      }
+      part = 0;
+      unit += gridDim.x;
+      if (p.causal && s < heavy) {
+        it = make_item<PAGED>(bh, s, p);
+        return true;
+      }
+    }
+    return false;
+  }
+  // Next item that has work.
+  __device__ __forceinline__ bool next_busy(Item& it) {
+    while (next(it))
+      if (it.nmax > 0) return true;
+    return false;
+  }
+};
+
+template <typename T, int HD, bool PAGED>
 __global__ void __launch_bounds__(kAttnThreads, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
                     const AttnParams p) {
+  using L = AttnSmem<HD>;
+  constexpr int kBlocks = L::kBlocks;
+  constexpr int kTileBytes = L::kTileBytes;
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
-  constexpr uint32_t kIdescS = make_idesc(kFmt, kFmt, 128, 128, 0, 0);   // Q, K both K-major
-  constexpr uint32_t kIdescPV = make_idesc(kFmt, kFmt, 128, 128, 0, 1);  // V is MN-major
+  constexpr uint32_t kIdescS = make_idesc(kFmt, kFmt, 128, 128, 0, 0);  // Q, K both K-major
+  constexpr uint32_t kIdescPV = make_idesc(kFmt, kFmt, 128, HD, 0, 1);  // V is MN-major
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* lsum = reinterpret_cast<float*>(smem + kLsumOffset);
-  float* xmax = reinterpret_cast<float*>(smem + kMaxOffset);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOffset);
-  uint64_t* q_full = bars;
-  uint64_t* q_empty = bars + 1;
-  uint64_t* k_full = bars + 2;
-  uint64_t* k_empty = k_full + kKStages;
-  uint64_t* v_full = k_empty + kKStages;
-  uint64_t* v_empty = v_full + kVStages;
-  uint64_t* s_full = v_empty + kVStages;  // [buffer] score tile written
-  uint64_t* s_free = s_full + 2;          // [buffer] score tile is in the softmax threads' registers
-  uint64_t* p_full = s_free + 2;          // [buffer] probabilities written
-  uint64_t* x_full = p_full + 2;          // [warpgroup] it has published the row maxima after its step
-  uint64_t* o_done = x_full + 2;          // [step parity] "O += P V" of that step complete
-  uint64_t* o_full = o_done + 2;          // last P V of an item complete
-  uint64_t* o_free = o_full + 1;          // epilogue has read the accumulator
-  uint64_t* l_full = o_free + 1;          // row sums written
-  uint64_t* l_free = l_full + 1;          // row sums read
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  float* lsum = reinterpret_cast<float*>(smem + L::kLsumOffset);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* q_full = bars;            // [tile] Q tile loaded
+  uint64_t* q_empty = q_full + 2;     // [tile] the item's last score MMA of that tile has read Q
+  uint64_t* kv_full = q_empty + 2;    // [stage]
+  uint64_t* kv_empty = kv_full + kKvStages;
+  uint64_t* s_full = kv_empty + kKvStages;  // [tile] score tile written
+  uint64_t* p_full = s_full + 2;            // [tile] probabilities written (and O rescaled if it had to be)
+  uint64_t* o_full = p_full + 2;            // [tile] last PV of an item complete
+  uint64_t* o_free = o_full + 2;            // [tile] epilogue has read the accumulator
+  uint64_t* l_full = o_free + 2;            // [tile] (max, sum) of the item written
+  uint64_t* l_free = l_full + 2;            // [tile] ... and read
+  uint64_t* turn = l_free + 2;              // [tile] it is this tile's turn to put MMAs into the pipe
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-#ifdef B200K_ATTN_TRACE
-  const bool trace_on = blockIdx.x == 0 && p.status != nullptr && lane == 0;
-  int trace_n = 0;
-  const uint64_t trace_t0 = globaltimer_ns();
-  const long long trace_c0 = clock64();
-#endif
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    for (int i = 0; i < kKStages; ++i) {
-      mbar_init(k_full + i, 1);
-      mbar_init(k_empty + i, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(q_full + t, 1);
+      mbar_init(q_empty + t, 1);
+      mbar_init(s_full + t, 1);
+      mbar_init(p_full + t, 4);
+      mbar_init(o_full + t, 1);
+      mbar_init(o_free + t, 4);
+      mbar_init(l_full + t, 4);
+      mbar_init(l_free + t, 4);
+      mbar_init(turn + t, 1);
     }
-    for (int i = 0; i < kVStages; ++i) {
-      mbar_init(v_full + i, 1);
-      mbar_init(v_empty + i, 1);
+    for (int i = 0; i < kKvStages; ++i) {
+      mbar_init(kv_full + i, 1);
+      mbar_init(kv_empty + i, 2);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(s_full + i, 1);
-      mbar_init(s_free + i, 4);
-      mbar_init(p_full + i, 4);
-      mbar_init(x_full + i, 4);
-      mbar_init(o_done + i, 1);
-    }
-    mbar_init(o_full, 1);
-    mbar_init(o_free, 4);
-    mbar_init(l_full, 8);
-    mbar_init(l_free, 4);
     *abort_word = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -277,7 +302,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     prefetch_tmap(&tmap_v);
     prefetch_tmap(&tmap_o);
   }
-  if (warp == kScoreWarp) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -289,21 +314,27 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
   if (warp >= 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-    if (warp == kTmaWarp) {
-      // ---------------- TMA producer ----------------
+    if (warp == kKvWarp) {
+      // ---------------- K / V producer: ring entries K_0 V_0 K_1 V_1 ... of every item ----------------
       if (lane == 0) {
-        uint32_t qc = 0, kc = 0, vc = 0;  // Q loads, K tiles, V tiles issued so far
+        uint32_t e = 0;  // ring entries issued so far
         bool ok = true;
         // One 128-row K or V tile.  Dense: one box per 64-column block.  Paged: one box per page and
         // block; a page past the sequence's length is replaced by the sequence's first page (those
         // rows are masked; the data only has to be finite), an entry outside the pool is reported
         // and reads as zeros (the tensor map clips it).
-        auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, const Item& it, int j) {
+        auto load_tile = [&](const CUtensorMap* tm, const Item& it, int j) {
+          const uint32_t stage = e % kKvStages;
+          if (!mbar_wait(kv_empty + stage, ((e / kKvStages) & 1) ^ 1, abort_word)) return false;
+          uint8_t* dst = smem + L::kKvOffset + stage * kTileBytes;
+          uint64_t* bar = kv_full + stage;
+          mbar_arrive_expect_tx(bar, kTileBytes);
+          ++e;
           if (!PAGED) {
 #pragma unroll
-            for (int db = 0; db < 2; ++db)
+            for (int db = 0; db < kBlocks; ++db)
               tma_load_4d(dst + db * kHalfTileBytes, tm, bar, db * 64, j * kTileRows, it.head / group, it.batch);
-            return;
+            return true;
           }
           const int32_t* row = p.block_table + static_cast<int64_t>(it.batch) * p.block_table_stride;
           const int pages_per_tile = kTileRows / p.page_size;
@@ -313,167 +344,171 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             const int page = __ldg(row + (lp < valid_pages ? lp : 0));
             if ((page < 0 || page >= p.num_pages) && p.status) atomicOr(p.status, kStatusDecodeBadPage);
 #pragma unroll
-            for (int db = 0; db < 2; ++db)
+            for (int db = 0; db < kBlocks; ++db)
               tma_load_4d(dst + db * kHalfTileBytes + pp * p.page_size * 128, tm, bar, db * 64, 0, it.head / group, page);
           }
-        };
-        auto load_k = [&](const Item& it, int j) {
-          const int ks = kc % kKStages;
-          if (!mbar_wait(k_empty + ks, ((kc / kKStages) & 1) ^ 1, abort_word)) return false;
-          mbar_arrive_expect_tx(k_full + ks, kTileBytes);
-          load_tile(smem + kKOffset + ks * kTileBytes, &tmap_k, k_full + ks, it, j);
-          ++kc;
           return true;
         };
-        // Q and the first K tiles of an item.  Q's buffer is free once the previous item's last
-        // score MMA has run, which is earlier than the release of its last V stage.
-        auto load_head = [&](const Item& it) {
-          if (!mbar_wait(q_empty, (qc & 1) ^ 1, abort_word)) return false;
-          mbar_arrive_expect_tx(q_full, kTileBytes);
+        ItemWalk<PAGED> walk(p);
+        Item it;
+        while (ok && walk.next_busy(it)) {
+          for (int j = 0; j < it.nmax && ok; ++j) ok = load_tile(&tmap_k, it, j) && load_tile(&tmap_v, it, j);
+        }
+      }
+      __syncwarp();
+    } else if (warp == kQWarp) {
+      // ---------------- Q producer ----------------
+      if (lane == 0) {
+        uint32_t ci[2] = {0, 0};  // items of each tile so far
+        bool ok = true;
+        ItemWalk<PAGED> walk(p);
+        Item it, nx;
+        bool have = walk.next_busy(it);
+        while (ok && have) {
+          const bool have_next = walk.next_busy(nx);
 #pragma unroll
-          for (int db = 0; db < 2; ++db)
-            tma_load_4d(smem + kQOffset + db * kHalfTileBytes, &tmap_q, q_full, db * 64, it.qtile * kTileRows, it.head,
-                        it.batch);
-          ++qc;
-          ATTN_TRACE(0, 9000);
-          for (int jj = 0; jj < kKStages && jj < it.n; ++jj)
-            if (!load_k(it, jj)) return false;
-          return true;
-        };
-        auto next_item = [&](int idx, Item& nx) {  // next item of this CTA that has work; num_items if none
-          for (idx += gridDim.x; idx < p.num_items; idx += gridDim.x) {
-            nx = decode_item<PAGED>(idx, p);
-            if (nx.n > 0) return idx;
+          for (int t = 0; t < 2; ++t) {
+            if (it.n[t] == 0) continue;
+            if (!mbar_wait(q_empty + t, (ci[t] & 1) ^ 1, abort_word)) { ok = false; break; }
+            ++ci[t];
+            mbar_arrive_expect_tx(q_full + t, kTileBytes);
+#pragma unroll
+            for (int db = 0; db < kBlocks; ++db)
+              tma_load_4d(smem + L::kQOffset + t * kTileBytes + db * kHalfTileBytes, &tmap_q, q_full + t, db * 64,
+                          it.pair * kPairRows + t * kTileRows, it.head, it.batch);
           }
-          return p.num_items;
-        };
-        Item it = {};
-        int idx = next_item(static_cast<int>(blockIdx.x) - static_cast<int>(gridDim.x), it);
-        if (idx < p.num_items) ok = load_head(it);
-        while (idx < p.num_items && ok) {
-          Item nx = {};
-          const int nidx = next_item(idx, nx);
-          const bool have_next = nidx < p.num_items;
-          // Order within an item: V_j, then K_(j+3); a K stage is released (by the score MMA that
-          // read it) earlier than a V stage.  The head of the next item goes before the last V.
-          for (int j = 0; j < it.n && ok; ++j) {
-            if (j == it.n - 1 && have_next) {
-              ok = load_head(nx);
-              if (!ok) break;
-            }
-            const int vs = vc % kVStages;
-            if (!mbar_wait(v_empty + vs, ((vc / kVStages) & 1) ^ 1, abort_word)) { ok = false; break; }
-            mbar_arrive_expect_tx(v_full + vs, kTileBytes);
-            load_tile(smem + kVOffset + vs * kTileBytes, &tmap_v, v_full + vs, it, j);
-            ++vc;
-            if (j + kKStages < it.n) ok = load_k(it, j + kKStages);
-            if (kPrefetchNext && !PAGED && j == 0 && have_next) {
-              // The first tiles of the next item are wanted soon after this item's last score MMA
-              // frees Q, less than a trip to HBM later: ask for them in L2 now.
-              const int nkv = nx.head / group;
+          // A Q buffer frees up only a step or so before the next item needs it, less than a trip
+          // to HBM: ask for the next item's Q tiles in L2 now, an item ahead.
+          if (have_next && !VAR_NOPREFETCH) {
 #pragma unroll
-              for (int db = 0; db < 2; ++db) tma_prefetch_4d(&tmap_q, db * 64, nx.qtile * kTileRows, nx.head, nx.batch);
-              for (int jj = 0; jj < kKStages && jj < nx.n; ++jj) {
+            for (int t = 0; t < 2; ++t) {
+              if (nx.n[t] == 0) continue;
 #pragma unroll
-                for (int db = 0; db < 2; ++db) tma_prefetch_4d(&tmap_k, db * 64, jj * kTileRows, nkv, nx.batch);
-              }
-              for (int jj = 0; jj < kVStages && jj < nx.n; ++jj) {
-#pragma unroll
-                for (int db = 0; db < 2; ++db) tma_prefetch_4d(&tmap_v, db * 64, jj * kTileRows, nkv, nx.batch);
-              }
+              for (int db = 0; db < kBlocks; ++db)
+                tma_prefetch_4d(&tmap_q, db * 64, nx.pair * kPairRows + t * kTileRows, nx.head, nx.batch);
             }
           }
           it = nx;
-          idx = nidx;
+          have = have_next;
         }
       }
       __syncwarp();
-    } else if (warp == kScoreWarp) {
-      // ---------------- score MMAs: S[g & 1] = Q K_g^T for every KV step g of this CTA ----------------
-      // Two threads issue MMAs, this one and the one below.  A tcgen05.mma does not return until
-      // the tensor pipe has room for it, so a group of eight blocks its thread for about as long
-      // as it executes (plus some 300 cycles when the pipe was idle): one thread for both kinds
-      // was busy nearly the whole step and every wait of one kind delayed the other.  The streams
-      // are independent: each orders itself through barriers (score buffer taken by the softmax,
-      // P written, stages loaded), never through issue order.
+    } else {
+      // ---------------- MMA issue: warp 13 for query tile 0, warp 15 for query tile 1 ----------------
+      // One thread per query tile, each with its own in-order stream
+      //     wait P(j) : O += P(j) V_j : S = Q K_(j+1)^T : ...
+      // so neither tile ever waits behind the other's barriers, and a tile that is done with an
+      // item runs on into its next item as far as the K/V ring lets it.  A tcgen05.mma does not
+      // return until the tensor pipe has room for it, so a thread is busy for about as long as its
+      // MMAs execute; with one thread for both tiles every wait of one tile delayed the other.
+      // A K/V ring entry is released by BOTH threads (kv_empty counts two arrivals); a thread
+      // that does not use an entry still waits for it to be loaded before it lets it go, so its
+      // arrival can never be counted towards the stage's previous use.
       if (lane == 0) {
-        // The issuing thread runs scalar, latency-bound code: descriptors are a constant high word
-        // plus a low word that is a precomputed base plus a compile-time offset.
+        const uint32_t t = (warp == kMmaWarp) ? 0u : 1u;
+        // Scalar, latency-bound code in few registers: descriptors are a constant high word plus a
+        // low word that is a precomputed base plus a small offset, and barriers are addressed as
+        // one 32-bit base plus an index.
         const uint32_t hi_k = static_cast<uint32_t>(make_desc_kmajor_sw128(0) >> 32);
-        const uint32_t q_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem + kQOffset)));
-        const uint32_t k_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem + kKOffset)));
-        auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
-        uint32_t g = 0;                // score tiles issued so far
-        uint32_t kstage = 0, kpar = 0; // K ring position
-        uint32_t qpar = 0;
-        bool ok = true;
-        for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-          const Item it = decode_item<PAGED>(idx, p);
-          if (it.n == 0) continue;
-          if (!mbar_wait(q_full, qpar, abort_word)) break;
-          qpar ^= 1;
-          for (int j = 0; j < it.n; ++j, ++g) {
-            const uint32_t buf = g & 1;
-            if (!mbar_wait(k_full + kstage, kpar, abort_word)) { ok = false; break; }
-            // the buffer last held tile g - 2; the softmax threads have it in registers
-            // (passes at once for the first two tiles)
-            if (!mbar_wait(s_free + buf, ((g >> 1) & 1) ^ 1, abort_word)) { ok = false; break; }
-            tc_fence_after();
-            ATTN_TRACE(1, 1000 + j);
-            const uint32_t b0 = k_lo + kstage * (kTileBytes >> 4);
-            const uint32_t d = tmem_base + kTmemS + buf * 128;
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {  // 8 k-steps of 16 over the head dimension (two 64-wide blocks)
-              const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
-              umma_f16_ss(d, desc(q_lo + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
-            }
-            umma_commit(s_full + buf);
-            umma_commit(k_empty + kstage);
-            if (j == it.n - 1) umma_commit(q_empty);  // Q is free once the item's last score MMA has run
-            ATTN_TRACE(1, 2000 + j);
-            if (++kstage == kKStages) {
-              kstage = 0;
-              kpar ^= 1;
-            }
-          }
-        }
-      }
-      __syncwarp();
-    } else if (warp == kPvWarp) {
-      // ---------------- second MMAs: O (+)= P[g & 1] V_g ----------------
-      if (lane == 0) {
         const uint32_t hi_mn = static_cast<uint32_t>(make_desc_mnmajor_sw128(0, kHalfTileBytes) >> 32);
-        const uint32_t v_lo = static_cast<uint32_t>(make_desc_mnmajor_sw128(smem_u32(smem + kVOffset), kHalfTileBytes));
+        const uint32_t q_lo =
+            static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem + L::kQOffset + t * kTileBytes)));
+        const uint32_t k_lo = static_cast<uint32_t>(make_desc_kmajor_sw128(smem_u32(smem + L::kKvOffset)));
+        const uint32_t v_lo =
+            static_cast<uint32_t>(make_desc_mnmajor_sw128(smem_u32(smem + L::kKvOffset), kHalfTileBytes));
+        const uint32_t tmem_s = tmem_base + L::kTmemS + t * 128;
+        const uint32_t tmem_o = tmem_base + L::kTmemO + t * HD;
+        const uint32_t bar0 = smem_u32(bars);
+        // barrier indices in `bars`
+        constexpr uint32_t kQFull = 0, kQEmpty = 2, kKvFull = 4, kKvEmpty = 4 + kKvStages, kSFull = 4 + 2 * kKvStages,
+                           kPFull = kSFull + 2, kOFull = kSFull + 4, kOFree = kSFull + 6;
         auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
-        uint32_t g = 0, ic = 0;  // KV steps and items so far
-        uint32_t vstage = 0, vpar = 0;
-        bool ok = true;
-        for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-          const Item it = decode_item<PAGED>(idx, p);
-          if (it.n == 0) continue;
-          for (int j = 0; j < it.n; ++j, ++g) {
-            const uint32_t buf = g & 1;
-            if (!mbar_wait(v_full + vstage, vpar, abort_word)) { ok = false; break; }
-            if (!mbar_wait(p_full + buf, (g >> 1) & 1, abort_word)) { ok = false; break; }
-            // the accumulator is read by the epilogue of the previous item
-            if (j == 0 && !mbar_wait(o_free, (ic & 1) ^ 1, abort_word)) { ok = false; break; }
-            tc_fence_after();
-            // 8 k-steps of 16 KV rows; A = P from tensor memory, B = V (MN-major)
-            const uint32_t b0 = v_lo + vstage * (kTileBytes >> 4);
-            const uint32_t d = tmem_base + kTmemO;
-            const uint32_t a = tmem_base + kTmemP + buf * 64;
-            umma_f16_ts(d, a, desc(b0, hi_mn), kIdescPV, j == 0 ? 0u : 1u);
+        auto wait = [&](uint32_t index, uint32_t parity) { return mbar_wait_addr(bar0 + 8 * index, parity, abort_word); };
+        auto commit = [&](uint32_t index) { umma_commit_addr(bar0 + 8 * index); };
+        auto wait_entry = [&](uint32_t e) { return wait(kKvFull + e % kKvStages, (e / kKvStages) & 1); };
+        auto free_entry = [&](uint32_t e) { commit(kKvEmpty + e % kKvStages); };  // arrives once this thread's MMAs are done
+        // S = Q K^T with K in ring entry e
+        auto issue_scores = [&](uint32_t e) {
+          const uint32_t b0 = k_lo + (e % kKvStages) * (kTileBytes >> 4);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) umma_f16_ts(d, a + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, 1u);
-            umma_commit(v_empty + vstage);
-            umma_commit(o_done + buf);
-            if (j == it.n - 1) umma_commit(o_full);
-            if (++vstage == kVStages) {
-              vstage = 0;
-              vpar ^= 1;
-            }
+          for (int ks = 0; ks < HD / 16; ++ks) {  // k-steps of 16 over the head dimension (64-wide blocks)
+            const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
+            umma_f16_ss(tmem_s, desc(q_lo + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
           }
-          ++ic;
+          commit(kSFull + t);
+        };
+        // O (+)= P V with V in ring entry e: 8 k-steps of 16 KV rows; A = P from tensor memory
+        auto issue_pv = [&](uint32_t e, uint32_t accumulate) {
+          const uint32_t b0 = v_lo + (e % kKvStages) * (kTileBytes >> 4);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_f16_ts(tmem_o, tmem_s + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, ks > 0 ? 1u : accumulate);
+        };
+        uint32_t e0 = 0;              // ring entry of K_0 of the current item
+        uint32_t cq = 0, cp = 0, co = 0;  // Q tiles, P tiles and accumulators of this query tile consumed so far
+        // The two threads take turns: tile 0 then tile 1, for the item's first score tiles and for
+        // every KV step.  Without an order the two streams share the pipe evenly, both tiles' MMAs
+        // end together, both softmaxes run together and nothing overlaps; in turns one tile's
+        // softmax runs while the tensor core works for the other.  A thread collects everything
+        // its MMAs need BEFORE it asks for its turn, and hands the turn on as soon as its MMAs are
+        // issued (not completed), so the next group queues up behind them and the pipe stays busy.
+        uint32_t ct = 0;  // turns taken
+        constexpr uint32_t kTurn = kSFull + 12;
+        auto take_turn = [&]() {
+          const bool got = wait(kTurn + t, t ? (ct & 1u) : ((ct & 1u) ^ 1u));
+          ++ct;
+          return got;
+        };
+        auto pass_turn = [&]() { mbar_arrive(turn + (t ^ 1u)); };
+        bool ok = true;
+        ItemWalk<PAGED> walk(p);
+        Item it;
+        while (ok && walk.next_busy(it)) {
+          const int n = t ? it.n[1] : it.n[0];
+          const int nmax = it.nmax;
+          if (!wait_entry(e0)) break;
+          if (n > 0 && !wait(kQFull + t, cq & 1u)) break;
+          if (!take_turn()) break;
+          if (n > 0) {
+            ++cq;
+            tc_fence_after();
+            issue_scores(e0);
+            if (n == 1) commit(kQEmpty + t);
+          }
+          free_entry(e0);
+          pass_turn();
+          for (int j = 0; j < nmax; ++j) {
+            const uint32_t ev = e0 + 2 * j + 1;  // V_j; K_(j+1) is entry ev + 1
+            const bool more = j + 1 < nmax;
+            if (j < n) {
+              if (!wait(kPFull + t, cp & 1u)) { ok = false; break; }
+              ++cp;
+              if (j == 0) {  // the accumulator is read by the epilogue of the tile's previous item
+                if (!wait(kOFree + t, (co & 1u) ^ 1u)) { ok = false; break; }
+                ++co;
+              }
+            }
+            if (!wait_entry(ev) || (more && !wait_entry(ev + 1)) || !take_turn()) { ok = false; break; }
+            if (j < n) {
+              tc_fence_after();
+              issue_pv(ev, j > 0 ? 1u : 0u);
+              if (j == n - 1) commit(kOFull + t);
+              free_entry(ev);
+              if (more) {
+                if (j + 1 < n) {
+                  issue_scores(ev + 1);
+                  if (j + 2 == n) commit(kQEmpty + t);  // that was the item's last score MMA of this tile
+                }
+                free_entry(ev + 1);
+              }
+            } else {
+              // past this tile's diagonal: let the entries go (they have been loaded, see above)
+              mbar_arrive(kv_empty + ev % kKvStages);
+              if (more) mbar_arrive(kv_empty + (ev + 1) % kKvStages);
+            }
+            pass_turn();
+          }
+          e0 += 2 * nmax;
         }
       }
       __syncwarp();
@@ -484,127 +519,219 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    uint8_t* stage = smem + kOStageOffset;
+    uint8_t* stage = smem + L::kStageOffset;
     const bool store_thread = (warp == 8 && lane == 0);
     auto epi_barrier = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
-    uint32_t ic = 0, g0 = 0;  // items so far, KV steps before the current item
+    uint32_t ci[2] = {0, 0};  // items with work per tile so far
     bool ok = true;
-    for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-      const Item it = decode_item<PAGED>(idx, p);
-      if (it.n == 0) {
-        // no visible key: zeros (rare; plain stores)
-        const int q_row = it.qtile * kTileRows + row_in_tile;
-        if (q_row < p.seq_q) {
-          T* orow = reinterpret_cast<T*>(p.o) + it.batch * p.o_stride_b + it.head * p.o_stride_h +
-                    static_cast<int64_t>(q_row) * p.o_stride_s;
+    ItemWalk<PAGED> walk(p);
+    Item it;
+    while (ok && walk.next(it)) {
+#pragma unroll 1
+      for (int t = 0; t < 2; ++t) {
+        const int tile_r0 = it.pair * kPairRows + t * kTileRows;
+        if (tile_r0 >= p.seq_q) continue;
+        const int q_row = tile_r0 + row_in_tile;
+        if (it.n[t] == 0) {
+          // no visible key: zeros (rare; plain stores)
+          if (q_row < p.seq_q) {
+            T* orow = reinterpret_cast<T*>(p.o) + it.batch * p.o_stride_b + it.head * p.o_stride_h +
+                      static_cast<int64_t>(q_row) * p.o_stride_s;
 #pragma unroll
-          for (int v = 0; v < 16; ++v) reinterpret_cast<uint4*>(orow)[v] = make_uint4(0u, 0u, 0u, 0u);
-          if (p.lse) p.lse[(static_cast<int64_t>(it.batch) * p.q_heads + it.head) * p.seq_q + q_row] = -INFINITY;
+            for (int v = 0; v < HD / 8; ++v) reinterpret_cast<uint4*>(orow)[v] = make_uint4(0u, 0u, 0u, 0u);
+            if (p.lse) p.lse[(static_cast<int64_t>(it.batch) * p.q_heads + it.head) * p.seq_q + q_row] = -INFINITY;
+          }
+          continue;
         }
-        continue;
-      }
-      const uint32_t par = ic & 1;
-      ok = mbar_wait(o_full, par, abort_word) && mbar_wait(l_full, par, abort_word);
-      // the four warps meet at named barriers below: they give up together or not at all
-      ok = bar_red_and(1, 128, ok);
-      if (!ok) break;
-      tc_fence_after();
-      if (quarter == 0) ATTN_TRACE(3, 100);
-      // The two warpgroups' partial row sums, each relative to the running max the warpgroup last
-      // used; the accumulator is relative to the larger one.  They are added in the order "the
-      // warpgroup that took the item's even steps first", so that the result does not depend on
-      // what the CTA processed before this item.
-      const int we = g0 & 1, wo = we ^ 1;
-      const float m0 = lsum[(we * 2 + 0) * kTileRows + row_in_tile], l0 = lsum[(we * 2 + 1) * kTileRows + row_in_tile];
-      const float m1 = lsum[(wo * 2 + 0) * kTileRows + row_in_tile], l1 = lsum[(wo * 2 + 1) * kTileRows + row_in_tile];
-      const float mm = fmaxf(m0, m1);
-      const float a0 = (m0 == -INFINITY) ? 0.f : ex2(m0 - mm);
-      const float a1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - mm);
-      const float l = l0 * a0 + l1 * a1;
-      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
-      if (p.lse) {
-        // mm is in the log2 domain (scores times scale * log2 e), l is relative to it
-        const int q_row = it.qtile * kTileRows + row_in_tile;
-        if (q_row < p.seq_q)
+        const uint32_t par = ci[t] & 1;
+        ++ci[t];
+        ok = mbar_wait(o_full + t, par, abort_word) && mbar_wait(l_full + t, par, abort_word);
+        // the four warps meet at named barriers below: they give up together or not at all
+        ok = bar_red_and(1, 128, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const float m = lsum[(t * 2 + 0) * kTileRows + row_in_tile];
+        const float l = lsum[(t * 2 + 1) * kTileRows + row_in_tile];
+        const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+        if (p.lse && q_row < p.seq_q) {
+          // m is in the log2 domain (scores times scale * log2 e), l is relative to it
           p.lse[(static_cast<int64_t>(it.batch) * p.q_heads + it.head) * p.seq_q + q_row] =
-              (l > 0.f) ? (mm + log2f(l)) * 0.6931471805599453f : -INFINITY;
-      }
-      const uint32_t t_o = tmem_base + lane_field + kTmemO;
+              (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        }
+        const uint32_t t_o = tmem_base + lane_field + L::kTmemO + t * HD;
 #pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {  // one 64-column block at a time
-        // the staging block is free once the previous TMA store has read it
-        if (store_thread) tma_store_wait_read<0>();
-        epi_barrier();
+        for (int c2 = 0; c2 < kBlocks; ++c2) {  // one 64-column block at a time
+          // the staging block is free once the previous TMA store has read it
+          if (store_thread) tma_store_wait_read<0>();
+          epi_barrier();
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_o + (c2 * 2 + cc) * 32, r);
-          tmem_wait_ld();
-          uint8_t* blk = stage + row_in_tile * 128;
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_o + (c2 * 2 + cc) * 32, r);
+            tmem_wait_ld();
+            uint8_t* blk = stage + row_in_tile * 128;
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 u;
-            u.x = pack_pair<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
-            u.y = pack_pair<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
-            u.z = pack_pair<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
-            u.w = pack_pair<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
-            const int chunk = cc * 4 + v;
-            *reinterpret_cast<uint4*>(blk + ((chunk ^ (row_in_tile & 7)) << 4)) = u;
+            for (int v = 0; v < 4; ++v) {
+              uint4 u;
+              u.x = pack_pair<T>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+              u.y = pack_pair<T>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+              u.z = pack_pair<T>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+              u.w = pack_pair<T>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+              const int chunk = cc * 4 + v;
+              *reinterpret_cast<uint4*>(blk + ((chunk ^ (row_in_tile & 7)) << 4)) = u;
+            }
+          }
+          if (c2 == kBlocks - 1) {
+            // accumulator and row sums have been read: release them for the tile's next item
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(o_free + t);
+              mbar_arrive(l_free + t);
+            }
+          }
+          fence_proxy_async_smem();
+          epi_barrier();
+          if (store_thread) {
+            tma_store_4d(&tmap_o, stage, c2 * 64, tile_r0, it.head, it.batch);
+            tma_store_commit();
           }
         }
-        if (c2 == 1) {
-          // accumulator and row sums have been read: release them for the next item
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(o_free);
-            mbar_arrive(l_free);
-          }
-        }
-        fence_proxy_async_smem();
-        epi_barrier();
-        if (store_thread) {
-          tma_store_4d(&tmap_o, stage, c2 * 64, it.qtile * kTileRows, it.head, it.batch);
-          tma_store_commit();
-        }
       }
-      if (quarter == 0) ATTN_TRACE(3, 200);
-      ++ic;
-      g0 += it.n;
     }
     if (store_thread) tma_store_wait<0>();
   } else {
-    // ---------------- softmax / correction: warpgroup w takes the KV steps g with (g & 1) == w ----------------
+    // ---------------- softmax of query tile t = warp / 4 ----------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-    const int w = warp >> 2;  // also the score buffer and the P buffer this warpgroup works on
+    const int t = warp >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_field + kTmemS + w * 128;
-    const uint32_t t_p = tmem_base + lane_field + kTmemP + w * 64;
-    const uint32_t t_o = tmem_base + lane_field + kTmemO;
-    float* m_mine = xmax + w * kTileRows + row_in_tile;
-    const float* m_theirs = xmax + (w ^ 1) * kTileRows + row_in_tile;
+    const uint32_t t_s = tmem_base + lane_field + L::kTmemS + t * 128;  // scores, and P over their first half
+    const uint32_t t_o = tmem_base + lane_field + L::kTmemO + t * HD;
     const float scale_log2 = p.scale_log2;
     const float2 scale2 = make_float2(scale_log2, scale_log2);
-    uint32_t g = 0, ic = 0;  // KV steps (of both warpgroups) and items so far
+    uint32_t cs = 0, ci = 0;  // score tiles and items of this query tile so far
     bool ok = true;
-    for (int idx = blockIdx.x; idx < p.num_items && ok; idx += gridDim.x) {
-      const Item it = decode_item<PAGED>(idx, p);
-      if (it.n == 0) continue;
-      const int tile_r0 = it.qtile * kTileRows;
+    ItemWalk<PAGED> walk(p);
+    Item it;
+    while (ok && walk.next_busy(it)) {
+      const int n = it.n[t];
+      if (n == 0) continue;
+      const int tile_r0 = it.pair * kPairRows + t * kTileRows;
       const int q_row = tile_r0 + row_in_tile;
-      const int kv_len = PAGED ? it.kv_len : p.seq_kv;
-      const int causal_offset = PAGED ? it.causal_offset : p.causal_offset;
-      float m_ref = -INFINITY;  // running max this warpgroup's row sum is relative to
+      const int kv_len = it.kv_len;
+      const int causal_offset = it.causal_offset;
+      float m_ref = -INFINITY;  // the max the row's P and running sum are relative to
       float2 l2 = make_float2(0.f, 0.f);
-      for (int j = 0; j < it.n; ++j, ++g) {
-        if ((g & 1u) != static_cast<uint32_t>(w)) continue;
-        const uint32_t ph = (g >> 1) & 1;  // phase of this warpgroup's own barriers in this step
-        ok = mbar_wait(s_full + w, ph, abort_word);
+      for (int j = 0; j < n; ++j, ++cs) {
+        ok = mbar_wait(s_full + t, cs & 1, abort_word);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+#if VAR_SWEEP2
+        // One sweep over the row in two halves of 64 columns.  From the second KV tile of an item
+        // on, the exponentials are taken at once against the running max (which may lag the true
+        // max by up to 2^8) while the tile's own max is folded along in the same sweep, and the
+        // second half of the row is still on its way from tensor memory while the first half is
+        // processed.  Only if the tile's max turns out to raise the running max by more than 2^8
+        // (rare after the first tile) are O and the running sum rescaled and the sweep repeated;
+        // the probabilities are stored after that decision, so S is still intact for the reload.
+        const int col0 = j * kTileRows;
+        const bool need_mask =
+            (p.causal && col0 + kTileRows - 1 > tile_r0 + causal_offset) || (col0 + kTileRows > kv_len);
+        int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
+        if (need_mask) {
+          int vis = kv_len;
+          if (p.causal) vis = min(vis, q_row + causal_offset + 1);
+          limit = vis - col0;
+        }
+        uint32_t sr[128];  // scores; the packed probabilities take over sr[0..63] as the scores are consumed
+        auto mask_half = [&](int h) {
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (h * 64 + i >= limit) sr[h * 64 + i] = 0xff800000u;  // -inf
+          }
+        };
+        tmem_ld_32x32b_x64(t_s, sr);
+        tmem_wait_ld();
+        tmem_ld_32x32b_x64(t_s + 64, sr + 64);
+        mask_half(0);
+        bool second_half_pending = true;
+        bool unchecked = j > 0;
+        if (j == 0) {
+          // the first tile of an item has no running max yet: take the row max first
+          tmem_wait_ld();
+          second_half_pending = false;
+          mask_half(1);
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 128; i += 8) {
+            mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+            mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+            mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+          }
+          m_ref = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;  // -inf: the row sees no key in this tile
+        }
+        float2 lt;
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass) {
+          const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
+          const float2 negm2 = make_float2(-m_sub, -m_sub);
+          lt = make_float2(0.f, 0.f);
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (h == 1 && second_half_pending) {
+              tmem_wait_ld();
+              second_half_pending = false;
+              mask_half(1);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float s0 = __uint_as_float(sr[h * 64 + 2 * i]), s1 = __uint_as_float(sr[h * 64 + 2 * i + 1]);
+              const float2 x = ffma2(make_float2(s0, s1), scale2, negm2);
+              const float2 e = ((kPolyPairMask >> (i & 7)) & 1u) ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
+              lt = fadd2(lt, e);
+              if (i & 1) mx1 = fmax3(mx1, s0, s1); else mx0 = fmax3(mx0, s0, s1);
+              sr[h * 32 + i] = pack_pair<T>(e.x, e.y);  // (pair k of the row lands in sr[k], consumed as a score at pair k / 2)
+            }
+          }
+          if (!unchecked) break;
+          unchecked = false;
+          const float m_new = fmaxf(mx0, mx1) * scale_log2;
+          const bool grow = m_new > m_ref + kRescaleThreshold;  // also true for the first finite max
+          if (!__any_sync(0xffffffffu, grow)) break;
+          // Rescale O in place and repeat the sweep against the new max.  Every MMA of this tile
+          // issued before this score tile has completed (the score tile was committed behind them
+          // by the same thread), the previous PV included, and the next one waits for p_full below.
+          const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // m_ref = -inf gives 0
+#pragma unroll 1
+          for (int c = 0; c < HD / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(t_o + c * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x16(t_o + c * 16, r);
+          }
+          l2.x *= alpha;
+          l2.y *= alpha;
+          if (grow) m_ref = m_new;
+          tmem_ld_32x32b_x64(t_s, sr);
+          tmem_ld_32x32b_x64(t_s + 64, sr + 64);
+          tmem_wait_ld();
+          mask_half(0);
+          mask_half(1);
+        }
+        l2 = fadd2(l2, lt);
+        // probabilities -> tensor memory (16-bit pairs) over the first half of the score tile; masked
+        // scores were -inf and gave exactly 0
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_st_32x32b_x16(t_s + c * 16, reinterpret_cast<uint32_t(&)[16]>(sr[c * 16]));
+#else
         uint32_t sr[128];
         tmem_ld_32x32b_x64(t_s, sr);
         tmem_ld_32x32b_x64(t_s + 64, sr + 64);
@@ -619,56 +746,92 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           limit = vis - col0;
         }
         tmem_wait_ld();
-        // the row is in registers: the tensor core may write the tile two steps ahead over it
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(s_free + w);
-        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 100 + j);  // S_j in registers
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 128; ++i)
             if (i >= limit) sr[i] = 0xff800000u;  // -inf
         }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+#if VAR_STALE
+        bool unchecked = j > 0;
+        if (j == 0) {
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 128; i += 8) {
+            mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+            mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+            mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+          }
+          m_ref = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;  // -inf: the row sees no key in this tile
+        }
+        float2 lt;
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass) {
+          const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
+          const float2 negm2 = make_float2(-m_sub, -m_sub);
+          lt = make_float2(0.f, 0.f);
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float s0 = __uint_as_float(sr[c * 32 + 2 * i]), s1 = __uint_as_float(sr[c * 32 + 2 * i + 1]);
+              const float2 x = ffma2(make_float2(s0, s1), scale2, negm2);
+              const float2 e = ((kPolyPairMask >> (i & 7)) & 1u) ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
+              lt = fadd2(lt, e);
+              pk[i] = pack_pair<T>(e.x, e.y);
+              if (i & 1) mx1 = fmax3(mx1, s0, s1); else mx0 = fmax3(mx0, s0, s1);
+            }
+            tmem_st_32x32b_x16(t_s + c * 16, pk);
+          }
+          if (!unchecked) break;
+          unchecked = false;
+          const float m_new = fmaxf(mx0, mx1) * scale_log2;
+          const bool grow = m_new > m_ref + kRescaleThreshold;
+          if (!__any_sync(0xffffffffu, grow)) break;
+          const float alpha = grow ? ex2(m_ref - m_new) : 1.f;
+#pragma unroll 1
+          for (int c = 0; c < HD / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(t_o + c * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x16(t_o + c * 16, r);
+          }
+          l2.x *= alpha;
+          l2.y *= alpha;
+          if (grow) m_ref = m_new;
+        }
+        l2 = fadd2(l2, lt);
+#else
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#if VAR_MAX2
 #pragma unroll
         for (int i = 0; i < 128; i += 4) {
           mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
           mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
         }
-        const float m_new = fmaxf(mx0, mx1) * scale_log2;
-        // The running max after the previous step, published by the other warpgroup early in that
-        // step (half a step ago).  Every phase of x_full is observed, also when the value is not
-        // needed (first step of an item).
-        float m_prev = -INFINITY;
-        if (g > 0) {
-          ok = mbar_wait(x_full + (w ^ 1), ((g - 1) >> 1) & 1, abort_word);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          if (j > 0) m_prev = *m_theirs;
+#else
+#pragma unroll
+        for (int i = 0; i < 128; i += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
         }
-        const bool grow = m_new > m_prev + kRescaleThreshold;  // also true for the first finite max
-        const float m_cur = grow ? m_new : m_prev;
-        *m_mine = m_cur;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(x_full + w);
-        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 200 + j);  // running max published
-        // this warpgroup's partial row sum follows the running max
-        if (m_prev != m_ref) {  // m_prev > m_ref: the other warpgroup raised it
-          const float a = ex2(m_ref - m_prev);  // m_ref = -inf gives 0 (and the sum is 0 then)
-          l2.x *= a;
-          l2.y *= a;
-        }
+#endif
+        const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+        const bool grow = m_new > m_ref + kRescaleThreshold;  // also true for the first finite max
         if (j > 0 && __any_sync(0xffffffffu, grow)) {
-          // Rescale O between "O += P V" of the previous step (the other warpgroup's P) and this
-          // step's.  Rare after the first steps of an item: the max must grow by 2^8.
-          float alpha = 1.f;
-          if (grow) alpha = ex2(m_prev - m_new);  // m_prev = -inf gives 0
-          ok = mbar_wait(o_done + (w ^ 1), ((g - 1) >> 1) & 1, abort_word);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
+          // Rescale O in place.  Every MMA issued before this score tile has completed (it was
+          // committed behind them on the same in-order stream), the previous PV of this tile
+          // included, and the next one waits for p_full below.  Rare after the first steps of an
+          // item: the max must grow by 2^8.
+          const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // m_ref = -inf gives 0
 #pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < HD / 16; ++c) {
             uint32_t r[16];
             tmem_ld_32x32b_x16(t_o + c * 16, r);
             tmem_wait_ld();
@@ -679,17 +842,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           l2.x *= alpha;
           l2.y *= alpha;
         }
-        m_ref = m_cur;
-        const float m_sub = (m_cur == -INFINITY) ? 0.f : m_cur;
+        if (grow) m_ref = m_new;
+        const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
         const float2 negm2 = make_float2(-m_sub, -m_sub);
-        // this warpgroup's P buffer was last read by "O += P V" two steps ago
-        if (g >= 2) {
-          ok = mbar_wait(o_done + w, ph ^ 1, abort_word);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
 
-        // probabilities -> tensor memory (16-bit pairs); masked scores are -inf and give (almost) exactly 0
+        // probabilities -> tensor memory (16-bit pairs) over the first half of the score tile; masked
+        // scores are -inf and give exactly 0
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
@@ -701,42 +859,31 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             l2 = fadd2(l2, e);
             pk[i] = pack_pair<T>(e.x, e.y);
           }
-          tmem_st_32x32b_x16(t_p + c * 16, pk);
+          tmem_st_32x32b_x16(t_s + c * 16, pk);
         }
-        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 300 + j);  // exponentials done, P stores issued
+#endif
+#endif
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + w);
-        if (quarter == 0) ATTN_TRACE(2 + 2 * w, 400 + j);  // P signalled
+        if (lane == 0) mbar_arrive(p_full + t);
       }
       if (!ok) break;
-      // hand (max, sum) of this warpgroup's steps to the epilogue warps
-      ok = mbar_wait(l_free, (ic & 1) ^ 1, abort_word);
+      // hand (max, sum) of the item to the epilogue warps
+      ok = mbar_wait(l_free + t, (ci & 1) ^ 1, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      lsum[(w * 2 + 0) * kTileRows + row_in_tile] = m_ref;
-      lsum[(w * 2 + 1) * kTileRows + row_in_tile] = l2.x + l2.y;
+      ++ci;
+      lsum[(t * 2 + 0) * kTileRows + row_in_tile] = m_ref;
+      lsum[(t * 2 + 1) * kTileRows + row_in_tile] = l2.x + l2.y;
       __syncwarp();
-      if (lane == 0) mbar_arrive(l_full);
-      ++ic;
+      if (lane == 0) mbar_arrive(l_full + t);
     }
   }
 
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
-#ifdef B200K_ATTN_TRACE
-  if (threadIdx.x == 0 && p.status != nullptr) {
-    long long* tb = reinterpret_cast<long long*>(p.status) + 5 * 256 * 2 + blockIdx.x * 2;
-    tb[0] = static_cast<long long>(trace_t0);
-    tb[1] = static_cast<long long>(globaltimer_ns());
-    if (blockIdx.x == 0) {
-      long long* tc = reinterpret_cast<long long*>(p.status) + 5 * 256 * 2 + 148 * 2;
-      tc[0] = clock64() - trace_c0;
-    }
-  }
-#endif
   if (*abort_word != 0) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) {
@@ -744,27 +891,44 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusAttnTimeout);
     __syncthreads();
   }
-  if (warp == kScoreWarp) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
 }
 
-template <typename T, bool PAGED>
+template <typename T, int HD, bool PAGED>
 int launch_typed(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                  const AttnParams& p, cudaStream_t stream) {
-  auto kfn = attn_fwd_kernel<T, PAGED>;
-  static bool configured = false;
-  if (!configured) {
-    int rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem),
-                        "cudaFuncSetAttribute(attention smem)");
-    if (rc) return rc;
-    configured = true;
-  }
+  auto kfn = attn_fwd_kernel<T, HD, PAGED>;
+  static bool configured[64] = {};  // per instantiation and device ordinal
+  int rc = ensure_dynamic_smem(kfn, AttnSmem<HD>::kTotal, configured, "cudaFuncSetAttribute(attention smem)");
+  if (rc) return rc;
   const int sms = num_sms();
-  const int grid = p.num_items < sms ? p.num_items : sms;
-  kfn<<<grid, kAttnThreads, kAttnSmem, stream>>>(tq, tk, tv, to, p);
+  const int grid = p.num_units < sms ? p.num_units : sms;
+  kfn<<<grid, kAttnThreads, AttnSmem<HD>::kTotal, stream>>>(tq, tk, tv, to, p);
   return check_cuda(cudaGetLastError(), "attn_fwd_kernel launch");
+}
+
+template <bool PAGED>
+int launch_any(int dtype, int head_dim, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+               const CUtensorMap& to, const AttnParams& p, cudaStream_t stream) {
+  if (head_dim == 128) {
+    if (dtype == B200K_F16) return launch_typed<__half, 128, PAGED>(tq, tk, tv, to, p, stream);
+    return launch_typed<__nv_bfloat16, 128, PAGED>(tq, tk, tv, to, p, stream);
+  }
+  if (dtype == B200K_F16) return launch_typed<__half, 64, PAGED>(tq, tk, tv, to, p, stream);
+  return launch_typed<__nv_bfloat16, 64, PAGED>(tq, tk, tv, to, p, stream);
+}
+
+// Work units: see ItemWalk.
+int fill_units(AttnParams& p, const char* who) {
+  p.num_pairs = (p.seq_q + kPairRows - 1) / kPairRows;
+  p.units_per_head = p.causal ? (p.num_pairs + 1) / 2 : p.num_pairs;
+  const int64_t units = static_cast<int64_t>(p.batch) * p.q_heads * p.units_per_head;
+  if (units > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "%s: too many query tiles", who);
+  p.num_units = static_cast<int32_t>(units);
+  return B200K_OK;
 }
 
 }  // namespace
@@ -773,7 +937,8 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   if (!a.q || !a.k || !a.v || !a.o) return set_error(B200K_ERR_NULL, "attention_fwd: q, k, v and o must be non-NULL");
   if (a.batch <= 0 || a.q_heads <= 0 || a.kv_heads <= 0 || a.seq_q <= 0 || a.seq_kv <= 0)
     return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: all dimensions must be positive");
-  if (a.head_dim != kD) return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: head_dim must be 128");
+  if (a.head_dim != 128 && a.head_dim != 64)
+    return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: head_dim must be 128 or 64");
   if (a.q_heads % a.kv_heads != 0)
     return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: q_heads must be a multiple of kv_heads");
   if (a.dtype != B200K_F16 && a.dtype != B200K_BF16)
@@ -793,8 +958,9 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
 
   CUtensorMap tq, tk, tv, to;
   const uint32_t box[4] = {64, kTileRows, 1, 1};
+  const uint64_t hd = static_cast<uint64_t>(a.head_dim);
   {
-    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
+    uint64_t dims[4] = {hd, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
                         static_cast<uint64_t>(a.batch)};
     uint64_t st[3] = {static_cast<uint64_t>(a.q_stride_s) * 2, static_cast<uint64_t>(a.q_stride_h) * 2,
                       static_cast<uint64_t>(a.q_stride_b) * 2};
@@ -802,7 +968,7 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
     if (rc) return rc;
   }
   {
-    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.seq_kv), static_cast<uint64_t>(a.kv_heads),
+    uint64_t dims[4] = {hd, static_cast<uint64_t>(a.seq_kv), static_cast<uint64_t>(a.kv_heads),
                         static_cast<uint64_t>(a.batch)};
     uint64_t st[3] = {static_cast<uint64_t>(a.k_stride_s) * 2, static_cast<uint64_t>(a.k_stride_h) * 2,
                       static_cast<uint64_t>(a.k_stride_b) * 2};
@@ -815,7 +981,7 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   }
 
   {
-    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
+    uint64_t dims[4] = {hd, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
                         static_cast<uint64_t>(a.batch)};
     uint64_t st[3] = {static_cast<uint64_t>(a.o_stride_s) * 2, static_cast<uint64_t>(a.o_stride_h) * 2,
                       static_cast<uint64_t>(a.o_stride_b) * 2};
@@ -835,18 +1001,15 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   p.seq_kv = a.seq_kv;
   p.causal = a.causal ? 1 : 0;
   p.causal_offset = a.seq_kv - a.seq_q;
-  p.num_q_tiles = (a.seq_q + kTileRows - 1) / kTileRows;
-  const int64_t items = static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles;
-  if (items > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: too many query tiles");
-  p.num_items = static_cast<int32_t>(items);
+  rc = fill_units(p, "attention_fwd");
+  if (rc) return rc;
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
   p.lse = a.lse;
   p.block_table = nullptr;
   p.seq_lens = nullptr;
   p.block_table_stride = p.page_size = p.num_pages = 0;
-  if (a.dtype == B200K_F16) return launch_typed<__half, false>(tq, tk, tv, to, p, stream);
-  return launch_typed<__nv_bfloat16, false>(tq, tk, tv, to, p, stream);
+  return launch_any<false>(a.dtype, a.head_dim, tq, tk, tv, to, p, stream);
 }
 
 int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t stream) {
@@ -854,7 +1017,8 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
     return set_error(B200K_ERR_NULL, "paged_attention_fwd: q, k_cache, v_cache, o, block_table, seq_lens must be non-NULL");
   if (a.batch <= 0 || a.q_heads <= 0 || a.kv_heads <= 0 || a.seq_q <= 0 || a.max_seq_kv <= 0)
     return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: all dimensions must be positive");
-  if (a.head_dim != kD) return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: head_dim must be 128");
+  if (a.head_dim != 128 && a.head_dim != 64)
+    return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: head_dim must be 128 or 64");
   if (a.q_heads % a.kv_heads != 0)
     return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: q_heads must be a multiple of kv_heads");
   if (a.dtype != B200K_F16 && a.dtype != B200K_BF16)
@@ -879,8 +1043,9 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
   CUtensorMap tq, tk, tv, to;
   const uint32_t box[4] = {64, kTileRows, 1, 1};
   const uint32_t page_box[4] = {64, static_cast<uint32_t>(a.page_size), 1, 1};
+  const uint64_t hd = static_cast<uint64_t>(a.head_dim);
   {
-    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
+    uint64_t dims[4] = {hd, static_cast<uint64_t>(a.seq_q), static_cast<uint64_t>(a.q_heads),
                         static_cast<uint64_t>(a.batch)};
     uint64_t st[3] = {static_cast<uint64_t>(a.q_stride_s) * 2, static_cast<uint64_t>(a.q_stride_h) * 2,
                       static_cast<uint64_t>(a.q_stride_b) * 2};
@@ -892,9 +1057,9 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
     if (rc) return rc;
   }
   {
-    uint64_t dims[4] = {kD, static_cast<uint64_t>(a.page_size), static_cast<uint64_t>(a.kv_heads),
+    uint64_t dims[4] = {hd, static_cast<uint64_t>(a.page_size), static_cast<uint64_t>(a.kv_heads),
                         static_cast<uint64_t>(a.num_pages)};
-    uint64_t st[3] = {static_cast<uint64_t>(kD) * 2, static_cast<uint64_t>(a.kv_head_stride) * 2,
+    uint64_t st[3] = {hd * 2, static_cast<uint64_t>(a.kv_head_stride) * 2,
                       static_cast<uint64_t>(a.kv_page_stride) * 2};
     rc = encode_tmap(&tk, a.dtype, 4, const_cast<void*>(a.k_cache), dims, st, page_box);
     if (rc) return rc;
@@ -914,10 +1079,8 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
   p.seq_kv = a.max_seq_kv;
   p.causal = a.causal ? 1 : 0;
   p.causal_offset = a.max_seq_kv - a.seq_q;
-  p.num_q_tiles = (a.seq_q + kTileRows - 1) / kTileRows;
-  const int64_t items = static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles;
-  if (items > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: too many query tiles");
-  p.num_items = static_cast<int32_t>(items);
+  rc = fill_units(p, "paged_attention_fwd");
+  if (rc) return rc;
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
   p.lse = nullptr;
@@ -926,8 +1089,7 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
   p.block_table_stride = a.block_table_stride;
   p.page_size = a.page_size;
   p.num_pages = a.num_pages;
-  if (a.dtype == B200K_F16) return launch_typed<__half, true>(tq, tk, tv, to, p, stream);
-  return launch_typed<__nv_bfloat16, true>(tq, tk, tv, to, p, stream);
+  return launch_any<true>(a.dtype, a.head_dim, tq, tk, tv, to, p, stream);
 }
 
 }  // namespace b200k
