@@ -158,9 +158,19 @@ int b200k_gemm_nt_allgather(const b200k_gemm_allgather_args* args, void* stream)
  * Layout: Q [batch, q_heads, seq_q, head_dim], K/V [batch, kv_heads, seq_kv, head_dim],
  * O like Q; innermost dimension contiguous; strides below are in ELEMENTS.
  * q_heads must be a multiple of kv_heads (query head h reads kv head h / (q_heads/kv_heads)).
- * head_dim must be 128.  Causal masking aligns the last query with the last key
+ * head_dim must be 128 or 64.  Causal masking aligns the last query with the last key
  * (query i sees keys j <= i + seq_kv - seq_q).
+ *
+ * Two kernels implement the call.  B200K_ATTN_ONE_TILE: a work item is one 128-row query tile,
+ * two softmax warpgroups take alternate KV steps (head_dim 128 only).  B200K_ATTN_TILE_PAIR: a
+ * work item is a pair of query tiles that share every K/V tile, one softmax warpgroup each; causal
+ * problems are dealt out in (heavy, light) couples of equal cost.  B200K_ATTN_AUTO picks the pair
+ * kernel for head_dim 64 and for causal problems whose couples fill the SMs evenly, else the
+ * one-tile kernel (the measured winner in each case).  Results of the two agree within rounding
+ * of the 16-bit probabilities, not bitwise.
  */
+enum { B200K_ATTN_AUTO = 0, B200K_ATTN_ONE_TILE = 1, B200K_ATTN_TILE_PAIR = 2 };
+
 typedef struct b200k_attention_args {
   const void* q;
   const void* k;
@@ -178,6 +188,8 @@ typedef struct b200k_attention_args {
   float* lse;      /* optional output [batch, q_heads, seq_q] (contiguous fp32), may be NULL:
                       ln sum_j exp(scale * q_i . k_j) over the visible keys, -inf for a row that sees
                       none; b200k_attention_bwd takes it to skip recomputing the row statistics */
+  int32_t kernel;  /* B200K_ATTN_AUTO | B200K_ATTN_ONE_TILE | B200K_ATTN_TILE_PAIR */
+  int32_t reserved;
 } b200k_attention_args;
 
 int b200k_attention_fwd(const b200k_attention_args* args, void* stream);
@@ -234,7 +246,7 @@ int b200k_attention_bwd(const b200k_attention_bwd_args* args, void* stream);
  * and seq_lens[b] <= max_seq_kv keys for sequence b.  The seq_q queries of a sequence are its last
  * seq_q tokens: with causal != 0 query i sees keys j <= i + seq_lens[b] - seq_q.  A sequence with
  * no visible key yields zeros.  k_cache / v_cache: [num_pages, kv_heads, page_size, head_dim] with
- * contiguous rows, page_size in {16, 32, 64, 128}.  Whole pages are fetched, so the rows of a
+ * contiguous rows, page_size in {16, 32, 64, 128}, head_dim 128 or 64.  Whole pages are fetched, so the rows of a
  * sequence's last page past seq_lens[b] must hold finite values (they are masked, but 0 * NaN is
  * NaN).  A block-table entry outside the pool reads as zeros and sets status bit 4.
  * The reference has no call site for this; its layout is the decode path's.
@@ -254,7 +266,7 @@ typedef struct b200k_paged_attention_args {
   int32_t dtype; /* F16 | BF16 */
   int32_t causal;
   float scale;
-  int32_t reserved2;
+  int32_t kernel;  /* B200K_ATTN_AUTO | B200K_ATTN_ONE_TILE | B200K_ATTN_TILE_PAIR */
   int32_t* status; /* device status word, may be NULL */
 } b200k_paged_attention_args;
 

@@ -53,6 +53,9 @@ DECODE_STATIC_SCRATCH_BYTES = 32 << 20
 # b200k_dtype
 F16, BF16, F32, E4M3 = 0, 1, 2, 3
 
+# attention forward kernel choice (B200K_ATTN_*)
+ATTN_AUTO, ATTN_ONE_TILE, ATTN_TILE_PAIR = 0, 1, 2
+
 
 class B200kError(RuntimeError):
     """A C-ABI call returned a non-OK status (CUDA failure, unsupported device, ...)."""
@@ -129,6 +132,8 @@ class AttentionArgs(C.Structure):
         ("scale", C.c_float),
         ("status", C.c_void_p),
         ("lse", C.c_void_p),
+        ("kernel", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -182,7 +187,7 @@ class PagedAttentionArgs(C.Structure):
         ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("q_stride_s", C.c_int64),
         ("o_stride_b", C.c_int64), ("o_stride_h", C.c_int64), ("o_stride_s", C.c_int64),
         ("kv_page_stride", C.c_int64), ("kv_head_stride", C.c_int64),
-        ("dtype", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float), ("reserved2", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("scale", C.c_float), ("kernel", C.c_int32),
         ("status", C.c_void_p),
     ]
 

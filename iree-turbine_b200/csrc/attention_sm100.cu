@@ -1,4 +1,6 @@
-// Attention forward (vanilla and causal, dense or paged K/V, head dim 128 or 64) on sm_100a.
+// Attention forward (vanilla and causal, dense or paged K/V, head dim 128 or 64) on sm_100a: the
+// TILE-PAIR kernel, and the entry points that choose between it and the one-tile kernel of
+// attention_tile_sm100.cu (see choose_pair_kernel at the end of this file).
 //
 // Persistent CTAs, one per SM.  A work item is one PAIR of 128-row query tiles (256 consecutive
 // query rows) of one (batch, head).  The two tiles of a pair are independent problems that share
@@ -55,8 +57,7 @@ namespace {
 constexpr int kAttnThreads = 512;
 constexpr int kKvWarp = 12;
 constexpr int kMmaWarp = 13;
-constexpr int kQWarp = 14;
-constexpr int kMmaWarp2 = 15;
+constexpr int kQWarp = 14;  // (warp 15 issues the MMAs of query tile 1)
 // Registers: 4 warps per SM sub-partition x 128 at launch = 512 per lane, redistributed.  A
 // setmaxnreg.inc beyond what the others gave up never completes.
 constexpr int kRegsSoftmax = 184;
@@ -67,24 +68,6 @@ constexpr int kTileRows = 128;           // query rows per tile, KV rows per til
 constexpr int kPairRows = 2 * kTileRows;  // query rows per work item
 constexpr int kHalfTileBytes = kTileRows * 128;  // one 64-element column block of a tile: 16 KB
 constexpr int kKvStages = 4;
-#ifndef VAR_NOPREFETCH
-#define VAR_NOPREFETCH 0
-#endif
-#ifndef VAR_NOLOOKAHEAD
-#define VAR_NOLOOKAHEAD 0
-#endif
-#ifndef VAR_BLOCKLA
-#define VAR_BLOCKLA 0
-#endif
-#ifndef VAR_MAX2
-#define VAR_MAX2 0
-#endif
-#ifndef VAR_STALE
-#define VAR_STALE 0
-#endif
-#ifndef VAR_SWEEP2
-#define VAR_SWEEP2 0
-#endif
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -155,10 +138,7 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 // The special-function unit delivers 16 results per cycle and SM: 128 x 128 exponentials are 1024
 // cycles, as long as the two MMAs of the same tile, so whatever share of them moves to the FMA
 // pipe comes off the softmax's critical resource.
-#ifndef VAR_POLY
-#define VAR_POLY 0x00u
-#endif
-constexpr uint32_t kPolyPairMask = VAR_POLY;
+constexpr uint32_t kPolyPairMask = 0x00u;
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
@@ -211,15 +191,18 @@ __device__ __forceinline__ Item make_item(int bh, int pair, const AttnParams& p)
 
 // The CTA's items, in the order every role walks them: units blockIdx.x, blockIdx.x + gridDim.x, ...;
 // a unit is one pair of a (batch, head), heaviest first, or -- causal -- the k-th heaviest pair
-// followed by the k-th lightest of the same head.
+// followed by the k-th lightest of the same head.  Units are numbered (batch, head)-major, so the
+// CTAs that run at one time work on a few neighbouring heads and share their K/V in L2.  (Giving
+// each CTA a contiguous range of units instead -- one head per CTA at a time -- puts 148 heads'
+// K/V in flight at once, more than L2 holds at S = 4096: measured 9 % slower.)
 template <bool PAGED>
 struct ItemWalk {
   const AttnParams& p;
-  int unit, part;
-  __device__ ItemWalk(const AttnParams& params) : p(params), unit(blockIdx.x), part(0) {}
+  int unit, end, part;
+  __device__ ItemWalk(const AttnParams& params) : p(params), unit(blockIdx.x), end(params.num_units), part(0) {}
   // Next item, empty ones (nmax == 0) included; false when the CTA has no more.
   __device__ __forceinline__ bool next(Item& it) {
-    while (unit < p.num_units) {
+    while (unit < end) {
       const int bh = unit / p.units_per_head;
       const int s = unit - bh * p.units_per_head;
       const int heavy = p.num_pairs - 1 - s;
@@ -379,7 +362,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           }
           // A Q buffer frees up only a step or so before the next item needs it, less than a trip
           // to HBM: ask for the next item's Q tiles in L2 now, an item ahead.
-          if (have_next && !VAR_NOPREFETCH) {
+          if (have_next) {
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
               if (nx.n[t] == 0) continue;
@@ -446,8 +429,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         };
         uint32_t e0 = 0;              // ring entry of K_0 of the current item
         uint32_t cq = 0, cp = 0, co = 0;  // Q tiles, P tiles and accumulators of this query tile consumed so far
-        // The two threads take turns: tile 0 then tile 1, for the item's first score tiles and for
-        // every KV step.  Without an order the two streams share the pipe evenly, both tiles' MMAs
+        // The two threads take turns, tile 0 then tile 1, for every KV step.  Without an order the two streams share the pipe evenly, both tiles' MMAs
         // end together, both softmaxes run together and nothing overlaps; in turns one tile's
         // softmax runs while the tensor core works for the other.  A thread collects everything
         // its MMAs need BEFORE it asks for its turn, and hands the turn on as soon as its MMAs are
@@ -466,47 +448,50 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         while (ok && walk.next_busy(it)) {
           const int n = t ? it.n[1] : it.n[0];
           const int nmax = it.nmax;
+          // The first score tile of an item needs no turn: a tile that is done with the previous
+          // item starts the next one at once, whatever the other tile is still doing.
           if (!wait_entry(e0)) break;
-          if (n > 0 && !wait(kQFull + t, cq & 1u)) break;
-          if (!take_turn()) break;
           if (n > 0) {
+            if (!wait(kQFull + t, cq & 1u)) break;
             ++cq;
             tc_fence_after();
             issue_scores(e0);
             if (n == 1) commit(kQEmpty + t);
           }
           free_entry(e0);
-          pass_turn();
           for (int j = 0; j < nmax; ++j) {
             const uint32_t ev = e0 + 2 * j + 1;  // V_j; K_(j+1) is entry ev + 1
             const bool more = j + 1 < nmax;
+            // Everything that is normally there long before the probabilities first (the K/V tiles,
+            // the turn: the order of turns is fixed, so holding it while waiting delays nobody),
+            // so that the path from "P written" to the first MMA is as short as possible.
+            if (!wait_entry(ev) || (more && !wait_entry(ev + 1)) || !take_turn()) { ok = false; break; }
             if (j < n) {
-              if (!wait(kPFull + t, cp & 1u)) { ok = false; break; }
-              ++cp;
               if (j == 0) {  // the accumulator is read by the epilogue of the tile's previous item
                 if (!wait(kOFree + t, (co & 1u) ^ 1u)) { ok = false; break; }
                 ++co;
               }
-            }
-            if (!wait_entry(ev) || (more && !wait_entry(ev + 1)) || !take_turn()) { ok = false; break; }
-            if (j < n) {
+              if (!wait(kPFull + t, cp & 1u)) { ok = false; break; }
+              ++cp;
               tc_fence_after();
               issue_pv(ev, j > 0 ? 1u : 0u);
+              // The other tile's thread needs a few hundred cycles from here to its first MMA: hand
+              // the turn on now, with this tile's score MMAs still to be issued, so that its MMAs
+              // arrive before the pipe runs dry (the two tiles' MMAs may interleave from here on).
+              pass_turn();
+              if (more && j + 1 < n) {
+                issue_scores(ev + 1);  // (its commit to s_full, the one the softmax waits for, goes first)
+                if (j + 2 == n) commit(kQEmpty + t);  // that was the item's last score MMA of this tile
+              }
               if (j == n - 1) commit(kOFull + t);
               free_entry(ev);
-              if (more) {
-                if (j + 1 < n) {
-                  issue_scores(ev + 1);
-                  if (j + 2 == n) commit(kQEmpty + t);  // that was the item's last score MMA of this tile
-                }
-                free_entry(ev + 1);
-              }
+              if (more) free_entry(ev + 1);
             } else {
               // past this tile's diagonal: let the entries go (they have been loaded, see above)
+              pass_turn();
               mbar_arrive(kv_empty + ev % kKvStages);
               if (more) mbar_arrive(kv_empty + (ev + 1) % kKvStages);
             }
-            pass_turn();
           }
           e0 += 2 * nmax;
         }
@@ -629,109 +614,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-#if VAR_SWEEP2
-        // One sweep over the row in two halves of 64 columns.  From the second KV tile of an item
-        // on, the exponentials are taken at once against the running max (which may lag the true
-        // max by up to 2^8) while the tile's own max is folded along in the same sweep, and the
-        // second half of the row is still on its way from tensor memory while the first half is
-        // processed.  Only if the tile's max turns out to raise the running max by more than 2^8
-        // (rare after the first tile) are O and the running sum rescaled and the sweep repeated;
-        // the probabilities are stored after that decision, so S is still intact for the reload.
-        const int col0 = j * kTileRows;
-        const bool need_mask =
-            (p.causal && col0 + kTileRows - 1 > tile_r0 + causal_offset) || (col0 + kTileRows > kv_len);
-        int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
-        if (need_mask) {
-          int vis = kv_len;
-          if (p.causal) vis = min(vis, q_row + causal_offset + 1);
-          limit = vis - col0;
-        }
-        uint32_t sr[128];  // scores; the packed probabilities take over sr[0..63] as the scores are consumed
-        auto mask_half = [&](int h) {
-          if (need_mask) {
-#pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (h * 64 + i >= limit) sr[h * 64 + i] = 0xff800000u;  // -inf
-          }
-        };
-        tmem_ld_32x32b_x64(t_s, sr);
-        tmem_wait_ld();
-        tmem_ld_32x32b_x64(t_s + 64, sr + 64);
-        mask_half(0);
-        bool second_half_pending = true;
-        bool unchecked = j > 0;
-        if (j == 0) {
-          // the first tile of an item has no running max yet: take the row max first
-          tmem_wait_ld();
-          second_half_pending = false;
-          mask_half(1);
-          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 128; i += 8) {
-            mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-            mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
-            mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
-            mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
-          }
-          m_ref = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;  // -inf: the row sees no key in this tile
-        }
-        float2 lt;
-#pragma unroll 1
-        for (int pass = 0; pass < 2; ++pass) {
-          const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
-          const float2 negm2 = make_float2(-m_sub, -m_sub);
-          lt = make_float2(0.f, 0.f);
-          float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (h == 1 && second_half_pending) {
-              tmem_wait_ld();
-              second_half_pending = false;
-              mask_half(1);
-            }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float s0 = __uint_as_float(sr[h * 64 + 2 * i]), s1 = __uint_as_float(sr[h * 64 + 2 * i + 1]);
-              const float2 x = ffma2(make_float2(s0, s1), scale2, negm2);
-              const float2 e = ((kPolyPairMask >> (i & 7)) & 1u) ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
-              lt = fadd2(lt, e);
-              if (i & 1) mx1 = fmax3(mx1, s0, s1); else mx0 = fmax3(mx0, s0, s1);
-              sr[h * 32 + i] = pack_pair<T>(e.x, e.y);  // (pair k of the row lands in sr[k], consumed as a score at pair k / 2)
-            }
-          }
-          if (!unchecked) break;
-          unchecked = false;
-          const float m_new = fmaxf(mx0, mx1) * scale_log2;
-          const bool grow = m_new > m_ref + kRescaleThreshold;  // also true for the first finite max
-          if (!__any_sync(0xffffffffu, grow)) break;
-          // Rescale O in place and repeat the sweep against the new max.  Every MMA of this tile
-          // issued before this score tile has completed (the score tile was committed behind them
-          // by the same thread), the previous PV included, and the next one waits for p_full below.
-          const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // m_ref = -inf gives 0
-#pragma unroll 1
-          for (int c = 0; c < HD / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld_32x32b_x16(t_o + c * 16, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x16(t_o + c * 16, r);
-          }
-          l2.x *= alpha;
-          l2.y *= alpha;
-          if (grow) m_ref = m_new;
-          tmem_ld_32x32b_x64(t_s, sr);
-          tmem_ld_32x32b_x64(t_s + 64, sr + 64);
-          tmem_wait_ld();
-          mask_half(0);
-          mask_half(1);
-        }
-        l2 = fadd2(l2, lt);
-        // probabilities -> tensor memory (16-bit pairs) over the first half of the score tile; masked
-        // scores were -inf and gave exactly 0
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_st_32x32b_x16(t_s + c * 16, reinterpret_cast<uint32_t(&)[16]>(sr[c * 16]));
-#else
         uint32_t sr[128];
         tmem_ld_32x32b_x64(t_s, sr);
         tmem_ld_32x32b_x64(t_s + 64, sr + 64);
@@ -751,69 +633,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           for (int i = 0; i < 128; ++i)
             if (i >= limit) sr[i] = 0xff800000u;  // -inf
         }
-#if VAR_STALE
-        bool unchecked = j > 0;
-        if (j == 0) {
-          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 128; i += 8) {
-            mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-            mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
-            mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
-            mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
-          }
-          m_ref = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;  // -inf: the row sees no key in this tile
-        }
-        float2 lt;
-#pragma unroll 1
-        for (int pass = 0; pass < 2; ++pass) {
-          const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
-          const float2 negm2 = make_float2(-m_sub, -m_sub);
-          lt = make_float2(0.f, 0.f);
-          float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float s0 = __uint_as_float(sr[c * 32 + 2 * i]), s1 = __uint_as_float(sr[c * 32 + 2 * i + 1]);
-              const float2 x = ffma2(make_float2(s0, s1), scale2, negm2);
-              const float2 e = ((kPolyPairMask >> (i & 7)) & 1u) ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
-              lt = fadd2(lt, e);
-              pk[i] = pack_pair<T>(e.x, e.y);
-              if (i & 1) mx1 = fmax3(mx1, s0, s1); else mx0 = fmax3(mx0, s0, s1);
-            }
-            tmem_st_32x32b_x16(t_s + c * 16, pk);
-          }
-          if (!unchecked) break;
-          unchecked = false;
-          const float m_new = fmaxf(mx0, mx1) * scale_log2;
-          const bool grow = m_new > m_ref + kRescaleThreshold;
-          if (!__any_sync(0xffffffffu, grow)) break;
-          const float alpha = grow ? ex2(m_ref - m_new) : 1.f;
-#pragma unroll 1
-          for (int c = 0; c < HD / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld_32x32b_x16(t_o + c * 16, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x16(t_o + c * 16, r);
-          }
-          l2.x *= alpha;
-          l2.y *= alpha;
-          if (grow) m_ref = m_new;
-        }
-        l2 = fadd2(l2, lt);
-#else
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#if VAR_MAX2
-#pragma unroll
-        for (int i = 0; i < 128; i += 4) {
-          mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
-        }
-#else
 #pragma unroll
         for (int i = 0; i < 128; i += 8) {
           mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
@@ -821,7 +641,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
           mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
         }
-#endif
         const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
         const bool grow = m_new > m_ref + kRescaleThreshold;  // also true for the first finite max
         if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -861,8 +680,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           }
           tmem_st_32x32b_x16(t_s + c * 16, pk);
         }
-#endif
-#endif
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -931,6 +748,23 @@ int fill_units(AttnParams& p, const char* who) {
   return B200K_OK;
 }
 
+// Which kernel runs a problem (B200K_ATTN_AUTO).  Measured on B200, head dim 128, same box and
+// timing loop, one-tile / tile-pair in microseconds: non-causal 8x32x1024 130 / 140, 8x32x2048
+// 514 / 537, 1x16x16384 1809 / 1932; causal 4x32x4096 521 / 505, 2x32(8)x8192 960 / 924,
+// 1x32(8)x16384 2214 / 2052, 64x16x256 80 / 66, but 4x32(8)x2048 155 / 173, where the pair
+// kernel's 512 units leave the last of four rounds over 148 SMs half empty.  So: head dim 64 only
+// exists in the pair kernel; causal problems take it when its units fill the SMs to 90 % or more;
+// everything else takes the one-tile kernel.
+bool choose_pair_kernel(int kernel, int head_dim, bool causal, int64_t pair_units) {
+  if (head_dim != 128) return true;
+  if (kernel == B200K_ATTN_TILE_PAIR) return true;
+  if (kernel == B200K_ATTN_ONE_TILE) return false;
+  if (!causal) return false;
+  const int64_t sms = num_sms();
+  const int64_t rounds = (pair_units + sms - 1) / sms;
+  return pair_units * 10 >= rounds * sms * 9;
+}
+
 }  // namespace
 
 int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
@@ -953,8 +787,17 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
     return set_error(B200K_ERR_BAD_ALIGN, "attention_fwd: q, k, v, o must be 16-byte aligned");
   if (!(a.scale > 0.f)) return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: scale must be positive");
   if (reinterpret_cast<uintptr_t>(a.lse) & 3) return set_error(B200K_ERR_BAD_ALIGN, "attention_fwd: lse must be 4-byte aligned");
+  if (a.kernel < B200K_ATTN_AUTO || a.kernel > B200K_ATTN_TILE_PAIR)
+    return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: unknown kernel choice %d", a.kernel);
+  if (a.kernel == B200K_ATTN_ONE_TILE && a.head_dim != 128)
+    return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: the one-tile kernel covers head_dim 128 only");
   int rc = ensure_sm100();
   if (rc) return rc;
+  {
+    const int64_t pairs = (a.seq_q + kPairRows - 1) / kPairRows;
+    const int64_t units = static_cast<int64_t>(a.batch) * a.q_heads * (a.causal ? (pairs + 1) / 2 : pairs);
+    if (!choose_pair_kernel(a.kernel, a.head_dim, a.causal != 0, units)) return launch_attention_fwd_tile(a, stream);
+  }
 
   CUtensorMap tq, tk, tv, to;
   const uint32_t box[4] = {64, kTileRows, 1, 1};
@@ -1037,8 +880,17 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
       (reinterpret_cast<uintptr_t>(a.v_cache) & 15) || (reinterpret_cast<uintptr_t>(a.o) & 15))
     return set_error(B200K_ERR_BAD_ALIGN, "paged_attention_fwd: q, caches and o must be 16-byte aligned");
   if (!(a.scale > 0.f)) return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: scale must be positive");
+  if (a.kernel < B200K_ATTN_AUTO || a.kernel > B200K_ATTN_TILE_PAIR)
+    return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: unknown kernel choice %d", a.kernel);
+  if (a.kernel == B200K_ATTN_ONE_TILE && a.head_dim != 128)
+    return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: the one-tile kernel covers head_dim 128 only");
   int rc = ensure_sm100();
   if (rc) return rc;
+  {
+    const int64_t pairs = (a.seq_q + kPairRows - 1) / kPairRows;
+    const int64_t units = static_cast<int64_t>(a.batch) * a.q_heads * (a.causal ? (pairs + 1) / 2 : pairs);
+    if (!choose_pair_kernel(a.kernel, a.head_dim, a.causal != 0, units)) return launch_paged_attention_fwd_tile(a, stream);
+  }
 
   CUtensorMap tq, tk, tv, to;
   const uint32_t box[4] = {64, kTileRows, 1, 1};

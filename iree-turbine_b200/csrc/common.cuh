@@ -32,6 +32,8 @@ int encode_tmap(CUtensorMap* out, int dtype, int rank, void* base, const uint64_
 int launch_gemm_nt(const b200k_gemm_args& a, cudaStream_t stream);
 int launch_gemm_nt_allgather(const b200k_gemm_allgather_args& g, cudaStream_t stream);
 int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream);
+int launch_attention_fwd_tile(const b200k_attention_args& a, cudaStream_t stream);  // attention_tile_sm100.cu
+int launch_paged_attention_fwd_tile(const b200k_paged_attention_args& a, cudaStream_t stream);
 int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t stream);
 int launch_decode(const b200k_decode_args& a, cudaStream_t stream);
 int launch_decode_static(const b200k_decode_args& a, cudaStream_t stream);

@@ -22,7 +22,7 @@ Backends: ``b200k`` (default; this library's kernels) and ``torch`` (the ATen op
 device).  The GEMM kernel reads either storage order of each operand ([M, K] or [K, M]; [K, N] or
 [N, K]), so the four transA / transB forms run as given; an operand with no contiguous dimension is
 repacked once before timing, and the line printed for the command says so.
-A command or backend that cannot run (float32 GEMM, head dim other than 128, a mask, ...) gets
+A command or backend that cannot run (float32 GEMM, head dim other than 128 / 64, a mask, ...) gets
 ``N.A.`` in its columns, as in the reference.  Times are microseconds per call, measured with CUDA
 events on the current stream after 3 untimed calls.  There is no CPU path.
 """
@@ -219,8 +219,8 @@ def build_callable(cmd, backend: str, device, notes: List[str]) -> Callable[[], 
             return lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, mask, dropout_p, is_causal, **kwargs)
         if mask is not None or dropout_p != 0.0:
             raise Unsupported("b200k attention takes no mask and no dropout")
-        if q.size(-1) != 128 or q.dtype not in (torch.float16, torch.bfloat16):
-            raise Unsupported("b200k attention covers head dim 128 in float16 / bfloat16")
+        if q.size(-1) not in (64, 128) or q.dtype not in (torch.float16, torch.bfloat16):
+            raise Unsupported("b200k attention covers head dims 128 and 64 in float16 / bfloat16")
         if is_causal and q.size(2) != k.size(2):
             raise Unsupported("causal with different query / key lengths is aligned differently by the two ops")
         s = float(scale) if scale is not None else 1.0 / math.sqrt(q.size(-1))

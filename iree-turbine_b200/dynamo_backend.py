@@ -19,7 +19,7 @@ What is rewritten (forward graph only; the backward graph, if any, goes to the n
   lowers to.
 * ``aten._scaled_dot_product_{flash,efficient,cudnn}_attention`` and
   ``aten.scaled_dot_product_attention`` -> ``b200k.attention(q, k, v, scale, is_causal)``
-  for [B, H, S, 128] f16 / bf16 CUDA tensors, no mask / bias, dropout 0, q_heads a multiple of
+  for [B, H, S, 128 or 64] f16 / bf16 CUDA tensors, no mask / bias, dropout 0, q_heads a multiple of
   kv_heads, and -- when causal -- equal query and key lengths (torch aligns the causal mask to the
   top-left corner, the kernel to the bottom-right; they coincide only then).
 
@@ -151,7 +151,7 @@ def _sdpa_supported(q, k, v, mask, dropout_p, is_causal) -> bool:
         return False
     if not (vq.dtype == vk.dtype == vv.dtype) or vk.shape != vv.shape:
         return False
-    if vq.size(-1) != 128 or vk.size(-1) != 128 or vq.size(0) != vk.size(0):
+    if vq.size(-1) not in (64, 128) or vk.size(-1) != vq.size(-1) or vq.size(0) != vk.size(0):
         return False
     if vk.size(1) == 0 or vq.size(1) % vk.size(1) != 0:
         return False

@@ -28,11 +28,11 @@ def _check_host(t: torch.Tensor, shape, dtype, what: str):
 
 
 class AttentionHost:
-    def __init__(self, batch, q_heads, kv_heads, seq_q, seq_kv, dtype, device):
+    def __init__(self, batch, q_heads, kv_heads, seq_q, seq_kv, dtype, device, head_dim: int = 128):
         self.device = torch.device(device)
         self.dtype = dtype
-        self.qs = (batch, q_heads, seq_q, 128)
-        self.ks = (batch, kv_heads, seq_kv, 128)
+        self.qs = (batch, q_heads, seq_q, head_dim)
+        self.ks = (batch, kv_heads, seq_kv, head_dim)
         self.dq = torch.empty(self.qs, dtype=dtype, device=self.device)
         self.dk = torch.empty(self.ks, dtype=dtype, device=self.device)
         self.dv = torch.empty(self.ks, dtype=dtype, device=self.device)

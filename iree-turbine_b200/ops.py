@@ -332,8 +332,15 @@ def _bhsd(t: Tensor) -> Tensor:
     return t if ok else t.contiguous()
 
 
+# Which forward kernel ``attention`` / ``attention_lse`` / ``paged_attention`` ask for: 0 lets the
+# library choose (one-tile or tile-pair kernel, see include/b200k.h), 1 / 2 force one of them
+# (head dim 64 only exists in the pair kernel).  A tuning and testing knob, like the GEMM tile shape.
+ATTENTION_KERNEL = L.ATTN_AUTO
+
+
 def _fill_attention_args(q: Tensor, k: Tensor, v: Tensor, o: Tensor, scale: float, causal: bool) -> L.AttentionArgs:
     args = L.AttentionArgs()
+    args.kernel = ATTENTION_KERNEL if q.size(3) == 128 else L.ATTN_AUTO
     args.q, args.k, args.v, args.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
     args.batch, args.q_heads, args.seq_q, args.head_dim = q.size(0), q.size(1), q.size(2), q.size(3)
     args.kv_heads, args.seq_kv = k.size(1), k.size(2)
@@ -366,7 +373,8 @@ def _attention_select(sel: KernelSelection):
     torch._check(q.t.dim() == 4 and k.t.dim() == 4 and v.t.dim() == 4, lambda: "attention: q, k, v must be 4-D [B,H,S,D]")
     torch._check(q.t.dtype in _HALF_TYPES, lambda: f"attention: dtype must be float16 or bfloat16, got {q.t.dtype}")
     torch._check(q.t.dtype == k.t.dtype == v.t.dtype, lambda: "attention: q, k, v must share a dtype")
-    torch._check(q.t.size(3) == 128 and k.t.size(3) == 128 and v.t.size(3) == 128, lambda: "attention: head dim must be 128")
+    torch._check(q.t.size(3) in (64, 128) and k.t.size(3) == q.t.size(3) and v.t.size(3) == q.t.size(3),
+                 lambda: "attention: head dim must be 128 or 64, the same for q, k and v")
     torch._check(k.t.shape == v.t.shape, lambda: "attention: k and v must have the same shape")
     torch._check(q.t.size(0) == k.t.size(0), lambda: "attention: batch mismatch")
     torch._check(q.t.size(1) % k.t.size(1) == 0, lambda: "attention: query heads must be a multiple of kv heads")
@@ -377,7 +385,7 @@ def _attention_select(sel: KernelSelection):
 
 @CustomOp.register(library=LIBRARY)
 class attention(CustomOp):
-    """O = softmax(scale * Q K^T [causal]) V.  q [B,Hq,Sq,128], k/v [B,Hkv,Skv,128] -> [B,Hq,Sq,128]."""
+    """O = softmax(scale * Q K^T [causal]) V.  q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] -> [B,Hq,Sq,D], D = 128 or 64."""
 
     signature = "attention(Tensor q, Tensor k, Tensor v, float scale, bool is_causal) -> Tensor"
 
@@ -497,7 +505,10 @@ class _AttentionFunction(torch.autograd.Function):
 
 def sdpa(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, is_causal: bool = False) -> Tensor:
     """Differentiable scaled-dot-product attention on the b200k kernels ([B, H, S, 128] f16 / bf16
-    CUDA tensors; grouped-query heads; causal mask aligned to the bottom-right corner)."""
+    CUDA tensors; grouped-query heads; causal mask aligned to the bottom-right corner).  The backward
+    kernels cover head dim 128 only; for head dim 64 use ``torch.ops.b200k.attention`` (forward)."""
+    if q.size(-1) != 128:
+        raise ValueError("sdpa: the backward kernels cover head dim 128 only")
     if scale is None:
         scale = 1.0 / (q.size(-1) ** 0.5)
     return _AttentionFunction.apply(q, k, v, float(scale), bool(is_causal))
@@ -724,10 +735,10 @@ class paged_attention(CustomOp):
         lens = sel.arg_tensor(4)
         sel.attr_float(5)
         sel.attr_bool(6)
-        torch._check(q.t.dim() == 4 and q.t.size(3) == 128, lambda: "paged_attention: q must be [B, Hq, Sq, 128]")
+        torch._check(q.t.dim() == 4 and q.t.size(3) in (64, 128), lambda: "paged_attention: q must be [B, Hq, Sq, 128 or 64]")
         torch._check(q.t.dtype in _HALF_TYPES, lambda: f"paged_attention: dtype must be float16 or bfloat16, got {q.t.dtype}")
-        torch._check(kc.t.dim() == 4 and kc.t.shape == vc.t.shape and kc.t.size(3) == 128,
-                     lambda: "paged_attention: caches must be [num_pages, Hkv, page_size, 128] and equal in shape")
+        torch._check(kc.t.dim() == 4 and kc.t.shape == vc.t.shape and kc.t.size(3) == q.t.size(3),
+                     lambda: "paged_attention: caches must be [num_pages, Hkv, page_size, head dim of q] and equal in shape")
         torch._check(kc.t.dtype == q.t.dtype and vc.t.dtype == q.t.dtype, lambda: "paged_attention: dtypes must match")
         torch._check(kc.t.size(2) in (16, 32, 64, 128), lambda: "paged_attention: page_size must be 16, 32, 64 or 128")
         torch._check(q.t.size(1) % kc.t.size(1) == 0, lambda: "paged_attention: query heads must be a multiple of kv heads")
@@ -748,7 +759,7 @@ class paged_attention(CustomOp):
         a.batch, a.q_heads, a.kv_heads, a.seq_q = q.size(0), q.size(1), k_cache.size(1), q.size(2)
         a.page_size, a.num_pages, a.block_table_stride = k_cache.size(2), k_cache.size(0), block_table.stride(0)
         a.max_seq_kv = block_table.size(1) * k_cache.size(2)
-        a.head_dim = 128
+        a.head_dim = q.size(3)
         a.q_stride_b, a.q_stride_h, a.q_stride_s = q.stride(0), q.stride(1), q.stride(2)
         a.o_stride_b, a.o_stride_h, a.o_stride_s = o.stride(0), o.stride(1), o.stride(2)
         a.kv_page_stride, a.kv_head_stride = k_cache.stride(0), k_cache.stride(1)
@@ -756,5 +767,6 @@ class paged_attention(CustomOp):
         a.causal = 1 if is_causal else 0
         a.scale = float(scale)
         a.status = _status_ptr(q.device)
+        a.kernel = ATTENTION_KERNEL if q.size(3) == 128 else L.ATTN_AUTO
         L.check(L.lib().b200k_paged_attention_fwd(C.byref(a), _stream(q)))
         return o

@@ -86,8 +86,8 @@ def get_fp8_gemm_kernel(shape: GemmShape, out_dtype: torch.dtype = torch.bfloat1
 def _attention_kernel(shape: AttentionShape, dtype: torch.dtype, causal: bool, scale: Optional[float]):
     if dtype not in _HALF:
         raise ValueError(f"attention: dtype must be float16 or bfloat16, got {dtype}")
-    if shape.head_size != 128 or shape.head_size_kv != 128:
-        raise ValueError("attention: head_size and head_size_kv must be 128")
+    if shape.head_size not in (64, 128) or shape.head_size_kv != shape.head_size:
+        raise ValueError("attention: head_size must be 128 or 64, and head_size_kv equal to it")
     sc = shape.head_size ** -0.5 if scale is None else float(scale)
     qs = (shape.num_seqs, shape.num_query_heads, shape.query_seq_len, shape.head_size)
     ks = (shape.num_seqs, shape.num_kv_heads, shape.kv_seq_len, shape.head_size)
@@ -103,7 +103,8 @@ def _attention_kernel(shape: AttentionShape, dtype: torch.dtype, causal: bool, s
 
 def get_vanilla_attention_kernel(shape: AttentionShape, dtype: torch.dtype = torch.float16,
                                  scale: Optional[float] = None) -> LaunchableKernel:
-    """softmax(scale * Q K^T) V over [num_seqs, heads, seq, 128] tensors (scale defaults to 128^-0.5)."""
+    """softmax(scale * Q K^T) V over [num_seqs, heads, seq, head_size] tensors, head_size 128 or 64
+    (scale defaults to head_size^-0.5)."""
     return _attention_kernel(shape, dtype, False, scale)
 
 
@@ -153,9 +154,9 @@ def get_paged_decode_attention_kernel(shape: AttentionShape, dtype: torch.dtype 
 def get_paged_prefill_attention_kernel(shape: AttentionShape, dtype: torch.dtype = torch.bfloat16,
                                        causal: bool = True, scale: Optional[float] = None) -> LaunchableKernel:
     """Prefill (or one chunk of it) over the paged cache: kernel(q, k_cache, v_cache, block_table, seq_lens)
-    with q [num_seqs, heads, query_seq_len, 128]; the queries of a sequence are its last query_seq_len tokens."""
-    if shape.head_size != 128:
-        raise ValueError("paged prefill attention: head_size must be 128")
+    with q [num_seqs, heads, query_seq_len, head_size]; the queries of a sequence are its last query_seq_len tokens."""
+    if shape.head_size not in (64, 128):
+        raise ValueError("paged prefill attention: head_size must be 128 or 64")
     if shape.block_size not in (16, 32, 64, 128):
         raise ValueError("paged prefill attention: block_size must be 16, 32, 64 or 128")
     sc = shape.head_size ** -0.5 if scale is None else float(scale)

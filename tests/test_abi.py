@@ -37,13 +37,13 @@ def test_struct_layouts_match_the_header():
     fields = {
         "b200k_gemm_args": (L.GemmArgs, ["a", "ldc", "in_dtype", "scale_a", "status", "tile_n"]),
         "b200k_attention_args": (L.AttentionArgs, ["q", "batch", "head_dim", "q_stride_b", "o_stride_s", "dtype",
-                                                   "scale", "status", "lse"]),
+                                                   "scale", "status", "lse", "kernel"]),
         "b200k_decode_args": (L.DecodeArgs, ["q", "workspace_bytes", "num_seqs", "max_seq_len", "kv_batch_stride",
                                              "kv_page_stride", "dtype", "scale", "status"]),
         "b200k_paged_attention_args": (L.PagedAttentionArgs, ["q", "seq_lens", "batch", "head_dim", "page_size",
                                                               "block_table_stride", "q_stride_b", "o_stride_s",
                                                               "kv_page_stride", "kv_head_stride", "dtype", "scale",
-                                                              "status"]),
+                                                              "kernel", "status"]),
         "b200k_attention_bwd_args": (L.AttentionBwdArgs, ["q", "d_o", "d_v", "workspace", "workspace_bytes", "batch",
                                                           "head_dim", "q_stride_b", "do_stride_h", "dv_stride_s",
                                                           "dtype", "scale", "status", "lse"]),
@@ -94,7 +94,7 @@ def test_argument_errors_are_status_codes(kernel_lib):
     a.q = a.k = a.v = a.o = 0x1000
     a.batch = a.q_heads = a.kv_heads = 1
     a.seq_q = a.seq_kv = 128
-    a.head_dim = 64
+    a.head_dim = 96
     assert lib.b200k_attention_fwd(C.byref(a), None) == L.ERR_BAD_SHAPE
     assert b"head_dim" in lib.b200k_last_error()
 

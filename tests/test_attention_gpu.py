@@ -1,4 +1,8 @@
-"""Attention forward parity on the GPU vs. the CPU oracle (rtol = atol = 1e-2, f16 / bf16)."""
+"""Attention forward parity on the GPU vs. the CPU oracle (rtol = atol = 1e-2, f16 / bf16).
+
+Two kernels implement the forward (one 128-row query tile per work item, or a pair of tiles; see
+include/b200k.h): every test in this file runs once with each of them forced, so both are checked
+on every shape whatever the library would pick by itself; head dim 64 exists in the pair kernel only."""
 
 import os
 
@@ -13,6 +17,16 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 SCALE = 128 ** -0.5
+
+
+@pytest.fixture(autouse=True, params=["one_tile", "tile_pair"])
+def forced_kernel(request):
+    from iree_turbine_b200 import _launcher as L
+
+    old = tb.ops.ATTENTION_KERNEL
+    tb.ops.ATTENTION_KERNEL = L.ATTN_ONE_TILE if request.param == "one_tile" else L.ATTN_TILE_PAIR
+    yield request.param
+    tb.ops.ATTENTION_KERNEL = old
 
 
 def _run(q, k, v, scale, causal):
@@ -75,6 +89,58 @@ def test_strided_views_and_determinism():
     oracle.assert_close_half(o1, oracle.attention(q, k, v, SCALE, True))
     for _ in range(5):
         assert torch.equal(torch.ops.b200k.attention(qd, kd, vd, SCALE, True), o1)
+
+
+@pytest.mark.parametrize("sq,skv,causal", [(128, 128, False), (256, 256, True), (300, 333, True), (1, 17, False),
+                                           (640, 1024, True), (1024, 1024, False), (700, 200, False)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_64(sq, skv, causal, dtype, forced_kernel):
+    """Head dim 64 (the reference's own SDPA sample, kernel/boo/driver/sample_commands.txt:26, and its
+    in-tree attention statement, tests/kernel/fused_attention_test.py:79-90, use it)."""
+    if forced_kernel == "one_tile":
+        pytest.skip("head dim 64 always takes the pair kernel")
+    q, k, v = oracle.make_attention_inputs(2, 4, 2, sq, skv, 64, dtype, seed=6, std=0.7)
+    oracle.assert_close_half(_run(q, k, v, 0.125, causal), oracle.attention(q, k, v, 0.125, causal))
+
+
+def test_head_dim_64_reference_sample_shape_and_lse():
+    """[32, 8, 128, 64] bf16 causal: the shape of the reference driver's SDPA sample command."""
+    q, k, v = oracle.make_attention_inputs(32, 8, 8, 128, 128, 64, torch.bfloat16, seed=7)
+    o, lse = torch.ops.b200k.attention_lse(q.to(DEV), k.to(DEV), v.to(DEV), 0.125, True)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(o, oracle.attention(q, k, v, 0.125, True))
+    s = (q.float() @ k.float().transpose(-1, -2)) * 0.125
+    s = s.masked_fill(torch.ones(128, 128, dtype=torch.bool).triu(1), float("-inf"))
+    assert torch.allclose(lse.cpu(), torch.logsumexp(s, -1), rtol=1e-3, atol=1e-3)
+
+
+def test_library_choice_and_forced_kernels_agree(forced_kernel):
+    """What the library picks by itself (pair kernel for a causal problem that fills the SMs, the one-tile
+    kernel for a non-causal one) agrees with the forced kernels within rounding."""
+    from iree_turbine_b200 import _launcher as L
+
+    for causal, b, h, s in [(True, 4, 37, 512), (False, 2, 8, 512)]:
+        q, k, v = oracle.make_attention_inputs(b, h, h, s, s, 128, torch.bfloat16, seed=8, std=0.5)
+        forced = _run(q, k, v, SCALE, causal)
+        tb.ops.ATTENTION_KERNEL = L.ATTN_AUTO
+        auto = _run(q, k, v, SCALE, causal)
+        assert torch.allclose(auto.float(), forced.float(), rtol=1e-2, atol=1e-2)
+        oracle.assert_close_half(auto[:1, :2], oracle.attention(q[:1, :2], k[:1, :2], v[:1, :2], SCALE, causal))
+
+
+def test_one_tile_kernel_rejects_head_dim_64():
+    import ctypes as C
+
+    from iree_turbine_b200 import _launcher as L
+    from iree_turbine_b200.ops import _fill_attention_args
+
+    q = torch.zeros(1, 1, 128, 64, dtype=torch.float16, device=DEV)
+    a = _fill_attention_args(q, q, q, torch.empty_like(q), 0.125, False)
+    a.kernel = L.ATTN_ONE_TILE
+    assert L.lib().b200k_attention_fwd(C.byref(a), None) == L.ERR_BAD_SHAPE
+    a.kernel = 7
+    assert L.lib().b200k_attention_fwd(C.byref(a), None) == L.ERR_BAD_SHAPE
 
 
 def _check_heads(o, q, k, v, causal, picks, group=1):

@@ -140,12 +140,18 @@ def test_flash_sdpa_is_routed_with_scale_and_causal_flag():
     assert operator.getitem not in _targets(gm)
 
 
-@pytest.mark.parametrize("kw", [dict(aux_used=True), dict(causal=True, sq=128, skv=256), dict(d=64),
+@pytest.mark.parametrize("kw", [dict(aux_used=True), dict(causal=True, sq=128, skv=256), dict(d=96),
                                 dict(dropout=0.1), dict(hq=8, hkv=3)])
 def test_flash_sdpa_left_alone(kw):
     gm = _flash_graph(**kw)
     assert db.apply_replacements(gm) == 0
     assert aten._scaled_dot_product_flash_attention.default in _targets(gm)
+
+
+def test_flash_sdpa_head_dim_64_is_routed():
+    gm = _flash_graph(d=64)
+    assert db.apply_replacements(gm) == 1
+    assert torch.ops.b200k.attention.default in _targets(gm)
 
 
 def test_efficient_sdpa_with_bias_left_alone_and_without_routed():

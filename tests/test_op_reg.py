@@ -99,8 +99,11 @@ def test_shipped_ops_reject_bad_arguments():
         torch.ops.b200k.gemm_nt(m(8, 64), m(8, 32))
     with pytest.raises(RuntimeError, match="float16 or bfloat16"):
         torch.ops.b200k.gemm_nt(m(8, 64, dtype=torch.float32), m(8, 64, dtype=torch.float32))
-    with pytest.raises(RuntimeError, match="head dim must be 128"):
-        torch.ops.b200k.attention(m(1, 1, 8, 64), m(1, 1, 8, 64), m(1, 1, 8, 64), 1.0, False)
+    with pytest.raises(RuntimeError, match="head dim must be 128 or 64"):
+        torch.ops.b200k.attention(m(1, 1, 8, 96), m(1, 1, 8, 96), m(1, 1, 8, 96), 1.0, False)
+    with pytest.raises(RuntimeError, match="head dim must be 128 or 64"):
+        torch.ops.b200k.attention(m(1, 1, 8, 64), m(1, 1, 8, 128), m(1, 1, 8, 128), 1.0, False)
+    assert torch.ops.b200k.attention(m(1, 2, 8, 64), m(1, 1, 9, 64), m(1, 1, 9, 64), 1.0, True).shape == (1, 2, 8, 64)
     with pytest.raises(RuntimeError, match="multiple of kv heads"):
         torch.ops.b200k.attention(m(1, 3, 8, 128), m(1, 2, 8, 128), m(1, 2, 8, 128), 1.0, False)
 
@@ -144,6 +147,7 @@ def test_template_constructors_validate_shapes():
     with pytest.raises(ValueError):
         tb.AttentionShape(num_query_heads=6, num_kv_heads=4, head_size=128)
     with pytest.raises(ValueError, match="head_size"):
-        tb.get_vanilla_attention_kernel(tb.AttentionShape(4, 4, 64, 16, 16))
+        tb.get_vanilla_attention_kernel(tb.AttentionShape(4, 4, 96, 16, 16))
+    assert tb.get_vanilla_attention_kernel(tb.AttentionShape(4, 4, 64, 16, 16)).name == "vanilla_attention"
     with pytest.raises(ValueError, match="block_size"):
         tb.get_paged_decode_attention_kernel(tb.AttentionShape(32, 8, 128, num_seqs=4))
