@@ -289,7 +289,7 @@ class AttentionBwdWL(AttentionWL):
 class GemmWL(Workload):
     def __init__(self, name, n, fp8, mode="fused_gather"):
         self.name, self.n, self.fp8 = name, n, fp8
-        self.mode = mode  # N > 1, fp8 only: "shard_only" | "fused_gather" | "nccl_gather"
+        self.mode = mode  # N > 1, fp8 only: "shard_only" | "fused_gather" | "fused_gather_multimem" | "nccl_gather"
         self.traffic_bytes = 417.1e6 if (fp8 and n == 8192) else (16.9e6 if (not fp8 and n == 2048) else None)
         # the measured peak is a bf16 GEMM; e4m3 runs the tensor pipe at twice that rate
         self.peak_scale = 2.0 if fp8 else 1.0
@@ -316,6 +316,9 @@ class GemmWL(Workload):
             how = {"shard_only": "column shards of C left in place (no exchange)",
                    "fused_gather": "all-gather of C fused into the GEMM epilogue (peer stores) + cross-rank barrier "
                                    "inside the timed step",
+                   "fused_gather_multimem": "all-gather of C fused into the GEMM epilogue (one multimem.st per piece "
+                                            "through the NVSwitch multicast address) + cross-rank barrier inside "
+                                            "the timed step",
                    "nccl_gather": "local GEMM, then NCCL all-gather of C + de-interleaving copy inside the timed step"}
             cfg["parallelism"] = f"column-parallel over N on {self.world} GPUs, {how[self.mode]}"
         elif self.world > 1:
@@ -339,11 +342,12 @@ class GemmWL(Workload):
             lo, hi = tdist.shard_range(self.n, self.world, self.rank)
             self.col0 = lo
             self.b = self.b[lo:hi].contiguous()
-            if self.mode == "fused_gather":
-                self.fused = tdist.FusedColumnParallelGemm(self.n, self.n, torch.bfloat16)
+            if self.mode.startswith("fused_gather"):
+                self.fused = tdist.FusedColumnParallelGemm(self.n, self.n, torch.bfloat16,
+                                                           multicast=self.mode.endswith("multimem"))
 
     def step(self):
-        if self.sharded and self.mode == "fused_gather":
+        if self.sharded and self.mode.startswith("fused_gather"):
             self.fused(self.a, self.b, self.sa, self.sb)
             self.c = self.fused.finish()
         elif self.sharded and self.mode == "nccl_gather":
@@ -455,8 +459,9 @@ class PagedDecodeWL(Workload):
                "len_range": [512, 8192], "sum_len": int(self.sum_len) if hasattr(self, "sum_len") else None,
                "l2": "KV pool larger than L2 (about 1.1 GB read per step)"}
         if self.world > 1:
-            cfg["parallelism"] = (f"one problem, sequences sharded over {self.world} GPUs ({64 // self.world} per GPU, "
-                                  "each with the whole page pool resident), no collective")
+            cfg["parallelism"] = (f"one problem, KV heads sharded over {self.world} GPUs ({8 // self.world} KV heads and "
+                                  "their query heads per GPU, the rank's slice of the page pool resident), "
+                                  "no collective")
             cfg["l2"] = "L2 flushed between steps (256 MB write)"
         return cfg
 
@@ -470,11 +475,16 @@ class PagedDecodeWL(Workload):
         return oracle.make_paged_decode_inputs(seed=10)
 
     def setup(self, dev):
+        """N > 1: one problem sharded by KV head (8 KV heads, so N <= 8): a rank holds its heads' slice
+        of the page pool and the matching query heads of every sequence -- equal bytes on every rank
+        whatever the sequence lengths are."""
         from iree_turbine_b200 import dist as tdist
 
         q, kc, vc, bt, sl = self._host_inputs()
-        lo, hi = tdist.shard_range(64, self.world, self.rank)
-        q, bt, sl = q[lo:hi].contiguous(), bt[lo:hi].contiguous(), sl[lo:hi].contiguous()
+        lo, hi = tdist.shard_range(8, self.world, self.rank)
+        q = q[:, lo * 4:hi * 4].contiguous()
+        kc, vc = kc[:, lo:hi].contiguous(), vc[:, lo:hi].contiguous()
+        self.kv_heads = hi - lo
         self.sum_len = int(sl.sum())
         self.pages = int(((sl + 15) // 16).sum())
         self.host = (q, kc, vc, bt, sl)
@@ -485,7 +495,7 @@ class PagedDecodeWL(Workload):
 
     def units_per_step(self):
         # K and V rows actually read + Q and O + block-table entries + seq_lens
-        return self.sum_len * 8 * 128 * 2 * 2 + 2 * self.q.numel() * 2 + 4 * self.pages + 4 * self.sl.numel()
+        return self.sum_len * self.kv_heads * 128 * 2 * 2 + 2 * self.q.numel() * 2 + 4 * self.pages + 4 * self.sl.numel()
 
     def setup_e2e(self, dev):
         # The KV pool is state that lives on the device across decode steps; per step the host
@@ -536,6 +546,7 @@ WORKLOADS = {
     "gemm_fp8": lambda: GemmWL("gemm_fp8", 8192, True),
     "gemm_fp8_shard_only": lambda: GemmWL("gemm_fp8_shard_only", 8192, True, "shard_only"),
     "gemm_fp8_nccl_gather": lambda: GemmWL("gemm_fp8_nccl_gather", 8192, True, "nccl_gather"),
+    "gemm_fp8_multimem": lambda: GemmWL("gemm_fp8_multimem", 8192, True, "fused_gather_multimem"),
     "paged_decode": lambda: PagedDecodeWL("paged_decode"),
 }
 DEFAULT = "attn_causal"
@@ -827,8 +838,11 @@ def run_ours(args) -> dict:
             if name == "gemm_fp8" and ctx.world > 1:
                 # the one workload with an exchange step: three legs
                 legs = {}
-                for leg in ("gemm_fp8_shard_only", "gemm_fp8", "gemm_fp8_nccl_gather"):
-                    legs[WORKLOADS[leg]().mode] = measure(WORKLOADS[leg](), ctx, steps, warmup, with_cpu=False)
+                for leg in ("gemm_fp8_shard_only", "gemm_fp8", "gemm_fp8_multimem", "gemm_fp8_nccl_gather"):
+                    try:
+                        legs[WORKLOADS[leg]().mode] = measure(WORKLOADS[leg](), ctx, steps, warmup, with_cpu=False)
+                    except RuntimeError as e:  # no multicast address on this box: every rank raises alike
+                        legs[WORKLOADS[leg]().mode] = {"unavailable": str(e)}
                 extras[name] = {"legs": legs}
             else:
                 extras[name] = measure(WORKLOADS[name](), ctx, steps, warmup, with_cpu=True)

@@ -139,9 +139,14 @@ typedef struct b200k_gemm_allgather_args {
   b200k_gemm_args gemm;
   void* peer_c[8];
   int32_t num_peers;
-  int32_t reserved;
+  int32_t self_index;  /* this rank's position in peer_c: peers are written in the order self + 1,
+                          self + 2, ..., self, so that at any moment the ranks aim at different
+                          destinations */
   int64_t peer_ldc;
   int64_t col_offset;
+  void* multicast_c;   /* optional: the NVSwitch multicast address of the same matrix (one
+                          multimem.st then reaches every rank, the switch replicates it); NULL =
+                          one plain store per peer */
 } b200k_gemm_allgather_args;
 
 int b200k_gemm_nt_allgather(const b200k_gemm_allgather_args* args, void* stream);

@@ -97,9 +97,10 @@ class GemmAllGatherArgs(C.Structure):
         ("gemm", GemmArgs),
         ("peer_c", C.c_void_p * 8),
         ("num_peers", C.c_int32),
-        ("reserved", C.c_int32),
+        ("self_index", C.c_int32),
         ("peer_ldc", C.c_int64),
         ("col_offset", C.c_int64),
+        ("multicast_c", C.c_void_p),
     ]
 
 

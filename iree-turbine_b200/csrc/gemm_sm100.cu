@@ -49,9 +49,11 @@ struct GemmParams {
   // Fused all-gather of a column shard: when num_peers > 0 every output tile is written with plain
   // 16-byte stores into each peer's full matrix (peer-mapped memory) at column peer_col0.
   int32_t num_peers;
+  int32_t peer_first;  // index of the first peer written (the rank after this one); own copy last
   int64_t peer_ldc;
   int64_t peer_col0;
   void* peers[8];
+  void* peer_mc;  // NVSwitch multicast address of the matrix, or nullptr
 };
 
 template <int BN, int MT>
@@ -414,8 +416,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               if (grow < p.m && ecol < p.n) {
                 const int64_t off = (static_cast<int64_t>(grow) * p.peer_ldc + p.peer_col0 + ecol) *
                                     static_cast<int64_t>(sizeof(OutT));
-                for (int pe = 0; pe < p.num_peers; ++pe)
-                  *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peers[pe]) + off) = val;
+                if (p.peer_mc) {
+                  // one store to the multicast address: the switch writes every rank's copy
+                  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                                   reinterpret_cast<uint8_t*>(p.peer_mc) + off),
+                               "f"(__uint_as_float(val.x)), "f"(__uint_as_float(val.y)), "f"(__uint_as_float(val.z)),
+                               "f"(__uint_as_float(val.w))
+                               : "memory");
+                } else {
+                  int pe = p.peer_first;
+                  for (int i = 0; i < p.num_peers; ++i) {
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peers[pe]) + off) = val;
+                    pe = pe + 1 == p.num_peers ? 0 : pe + 1;
+                  }
+                }
               }
             }
           }
@@ -568,7 +582,9 @@ int dispatch_dtype(int in_dtype, int out_dtype, const CUtensorMap& ta, const CUt
 namespace {
 struct PeerTargets {
   int num = 0;
+  int first = 0;
   void* c[8] = {};
+  void* mc = nullptr;
   int64_t ldc = 0;
   int64_t col0 = 0;
 };
@@ -589,8 +605,14 @@ int launch_gemm_nt_allgather(const b200k_gemm_allgather_args& g, cudaStream_t st
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_allgather: column shard does not fit in the row pitch of the full matrix");
   if ((g.peer_ldc * out_es) % 16 != 0 || (g.col_offset * out_es) % 16 != 0 || (g.gemm.n * out_es) % 16 != 0)
     return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt_allgather: row pitch, column offset and shard width must be multiples of 16 bytes");
+  if (g.self_index < 0 || g.self_index >= g.num_peers)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_allgather: self_index must be in [0, num_peers)");
+  if (reinterpret_cast<uintptr_t>(g.multicast_c) & 15)
+    return set_error(B200K_ERR_BAD_ALIGN, "gemm_nt_allgather: multicast_c must be 16-byte aligned");
   PeerTargets t;
   t.num = g.num_peers;
+  t.first = (g.self_index + 1) % g.num_peers;
+  t.mc = g.multicast_c;
   t.ldc = g.peer_ldc;
   t.col0 = g.col_offset;
   for (int i = 0; i < g.num_peers; ++i) {
@@ -703,6 +725,8 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   p.num_kb = static_cast<int32_t>((a.k + k_per_stage - 1) / k_per_stage);
   p.vec_store_ok = ((reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && (a.ldc * out_es) % 16 == 0) ? 1 : 0;
   p.num_peers = peers.num;
+  p.peer_first = peers.first;
+  p.peer_mc = peers.mc;
   p.peer_ldc = peers.ldc;
   p.peer_col0 = peers.col0;
   for (int i = 0; i < 8; ++i) p.peers[i] = peers.c[i];

@@ -118,7 +118,11 @@ class FusedColumnParallelGemm:
     a caller that reads it from another stream must order that stream before its next ``finish()``.
     """
 
-    def __init__(self, m: int, n: int, out_dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, m: int, n: int, out_dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None,
+                 multicast: bool = False):
+        """``multicast``: store each piece once to the NVSwitch multicast address of the result matrix
+        (``multimem.st``; the switch replicates it to every rank) instead of once per peer.  Needs
+        multicast support in the symmetric-memory allocation; raises if it is missing."""
         import torch.distributed._symmetric_memory as symm_mem
 
         self.group = group if group is not None else dist.group.WORLD
@@ -130,6 +134,9 @@ class FusedColumnParallelGemm:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.bufs = [symm_mem.empty((m, n), dtype=out_dtype, device=dev) for _ in range(2)]
         self.handles = [symm_mem.rendezvous(c, self.group) for c in self.bufs]
+        self.multicast = bool(multicast)
+        if self.multicast and any(int(getattr(h, "multicast_ptr", 0) or 0) == 0 for h in self.handles):
+            raise RuntimeError("FusedColumnParallelGemm: this symmetric-memory allocation has no multicast address")
         self.turn = ResultTurn(2)
 
     @property
@@ -161,6 +168,8 @@ class FusedColumnParallelGemm:
         for i, ptr in enumerate(self.handles[idx].buffer_ptrs):
             g.peer_c[i] = int(ptr)
         g.num_peers = self.world
+        g.self_index = self.rank
+        g.multicast_c = int(self.handles[idx].multicast_ptr) if self.multicast else None
         g.peer_ldc = c.stride(0)
         g.col_offset = lo
         stream = C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)

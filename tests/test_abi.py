@@ -47,7 +47,8 @@ def test_struct_layouts_match_the_header():
         "b200k_attention_bwd_args": (L.AttentionBwdArgs, ["q", "d_o", "d_v", "workspace", "workspace_bytes", "batch",
                                                           "head_dim", "q_stride_b", "do_stride_h", "dv_stride_s",
                                                           "dtype", "scale", "status", "lse"]),
-        "b200k_gemm_allgather_args": (L.GemmAllGatherArgs, ["gemm", "peer_c", "num_peers", "peer_ldc", "col_offset"]),
+        "b200k_gemm_allgather_args": (L.GemmAllGatherArgs, ["gemm", "peer_c", "num_peers", "self_index", "peer_ldc", "col_offset",
+                                                             "multicast_c"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for cname, (_, fs) in fields.items():

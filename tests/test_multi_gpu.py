@@ -54,6 +54,22 @@ def _worker(rank, world, port, results):
         ok_fused = (fro <= 3e-2 and mx <= 3e-2 and fro2 <= 3e-2 and mx2 <= 3e-2
                     and second.data_ptr() != first.data_ptr() and torch.equal(first, c_fused))
 
+        # the same exchange through the NVSwitch multicast address (one multimem.st per piece), where
+        # the allocation has one: identical bits
+        ok_mc = True
+        try:
+            fused_mc = tdist.FusedColumnParallelGemm(m, n, torch.bfloat16, multicast=True)
+        except RuntimeError:
+            fused_mc = None
+        if fused_mc is not None:
+            for buf in fused_mc.bufs:
+                buf.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            fused_mc(ad, bd, sad, sbd)
+            ok_mc = torch.equal(fused_mc.finish(), c_fused)
+            torch.cuda.synchronize()
+
         # the unfused baseline: local GEMM, then NCCL all-gather + de-interleave
         c_nccl = tdist.column_parallel_gemm(lambda l, h: torch.ops.b200k.gemm_fp8_nt(ad, bd, sad, sbd), n, world, rank,
                                             gather=True)
@@ -67,7 +83,7 @@ def _worker(rank, world, port, results):
         hl, hh = tdist.shard_range(world, world, rank)
         ok_attn = torch.allclose(o.float().cpu(), full[:, hl * 2:hh * 2], rtol=1e-2, atol=1e-2)
         torch.cuda.synchronize()
-        results[rank] = (ok_fused, ok_same, ok_attn, float(fro))
+        results[rank] = (ok_fused, ok_same and ok_mc, ok_attn, float(fro))
     finally:
         dist.destroy_process_group()
 
