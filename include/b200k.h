@@ -84,7 +84,6 @@ const char* b200k_status_string(int status);
  * multiple of 16 bytes.  C: base aligned to 16 bytes, ldc * sizeof(out) a multiple of 16.
  * K tails, M tails and N tails are handled (out-of-range operand elements read as zero).
  */
-enum { B200K_TILE_SM_PAIR = -2 };
 enum { B200K_ACT_NONE = 0, B200K_ACT_RELU = 1, B200K_ACT_GELU = 2 /* erf form */, B200K_ACT_SILU = 3 };
 
 typedef struct b200k_gemm_args {
@@ -99,9 +98,7 @@ typedef struct b200k_gemm_args {
   const float* scale_b; /* device scalar, E4M3 only, may be NULL (= 1.0) */
   int32_t* status;      /* device status word, may be NULL */
   int32_t tile_n;       /* 0 = choose; else 128 or 256 */
-  int32_t tile_m;       /* 0 = choose; else 128 or 256 (256 needs tile_n 256 or 0), or
-                           B200K_TILE_SM_PAIR: 256 x 256 tiles, each computed by a pair of SMs
-                           (F16 / BF16, NT storage, no fused epilogue) */
+  int32_t tile_m;       /* 0 = choose; else 128 or 256 (256 needs tile_n 256 or 0) */
   /* Optional fused epilogue (the bias / activation tail of a linear layer, cf. the reference's
    * ops/templates/test_linear_trailing_optional_biased.mlir):  C = act(A B^T * scales + bias[n]).
    * bias: device vector of n elements, NULL = none; activation: B200K_ACT_*. */
@@ -115,6 +112,13 @@ typedef struct b200k_gemm_args {
    * run without repacking an operand. */
   int32_t a_km;
   int32_t b_kn;
+  /* Batched product (aten::bmm, which the reference's BOO layer lists beside mm and addmm,
+   * kernel/boo/op_exports/registry.py:99-104): batch > 1 independent problems of the same shape,
+   * problem i reading a + i * a_batch_stride, b + i * b_batch_stride and writing c + i *
+   * c_batch_stride (strides in ELEMENTS; the A / B strides multiples of 16 bytes).  All problems'
+   * tiles go through one persistent launch.  batch 0 or 1 = a single problem (strides ignored). */
+  int64_t batch;
+  int64_t a_batch_stride, b_batch_stride, c_batch_stride;
 } b200k_gemm_args;
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);
@@ -296,7 +300,7 @@ int b200k_paged_attention_fwd(const b200k_paged_attention_args* args, void* stre
  *   k_cache/v_cache [num_seqs, kv_heads, kv_seq_stride/head_dim rows, head_dim]; token t of
  *   sequence s is at  s * kv_batch_stride + h * kv_head_stride + t * head_dim  (elements).
  *
- * head_dim must be 128, page_size a multiple of 16, chunk_tokens a multiple of 64 (0 = choose).
+ * head_dim must be 128 or 64, page_size a multiple of 16, chunk_tokens a multiple of 64 (0 = choose).
  * workspace: b200k_decode_workspace_bytes() bytes, 256-byte aligned; contents are scratch.
  */
 typedef struct b200k_decode_args {
@@ -392,6 +396,17 @@ int b200k_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v
  */
 int b200k_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n, void* stream);
 
+/* ---- self-test of the bounded device-side wait -------------------------------------- */
+/*
+ * Every barrier wait in the kernels of this library is bounded: when one runs out the kernel sets
+ * a shared abort word, all of its roles leave through the common exit, and a code is OR-ed into the
+ * caller's status word (the reference has no counterpart: its kernels are generated and it reports
+ * failures from the host side of the VM invoke, runtime/invoke.py:62-70).  This entry exercises
+ * that exit in isolation: a small kernel waits limit_us microseconds (1 .. 100000) on a barrier on
+ * which nobody arrives, returns, and ORs bit 4 (value 16) into *status.  The context stays usable.
+ */
+int b200k_selftest_bounded_wait(int32_t* status, uint32_t limit_us, void* stream);
+
 /* ---- host-buffer convenience entry points (copies inside the call) ------------------ */
 /*
  * Same operations with HOST pointers: the call stages inputs to the device buffers given in
@@ -401,7 +416,7 @@ int b200k_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* ama
  * The copy-back runs on a stream the library keeps per device, ordered with two events that all
  * calls on that device share: call these two functions from ONE host thread per device at a time
  * (calls on different devices are independent).  b200k_gemm_nt_host takes the [M, K] x [N, K]
- * storage with single-SM tiles only (a_km, b_kn and B200K_TILE_SM_PAIR are rejected); the row
+ * storage only (a_km and b_kn are rejected); the row
  * pitches of both images are checked against the row lengths before any copy.
  */
 int b200k_gemm_nt_host(const b200k_gemm_args* host, const b200k_gemm_args* dev, void* stream);

@@ -89,6 +89,10 @@ class GemmArgs(C.Structure):
         ("activation", C.c_int32),
         ("a_km", C.c_int32),
         ("b_kn", C.c_int32),
+        ("batch", C.c_int64),
+        ("a_batch_stride", C.c_int64),
+        ("b_batch_stride", C.c_int64),
+        ("c_batch_stride", C.c_int64),
     ]
 
 
@@ -195,10 +199,6 @@ class PagedAttentionArgs(C.Structure):
 
 ACTIVATION_CODES = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
 
-# GemmArgs.tile_m value that asks b200k_gemm_nt for 256 x 256 tiles computed by pairs of SMs
-# (B200K_TILE_SM_PAIR).
-TILE_SM_PAIR = -2
-
 # name -> (restype, argtypes); this table is also what the symbol-export test walks.
 EXPORTED_SYMBOLS = {
     "b200k_abi_version": (C.c_int, []),
@@ -224,6 +224,7 @@ EXPORTED_SYMBOLS = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p],
     ),
+    "b200k_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p]),
     "b200k_quantize_e4m3": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "b200k_gemm_nt_host": (C.c_int, [C.POINTER(GemmArgs), C.POINTER(GemmArgs), C.c_void_p]),
     "b200k_attention_fwd_host": (C.c_int, [C.POINTER(AttentionArgs), C.POINTER(AttentionArgs), C.c_void_p]),

@@ -169,9 +169,6 @@ int get_side_stream(SideStream* out) {
 }  // namespace b200k
 
 namespace b200k {
-// gemm_pair_sm100.cu: 256 x 256 tiles computed by pairs of SMs
-int launch_gemm_pair(const b200k_gemm_args& a, cudaStream_t stream);
-bool gemm_pair_eligible(const b200k_gemm_args& a);
 // attention_bwd_sm100.cu
 int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream);
 uint64_t attention_bwd_workspace_bytes(const b200k_attention_bwd_args& a);
@@ -212,7 +209,6 @@ const char* b200k_status_string(int status) {
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream) {
   if (!args) return set_error(B200K_ERR_NULL, "gemm_nt: args is NULL");
-  if (args->tile_m == B200K_TILE_SM_PAIR) return launch_gemm_pair(*args, static_cast<cudaStream_t>(stream));
   return launch_gemm_nt(*args, static_cast<cudaStream_t>(stream));
 }
 
@@ -278,6 +274,10 @@ int b200k_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v
                           status, static_cast<cudaStream_t>(stream));
 }
 
+int b200k_selftest_bounded_wait(int32_t* status, uint32_t limit_us, void* stream) {
+  return launch_bounded_wait_selftest(status, limit_us, static_cast<cudaStream_t>(stream));
+}
+
 int b200k_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n, void* stream) {
   return launch_quantize_e4m3(x, y, scale_out, amax_scratch, n, static_cast<cudaStream_t>(stream));
 }
@@ -290,11 +290,9 @@ int b200k_gemm_nt_host(const b200k_gemm_args* host, const b200k_gemm_args* dev, 
   const size_t in_es = dtype_size(dev->in_dtype), out_es = dtype_size(dev->out_dtype);
   if (in_es == 0 || out_es == 0) return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt_host: bad dtype");
   if (dev->m <= 0 || dev->n <= 0 || dev->k <= 0) return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: bad shape");
-  // The row-block slicing below assumes A stored [M, K] and B stored [N, K], single-CTA tiles.
+  // The row-block slicing below assumes A stored [M, K] and B stored [N, K].
   if (dev->a_km || dev->b_kn || host->a_km || host->b_kn)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: operands stored [K, M] / [K, N] are not supported on the host-buffer path");
-  if (dev->tile_m == B200K_TILE_SM_PAIR)
-    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: the SM-pair tile is not supported on the host-buffer path");
   if (dev->lda < dev->k || dev->ldb < dev->k || dev->ldc < dev->n || host->lda < dev->k || host->ldb < dev->k ||
       host->ldc < dev->n)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_host: a row pitch of the host or device image is smaller than the row");

@@ -15,6 +15,7 @@ enum : int32_t {
   kStatusAttnTimeout = 2,
   kStatusDecodeBadPage = 4,
   kStatusDecodeLenClamped = 8,
+  kStatusSelftestTimeout = 16,
 };
 
 // ---- host-side error plumbing (abi.cu) ----
@@ -47,6 +48,7 @@ int launch_kv_append(const void* k_new, const void* v_new, void* k_cache, void* 
                      const int32_t* positions, int32_t num_seqs, int32_t new_tokens, int32_t kv_heads, int32_t head_dim,
                      int32_t page_size, int32_t num_pages, int32_t block_table_stride, int64_t kv_page_stride,
                      int64_t kv_head_stride, int32_t elem_bytes, int32_t* status, cudaStream_t stream);
+int launch_bounded_wait_selftest(int32_t* status, uint32_t limit_us, cudaStream_t stream);
 int launch_quantize_e4m3(const float* x, void* y, float* scale_out, uint32_t* amax_scratch, int64_t n,
                          cudaStream_t stream);
 

@@ -9,9 +9,10 @@
 //     contiguous bytes of a page slab; the page id comes from the block table once per tile;
 //   * all query heads of the group share each K/V tile through mma.sync.m16n8k16 with the
 //     group's heads as (zero-padded) rows, so issue slots stay free for the loads;
+//   * head dim 128 or 64 (template parameter HD): everything below scales with the row length;
 //   * softmax state is fp32; row max / sum are reduced across the quad with warp shuffles.
 //
-// Shared memory tile layout: 16 rows (tokens) x 256 bytes (128 halves); the 16-byte chunk c of
+// Shared memory tile layout: 16 rows (tokens) x HD halves (256 or 128 bytes); the 16-byte chunk c of
 // row r is stored at chunk position c ^ (r & 7) so ldmatrix reads are bank-conflict free.
 #include <mutex>
 #include <type_traits>
@@ -24,13 +25,18 @@
 namespace b200k {
 namespace {
 
-constexpr int kHeadDim = 128;
 constexpr int kTileTokens = 16;
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kDecodeStages = 3;
-constexpr int kTileBytes = kTileTokens * kHeadDim * 2;  // 4 KB for K, same for V
-constexpr int kDecodeSmem = kDecodeWarps * kDecodeStages * 2 * kTileBytes;  // 96 KB
+// per head dim HD (128 or 64): a tile is 16 tokens x HD halves for K and the same for V
+template <int HD>
+struct DecodeTile {
+  static constexpr int kRowBytes = HD * 2;
+  static constexpr int kBytes = kTileTokens * kRowBytes;                        // 4 KB (HD 128) or 2 KB
+  static constexpr int kSmem = kDecodeWarps * kDecodeStages * 2 * kBytes;       // 96 KB or 48 KB
+  static constexpr int kChunksPerRow = kRowBytes / 16;                          // 16-byte pieces per row
+};
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeParams {
@@ -135,8 +141,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // ------------------------------------------------------------------------------------------
 // phase 1
 // ------------------------------------------------------------------------------------------
-template <typename T, bool PAGED>
+template <typename T, bool PAGED, int HD>
 __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const DecodeParams p) {
+  constexpr int kHeadDim = HD;
+  constexpr int kTileBytes = DecodeTile<HD>::kBytes;
+  constexpr int kRowBytes = DecodeTile<HD>::kRowBytes;
+  constexpr int kChunks = DecodeTile<HD>::kChunksPerRow;
+  constexpr int kKSteps = HD / 16;  // k-steps of the score product = 16-dim slices of the head dim
   const int chunk = blockIdx.x;
   const int kvh = blockIdx.y;
   const int seq = blockIdx.z;
@@ -163,12 +174,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
   const T* kbase = reinterpret_cast<const T*>(p.k);
   const T* vbase = reinterpret_cast<const T*>(p.v);
 
-  // Query fragments: rows = heads of the group (zero beyond G), 8 k-steps of 16 dims.
-  uint32_t qf[8][4];
+  // Query fragments: rows = heads of the group (zero beyond G), HD / 16 k-steps of 16 dims.
+  uint32_t qf[kKSteps][4];
   {
     const T* qrow0 = reinterpret_cast<const T*>(p.q) + (static_cast<int64_t>(seq) * p.q_heads + kvh * G) * kHeadDim;
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
+    for (int ks = 0; ks < kKSteps; ++ks) {
       const int col = ks * 16 + 2 * t;
       qf[ks][0] = (g < G) ? *reinterpret_cast<const uint32_t*>(qrow0 + g * kHeadDim + col) : 0u;
       qf[ks][1] = (g + 8 < G) ? *reinterpret_cast<const uint32_t*>(qrow0 + (g + 8) * kHeadDim + col) : 0u;
@@ -177,7 +188,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
     }
   }
 
-  // Issues the 16 cp.async of one tile (8 for K, 8 for V) for this lane.
+  // Issues this lane's cp.async of one tile (HD / 16 for K, as many for V).
   auto issue_tile = [&](int tile, int stage) {
     const int tok0 = chunk_start + tile * kTileTokens;
     const uint32_t sk = warp_smem_u32 + stage * (2 * kTileBytes);
@@ -187,21 +198,21 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
                                               p.kv_page_stride, p.kv_head_stride, p.kv_batch_stride, kHeadDim, seq,
                                               kvh, tok0);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int id = i * 32 + lane;  // 16-byte chunk id inside the 4 KB slab
-      const int row = id >> 4;
-      const int c = id & 15;
+    for (int i = 0; i < kKSteps; ++i) {
+      const int id = i * 32 + lane;  // 16-byte chunk id inside the slab
+      const int row = id / kChunks;
+      const int c = id % kChunks;
       const bool valid = (base >= 0) && (tok0 + row < len);
       const int64_t off = valid ? base + row * kHeadDim + c * 8 : 0;
-      const uint32_t dst = (row << 8) + ((c ^ (row & 7)) << 4);
+      const uint32_t dst = row * kRowBytes + ((c ^ (row & 7)) << 4);
       cp_async_16(sk + dst, kbase + off, valid ? 16u : 0u);
       cp_async_16(sv + dst, vbase + off, valid ? 16u : 0u);
     }
   };
 
-  float o[16][4];
+  float o[HD / 8][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
   const int my_tiles = (n_tiles > warp) ? (n_tiles - warp + kDecodeWarps - 1) / kDecodeWarps : 0;
@@ -234,10 +245,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
       const int mi = lane >> 3;
       const int row = (lane & 7) + ((mi >> 1) << 3);
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < kKSteps; ++ks) {
         const int c = ks * 2 + (mi & 1);
         uint32_t r0, r1, r2, r3;
-        ldmatrix_x4(sk + (row << 8) + ((c ^ (row & 7)) << 4), r0, r1, r2, r3);
+        ldmatrix_x4(sk + row * kRowBytes + ((c ^ (row & 7)) << 4), r0, r1, r2, r3);
         mma_16816<T>(s[0], qf[ks], r0, r1);
         mma_16816<T>(s[1], qf[ks], r2, r3);
       }
@@ -278,14 +289,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
     l_lo = l_lo * a_lo + ps_lo;
     l_hi = l_hi * a_hi + ps_hi;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < HD / 8; ++i) {
       o[i][0] *= a_lo;
       o[i][1] *= a_lo;
       o[i][2] *= a_hi;
       o[i][3] *= a_hi;
     }
 
-    // ---- O += P V : 16 (heads) x 128 (dims), k = 16 tokens ----
+    // ---- O += P V : 16 (heads) x HD (dims), k = 16 tokens ----
     uint32_t pf[4];
     pf[0] = pack2<T>(s[0][0], s[0][1]);
     pf[1] = pack2<T>(s[0][2], s[0][3]);
@@ -295,10 +306,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
       const int mi = lane >> 3;
       const int row = (lane & 7) + ((mi & 1) << 3);
 #pragma unroll
-      for (int dn = 0; dn < 8; ++dn) {
+      for (int dn = 0; dn < HD / 16; ++dn) {
         const int c = dn * 2 + (mi >> 1);
         uint32_t r0, r1, r2, r3;
-        ldmatrix_x4_trans(sv + (row << 8) + ((c ^ (row & 7)) << 4), r0, r1, r2, r3);
+        ldmatrix_x4_trans(sv + row * kRowBytes + ((c ^ (row & 7)) << 4), r0, r1, r2, r3);
         mma_16816<T>(o[2 * dn], pf, r0, r1);
         mma_16816<T>(o[2 * dn + 1], pf, r2, r3);
       }
@@ -313,13 +324,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
   __syncthreads();  // every warp is done with its ring; reuse shared memory
-  float* sm_o = reinterpret_cast<float*>(smem);                 // [warps][16][128]
+  float* sm_o = reinterpret_cast<float*>(smem);                 // [warps][16][HD]
   float* sm_m = sm_o + kDecodeWarps * 16 * kHeadDim;            // [warps][16]
   float* sm_l = sm_m + kDecodeWarps * 16;                       // [warps][16]
   {
     float* wo = sm_o + warp * 16 * kHeadDim;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < HD / 8; ++i) {
       const int col = i * 8 + 2 * t;
       if (g < G) *reinterpret_cast<float2*>(wo + g * kHeadDim + col) = make_float2(o[i][0], o[i][1]);
       if (g + 8 < G) *reinterpret_cast<float2*>(wo + (g + 8) * kHeadDim + col) = make_float2(o[i][2], o[i][3]);
@@ -333,8 +344,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
   }
   __syncthreads();
   {
-    const int d = threadIdx.x;  // 128 threads, one per output dim
-    for (int r = 0; r < G; ++r) {
+    const int d = threadIdx.x;  // one thread per output dim (the upper half idles at HD 64)
+    for (int r = 0; r < G && d < kHeadDim; ++r) {
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
@@ -356,8 +367,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitkv_kernel(const
 // ------------------------------------------------------------------------------------------
 // phase 2: merge chunks
 // ------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(kHeadDim) decode_reduce_kernel(const DecodeParams p) {
+template <typename T, int HD>
+__global__ void __launch_bounds__(HD) decode_reduce_kernel(const DecodeParams p) {
+  constexpr int kHeadDim = HD;
   const int qh = blockIdx.x;
   const int seq = blockIdx.y;
   const int d = threadIdx.x;
@@ -411,7 +423,8 @@ int validate_decode(const b200k_decode_args& a) {
     return set_error(B200K_ERR_NULL, "decode_attention: q, k_cache, v_cache, seq_lens and o must be non-NULL");
   if (a.num_seqs <= 0 || a.q_heads <= 0 || a.kv_heads <= 0 || a.max_seq_len <= 0)
     return set_error(B200K_ERR_BAD_SHAPE, "decode_attention: num_seqs, q_heads, kv_heads, max_seq_len must be > 0");
-  if (a.head_dim != kHeadDim) return set_error(B200K_ERR_BAD_SHAPE, "decode_attention: head_dim must be 128");
+  if (a.head_dim != 128 && a.head_dim != 64)
+    return set_error(B200K_ERR_BAD_SHAPE, "decode_attention: head_dim must be 128 or 64");
   if (a.q_heads % a.kv_heads != 0 || a.q_heads / a.kv_heads > 16)
     return set_error(B200K_ERR_BAD_SHAPE, "decode_attention: q_heads must be a multiple (<= 16x) of kv_heads");
   if (a.dtype != B200K_F16 && a.dtype != B200K_BF16)
@@ -439,26 +452,27 @@ int validate_decode(const b200k_decode_args& a) {
   return B200K_OK;
 }
 
-template <typename T>
+template <typename T, int HD>
 int launch_decode_typed(const DecodeParams& p, bool paged, int num_seqs, cudaStream_t stream) {
   dim3 grid(p.max_chunks, p.kv_heads, num_seqs);
+  constexpr int kSmem = DecodeTile<HD>::kSmem;
   int rc;
   if (paged) {
-    auto kfn = decode_splitkv_kernel<T, true>;
-    rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem),
-                    "cudaFuncSetAttribute(decode smem)");
+    auto kfn = decode_splitkv_kernel<T, true, HD>;
+    static bool configured[64] = {};
+    rc = ensure_dynamic_smem(kfn, kSmem, configured, "cudaFuncSetAttribute(decode smem)");
     if (rc) return rc;
-    kfn<<<grid, kDecodeThreads, kDecodeSmem, stream>>>(p);
+    kfn<<<grid, kDecodeThreads, kSmem, stream>>>(p);
   } else {
-    auto kfn = decode_splitkv_kernel<T, false>;
-    rc = check_cuda(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem),
-                    "cudaFuncSetAttribute(decode smem)");
+    auto kfn = decode_splitkv_kernel<T, false, HD>;
+    static bool configured[64] = {};
+    rc = ensure_dynamic_smem(kfn, kSmem, configured, "cudaFuncSetAttribute(decode smem)");
     if (rc) return rc;
-    kfn<<<grid, kDecodeThreads, kDecodeSmem, stream>>>(p);
+    kfn<<<grid, kDecodeThreads, kSmem, stream>>>(p);
   }
   rc = check_cuda(cudaGetLastError(), "decode_splitkv_kernel launch");
   if (rc) return rc;
-  decode_reduce_kernel<T><<<dim3(p.q_heads, num_seqs), kHeadDim, 0, stream>>>(p);
+  decode_reduce_kernel<T, HD><<<dim3(p.q_heads, num_seqs), HD, 0, stream>>>(p);
   return check_cuda(cudaGetLastError(), "decode_reduce_kernel launch");
 }
 
@@ -480,7 +494,7 @@ uint64_t decode_workspace_bytes(const b200k_decode_args& a) {
   const int32_t ch = decode_default_chunk(a);
   const uint64_t max_chunks = (static_cast<uint64_t>(a.max_seq_len) + ch - 1) / ch;
   const uint64_t slots = static_cast<uint64_t>(a.num_seqs) * a.q_heads * max_chunks;
-  return slots * kHeadDim * sizeof(float) + slots * sizeof(float2);
+  return slots * static_cast<uint64_t>(a.head_dim > 0 ? a.head_dim : 128) * sizeof(float) + slots * sizeof(float2);
 }
 
 int launch_decode(const b200k_decode_args& a, cudaStream_t stream) {
@@ -519,11 +533,16 @@ int launch_decode(const b200k_decode_args& a, cudaStream_t stream) {
   p.scale_log2 = a.scale * kLog2e;
   const uint64_t slots = static_cast<uint64_t>(a.num_seqs) * a.q_heads * p.max_chunks;
   p.ws_o = reinterpret_cast<float*>(a.workspace);
-  p.ws_ml = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(a.workspace) + slots * kHeadDim * sizeof(float));
+  p.ws_ml = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(a.workspace) + slots * a.head_dim * sizeof(float));
   if (p.max_chunks > 65535 * 32)
     return set_error(B200K_ERR_BAD_SHAPE, "decode_attention: too many chunks (raise chunk_tokens)");
-  if (a.dtype == B200K_F16) return launch_decode_typed<__half>(p, a.block_table != nullptr, a.num_seqs, stream);
-  return launch_decode_typed<__nv_bfloat16>(p, a.block_table != nullptr, a.num_seqs, stream);
+  const bool paged = a.block_table != nullptr;
+  if (a.head_dim == 128) {
+    if (a.dtype == B200K_F16) return launch_decode_typed<__half, 128>(p, paged, a.num_seqs, stream);
+    return launch_decode_typed<__nv_bfloat16, 128>(p, paged, a.num_seqs, stream);
+  }
+  if (a.dtype == B200K_F16) return launch_decode_typed<__half, 64>(p, paged, a.num_seqs, stream);
+  return launch_decode_typed<__nv_bfloat16, 64>(p, paged, a.num_seqs, stream);
 }
 
 int launch_paged_gather(const void* cache, const int32_t* block_table, const int32_t* seq_lens, void* out,

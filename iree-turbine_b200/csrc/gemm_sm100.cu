@@ -36,6 +36,8 @@ struct GemmParams {
   int64_t ldc;
   int32_t m, n;
   int32_t tiles_m, tiles_n, num_kb;  // tiles_m counts MT * 128-row tiles
+  int32_t batch;                     // independent problems (tensor maps are 3-D: [batch][rows][k])
+  int64_t c_batch_stride;            // elements between the C matrices of consecutive problems
   // Optional fused epilogue: y = act(acc * scale + bias[col]); bias == nullptr and act == 0 leave
   // the plain path untouched.
   const void* bias;
@@ -217,7 +219,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tiles_per_problem = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_problem * p.batch;  // tile t: problem t / tiles_per_problem
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -227,7 +230,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const int bz = t / tiles_per_problem;
+        tile_coords(t - bz * tiles_per_problem, p.tiles_m, p.tiles_n, tm, tn);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(empty + stage, phase ^ 1, abort_word)) {
             ok = false;
@@ -238,16 +242,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (GEN && p.a_mn) {
 #pragma unroll
             for (int b = 0; b < kTileM / 64; ++b)
-              tma_load_2d(sa + b * 8192, &tmap_a, full + stage, tm * kTileM + b * 64, kb * kElemsPerStage);
+              tma_load_3d(sa + b * 8192, &tmap_a, full + stage, tm * kTileM + b * 64, kb * kElemsPerStage, bz);
           } else {
-            tma_load_2d(sa, &tmap_a, full + stage, kb * kElemsPerStage, tm * kTileM);
+            tma_load_3d(sa, &tmap_a, full + stage, kb * kElemsPerStage, tm * kTileM, bz);
           }
           if (GEN && p.b_mn) {
 #pragma unroll
             for (int b = 0; b < BN / 64; ++b)
-              tma_load_2d(sa + S::kABytes + b * 8192, &tmap_b, full + stage, tn * BN + b * 64, kb * kElemsPerStage);
+              tma_load_3d(sa + S::kABytes + b * 8192, &tmap_b, full + stage, tn * BN + b * 64, kb * kElemsPerStage, bz);
           } else {
-            tma_load_2d(sa + S::kABytes, &tmap_b, full + stage, kb * kElemsPerStage, tn * BN);
+            tma_load_3d(sa + S::kABytes, &tmap_b, full + stage, kb * kElemsPerStage, tn * BN, bz);
           }
           if (++stage == S::kStages) {
             stage = 0;
@@ -343,7 +347,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int bz = t / tiles_per_problem;
+      tile_coords(t - bz * tiles_per_problem, p.tiles_m, p.tiles_n, tm, tn);
       const int acc = it % kAccBufs;
       const uint32_t acc_phase = (it / kAccBufs) & 1;
       bool ok = mbar_wait(tfull + acc, acc_phase, abort_word);
@@ -485,7 +490,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_2d(&tmap_c, buf, tn * BN + c * kCols, row0);
+              tma_store_3d(&tmap_c, buf, tn * BN + c * kCols, row0, bz);
               tma_store_commit();
             }
             ++stg_count;
@@ -503,7 +508,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               sc = 1.f;
             }
             if (row < p.m && col < p.n) {
-              store_chunk<OutT>(cbase + static_cast<int64_t>(row) * p.ldc + col, r, sc, p.n - col,
+              store_chunk<OutT>(cbase + bz * p.c_batch_stride + static_cast<int64_t>(row) * p.ldc + col, r, sc, p.n - col,
                                 p.vec_store_ok != 0);
             }
           }
@@ -633,6 +638,15 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   if (in_es == 0 || out_es == 0 || a.in_dtype == B200K_F32)
     return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: unsupported dtype in=%d out=%d", a.in_dtype, a.out_dtype);
   const bool a_mn = a.a_km != 0, b_mn = a.b_kn != 0;
+  const int64_t batch = a.batch > 1 ? a.batch : 1;
+  if (a.batch < 0 || batch > 65535) return set_error(B200K_ERR_BAD_SHAPE, "gemm: batch must be in [0, 65535]");
+  if (batch > 1) {
+    if (peers.num > 0) return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_allgather: batched problems are not supported");
+    if (a.a_batch_stride <= 0 || a.b_batch_stride <= 0 || a.c_batch_stride <= 0)
+      return set_error(B200K_ERR_BAD_SHAPE, "gemm: batch strides must be positive");
+    if ((a.a_batch_stride * in_es) % 16 != 0 || (a.b_batch_stride * in_es) % 16 != 0)
+      return set_error(B200K_ERR_BAD_ALIGN, "gemm: the A / B batch strides must be multiples of 16 bytes");
+  }
   if ((a_mn || b_mn) && a.in_dtype == B200K_E4M3)
     return set_error(B200K_ERR_BAD_DTYPE, "gemm: a_km / b_kn operand storage is for F16 / BF16 only");
   if (a.lda < (a_mn ? a.m : a.k) || a.ldb < (b_mn ? a.n : a.k) || (peers.num == 0 && a.ldc < a.n))
@@ -649,7 +663,7 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_n must be 0, 128 or 256");
   if (a.tile_m != 0 && a.tile_m != 128 && a.tile_m != 256)
-    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_m must be 0, 128 or 256 (the SM-pair tile is taken by b200k_gemm_nt only)");
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_m must be 0, 128 or 256");
   int rc = ensure_sm100();
   if (rc) return rc;
 
@@ -661,7 +675,7 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   // is not.  (An earlier model with 0.67 / 0.67 / 0.72 chose 128 x 128 tiles for 4096^3, which
   // run at 983 TFLOP/s where 256 x 256 tiles reach 1398.)
   auto cost = [&](int bm, int bn) {
-    const int64_t tiles = ((a.m + bm - 1) / bm) * ((a.n + bn - 1) / bn);
+    const int64_t tiles = ((a.m + bm - 1) / bm) * ((a.n + bn - 1) / bn) * batch;
     const int64_t waves = (tiles + sms - 1) / sms;
     const double eff = bm == 256 ? 0.93 : (bn == 256 ? 0.83 : 0.62);
     return static_cast<double>(waves) * bm * bn / eff;
@@ -693,17 +707,21 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   {
     // K-major: rows of the stored matrix are rows of the tile; MN-major ([K, M] storage): one box
     // is 64 contiguous M-elements x 64 K-rows
-    uint64_t dims[2] = {static_cast<uint64_t>(a_mn ? a.m : a.k), static_cast<uint64_t>(a_mn ? a.k : a.m)};
-    uint64_t strides[1] = {static_cast<uint64_t>(a.lda) * in_es};
-    uint32_t box[2] = {static_cast<uint32_t>(a_mn ? 64 : k_per_stage), static_cast<uint32_t>(a_mn ? 64 : bm)};
-    rc = encode_tmap(&ta, a.in_dtype, 2, const_cast<void*>(a.a), dims, strides, box);
+    uint64_t dims[3] = {static_cast<uint64_t>(a_mn ? a.m : a.k), static_cast<uint64_t>(a_mn ? a.k : a.m),
+                        static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(a.lda) * in_es,
+                           static_cast<uint64_t>(batch > 1 ? a.a_batch_stride : a.lda) * in_es};
+    uint32_t box[3] = {static_cast<uint32_t>(a_mn ? 64 : k_per_stage), static_cast<uint32_t>(a_mn ? 64 : bm), 1u};
+    rc = encode_tmap(&ta, a.in_dtype, 3, const_cast<void*>(a.a), dims, strides, box);
     if (rc) return rc;
   }
   {
-    uint64_t dims[2] = {static_cast<uint64_t>(b_mn ? a.n : a.k), static_cast<uint64_t>(b_mn ? a.k : a.n)};
-    uint64_t strides[1] = {static_cast<uint64_t>(a.ldb) * in_es};
-    uint32_t box[2] = {static_cast<uint32_t>(b_mn ? 64 : k_per_stage), static_cast<uint32_t>(b_mn ? 64 : bn)};
-    rc = encode_tmap(&tb, a.in_dtype, 2, const_cast<void*>(a.b), dims, strides, box);
+    uint64_t dims[3] = {static_cast<uint64_t>(b_mn ? a.n : a.k), static_cast<uint64_t>(b_mn ? a.k : a.n),
+                        static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(a.ldb) * in_es,
+                           static_cast<uint64_t>(batch > 1 ? a.b_batch_stride : a.ldb) * in_es};
+    uint32_t box[3] = {static_cast<uint32_t>(b_mn ? 64 : k_per_stage), static_cast<uint32_t>(b_mn ? 64 : bn), 1u};
+    rc = encode_tmap(&tb, a.in_dtype, 3, const_cast<void*>(a.b), dims, strides, box);
     if (rc) return rc;
   }
 
@@ -723,7 +741,10 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   p.tiles_m = tiles_m;
   p.tiles_n = tiles_n;
   p.num_kb = static_cast<int32_t>((a.k + k_per_stage - 1) / k_per_stage);
-  p.vec_store_ok = ((reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && (a.ldc * out_es) % 16 == 0) ? 1 : 0;
+  p.batch = static_cast<int32_t>(batch);
+  p.c_batch_stride = batch > 1 ? a.c_batch_stride : 0;
+  p.vec_store_ok = ((reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && (a.ldc * out_es) % 16 == 0 &&
+                    (p.c_batch_stride * out_es) % 16 == 0) ? 1 : 0;
   p.num_peers = peers.num;
   p.peer_first = peers.first;
   p.peer_mc = peers.mc;
@@ -736,13 +757,15 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   CUtensorMap tc;
   memset(&tc, 0, sizeof(tc));
   if (p.tma_store_ok) {
-    uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m)};
-    uint64_t strides[1] = {static_cast<uint64_t>(a.ldc) * out_es};
-    uint32_t box[2] = {static_cast<uint32_t>(128 / out_es), 32u};
-    rc = encode_tmap(&tc, a.out_dtype, 2, a.c, dims, strides, box);
+    uint64_t dims[3] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m), static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(a.ldc) * out_es,
+                           static_cast<uint64_t>(batch > 1 ? a.c_batch_stride : a.ldc) * out_es};
+    uint32_t box[3] = {static_cast<uint32_t>(128 / out_es), 32u, 1u};
+    rc = encode_tmap(&tc, a.out_dtype, 3, a.c, dims, strides, box);
     if (rc) return rc;
   }
-  const int64_t num_tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+  const int64_t num_tiles = static_cast<int64_t>(tiles_m) * tiles_n * batch;
+  if (num_tiles > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "gemm: too many tiles");
   const int grid = static_cast<int>(num_tiles < sms ? num_tiles : sms);
   if (bm == 256) return dispatch_dtype<256, 2>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
   if (bn == 256) return dispatch_dtype<256, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);

@@ -109,7 +109,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 // Bounded wait.  `abort_word` is a shared-memory word shared by all roles of the CTA; once any
 // waiter times out it becomes non-zero and every other waiter gives up at its next poll.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
+                                                uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
@@ -119,12 +120,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_word != 0) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > limit_ns) {
         *abort_word = 1;
         return false;
       }
     }
   }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
+  return mbar_wait_limit(bar, parity, abort_word, kWaitLimitNs);
 }
 
 // The same wait and the commit below for a barrier given by its 32-bit shared-memory address.  A

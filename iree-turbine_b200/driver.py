@@ -150,6 +150,10 @@ def _randn_strided(dims, strides, dtype, device, gen) -> torch.Tensor:
     return torch.as_strided(base, dims, strides)
 
 
+def _fp64_cpu(*tensors):
+    return [t.detach().cpu().double() if isinstance(t, torch.Tensor) else t for t in tensors]
+
+
 def _rows_contiguous(t: torch.Tensor) -> bool:
     return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.size(1)
 
@@ -158,6 +162,9 @@ def _mm_callable(backend: str, a: torch.Tensor, b: torch.Tensor, notes: List[str
     """a [M, K], b [K, N] as the op sees them (views with arbitrary strides)."""
     if backend == "torch":
         return lambda: torch.mm(a, b)
+    if backend == "cpu_fp64":
+        a64, b64 = _fp64_cpu(a, b)
+        return lambda: torch.mm(a64, b64)
     if a.dtype not in (torch.float16, torch.bfloat16) or a.dtype != b.dtype:
         raise Unsupported(f"b200k GEMM takes float16 / bfloat16 operands, not {a.dtype}")
     # the kernel reads either storage order of each operand; only a layout with no contiguous
@@ -176,11 +183,24 @@ def _mm_callable(backend: str, a: torch.Tensor, b: torch.Tensor, notes: List[str
     return lambda: torch.ops.b200k.gemm(a_s, b_s, ta, tb_, a.dtype)
 
 
-def build_callable(cmd, backend: str, device, notes: List[str]) -> Callable[[], torch.Tensor]:
+def build_callable(cmd, backend: str, device, notes: List[str], fill: Optional[str] = None) -> Callable[[], torch.Tensor]:
+    """``backend``: "b200k", "torch" (the vendor kernel on the same device) or "cpu_fp64" (the torch
+    operator on CPU in float64: the reference value of the numerics report).  ``fill``: None = seeded
+    normal operands; "structured" = zeros with one block of ones per operand (numerics.apply_block_of_ones)."""
+    from .numerics import apply_block_of_ones
+
     gen = torch.Generator(device=device).manual_seed(SEED)
+    made = [0]
+
+    def shaped(t: torch.Tensor) -> torch.Tensor:
+        if fill == "structured" and t.is_floating_point():
+            apply_block_of_ones(t, seed=made[0])
+        made[0] += 1
+        return t
+
     if isinstance(cmd, GemmCommand):
         def stored(rows, cols):
-            return torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32).to(cmd.dtype)
+            return shaped(torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32).to(cmd.dtype))
 
         if cmd.mode == 1:
             a_store = stored(*((cmd.k, cmd.m) if cmd.transpose_a else (cmd.m, cmd.k)))
@@ -201,21 +221,35 @@ def build_callable(cmd, backend: str, device, notes: List[str]) -> Callable[[], 
     tensors = []
     for dims, ty, strides, concrete in zip(cmd.input_dims, cmd.input_type, cmd.input_strides, cmd.concrete_inputs):
         if concrete == "" and ty in _ATEN_DTYPES:
-            tensors.append(_randn_strided(dims, strides, _ATEN_DTYPES[ty], device, gen))
+            tensors.append(shaped(_randn_strided(dims, strides, _ATEN_DTYPES[ty], device, gen)))
         else:
             tensors.append(None if concrete in ("", "None") else ast.literal_eval(concrete))
     if name == "mm":
         return _mm_callable(backend, tensors[0], tensors[1], notes)
+    if name == "bmm":
+        a, b = tensors[:2]
+        if backend == "torch":
+            return lambda: torch.bmm(a, b)
+        if backend == "cpu_fp64":
+            a64, b64 = _fp64_cpu(a, b)
+            return lambda: torch.bmm(a64, b64)
+        if a.dtype not in (torch.float16, torch.bfloat16) or a.dtype != b.dtype:
+            raise Unsupported("b200k bmm covers float16 / bfloat16 operands of one dtype")
+        return lambda: torch.ops.b200k.bmm(a, b, a.dtype)
     if name == "scaled_dot_product_attention":
         q, k, v = tensors[:3]
         rest = tensors[3:] + [None] * 5
         mask, dropout_p, is_causal, scale, enable_gqa = rest[:5]
         dropout_p = 0.0 if dropout_p is None else float(dropout_p)
         is_causal = bool(is_causal)
-        if backend == "torch":
+        if backend in ("torch", "cpu_fp64"):
             kwargs = {} if scale is None else {"scale": float(scale)}
             if enable_gqa:
                 kwargs["enable_gqa"] = True
+            if backend == "cpu_fp64":
+                q64, k64, v64, m64 = _fp64_cpu(q, k, v, mask)
+                return lambda: torch.nn.functional.scaled_dot_product_attention(q64, k64, v64, m64, dropout_p, is_causal,
+                                                                                **kwargs)
             return lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, mask, dropout_p, is_causal, **kwargs)
         if mask is not None or dropout_p != 0.0:
             raise Unsupported("b200k attention takes no mask and no dropout")
@@ -262,6 +296,10 @@ def _meta_parser() -> argparse.ArgumentParser:
                    help=f"backend to run; may be given several times (default '{DEFAULT_BACKEND}')")
     p.add_argument("--csv", type=str, default=None, help="file to write the timing table to")
     p.add_argument("--gpu-id", type=int, default=0)
+    p.add_argument("--verify-numerics", action="store_true",
+                   help="per command, also print the numerics report (error statistics of b200k and of torch on the "
+                        "same device against a float64 CPU result, and the block-of-ones indexing test); a failed "
+                        "report makes the exit code non-zero")
     p.add_argument("--verbose", action="store_true", default=None)
     return p
 
@@ -288,10 +326,11 @@ def main(args: Optional[List[str]] = None) -> int:
         out.writerow(csv_headers(backends))
         if not torch.cuda.is_available():
             raise RuntimeError("b200k-driver needs a CUDA device: the kernels have no CPU path")
-        return _run_commands(commands, backends, out, torch.device("cuda", meta.gpu_id), verbose)
+        return _run_commands(commands, backends, out, torch.device("cuda", meta.gpu_id), verbose,
+                             verify_numerics=meta.verify_numerics)
 
 
-def _run_commands(commands, backends, out, device, verbose: bool) -> int:
+def _run_commands(commands, backends, out, device, verbose: bool, verify_numerics: bool = False) -> int:
     import iree_turbine_b200  # noqa: F401  (registers torch.ops.b200k.*)
 
     errors = 0
@@ -326,6 +365,15 @@ def _run_commands(commands, backends, out, device, verbose: bool) -> int:
                 row += ["N.A."] * len(ALL_STATS)
                 print(f"  {b}: failed: {e!r}")
         out.writerow(row)
+        if verify_numerics:
+            from . import numerics
+
+            try:
+                verdict = numerics.verify_command(cmd, device, command_text=shlex.join(argv))
+                print(numerics.format_verdict(verdict))
+                errors += 0 if verdict.passed else 1
+            except Unsupported as e:
+                print(f"numerics: N.A. ({e})")
     return 0 if errors == 0 else 1
 
 

@@ -12,6 +12,7 @@ What is rewritten (forward graph only; the backward graph, if any, goes to the n
 * ``aten.mm(a, t(w))``           -> ``b200k.gemm_nt(a, w, out_dtype=a.dtype)``
 * ``aten.mm`` in the other three storage forms (``mm(a, b)``, ``mm(t(a), b)``, ``mm(t(a), t(b))``)
                                  -> ``b200k.gemm(a, b, trans_a, trans_b)`` (no operand is repacked)
+* ``aten.bmm(a, b)``             -> ``b200k.bmm(a, b)`` (every problem's tiles in one launch)
 * ``aten.addmm(bias, a, t(w))``  -> ``b200k.linear_act(a, w, bias)`` (bias [N] added in the GEMM's
   epilogue; alpha = beta = 1)
   for 2-D f16 / bf16 CUDA operands of one dtype, where ``t`` is ``aten.t``, ``aten.transpose(0, 1)``
@@ -117,6 +118,27 @@ def replace_mm(node: fx.Node) -> bool:
             new = node.graph.call_function(torch.ops.b200k.gemm_nt.default, args=(a, b, _val(a).dtype))
         else:
             new = node.graph.call_function(torch.ops.b200k.gemm.default, args=(a, b, ta, tb_, _val(a).dtype))
+    new.meta = dict(node.meta)
+    node.replace_all_uses_with(new)
+    node.graph.erase_node(node)
+    return True
+
+
+def replace_bmm(node: fx.Node) -> bool:
+    """aten.bmm(a[B, M, K], b[B, K, N]) -> b200k.bmm(a, b, out_dtype=a.dtype).  The op reads either
+    storage order of each operand from the strides at run time (a transposed view, e.g.
+    ``k.transpose(1, 2)``, stays a view), so the traced operands are passed as they are; what the
+    op cannot read in place it copies, which is never worse than what aten.bmm does."""
+    a, b = node.args[:2]
+    va, vb = _val(a), _val(b)
+    if not (_is_cuda_half(va, 3) and _is_cuda_half(vb, 3)) or va.dtype != vb.dtype:
+        return False
+    if va.size(0) != vb.size(0) or va.size(2) != vb.size(1):
+        return False
+    if not (va.size(1) % 8 == 0 or va.size(2) % 8 == 0):
+        return False
+    with node.graph.inserting_before(node):
+        new = node.graph.call_function(torch.ops.b200k.bmm.default, args=(a, b, va.dtype))
     new.meta = dict(node.meta)
     node.replace_all_uses_with(new)
     node.graph.erase_node(node)
@@ -234,6 +256,7 @@ def _default_replacements() -> ReplacementSchema:
     schema: ReplacementSchema = {
         aten.mm.default: replace_mm,
         aten.addmm.default: replace_addmm,
+        aten.bmm.default: replace_bmm,
         aten.scaled_dot_product_attention.default: replace_sdpa,
     }
     for name in ("_scaled_dot_product_flash_attention", "_scaled_dot_product_efficient_attention",

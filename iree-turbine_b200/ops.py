@@ -28,6 +28,7 @@ __all__ = [
     "gemm_nt",
     "gemm_fp8_nt",
     "gemm",
+    "bmm",
     "linear",
     "linear_act",
     "attention",
@@ -130,6 +131,24 @@ def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: in
     L.check(L.lib().b200k_gemm_nt(C.byref(args), _stream(a)))
 
 
+def _batched_operand(t: Tensor):
+    """A [B, R, C] operand as the kernel can read it without a copy: (tensor, stored_transposed).
+    Either the last dim is contiguous (rows of the matrix) or the middle one is (the matrix is stored
+    transposed); row pitch and batch stride must be multiples of 16 bytes.  Otherwise a contiguous copy."""
+    es = t.element_size()
+
+    def ok(x):
+        return (x.stride(2) == 1 and (x.stride(1) * es) % 16 == 0 and (x.stride(0) * es) % 16 == 0
+                and x.stride(1) >= x.size(2) and x.data_ptr() % 16 == 0 and x.size(2) % 8 == 0)
+
+    if ok(t):
+        return t, False
+    tt = t.transpose(1, 2)
+    if ok(tt):
+        return tt, True
+    return t.contiguous(), False
+
+
 @CustomOp.register(library=LIBRARY)
 class gemm_nt(CustomOp):
     """C[M,N] = A[M,K] @ B[N,K]^T, f16 or bf16 operands, fp32 accumulation.
@@ -192,6 +211,49 @@ class gemm(CustomOp):
         m, n, _, _ = self._mnk(a, b, trans_a, trans_b)
         out = torch.empty((m, n), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
         _launch_gemm(a, b, out, None, None, a_km=bool(trans_a), b_kn=not trans_b)
+        return out
+
+
+@CustomOp.register(library=LIBRARY)
+class bmm(CustomOp):
+    """Batched product ``a[B, M, K] @ b[B, K, N]`` (aten::bmm; the reference's BOO layer registers it
+    beside mm and addmm, kernel/boo/op_exports/registry.py:99-104), f16 / bf16, fp32 accumulation, every
+    problem's tiles in one persistent launch.  Either operand may be a transposed view (e.g.
+    ``k.transpose(1, 2)``): the kernel reads both storage orders."""
+
+    signature = "bmm(Tensor a, Tensor b, ScalarType? out_dtype=None) -> Tensor"
+
+    def select(self, sel: KernelSelection):
+        a = sel.arg_tensor(0)
+        b = sel.arg_tensor(1)
+        od = sel.attr_optional(2)
+        torch._check(a.t.dim() == 3 and b.t.dim() == 3, lambda: "bmm: a and b must be 3-D")
+        torch._check(a.t.dtype in _HALF_TYPES and a.t.dtype == b.t.dtype,
+                     lambda: f"bmm: a and b must both be float16 or bfloat16, got {a.t.dtype}, {b.t.dtype}")
+        torch._check(a.t.size(0) == b.t.size(0) and a.t.size(2) == b.t.size(1),
+                     lambda: f"bmm: shapes {list(a.t.shape)} and {list(b.t.shape)} do not multiply")
+        torch._check(a.t.size(1) % 8 == 0 or a.t.size(2) % 8 == 0, lambda: "bmm: M or K must be a multiple of 8")
+        sel.return_new_tensor([a.t.size(0), a.t.size(1), b.t.size(2)], _gemm_out_dtype(a.t.dtype, od.v))
+
+    def eager_execute(self, a, b, out_dtype=None):
+        bsz, m, k = a.shape
+        n = b.size(2)
+        out = torch.empty((bsz, m, n), dtype=_gemm_out_dtype(a.dtype, out_dtype), device=a.device)
+        if bsz == 0 or m == 0 or n == 0:
+            return out
+        a_s, a_t = _batched_operand(a)   # a_t: stored [B, K, M]
+        b_s, b_t = _batched_operand(b)   # b_t: stored [B, N, K]  (the kernel's native form)
+        args = L.GemmArgs()
+        args.a, args.b, args.c = a_s.data_ptr(), b_s.data_ptr(), out.data_ptr()
+        args.m, args.n, args.k = m, n, k
+        args.a_km, args.b_kn = int(a_t), int(not b_t)
+        args.lda, args.ldb, args.ldc = a_s.stride(1), b_s.stride(1), out.stride(1)
+        args.batch = bsz
+        args.a_batch_stride, args.b_batch_stride, args.c_batch_stride = a_s.stride(0), b_s.stride(0), out.stride(0)
+        args.in_dtype = L.DTYPE_CODES[a.dtype]
+        args.out_dtype = L.DTYPE_CODES[out.dtype]
+        args.status = _status_ptr(a.device)
+        L.check(L.lib().b200k_gemm_nt(C.byref(args), _stream(a)))
         return out
 
 
@@ -518,12 +580,12 @@ def sdpa(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, is_caus
 # decode / paged decode
 # ---------------------------------------------------------------------------------------------
 def _decode_common_checks(name: str, q: Tensor, kc: Tensor, vc: Tensor, lens: Tensor):
-    torch._check(q.dim() == 3, lambda: f"{name}: q must be [num_seqs, q_heads, 128]")
+    torch._check(q.dim() == 3, lambda: f"{name}: q must be [num_seqs, q_heads, head_dim]")
     torch._check(q.dtype in _HALF_TYPES, lambda: f"{name}: dtype must be float16 or bfloat16, got {q.dtype}")
     torch._check(q.dtype == kc.dtype == vc.dtype, lambda: f"{name}: q and the KV cache must share a dtype")
-    torch._check(q.size(2) == 128, lambda: f"{name}: head dim must be 128")
+    torch._check(q.size(2) in (64, 128), lambda: f"{name}: head dim must be 128 or 64")
     torch._check(kc.dim() == 4 and kc.shape == vc.shape, lambda: f"{name}: k and v caches must be 4-D and equal in shape")
-    torch._check(kc.size(3) == 128, lambda: f"{name}: cache head dim must be 128")
+    torch._check(kc.size(3) == q.size(2), lambda: f"{name}: cache head dim must equal q's")
     torch._check(lens.dtype == torch.int32 and lens.dim() == 1 and lens.size(0) == q.size(0),
                  lambda: f"{name}: seq_lens must be int32 [num_seqs]")
     torch._check(q.size(1) % kc.size(1) == 0 and q.size(1) // kc.size(1) <= 16,
@@ -544,8 +606,8 @@ def _launch_decode(args: L.DecodeArgs, q: Tensor) -> None:
 class decode_attention(CustomOp):
     """One query token per sequence against a contiguous KV history.
 
-    q [num_seqs, Hq, 128]; k, v [num_seqs, Hkv, max_len, 128]; seq_lens int32 [num_seqs]
-    (tokens t >= seq_lens[s] are ignored).  Returns [num_seqs, Hq, 128].
+    q [num_seqs, Hq, D]; k, v [num_seqs, Hkv, max_len, D]; seq_lens int32 [num_seqs]
+    (tokens t >= seq_lens[s] are ignored; D = 128 or 64).  Returns [num_seqs, Hq, D].
     """
 
     signature = (
@@ -585,9 +647,9 @@ class decode_attention(CustomOp):
 class paged_decode_attention(CustomOp):
     """One query token per sequence against a paged KV cache.
 
-    q [num_seqs, Hq, 128]; k_cache, v_cache [num_pages, Hkv, page_size, 128];
+    q [num_seqs, Hq, D]; k_cache, v_cache [num_pages, Hkv, page_size, D], D = 128 or 64;
     block_table int32 [num_seqs, max_pages]: physical page of logical page p of sequence s;
-    seq_lens int32 [num_seqs].  Returns [num_seqs, Hq, 128].
+    seq_lens int32 [num_seqs].  Returns [num_seqs, Hq, D].
     """
 
     signature = (

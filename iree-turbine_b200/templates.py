@@ -117,8 +117,8 @@ def get_causal_attention_kernel(shape: AttentionShape, dtype: torch.dtype = torc
 def get_decode_attention_kernel(shape: AttentionShape, dtype: torch.dtype = torch.float16,
                                 scale: Optional[float] = None, chunk_tokens: int = 0) -> LaunchableKernel:
     """Split-KV decode against contiguous KV: kernel(q, k, v, seq_lens)."""
-    if shape.head_size != 128:
-        raise ValueError("decode attention: head_size must be 128")
+    if shape.head_size not in (64, 128):
+        raise ValueError("decode attention: head_size must be 128 or 64")
     sc = shape.head_size ** -0.5 if scale is None else float(scale)
 
     def run(q, k, v, seq_lens):
@@ -133,8 +133,8 @@ def get_decode_attention_kernel(shape: AttentionShape, dtype: torch.dtype = torc
 def get_paged_decode_attention_kernel(shape: AttentionShape, dtype: torch.dtype = torch.float16,
                                       scale: Optional[float] = None, chunk_tokens: int = 0) -> LaunchableKernel:
     """Split-KV decode through a block table: kernel(q, k_cache, v_cache, block_table, seq_lens)."""
-    if shape.head_size != 128:
-        raise ValueError("paged decode attention: head_size must be 128")
+    if shape.head_size not in (64, 128):
+        raise ValueError("paged decode attention: head_size must be 128 or 64")
     if not shape.block_size or shape.block_size % 16:
         raise ValueError("paged decode attention: block_size must be a positive multiple of 16")
     sc = shape.head_size ** -0.5 if scale is None else float(scale)

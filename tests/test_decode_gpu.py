@@ -60,6 +60,25 @@ def test_page_sizes(page_size):
     oracle.assert_close_half(_paged(q, kc, vc, bt, sl), ref)
 
 
+@pytest.mark.parametrize("q_heads,kv_heads", [(8, 8), (16, 2), (32, 8)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_64(q_heads, kv_heads, dtype):
+    """Head dim 64: paged decode against the oracle, the gather bit for bit, paged == contiguous bitwise."""
+    q, kc, vc, bt, sl = oracle.make_paged_decode_inputs(num_seqs=6, q_heads=q_heads, kv_heads=kv_heads, head_dim=64,
+                                                        min_len=1, max_len=900, dtype=dtype, seed=11)
+    scale = 0.125
+    qd, kcd, vcd, btd, sld = (t.to(DEV) for t in (q, kc, vc, bt, sl))
+    o = torch.ops.b200k.paged_decode_attention(qd, kcd, vcd, btd, sld, scale, 128)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(o, oracle.paged_decode_attention(q, kc, vc, bt, sl, scale))
+    max_len = bt.shape[1] * 16
+    kg = torch.ops.b200k.paged_gather(kcd, btd, sld, max_len)
+    vg = torch.ops.b200k.paged_gather(vcd, btd, sld, max_len)
+    assert torch.equal(kg.cpu().view(torch.int16), oracle.paged_gather(kc, bt, sl, max_len).view(torch.int16))
+    assert torch.equal(torch.ops.b200k.decode_attention(qd, kg, vg, sld, scale, 128), o)
+
+
 def test_paged_equals_contiguous_bitwise():
     """Same tokens, same chunking: fetching through the block table must not change a single bit."""
     q, kc, vc, bt, sl = oracle.make_paged_decode_inputs(num_seqs=7, q_heads=16, kv_heads=4, min_len=3, max_len=2100,

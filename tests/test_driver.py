@@ -57,3 +57,9 @@ def test_no_cpu_fallback(tmp_path):
         driver.main([f"--csv={tmp_path / 'x.csv'}", "gemmfp16", "--a_w", "32"])
     # the header is still written first, as in the reference
     assert (tmp_path / "x.csv").read_text().splitlines()[0].startswith("arguments,b200k min")
+
+
+def test_aten_bmm_command_parses():
+    c = driver.parse_command(["aten::bmm", "[[8, 128, 64], [8, 64, 256]]", "['c10::Half', 'c10::Half']",
+                              "[[8192, 64, 1], [16384, 256, 1]]", "['', '']"])
+    assert c.name == "aten::bmm" and c.input_dims == [[8, 128, 64], [8, 64, 256]]

@@ -59,6 +59,24 @@ def test_mm_nt_is_routed(transpose):
     assert node.args[2] == torch.float16 and [a.name for a in node.args[:2]] == ["a", "w"]
 
 
+def test_bmm_is_routed_and_float32_bmm_left_alone():
+    def build(dtype):
+        def f(g):
+            a = _ph(g, "a", _fake((4, 64, 128), dtype))
+            b = _ph(g, "b", _fake((4, 128, 32), dtype))
+            out = g.call_function(aten.bmm.default, (a, b))
+            out.meta["val"] = _fake((4, 64, 32), dtype)
+            return out
+        return f
+
+    gm = _graph(build(torch.bfloat16))
+    assert db.apply_replacements(gm) == 1
+    node = next(n for n in gm.graph.nodes if n.target is torch.ops.b200k.bmm.default)
+    assert [a.name for a in node.args[:2]] == ["a", "b"] and node.args[2] == torch.bfloat16
+    gm = _graph(build(torch.float32))
+    assert db.apply_replacements(gm) == 0 and aten.bmm.default in _targets(gm)
+
+
 def test_addmm_becomes_fused_linear():
     def build(g):
         bias = _ph(g, "bias", _fake((512,)))

@@ -55,33 +55,6 @@ def test_256x256_tiles(m, n, k, dtype):
     assert torch.equal(c, _run(a, b, tile_m=256))
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 320), (300, 520, 136), (1, 8, 8), (2560, 2304, 512),
-                                   (5120, 4096, 192)])
-@pytest.mark.parametrize("dtype,out_dtype", [(torch.float16, torch.float32), (torch.float16, torch.float16),
-                                             (torch.bfloat16, torch.bfloat16)])
-def test_sm_pair_tiles(m, n, k, dtype, out_dtype):
-    """256 x 256 tiles computed by pairs of SMs (clusters of two CTAs, one MMA spanning both).
-    Exact and ragged shapes; 2560 x 2304 gives 90 tiles and 5120 x 4096 gives 320 for the 74 pairs,
-    so pairs run several tiles through both accumulator buffers.  The same tile decomposition in
-    one CTA (tile_m=256) must give the same bits: both accumulate each element over k in one order."""
-    from iree_turbine_b200 import _launcher
-
-    a, b = oracle.make_gemm_inputs(m, n, k, dtype, seed=12)
-    c = _run(a, b, out_dtype=out_dtype, tile_m=_launcher.TILE_SM_PAIR)
-    oracle.assert_close_half(c, oracle.gemm_nt(a, b))
-    assert torch.equal(c, _run(a, b, out_dtype=out_dtype, tile_m=_launcher.TILE_SM_PAIR))
-    assert torch.equal(c, _run(a, b, out_dtype=out_dtype, tile_m=256))
-
-
-def test_sm_pair_tiles_reject_what_they_do_not_cover():
-    from iree_turbine_b200 import _launcher
-
-    a, w, bias = oracle.make_gemm_inputs(256, 256, 64, torch.float16, seed=1) + (torch.zeros(256, dtype=torch.float16),)
-    out = torch.empty(256, 256, dtype=torch.float16, device=DEV)
-    with pytest.raises((RuntimeError, ValueError)):
-        ops._launch_gemm(a.to(DEV), w.to(DEV), out, None, None, tile_m=_launcher.TILE_SM_PAIR, bias=bias.to(DEV))
-
-
 @pytest.mark.parametrize("m,n,k", [(200, 136, 72), (1, 8, 8), (130, 260, 1032), (1000, 24, 4096)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_ragged_shapes(m, n, k, dtype):
@@ -300,3 +273,42 @@ def test_linear_golden_fixture_forward_and_backward_products():
     oracle.assert_close_half(torch.ops.b200k.gemm(dy, w, False, False, None), torch.from_numpy(z["dx"]))
     oracle.assert_close_half(torch.ops.b200k.gemm(dy, x, True, False, None), torch.from_numpy(z["dw"]))
     assert tb.device_status() == 0
+
+
+# ---- batched product (aten::bmm) ----
+@pytest.mark.parametrize("bsz,m,n,k", [(1, 128, 128, 64), (3, 200, 136, 72), (16, 128, 64, 128), (5, 300, 520, 136),
+                                        (32, 64, 64, 64)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bmm_against_oracle_and_per_problem_calls(bsz, m, n, k, dtype):
+    g = torch.Generator().manual_seed(13)
+    a = torch.randn(bsz, m, k, generator=g).to(dtype)
+    b = torch.randn(bsz, k, n, generator=g).to(dtype)
+    ad, bd = a.to(DEV), b.to(DEV)
+    c = torch.ops.b200k.bmm(ad, bd)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    assert c.shape == (bsz, m, n) and c.dtype == torch.float32
+    oracle.assert_close_half(c, oracle.bmm(a, b))
+    # the batched launch gives each problem the bits of its own call
+    for i in (0, bsz - 1):
+        assert torch.equal(c[i], torch.ops.b200k.gemm(ad[i], bd[i], False, False))
+    # a transposed view of [B, N, K] storage (the attention-style q @ k^T) is read in place
+    bt = b.transpose(1, 2).contiguous().to(DEV)  # [B, N, K]
+    c2 = torch.ops.b200k.bmm(ad, bt.transpose(1, 2), dtype)
+    oracle.assert_close_half(c2, oracle.bmm(a, b))
+    # aten.bmm itself, in fp32, for reference
+    assert torch.allclose(c.cpu(), torch.bmm(a.float(), b.float()), rtol=1e-2, atol=1e-2)
+
+
+def test_bmm_block_of_ones_lands_in_the_right_problem():
+    """Structured indexing check (the reference's block-of-ones idea, kernel/boo/driver/numerics.py:319-355):
+    zeros everywhere except one block of ones in one problem of the batch."""
+    bsz, m, n, k = 7, 256, 384, 128
+    a = torch.zeros(bsz, m, k, dtype=torch.float16)
+    b = torch.zeros(bsz, k, n, dtype=torch.float16)
+    a[4, 130:140, 16:48] = 1
+    b[4, 16:48, 300:310] = 1
+    c = torch.ops.b200k.bmm(a.to(DEV), b.to(DEV)).cpu()
+    ref = torch.zeros(bsz, m, n)
+    ref[4, 130:140, 300:310] = 32
+    assert torch.equal(c, ref)

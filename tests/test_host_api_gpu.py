@@ -60,3 +60,28 @@ def test_gemm_host_single_block_ragged():
     GemmHost(m, n, k, torch.float16, torch.float32, DEV)(a, b, out)
     torch.cuda.synchronize()
     oracle.assert_close_half(out, oracle.gemm_nt(a, b))
+
+
+def test_bounded_wait_runs_out_and_reports():
+    """A device-side wait that nothing will ever satisfy gives up after its limit: the kernel returns,
+    the status word carries the code, and the context keeps working (the next kernel runs)."""
+    import ctypes as C
+    import time
+
+    import iree_turbine_b200 as tb
+    from iree_turbine_b200 import _launcher as L
+
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    t0 = time.perf_counter()
+    L.check(L.lib().b200k_selftest_bounded_wait(status.data_ptr(), 3000, stream))  # 3 ms
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert int(status.item()) == 16
+    assert 0.002 < dt < 1.0, dt
+    # the context is intact: an ordinary kernel still runs and no status bit leaks into the library's own word
+    a, b = oracle.make_gemm_inputs(128, 128, 64, torch.float16, seed=1)
+    oracle.assert_close_half(torch.ops.b200k.gemm_nt(a.to(DEV), b.to(DEV)), oracle.gemm_nt(a, b))
+    assert tb.device_status() == 0
+    assert L.lib().b200k_selftest_bounded_wait(None, 3000, stream) == L.ERR_NULL
+    assert L.lib().b200k_selftest_bounded_wait(status.data_ptr(), 0, stream) == L.ERR_BAD_SHAPE

@@ -253,3 +253,12 @@ def test_attention_bwd_golden_fixture():
     for g, r in zip(got, refs):
         assert g.shape == r.shape
         assert (g - r).abs().max().item() < 1e-4
+
+
+def test_bmm_oracle_is_aten_bmm_in_fp32():
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(3, 17, 24, generator=g).half()
+    b = torch.randn(3, 24, 9, generator=g).half()
+    ref = torch.stack([a[i].float() @ b[i].float() for i in range(3)])
+    assert torch.equal(oracle.bmm(a, b), torch.bmm(a.float(), b.float()))
+    assert torch.allclose(oracle.bmm(a, b), ref, rtol=1e-6, atol=1e-6)
