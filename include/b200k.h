@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define B200K_ABI_VERSION 2
+#define B200K_ABI_VERSION 3
 
 typedef enum b200k_status {
   B200K_OK = 0,
@@ -119,6 +119,14 @@ typedef struct b200k_gemm_args {
    * tiles go through one persistent launch.  batch 0 or 1 = a single problem (strides ignored). */
   int64_t batch;
   int64_t a_batch_stride, b_batch_stride, c_batch_stride;
+  /* Split-K: 0 = the library decides, 1 = never, 2 / 4 / 8 = that many CTAs (one thread-block
+   * cluster) share every 128-row output tile, each summing a slice of K; the fp32 partial tiles
+   * stay in the CTAs' shared memory and are added in rank order through distributed shared
+   * memory, so no scratch is needed and a result is reproducible bit for bit.  For problems whose
+   * whole tiles would leave most SMs idle (few output tiles, long K: weight gradients, narrow
+   * projections).  Not available with tile_m 256 or in b200k_gemm_nt_allgather. */
+  int32_t split_k;
+  int32_t reserved;
 } b200k_gemm_args;
 
 int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);

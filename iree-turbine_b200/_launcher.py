@@ -34,7 +34,7 @@ __all__ = [
 _PKG_DIR = Path(__file__).resolve().parent
 _LIB_NAME = "libb200kern.so"
 
-ABI_VERSION = 2  # B200K_ABI_VERSION this binding was written against
+ABI_VERSION = 3  # B200K_ABI_VERSION this binding was written against
 
 # Status codes (b200k_status).
 OK = 0
@@ -93,6 +93,8 @@ class GemmArgs(C.Structure):
         ("a_batch_stride", C.c_int64),
         ("b_batch_stride", C.c_int64),
         ("c_batch_stride", C.c_int64),
+        ("split_k", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

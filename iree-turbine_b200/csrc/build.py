@@ -22,8 +22,8 @@ LIB_NAME = "libb200kern.so"
 LIB_PATH = PKG / LIB_NAME
 BUILD_DIR = CSRC / "build"
 
-SOURCES = ["abi.cu", "gemm_sm100.cu", "attention_sm100.cu", "attention_tile_sm100.cu", "attention_bwd_sm100.cu", "decode_sm100.cu", "quant.cu", "selftest.cu"]
-HEADERS = ["common.cuh", "ptx.cuh", str(REPO / "include" / "b200k.h")]
+SOURCES = ["abi.cu", "gemm_sm100.cu", "gemm_splitk_sm100.cu", "attention_sm100.cu", "attention_tile_sm100.cu", "attention_bwd_sm100.cu", "decode_sm100.cu", "quant.cu", "selftest.cu"]
+HEADERS = ["common.cuh", "ptx.cuh", "gemm_common.cuh", str(REPO / "include" / "b200k.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

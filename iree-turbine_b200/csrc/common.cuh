@@ -16,6 +16,7 @@ enum : int32_t {
   kStatusDecodeBadPage = 4,
   kStatusDecodeLenClamped = 8,
   kStatusSelftestTimeout = 16,
+  kStatusGemmNoCluster = 32,  // split-K kernel found itself in a cluster of another size than asked for
 };
 
 // ---- host-side error plumbing (abi.cu) ----

@@ -16,151 +16,13 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "gemm_common.cuh"
 #include "ptx.cuh"
 
 namespace b200k {
 namespace {
 
-constexpr int kBM = 128;
-constexpr int kBKBytes = 128;
-constexpr int kGemmThreads = 192;
-constexpr int kGroupM = 16;  // m-tiles per rasterisation group (keeps one wave's operands L2-resident)
-
-enum GemmKind : int { kKindF16 = 0, kKindBF16 = 1, kKindE4M3 = 2 };
-
-struct GemmParams {
-  void* c;
-  const float* scale_a;
-  const float* scale_b;
-  int32_t* status;
-  int64_t ldc;
-  int32_t m, n;
-  int32_t tiles_m, tiles_n, num_kb;  // tiles_m counts MT * 128-row tiles
-  int32_t batch;                     // independent problems (tensor maps are 3-D: [batch][rows][k])
-  int64_t c_batch_stride;            // elements between the C matrices of consecutive problems
-  // Optional fused epilogue: y = act(acc * scale + bias[col]); bias == nullptr and act == 0 leave
-  // the plain path untouched.
-  const void* bias;
-  int32_t bias_dtype;  // B200K_F32 | B200K_F16 | B200K_BF16
-  int32_t act;         // B200K_ACT_*
-  // Operand storage (generic kernel only): a_mn = A is stored [K, M] (M contiguous), b_mn = B is
-  // stored [K, N] (N contiguous); 0 = the contraction dimension K is the contiguous one.
-  int32_t a_mn, b_mn;
-  int32_t vec_store_ok;
-  int32_t tma_store_ok;  // C is 16-byte aligned with a 16-byte-multiple row pitch: epilogue uses TMA stores
-  // Fused all-gather of a column shard: when num_peers > 0 every output tile is written with plain
-  // 16-byte stores into each peer's full matrix (peer-mapped memory) at column peer_col0.
-  int32_t num_peers;
-  int32_t peer_first;  // index of the first peer written (the rank after this one); own copy last
-  int64_t peer_ldc;
-  int64_t peer_col0;
-  void* peers[8];
-  void* peer_mc;  // NVSwitch multicast address of the matrix, or nullptr
-};
-
-template <int BN, int MT>
-struct GemmSmem {
-  static constexpr int kStages = MT == 2 ? 3 : (BN == 256 ? 4 : 6);
-  static constexpr int kABytes = MT * kBM * kBKBytes;
-  static constexpr int kBBytes = BN * kBKBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  // epilogue staging: per epilogue warp two 32-row x 128-byte buffers (TMA store source)
-  static constexpr int kStagingOffset = kStages * kStageBytes;
-  static constexpr int kStagingBytes = 4 * 2 * 32 * 128;
-  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
-  static constexpr int kNumBars = 2 * kStages + 4;
-  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
-  static constexpr int kDynamic = kTotal + 1024;  // slack for 1024-byte alignment of the tiles
-};
-
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int group_size = kGroupM * tiles_n;
-  const int group = t / group_size;
-  const int first_m = group * kGroupM;
-  const int gm = min(tiles_m - first_m, kGroupM);
-  const int r = t - group * group_size;
-  tm = first_m + r % gm;
-  tn = r / gm;
-}
-
-template <typename OutT>
-__device__ __forceinline__ OutT to_out(float v);
-template <>
-__device__ __forceinline__ float to_out<float>(float v) {
-  return v;
-}
-template <>
-__device__ __forceinline__ __half to_out<__half>(float v) {
-  return __float2half_rn(v);
-}
-template <>
-__device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) {
-  return __float2bfloat16_rn(v);
-}
-
-__device__ __forceinline__ float apply_act(float x, int act) {
-  switch (act) {
-    case B200K_ACT_RELU:
-      return fmaxf(x, 0.f);
-    case B200K_ACT_GELU:  // exact (erf) form, the default of aten::gelu
-      return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
-    case B200K_ACT_SILU:
-      return x / (1.f + __expf(-x));
-    default:
-      return x;
-  }
-}
-
-__device__ __forceinline__ float load_bias(const void* bias, int dtype, int col) {
-  if (dtype == B200K_F32) return __ldg(reinterpret_cast<const float*>(bias) + col);
-  if (dtype == B200K_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(bias) + col));
-  return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(bias) + col));
-}
-
-// Fused epilogue on N accumulator values of one row (columns col0 .. col0 + N - 1), in place:
-// r = act(r * scale + bias).  Every lane of a warp reads the same bias element (one broadcast
-// load per column).  Afterwards the caller's own scaling must be 1.
-template <int N>
-__device__ __forceinline__ void fused_epilogue(uint32_t (&r)[N], float scale, const void* bias, int bias_dtype, int act,
-                                               int col0, int n) {
-#pragma unroll
-  for (int j = 0; j < N; ++j) {
-    float x = __uint_as_float(r[j]) * scale;
-    if (bias != nullptr && col0 + j < n) x += load_bias(bias, bias_dtype, col0 + j);
-    r[j] = __float_as_uint(apply_act(x, act));
-  }
-}
-
-// Stores 32 consecutive columns of one output row.
-template <typename OutT>
-__device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t (&r)[32], float scale, int valid_cols,
-                                            bool vec_ok) {
-  if (valid_cols >= 32 && vec_ok) {
-    if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float4 v = make_float4(__uint_as_float(r[4 * i]) * scale, __uint_as_float(r[4 * i + 1]) * scale,
-                               __uint_as_float(r[4 * i + 2]) * scale, __uint_as_float(r[4 * i + 3]) * scale);
-        reinterpret_cast<float4*>(dst)[i] = v;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        union {
-          uint4 u;
-          OutT h[8];
-        } pk;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) pk.h[j] = to_out<OutT>(__uint_as_float(r[8 * i + j]) * scale);
-        reinterpret_cast<uint4*>(dst)[i] = pk.u;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < valid_cols) dst[i] = to_out<OutT>(__uint_as_float(r[i]) * scale);
-  }
-}
+using namespace gemm_detail;
 
 // GEN = false: both operands K-major (A [M, K], B [N, K]); the issue path is all compile-time
 // offsets.  GEN = true (16-bit types only): either operand may be MN-major, chosen at run time
@@ -699,9 +561,56 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   if (bm == 0) bm = 128;
   if (bm == 256 && bn != 256)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt: tile_m 256 requires tile_n 256");
+  const int k_per_stage = a.in_dtype == B200K_E4M3 ? 128 : 64;
+  const int64_t num_kb = (a.k + k_per_stage - 1) / k_per_stage;
+
+  // Split-K over a cluster (128-row tiles, gemm_splitk_sm100.cu): worth it when the whole tiles
+  // leave most SMs idle and K is long.  Estimated cycles = waves * k-blocks per CTA * cycles per
+  // k-block (operand delivery: 512 / 750 / 1250 for 128x128 / 128x256 / 256x256 tiles) + the part
+  // of the epilogue nothing overlaps; the split pays a partial-tile write and a reduction through
+  // peer shared memory instead of the plain epilogue.
+  if (a.split_k != 0 && a.split_k != 1 && a.split_k != 2 && a.split_k != 4 && a.split_k != 8)
+    return set_error(B200K_ERR_BAD_SHAPE, "gemm: split_k must be 0, 1, 2, 4 or 8");
+  int split = 1;
+  if (a.split_k > 1) {
+    if (peers.num > 0) return set_error(B200K_ERR_BAD_SHAPE, "gemm_nt_allgather: split_k is not supported");
+    if (a.tile_m == 256) return set_error(B200K_ERR_BAD_SHAPE, "gemm: split_k needs 128-row tiles (tile_m 0 or 128)");
+    if (num_kb < a.split_k) return set_error(B200K_ERR_BAD_SHAPE, "gemm: split_k exceeds the number of k-blocks");
+    bm = 128;
+    split = a.split_k;
+    if (splitk_resident_clusters(bn, split) == 0)
+      return set_error(B200K_ERR_UNSUPPORTED_ARCH, "gemm: clusters of %d CTAs cannot be launched", split);
+  } else if (a.split_k == 0 && peers.num == 0) {
+    auto cycles_kb = [](int tm, int tn) { return tm == 256 ? 1250.0 : (tn == 256 ? 750.0 : 512.0); };
+    auto tail = [](int tm, int tn) { return tm == 256 ? 6000.0 : (tn == 256 ? 3000.0 : 1500.0); };
+    const int64_t tiles0 = ((a.m + bm - 1) / bm) * ((a.n + bn - 1) / bn) * batch;
+    const int64_t waves0 = (tiles0 + sms - 1) / sms;
+    double best = static_cast<double>(waves0) * num_kb * cycles_kb(bm, bn) + tail(bm, bn);
+    best *= 0.9;  // a split has to win clearly
+    if (tiles0 * 2 <= sms && a.tile_m != 256) {
+      for (int tn = 128; tn <= 256; tn += 128) {
+        if (a.tile_n != 0 && a.tile_n != tn) continue;
+        if (tn == 256 && a.n <= 128) continue;
+        const int64_t tiles = ((a.m + 127) / 128) * ((a.n + tn - 1) / tn) * batch;
+        for (int s = 2; s <= 8; s *= 2) {
+          if (num_kb < 4 * s) continue;  // at least four k-blocks per slice
+          const int resident = splitk_resident_clusters(tn, s);
+          if (resident == 0) continue;
+          const int64_t waves = (tiles + resident - 1) / resident;
+          const int64_t per = (num_kb + s - 1) / s;
+          const double t = static_cast<double>(waves) * per * cycles_kb(128, tn) + 1.7 * tail(128, tn) + 150.0 * s;
+          if (t < best) {
+            best = t;
+            split = s;
+            bm = 128;
+            bn = tn;
+          }
+        }
+      }
+    }
+  }
   const int tiles_m = static_cast<int>((a.m + bm - 1) / bm);
   const int tiles_n = static_cast<int>((a.n + bn - 1) / bn);
-  const int k_per_stage = a.in_dtype == B200K_E4M3 ? 128 : 64;
 
   CUtensorMap ta, tb;
   {
@@ -740,7 +649,14 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   p.n = static_cast<int32_t>(a.n);
   p.tiles_m = tiles_m;
   p.tiles_n = tiles_n;
-  p.num_kb = static_cast<int32_t>((a.k + k_per_stage - 1) / k_per_stage);
+  p.num_kb = static_cast<int32_t>(num_kb);
+  p.kb_per_split = static_cast<int32_t>((num_kb + split - 1) / split);
+  // every slice must hold at least one k-block (an empty one would leave an accumulator unwritten)
+  while (split > 1 && static_cast<int64_t>(p.kb_per_split) * (split - 1) >= num_kb) {
+    split /= 2;
+    p.kb_per_split = static_cast<int32_t>((num_kb + split - 1) / split);
+  }
+  p.split = split;
   p.batch = static_cast<int32_t>(batch);
   p.c_batch_stride = batch > 1 ? a.c_batch_stride : 0;
   p.vec_store_ok = ((reinterpret_cast<uintptr_t>(a.c) & 15) == 0 && (a.ldc * out_es) % 16 == 0 &&
@@ -766,6 +682,10 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
   }
   const int64_t num_tiles = static_cast<int64_t>(tiles_m) * tiles_n * batch;
   if (num_tiles > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "gemm: too many tiles");
+  if (split > 1) {
+    if (num_tiles * split > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "gemm: too many tiles");
+    return launch_gemm_splitk(ta, tb, p, bn, a.in_dtype, a.out_dtype, stream);
+  }
   const int grid = static_cast<int>(num_tiles < sms ? num_tiles : sms);
   if (bm == 256) return dispatch_dtype<256, 2>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
   if (bn == 256) return dispatch_dtype<256, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);

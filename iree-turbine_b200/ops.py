@@ -104,8 +104,9 @@ def _gemm_out_dtype(in_dtype: torch.dtype, out_dtype) -> torch.dtype:
 
 def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: int = 0, tile_m: int = 0,
                  bias: Optional[Tensor] = None, activation: str = "none", a_km: bool = False,
-                 b_kn: bool = False) -> None:
-    """a is stored [M, K] ([K, M] with a_km); b is stored [N, K] ([K, N] with b_kn)."""
+                 b_kn: bool = False, split_k: int = 0) -> None:
+    """a is stored [M, K] ([K, M] with a_km); b is stored [N, K] ([K, N] with b_kn).  split_k: 0 = the
+    library decides, 1 = whole tiles only, 2 / 4 / 8 = CTAs per output tile."""
     a = _row_major_2d(a)
     b = _row_major_2d(b)
     args = L.GemmArgs()
@@ -121,6 +122,7 @@ def _launch_gemm(a: Tensor, b: Tensor, out: Tensor, scale_a, scale_b, tile_n: in
     args.status = _status_ptr(a.device)
     args.tile_n = tile_n
     args.tile_m = tile_m
+    args.split_k = split_k
     if activation not in L.ACTIVATION_CODES:
         raise ValueError(f"unknown activation {activation!r}; expected one of {sorted(L.ACTIVATION_CODES)}")
     args.activation = L.ACTIVATION_CODES[activation]

@@ -29,13 +29,13 @@ def test_every_declared_symbol_is_exported_and_bound(kernel_lib):
         assert hasattr(kernel_lib, name), f"{name} is declared in include/b200k.h but not exported"
         assert name in L.EXPORTED_SYMBOLS, f"{name} has no ctypes prototype"
     assert sorted(L.EXPORTED_SYMBOLS) == declared
-    assert kernel_lib.b200k_abi_version() == L.ABI_VERSION == 2
+    assert kernel_lib.b200k_abi_version() == L.ABI_VERSION == 3
 
 
 def test_struct_layouts_match_the_header():
     """Compiles a C probe against the header and compares sizeof / offsetof with ctypes."""
     fields = {
-        "b200k_gemm_args": (L.GemmArgs, ["a", "ldc", "in_dtype", "scale_a", "status", "tile_n"]),
+        "b200k_gemm_args": (L.GemmArgs, ["a", "ldc", "in_dtype", "scale_a", "status", "tile_n", "c_batch_stride", "split_k"]),
         "b200k_attention_args": (L.AttentionArgs, ["q", "batch", "head_dim", "q_stride_b", "o_stride_s", "dtype",
                                                    "scale", "status", "lse", "kernel"]),
         "b200k_decode_args": (L.DecodeArgs, ["q", "workspace_bytes", "num_seqs", "max_seq_len", "kv_batch_stride",

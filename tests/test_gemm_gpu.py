@@ -312,3 +312,106 @@ def test_bmm_block_of_ones_lands_in_the_right_problem():
     ref = torch.zeros(bsz, m, n)
     ref[4, 130:140, 300:310] = 32
     assert torch.equal(c, ref)
+
+
+# ---- split-K over a thread-block cluster ----
+def _run_split(a, b, out_dtype, tile_n, split_k, **kw):
+    m = a.size(1) if kw.get("a_km") else a.size(0)
+    n = b.size(1) if kw.get("b_kn") else b.size(0)
+    c = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    ops._launch_gemm(a.to(DEV), b.to(DEV), c, None, None, tile_n=tile_n, split_k=split_k, **kw)
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    return c
+
+
+@pytest.mark.parametrize("split_k", [2, 4, 8])
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("m,n,k,dtype,out_dtype", [
+    (128, 128, 512, torch.float16, torch.float32),
+    (256, 512, 4096, torch.float16, torch.float16),
+    (200, 300, 1000, torch.bfloat16, torch.bfloat16),     # ragged M, N and a K tail
+    (384, 136, 2056, torch.bfloat16, torch.float32),
+    (1, 8, 640, torch.float16, torch.float32),
+])
+def test_split_k_matches_oracle_and_is_reproducible(m, n, k, dtype, out_dtype, tile_n, split_k):
+    a, b = oracle.make_gemm_inputs(m, n, k, dtype, seed=21)
+    c = _run_split(a, b, out_dtype, tile_n, split_k)
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b))
+    assert torch.equal(c, _run_split(a, b, out_dtype, tile_n, split_k)), "split-K result depends on timing"
+
+
+def test_split_k_slices_that_do_not_divide_the_k_blocks():
+    """9 k-blocks over 4 and 8 CTAs: the library lowers the split until every slice has work."""
+    a, b = oracle.make_gemm_inputs(128, 256, 9 * 64, torch.float16, seed=22)
+    for s in (2, 4, 8):
+        oracle.assert_close_half(_run_split(a, b, torch.float32, 128, s), oracle.gemm_nt(a, b))
+
+
+@pytest.mark.parametrize("activation", ["none", "relu", "gelu", "silu"])
+@pytest.mark.parametrize("bias_dtype", [None, torch.float32, torch.bfloat16])
+def test_split_k_fused_bias_and_activation(activation, bias_dtype):
+    m, n, k = 200, 262, 2048      # N tail: the last chunk of a row is partly outside the matrix
+    a, w = oracle.make_gemm_inputs(m, n + 2, k, torch.bfloat16, seed=23)
+    a, w = a * 0.25, w[:n] * 0.25
+    bias = None if bias_dtype is None else torch.randn(n, generator=torch.Generator().manual_seed(24)).to(bias_dtype)
+    ref = oracle.linear_act(a, w, bias, activation)
+    for split_k, pitch in ((2, n + 2), (4, n + 1)):   # 16-byte-multiple pitch: vector stores + a ragged last chunk; odd pitch: scalar stores
+        c = torch.full((m, pitch), float("nan"), dtype=torch.float32, device=DEV)[:, :n]
+        ops._launch_gemm(a.to(DEV), w.to(DEV), c, None, None, tile_n=128, split_k=split_k,
+                         bias=None if bias is None else bias.to(DEV), activation=activation)
+        torch.cuda.synchronize()
+        assert tb.device_status() == 0
+        oracle.assert_close_half(c, ref)
+
+
+def test_split_k_fp8():
+    a8, b8, sa, sb = oracle.make_fp8_gemm_inputs(256, 384, 4096, seed=25)
+    ref = oracle.gemm_fp8_nt(a8, b8, sa, sb)
+    for split_k, tile_n in ((2, 128), (4, 256), (8, 128)):
+        c = torch.full((256, 384), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops._launch_gemm(a8.to(DEV), b8.to(DEV), c, sa.to(DEV), sb.to(DEV), tile_n=tile_n, split_k=split_k)
+        torch.cuda.synchronize()
+        assert tb.device_status() == 0
+        fro, mx = oracle.fp8_errors(c, ref)
+        assert fro < 3e-2, (split_k, fro, mx)
+
+
+@pytest.mark.parametrize("a_km,b_kn", [(True, False), (False, True), (True, True)])
+def test_split_k_with_transposed_storage(a_km, b_kn):
+    """The weight-gradient shape: few output tiles, K = the token count."""
+    m, n, k = 256, 384, 4096
+    g = torch.Generator().manual_seed(26)
+    a = (torch.randn((k, m) if a_km else (m, k), generator=g) * 0.5).half()
+    b = (torch.randn((k, n) if b_kn else (n, k), generator=g) * 0.5).half()
+    ref = oracle.gemm(a, b, a_km, not b_kn)
+    for split_k in (2, 8):
+        c = _run_split(a, b, torch.float32, 128, split_k, a_km=a_km, b_kn=b_kn)
+        oracle.assert_close_half(c, ref)
+
+
+def test_split_k_chosen_by_the_library_on_few_tiles_long_k():
+    """1024 x 1024 x 4096 has 64 tiles of 128 x 128 for 148 SMs; whatever the library picks, the result is the oracle's,
+    and the same bits on every call."""
+    a, b = oracle.make_gemm_inputs(1024, 1024, 4096, torch.float16, seed=27)
+    c = _run(a, b, torch.float16)
+    oracle.assert_close_half(c, oracle.gemm_nt(a, b))
+    assert torch.equal(c, _run(a, b, torch.float16))
+    # a batch of two narrow problems: four tiles in all
+    ab = torch.randn(2, 128, 8192, generator=torch.Generator().manual_seed(28)).half()
+    bb = torch.randn(2, 8192, 256, generator=torch.Generator().manual_seed(29)).half()
+    cb = torch.ops.b200k.bmm(ab.to(DEV), bb.to(DEV))
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    oracle.assert_close_half(cb, oracle.bmm(ab, bb))
+
+
+def test_split_k_argument_errors():
+    a = torch.zeros(128, 256, dtype=torch.float16, device=DEV)
+    c = torch.empty(128, 128, dtype=torch.float32, device=DEV)
+    with pytest.raises(RuntimeError, match="split_k must be"):
+        ops._launch_gemm(a, a, c, None, None, split_k=3)
+    with pytest.raises(RuntimeError, match="128-row tiles"):
+        ops._launch_gemm(a, a, c, None, None, tile_m=256, split_k=2)
+    with pytest.raises(RuntimeError, match="exceeds the number of k-blocks"):
+        ops._launch_gemm(a, a, c, None, None, split_k=8)
