@@ -99,7 +99,7 @@ class Workload:
 
     def release(self):
         for k in list(self.__dict__):
-            if isinstance(self.__dict__[k], torch.Tensor) or k in ("e2e", "fused", "host", "grads"):
+            if isinstance(self.__dict__[k], torch.Tensor) or k in ("e2e", "fused", "host", "grads", "sets", "used"):
                 del self.__dict__[k]
 
 
@@ -296,7 +296,15 @@ class GemmWL(Workload):
         self.dtype = "e4m3" if fp8 else "f16"
         out = "bf16" if fp8 else "f32"
         self.metric = f"GEMM TFLOP/s ({self.dtype} NT M=N=K={n}, fp32 accumulate, {out} out)"
-        self.needs_flush = (2 * n * n * (1 if fp8 else 2) + n * n * (2 if fp8 else 4)) < 200e6
+        # Operands smaller than L2 (the 2048^3 problem: 16.8 MB): the steps walk through enough
+        # operand sets that a set has left L2 before it is used again, and are launched back to back
+        # (no flush kernel in between, one CUDA-event pair around the K steps), which is how a chain
+        # of GEMMs runs; the kernel's programmatic dependent launch needs consecutive launches.
+        operand_bytes = 2 * n * n * (1 if fp8 else 2)
+        self.num_sets = 1 if fp8 or operand_bytes >= 200e6 else -(-320_000_000 // operand_bytes)
+        self.back_to_back = self.num_sets > 1
+        self.needs_flush = False
+        self.turn = 0
 
     def shard(self, world, rank):
         # fp8 GEMM: column-parallel over N (strong scaling).  f16 2048^3 is too small to shard:
@@ -311,7 +319,9 @@ class GemmWL(Workload):
 
     def config(self):
         cfg = {"workload": self.name, "m": self.n, "n": self.n, "k": self.n,
-               "l2": "L2 flushed between steps (256 MB write)" if self.needs_flush else "operands larger than L2"}
+               "l2": (f"{self.num_sets} operand sets used in turn ({self.num_sets * 2 * self.n * self.n * 2 / 1e6:.0f} MB "
+                      "between two uses of a set), launches back to back" if self.num_sets > 1
+                      else "operands larger than L2")}
         if self.sharded:
             how = {"shard_only": "column shards of C left in place (no exchange)",
                    "fused_gather": "all-gather of C fused into the GEMM epilogue (peer stores) + cross-rank barrier "
@@ -334,6 +344,10 @@ class GemmWL(Workload):
             self.b, self.sb = torch.ops.b200k.quantize_e4m3(b)
         else:
             self.a, self.b = a.half(), b.half()
+            self.sets = [(self.a, self.b)]
+            for _ in range(self.num_sets - 1):
+                self.sets.append((torch.randn(self.n, self.n, generator=g, device=dev).half(),
+                                  torch.randn(self.n, self.n, generator=g, device=dev).half()))
         del a, b
         self.col0 = 0
         if self.sharded:
@@ -357,7 +371,9 @@ class GemmWL(Workload):
         elif self.fp8:
             self.c = torch.ops.b200k.gemm_fp8_nt(self.a, self.b, self.sa, self.sb)
         else:
-            self.c = torch.ops.b200k.gemm_nt(self.a, self.b)
+            self.used = self.sets[self.turn % self.num_sets]
+            self.turn += 1
+            self.c = torch.ops.b200k.gemm_nt(*self.used)
 
     def units_per_step(self):
         return 2.0 * self.n ** 3 / (self.world if self.sharded else 1)
@@ -411,7 +427,10 @@ class GemmWL(Workload):
 
         rows = 128
         r0 = self.n - rows
-        a, b = self.a[r0:].cpu(), self.b.cpu()
+        if not self.fp8:
+            a, b = self.used[0][r0:].cpu(), self.used[1].cpu()  # the operand set of the last step
+        else:
+            a, b = self.a[r0:].cpu(), self.b.cpu()
         if not self.fp8:
             r = _close(self.c[r0:], oracle.gemm_nt(a, b))
             r["sample"] = f"last {rows} rows of C against oracle.gemm_nt"
@@ -672,13 +691,47 @@ def run_reference(wl: Workload, args) -> dict:
     }
 
 
-def timed_steps(step_fn, steps, warmup, flush_buf, stream):
-    """Runs warmup + steps; returns per-step milliseconds measured with CUDA events on `stream`."""
+def queued_launches(step_fn, steps):
+    """A callable that runs `steps` steps at the GPU's pace rather than the host's (a step of 17 us is
+    shorter than a Python call through the operator): the steps captured once in a CUDA graph and
+    replayed; if capture is refused, a plain loop queued behind a spin kernel.  Returns (run, how)."""
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(steps):
+                step_fn()
+        torch.cuda.synchronize()
+        return graph.replay, f"{steps} steps captured in one CUDA graph, replayed once"
+    except Exception as e:  # noqa: BLE001 - any capture failure falls back to the plain loop
+        torch.cuda.synchronize()
+        why = str(e).splitlines()[0][:80]
+
+        def run():
+            torch.cuda._sleep(int(4e6))  # ~2 ms: the launches below are all queued before it ends
+            for _ in range(steps):
+                step_fn()
+
+        return run, f"plain loop queued behind a spin kernel (graph capture refused: {why})"
+
+
+def timed_steps(step_fn, steps, warmup, flush_buf, stream, back_to_back=False):
+    """Runs warmup + steps; returns per-step milliseconds measured with CUDA events on `stream`.
+    back_to_back: nothing is put between the launches, one event pair brackets the K steps and every
+    step is given the mean."""
     for _ in range(warmup):
         if flush_buf is not None:
             flush_buf.fill_(1)
         step_fn()
     torch.cuda.synchronize()
+    if back_to_back and flush_buf is None:
+        run, how = queued_launches(step_fn, steps)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        run()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        timed_steps.how = how
+        return [e0.elapsed_time(e1) / steps] * steps
     evs = []
     for _ in range(steps):
         if flush_buf is not None:
@@ -748,7 +801,7 @@ def measure(wl: Workload, ctx: Ctx, steps: int, warmup: int, with_cpu: bool, sus
 
     ctx.barrier()
     t_begin = time.monotonic()
-    ms = timed_steps(wl.step, steps, warmup, flush, ctx.stream)
+    ms = timed_steps(wl.step, steps, warmup, flush, ctx.stream, getattr(wl, "back_to_back", False))
     ctx.barrier()
     clocks = ctx.sampler.window(t_begin, time.monotonic()) if ctx.sampler else None
     total_ms = ctx.max_over_ranks(sum(ms))
@@ -764,10 +817,19 @@ def measure(wl: Workload, ctx: Ctx, steps: int, warmup: int, with_cpu: bool, sus
         ctx.barrier()
         t_begin = time.monotonic()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(ctx.stream)
-        for _ in range(n):
-            wl.step()
-        e1.record(ctx.stream)
+        if getattr(wl, "back_to_back", False):
+            chunk = 100
+            run, _ = queued_launches(wl.step, chunk)
+            n = -(-n // chunk) * chunk
+            e0.record(ctx.stream)
+            for _ in range(n // chunk):
+                run()
+            e1.record(ctx.stream)
+        else:
+            e0.record(ctx.stream)
+            for _ in range(n):
+                wl.step()
+            e1.record(ctx.stream)
         ctx.barrier()
         loop_ms = ctx.max_over_ranks(e0.elapsed_time(e1))
         c2 = ctx.sampler.window(t_begin, time.monotonic()) if ctx.sampler else None
@@ -815,6 +877,8 @@ def measure(wl: Workload, ctx: Ctx, steps: int, warmup: int, with_cpu: bool, sus
         "gpu_launches": wl.launches_per_step * steps,
         "device_status": status,
     }
+    if getattr(wl, "back_to_back", False):
+        out["config"]["timed_region"] = getattr(timed_steps, "how", "") + "; one CUDA-event pair around the K steps"
     if wl.scaling == "weak" and world > 1:
         out["note"] = "independent replicas: value = N x one rank's units / max time"
     if sustained:

@@ -80,6 +80,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched no global memory, so under a programmatic dependent launch it ran
+  // while the previous kernel of the stream was still finishing.  From here on operands are read
+  // and C is written: wait for that kernel, then let the next one start its own set-up early (it
+  // cannot share an SM with a CTA of this grid, and waits here in turn).
+  grid_dependency_wait();
+  grid_dependency_trigger();
 
   const int tiles_per_problem = p.tiles_m * p.tiles_n;
   const int num_tiles = tiles_per_problem * p.batch;  // tile t: problem t / tiles_per_problem
@@ -410,8 +416,19 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
   static bool configured[64] = {};  // per instantiation and device ordinal
   int rc = ensure_dynamic_smem(kfn, S::kDynamic, configured, "cudaFuncSetAttribute(gemm smem)");
   if (rc) return rc;
-  kfn<<<grid, kGemmThreads, S::kDynamic, stream>>>(ta, tb, tc, p);
-  return check_cuda(cudaGetLastError(), "gemm_nt_kernel launch");
+  // Programmatic dependent launch: barrier set-up and the tensor-memory allocation of this kernel
+  // overlap the tail of whatever runs before it in the stream (see grid_dependency_wait in the kernel).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kDynamic;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kfn, ta, tb, tc, p), "gemm_nt_kernel launch");
 }
 
 template <int BN, int MT>
@@ -566,9 +583,10 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
 
   // Split-K over a cluster (128-row tiles, gemm_splitk_sm100.cu): worth it when the whole tiles
   // leave most SMs idle and K is long.  Estimated cycles = waves * k-blocks per CTA * cycles per
-  // k-block (operand delivery: 512 / 750 / 1250 for 128x128 / 128x256 / 256x256 tiles) + the part
-  // of the epilogue nothing overlaps; the split pays a partial-tile write and a reduction through
-  // peer shared memory instead of the plain epilogue.
+  // k-block (measured with operands from HBM: 568 / 750 / 1250 for 128x128 / 128x256 / 256x256
+  // tiles) + the part of the epilogue nothing overlaps; a split adds the cluster launch, two
+  // cluster barriers, the partial-tile write and the reduction through peer shared memory
+  // (measured: about 4 to 6 us more than an un-split launch of the same k-blocks).
   if (a.split_k != 0 && a.split_k != 1 && a.split_k != 2 && a.split_k != 4 && a.split_k != 8)
     return set_error(B200K_ERR_BAD_SHAPE, "gemm: split_k must be 0, 1, 2, 4 or 8");
   int split = 1;
@@ -581,7 +599,8 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
     if (splitk_resident_clusters(bn, split) == 0)
       return set_error(B200K_ERR_UNSUPPORTED_ARCH, "gemm: clusters of %d CTAs cannot be launched", split);
   } else if (a.split_k == 0 && peers.num == 0) {
-    auto cycles_kb = [](int tm, int tn) { return tm == 256 ? 1250.0 : (tn == 256 ? 750.0 : 512.0); };
+    auto cycles_kb = [](int tm, int tn) { return tm == 256 ? 1250.0 : (tn == 256 ? 750.0 : 568.0); };
+    auto split_cost = [](int tn, int s) { return tn == 256 ? 10000.0 + 2000.0 * s : 8000.0 + 1200.0 * s; };
     auto tail = [](int tm, int tn) { return tm == 256 ? 6000.0 : (tn == 256 ? 3000.0 : 1500.0); };
     const int64_t tiles0 = ((a.m + bm - 1) / bm) * ((a.n + bn - 1) / bn) * batch;
     const int64_t waves0 = (tiles0 + sms - 1) / sms;
@@ -598,7 +617,7 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
           if (resident == 0) continue;
           const int64_t waves = (tiles + resident - 1) / resident;
           const int64_t per = (num_kb + s - 1) / s;
-          const double t = static_cast<double>(waves) * per * cycles_kb(128, tn) + 1.7 * tail(128, tn) + 150.0 * s;
+          const double t = static_cast<double>(waves) * per * cycles_kb(128, tn) + tail(128, tn) + split_cost(tn, s);
           if (t < best) {
             best = t;
             split = s;

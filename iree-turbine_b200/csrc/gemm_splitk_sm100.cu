@@ -25,6 +25,104 @@ using namespace gemm_detail;
 __device__ const float kUnitScale = 1.0f;
 
 
+template <typename OutT>
+struct ReduceCtx {
+  const GemmParams& p;
+  uint32_t smem_base;  // shared-memory address of this CTA's partial tile
+  int rank, tm, tn, bz;
+};
+
+// CTA `rank` of a cluster of SPLIT sums rows [rank * 128 / SPLIT, (rank + 1) * 128 / SPLIT) of the
+// tile over all partial tiles, in rank order, and stores them.  A thread takes four 16-byte chunks
+// at a time and issues all their peer loads before the first add, so the latency of distributed
+// shared memory is paid once per batch, not once per chunk.
+template <int BN, int KIND, typename OutT, int EPI, int SPLIT>
+__device__ __forceinline__ void reduce_band(const ReduceCtx<OutT>& c) {
+  const GemmParams& p = c.p;
+  constexpr int kChunksPerRow = BN / 4;
+  constexpr int kRows = kBM / SPLIT;
+  constexpr int kUnits = kRows * kChunksPerRow;
+  constexpr int kBatch = 4;
+  float scale = 1.0f;
+  if constexpr (KIND == kKindE4M3) {
+    const float* sa = p.scale_a ? p.scale_a : &kUnitScale;
+    const float* sb = p.scale_b ? p.scale_b : &kUnitScale;
+    scale = *sa * *sb;
+  }
+  OutT* cbase = reinterpret_cast<OutT*>(p.c) + c.bz * p.c_batch_stride;
+  for (int u0 = threadIdx.x; u0 < kUnits; u0 += kGemmThreads * kBatch) {
+    float4 sum[kBatch];
+    uint32_t off[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int u = min(u0 + b * kGemmThreads, kUnits - 1);  // past the end: re-read the last unit, not stored
+      const int lr = c.rank * kRows + u / kChunksPerRow;
+      const int ch = u % kChunksPerRow;
+      off[b] = static_cast<uint32_t>(lr * (BN * 4) + ((ch ^ (lr & 7)) << 4));
+      sum[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float4 v[SPLIT][kBatch];
+#pragma unroll
+    for (int s = 0; s < SPLIT; ++s)
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+        v[s][b] = ld_shared_cluster_f32x4(cluster_map_shared(c.smem_base + off[b], static_cast<uint32_t>(s)));
+#pragma unroll
+    for (int s = 0; s < SPLIT; ++s)
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        sum[b].x += v[s][b].x;
+        sum[b].y += v[s][b].y;
+        sum[b].z += v[s][b].z;
+        sum[b].w += v[s][b].w;
+      }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int u = u0 + b * kGemmThreads;
+      if (u >= kUnits) break;
+      const int lr = c.rank * kRows + u / kChunksPerRow;
+      const int ch = u % kChunksPerRow;
+      const int row = c.tm * kBM + lr;
+      const int col = c.tn * BN + ch * 4;
+      if (row >= p.m || col >= p.n) continue;
+      uint32_t r[4] = {__float_as_uint(sum[b].x), __float_as_uint(sum[b].y), __float_as_uint(sum[b].z),
+                       __float_as_uint(sum[b].w)};
+      if constexpr (EPI == 2) {
+        // the bias index is clamped, not predicated: every load is in bounds whatever the compiler
+        // does with its order (columns past n are not stored)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          r[j] = __float_as_uint(apply_act(
+              __uint_as_float(r[j]) * scale + load_bias(p.bias, p.bias_dtype, min(col + j, p.n - 1)), p.act));
+      } else if constexpr (EPI == 1) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] = __float_as_uint(apply_act(__uint_as_float(r[j]) * scale, p.act));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * scale);
+      }
+      OutT* dst = cbase + static_cast<int64_t>(row) * p.ldc + col;
+      if (col + 4 <= p.n && p.vec_store_ok) {
+        if constexpr (sizeof(OutT) == 4) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(r[0], r[1], r[2], r[3]);
+        } else {
+          union {
+            uint2 u2;
+            OutT e[4];
+          } pk;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[j]));
+          *reinterpret_cast<uint2*>(dst) = pk.u2;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (col + j < p.n) dst[j] = to_out<OutT>(__uint_as_float(r[j]));
+      }
+    }
+  }
+}
+
 // EPI: 0 = plain store, 1 = activation only, 2 = bias (+ activation).  Separate instantiations, so
 // the plain kernel carries no epilogue code and the bias pointer is never tested at run time: the
 // activation-only kernel has no bias loads at all (with a run-time null test the compiler was seen
@@ -193,66 +291,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const bool cluster_ok = cluster_num_ctas() == static_cast<uint32_t>(p.split);
   if (!cluster_ok && threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusGemmNoCluster);
   if (cluster_ok) {
-    float scale = 1.0f;
-    if constexpr (KIND == kKindE4M3) {
-      const float* sa = p.scale_a ? p.scale_a : &kUnitScale;
-      const float* sb = p.scale_b ? p.scale_b : &kUnitScale;
-      scale = *sa * *sb;
-    }
-    OutT* cbase = reinterpret_cast<OutT*>(p.c) + bz * p.c_batch_stride;
-    constexpr int kChunksPerRow = BN / 4;
-    const int rows_per = kBM / p.split;
-    const int units = rows_per * kChunksPerRow;
-    const uint32_t smem_base = smem_u32(smem);
-    for (int u = threadIdx.x; u < units; u += kGemmThreads) {
-      const int lr = rank * rows_per + u / kChunksPerRow;
-      const int ch = u % kChunksPerRow;
-      const uint32_t off = static_cast<uint32_t>(lr * (BN * 4) + ((ch ^ (lr & 7)) << 4));
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int s = 0; s < p.split; ++s) {
-        const float4 v = ld_shared_cluster_f32x4(cluster_map_shared(smem_base + off, static_cast<uint32_t>(s)));
-        sum.x += v.x;
-        sum.y += v.y;
-        sum.z += v.z;
-        sum.w += v.w;
-      }
-      const int row = tm * kBM + lr;
-      const int col = tn * BN + ch * 4;
-      if (row >= p.m || col >= p.n) continue;
-      uint32_t r[4] = {__float_as_uint(sum.x), __float_as_uint(sum.y), __float_as_uint(sum.z), __float_as_uint(sum.w)};
-      if constexpr (EPI == 2) {
-        // the bias index is clamped, not predicated: every load is in bounds whatever the compiler
-        // does with its order (columns past n are not stored)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          r[j] = __float_as_uint(apply_act(
-              __uint_as_float(r[j]) * scale + load_bias(p.bias, p.bias_dtype, min(col + j, p.n - 1)), p.act));
-      } else if constexpr (EPI == 1) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) r[j] = __float_as_uint(apply_act(__uint_as_float(r[j]) * scale, p.act));
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * scale);
-      }
-      OutT* dst = cbase + static_cast<int64_t>(row) * p.ldc + col;
-      if (col + 4 <= p.n && p.vec_store_ok) {
-        if constexpr (sizeof(OutT) == 4) {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(r[0], r[1], r[2], r[3]);
-        } else {
-          union {
-            uint2 u2;
-            OutT e[4];
-          } pk;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) pk.e[j] = to_out<OutT>(__uint_as_float(r[j]));
-          *reinterpret_cast<uint2*>(dst) = pk.u2;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (col + j < p.n) dst[j] = to_out<OutT>(__uint_as_float(r[j]));
-      }
-    }
+    const ReduceCtx<OutT> ctx{p, smem_u32(smem), rank, tm, tn, bz};
+    if (p.split == 2)
+      reduce_band<BN, KIND, OutT, EPI, 2>(ctx);
+    else if (p.split == 4)
+      reduce_band<BN, KIND, OutT, EPI, 4>(ctx);
+    else
+      reduce_band<BN, KIND, OutT, EPI, 8>(ctx);
   }
   cluster_sync_all();  // no CTA leaves (and frees its shared memory) while a peer still reads it
 

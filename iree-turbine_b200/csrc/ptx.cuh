@@ -37,6 +37,18 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---------------------------------------------------------------------------------------
+// programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may start while its predecessor in the stream is still running.  grid_dependency_wait
+// blocks until the predecessor has completed and its writes are visible (a no-op for a normal
+// launch); grid_dependency_trigger lets the successor start as soon as every CTA of this grid has
+// called it or exited.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------
 // thread-block clusters: rank, the hardware cluster barrier, reads of a peer CTA's shared memory
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {

@@ -409,9 +409,9 @@ def test_split_k_chosen_by_the_library_on_few_tiles_long_k():
 def test_split_k_argument_errors():
     a = torch.zeros(128, 256, dtype=torch.float16, device=DEV)
     c = torch.empty(128, 128, dtype=torch.float32, device=DEV)
-    with pytest.raises(RuntimeError, match="split_k must be"):
+    with pytest.raises(ValueError, match="split_k must be"):
         ops._launch_gemm(a, a, c, None, None, split_k=3)
-    with pytest.raises(RuntimeError, match="128-row tiles"):
+    with pytest.raises(ValueError, match="128-row tiles"):
         ops._launch_gemm(a, a, c, None, None, tile_m=256, split_k=2)
-    with pytest.raises(RuntimeError, match="exceeds the number of k-blocks"):
+    with pytest.raises(ValueError, match="exceeds the number of k-blocks"):
         ops._launch_gemm(a, a, c, None, None, split_k=8)
