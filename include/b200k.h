@@ -68,7 +68,10 @@ const char* b200k_status_string(int status);
  * Device status word.  Kernels that wait on barriers bound every wait; when one gives up the
  * kernel ORs a non-zero code into this word and exits cleanly.  The word lives in device
  * memory owned by the caller (4 bytes, zero-initialised by the caller).  Passing NULL in the
- * args structs is allowed; the code is then dropped.
+ * args structs is allowed; the code is then dropped.  Bits: 0 GEMM wait gave up, 1 attention
+ * forward wait gave up, 2 block-table entry outside the pool, 3 a seq_lens entry was cut to
+ * max_seq_len, 4 the bounded-wait self-test, 5 a split-K GEMM found itself in a cluster of another
+ * size than it was launched for (nothing written), 6 attention backward wait gave up.
  */
 
 /* ---- GEMM:  C[M,N] = A[M,K] * B[N,K]^T  ------------------------------------------- */
@@ -83,6 +86,10 @@ const char* b200k_status_string(int status);
  * lda / ldb / ldc are row strides in ELEMENTS.  A, B: 16-byte aligned base, row stride a
  * multiple of 16 bytes.  C: base aligned to 16 bytes, ldc * sizeof(out) a multiple of 16.
  * K tails, M tails and N tails are handled (out-of-range operand elements read as zero).
+ *
+ * The kernel is launched as a programmatic dependent launch: its barrier set-up and tensor-memory
+ * allocation may overlap the end of the previous kernel of the stream, and it waits for that
+ * kernel before reading an operand or writing C, so the caller sees plain stream order.
  */
 enum { B200K_ACT_NONE = 0, B200K_ACT_RELU = 1, B200K_ACT_GELU = 2 /* erf form */, B200K_ACT_SILU = 3 };
 
@@ -265,7 +272,7 @@ int b200k_attention_bwd(const b200k_attention_bwd_args* args, void* stream);
  * no visible key yields zeros.  k_cache / v_cache: [num_pages, kv_heads, page_size, head_dim] with
  * contiguous rows, page_size in {16, 32, 64, 128}, head_dim 128 or 64.  Whole pages are fetched, so the rows of a
  * sequence's last page past seq_lens[b] must hold finite values (they are masked, but 0 * NaN is
- * NaN).  A block-table entry outside the pool reads as zeros and sets status bit 4.
+ * NaN).  A block-table entry outside the pool reads as zeros and sets status bit 2 (value 4).
  * The reference has no call site for this; its layout is the decode path's.
  */
 typedef struct b200k_paged_attention_args {
@@ -389,7 +396,7 @@ int b200k_paged_gather(const void* cache, const int32_t* block_table, const int3
  * for t in [0, new_tokens), for K and V alike.  k_new / v_new: [num_seqs, new_tokens, kv_heads,
  * head_dim] contiguous; caches and block table as in b200k_decode_args (paged form).  The address
  * function is the decode kernel's.  A row whose block-table entry is negative, outside the pool
- * or beyond the table is not written; B200K status bit 4 is OR-ed into *status (optional).
+ * or beyond the table is not written; status bit 2 (value 4) is OR-ed into *status (optional).
  */
 int b200k_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache, const int32_t* block_table,
                     const int32_t* positions, int32_t num_seqs, int32_t new_tokens, int32_t kv_heads, int32_t head_dim,
