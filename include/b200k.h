@@ -143,8 +143,10 @@ int b200k_gemm_nt(const b200k_gemm_args* args, void* stream);
  * GEMM when it is sharded over N across the GPUs of one box; no counterpart in the reference,
  * which has no collective call site).  The rank computes C[:, col_offset : col_offset + n] from
  * its rows of B and writes every tile directly into the FULL matrix of each rank listed in
- * peer_c (its own included), with plain 16-byte stores to peer-mapped memory: the transfer
- * overlaps the math tile by tile and no staging copy or separate collective is needed.
+ * peer_c (its own included) through peer-mapped memory: every staged piece of a tile (32 rows x
+ * 128 bytes) leaves as one bulk tensor store per rank (plain_stores: as 16-byte stores; multicast_c:
+ * as one multimem store).  The transfer overlaps the math tile by tile and no staging copy or
+ * separate collective is needed.  Only stores cross to other GPUs; nothing is loaded from a peer.
  *
  *   gemm        the local problem (a, b, m, n = shard width, k, lda, ldb, dtypes, scales);
  *               gemm.c and gemm.ldc are ignored
@@ -165,7 +167,11 @@ typedef struct b200k_gemm_allgather_args {
   int64_t col_offset;
   void* multicast_c;   /* optional: the NVSwitch multicast address of the same matrix (one
                           multimem.st then reaches every rank, the switch replicates it); NULL =
-                          one plain store per peer */
+                          one store per peer */
+  int32_t plain_stores; /* 0: every staged 32-row x 128-byte piece goes to each rank as one bulk tensor
+                           store (TMA) through a tensor map over that rank's matrix; != 0: as 16-byte
+                           stores issued by the epilogue warps.  Ignored with multicast_c. */
+  int32_t reserved;
 } b200k_gemm_allgather_args;
 
 int b200k_gemm_nt_allgather(const b200k_gemm_allgather_args* args, void* stream);

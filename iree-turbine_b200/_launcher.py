@@ -107,6 +107,8 @@ class GemmAllGatherArgs(C.Structure):
         ("peer_ldc", C.c_int64),
         ("col_offset", C.c_int64),
         ("multicast_c", C.c_void_p),
+        ("plain_stores", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

@@ -45,6 +45,13 @@ struct GemmParams {
   int64_t peer_col0;
   void* peers[8];
   void* peer_mc;  // NVSwitch multicast address of the matrix, or nullptr
+  int32_t peer_tma;  // the pieces go out as bulk tensor stores through PeerMaps (one per rank)
+};
+
+// Tensor maps over this rank's column shard inside every rank's full matrix (fused all-gather):
+// map i covers columns [col0, col0 + n) of rank i's matrix, so a store is clipped at the shard's edge.
+struct PeerMaps {
+  CUtensorMap m[8];
 };
 
 template <int BN, int MT>

@@ -33,7 +33,8 @@ using namespace gemm_detail;
 template <int BN, int MT, int KIND, typename OutT, bool GEN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                   const __grid_constant__ CUtensorMap tmap_c, const GemmParams p,
+                   const __grid_constant__ PeerMaps peer_maps) {
   using S = GemmSmem<BN, MT>;
   constexpr int kElemsPerStage = (KIND == kKindE4M3) ? 128 : 64;  // K elements in 128 bytes
   constexpr uint32_t kFmt = (KIND == kKindBF16) ? kFmtBF16 : (KIND == kKindF16 ? kFmtF16 : kFmtE4M3);
@@ -229,7 +230,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int row = row0 + lane;
         const uint32_t taddr =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (MT == 1 ? acc * BN : h * BN);
-        if (p.num_peers > 0) {
+        if (p.num_peers > 0 && !p.peer_tma) {
           // Column shard written straight into every rank's full C (own copy included): registers ->
           // swizzled staging buffer -> each store instruction writes four full 128-byte row segments
           // to one peer, so the NVLink traffic is made of whole lines.
@@ -306,10 +307,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               }
             }
           }
-        } else if (p.tma_store_ok) {
+        } else if (p.tma_store_ok || p.peer_tma) {
           // 128 bytes of each of this warp's 32 rows per step: registers -> swizzled staging
           // buffer -> one TMA store (full 128-byte lines, clipped at the matrix edge by the
           // tensor map).  Two buffers per warp; a buffer is reused once its store has been read.
+          // Fused all-gather: the same piece goes out once per rank, through that rank's map, as
+          // bulk stores to peer-mapped memory; the copy engine of the SM moves the data while the
+          // warp prepares the next piece.
           constexpr int kCols = 128 / static_cast<int>(sizeof(OutT));
 #pragma unroll 1
           for (int c = 0; c < BN / kCols; ++c) {
@@ -358,7 +362,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&tmap_c, buf, tn * BN + c * kCols, row0, bz);
+              if (p.num_peers > 0) {
+                int pe = p.peer_first;
+                for (int i = 0; i < p.num_peers; ++i) {
+                  tma_store_2d(&peer_maps.m[pe], buf, tn * BN + c * kCols, row0);
+                  pe = pe + 1 == p.num_peers ? 0 : pe + 1;
+                }
+              } else {
+                tma_store_3d(&tmap_c, buf, tn * BN + c * kCols, row0, bz);
+              }
               tma_store_commit();
             }
             ++stg_count;
@@ -409,8 +421,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }
 
 template <int BN, int MT, int KIND, typename OutT, bool GEN = false>
-int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
-               cudaStream_t stream) {
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+               const PeerMaps& pm, int grid, cudaStream_t stream) {
   using S = GemmSmem<BN, MT>;
   auto kfn = gemm_nt_kernel<BN, MT, KIND, OutT, GEN>;
   static bool configured[64] = {};  // per instantiation and device ordinal
@@ -428,36 +440,36 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, kfn, ta, tb, tc, p), "gemm_nt_kernel launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, kfn, ta, tb, tc, p, pm), "gemm_nt_kernel launch");
 }
 
 template <int BN, int MT>
 int dispatch_dtype(int in_dtype, int out_dtype, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                   const GemmParams& p, int grid, cudaStream_t stream) {
+                   const GemmParams& p, const PeerMaps& pm, int grid, cudaStream_t stream) {
   if (p.a_mn || p.b_mn) {  // generic operand storage: 16-bit types
     if (in_dtype == B200K_F16 && out_dtype == B200K_F32)
-      return launch_one<BN, MT, kKindF16, float, true>(ta, tb, tc, p, grid, stream);
+      return launch_one<BN, MT, kKindF16, float, true>(ta, tb, tc, p, pm, grid, stream);
     if (in_dtype == B200K_F16 && out_dtype == B200K_F16)
-      return launch_one<BN, MT, kKindF16, __half, true>(ta, tb, tc, p, grid, stream);
+      return launch_one<BN, MT, kKindF16, __half, true>(ta, tb, tc, p, pm, grid, stream);
     if (in_dtype == B200K_BF16 && out_dtype == B200K_F32)
-      return launch_one<BN, MT, kKindBF16, float, true>(ta, tb, tc, p, grid, stream);
+      return launch_one<BN, MT, kKindBF16, float, true>(ta, tb, tc, p, pm, grid, stream);
     if (in_dtype == B200K_BF16 && out_dtype == B200K_BF16)
-      return launch_one<BN, MT, kKindBF16, __nv_bfloat16, true>(ta, tb, tc, p, grid, stream);
+      return launch_one<BN, MT, kKindBF16, __nv_bfloat16, true>(ta, tb, tc, p, pm, grid, stream);
     return set_error(B200K_ERR_BAD_DTYPE, "gemm: operands stored [K, M] / [K, N] need F16 or BF16 (in=%d out=%d)",
                      in_dtype, out_dtype);
   }
   if (in_dtype == B200K_F16 && out_dtype == B200K_F32)
-    return launch_one<BN, MT, kKindF16, float>(ta, tb, tc, p, grid, stream);
+    return launch_one<BN, MT, kKindF16, float>(ta, tb, tc, p, pm, grid, stream);
   if (in_dtype == B200K_F16 && out_dtype == B200K_F16)
-    return launch_one<BN, MT, kKindF16, __half>(ta, tb, tc, p, grid, stream);
+    return launch_one<BN, MT, kKindF16, __half>(ta, tb, tc, p, pm, grid, stream);
   if (in_dtype == B200K_BF16 && out_dtype == B200K_F32)
-    return launch_one<BN, MT, kKindBF16, float>(ta, tb, tc, p, grid, stream);
+    return launch_one<BN, MT, kKindBF16, float>(ta, tb, tc, p, pm, grid, stream);
   if (in_dtype == B200K_BF16 && out_dtype == B200K_BF16)
-    return launch_one<BN, MT, kKindBF16, __nv_bfloat16>(ta, tb, tc, p, grid, stream);
+    return launch_one<BN, MT, kKindBF16, __nv_bfloat16>(ta, tb, tc, p, pm, grid, stream);
   if (in_dtype == B200K_E4M3 && out_dtype == B200K_BF16)
-    return launch_one<BN, MT, kKindE4M3, __nv_bfloat16>(ta, tb, tc, p, grid, stream);
+    return launch_one<BN, MT, kKindE4M3, __nv_bfloat16>(ta, tb, tc, p, pm, grid, stream);
   if (in_dtype == B200K_E4M3 && out_dtype == B200K_F32)
-    return launch_one<BN, MT, kKindE4M3, float>(ta, tb, tc, p, grid, stream);
+    return launch_one<BN, MT, kKindE4M3, float>(ta, tb, tc, p, pm, grid, stream);
   return set_error(B200K_ERR_BAD_DTYPE, "gemm_nt: unsupported dtype pair in=%d out=%d", in_dtype, out_dtype);
 }
 
@@ -469,6 +481,7 @@ struct PeerTargets {
   int first = 0;
   void* c[8] = {};
   void* mc = nullptr;
+  bool plain = false;  // 16-byte stores from the epilogue warps instead of bulk tensor stores
   int64_t ldc = 0;
   int64_t col0 = 0;
 };
@@ -497,6 +510,7 @@ int launch_gemm_nt_allgather(const b200k_gemm_allgather_args& g, cudaStream_t st
   t.num = g.num_peers;
   t.first = (g.self_index + 1) % g.num_peers;
   t.mc = g.multicast_c;
+  t.plain = g.plain_stores != 0;
   t.ldc = g.peer_ldc;
   t.col0 = g.col_offset;
   for (int i = 0; i < g.num_peers; ++i) {
@@ -713,6 +727,23 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
     rc = encode_tmap(&tc, a.out_dtype, 3, a.c, dims, strides, box);
     if (rc) return rc;
   }
+  // Fused all-gather by bulk tensor stores: one map per rank over this rank's columns of that
+  // rank's matrix (validated above: bases, column offset and row pitch are multiples of 16 bytes).
+  static const PeerMaps kNoPeerMaps = {};
+  PeerMaps peer_maps;
+  p.peer_tma = (peers.num > 0 && peers.mc == nullptr && !peers.plain) ? 1 : 0;
+  if (p.peer_tma) {
+    memset(&peer_maps, 0, sizeof(peer_maps));
+    for (int i = 0; i < peers.num; ++i) {
+      uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m)};
+      uint64_t strides[1] = {static_cast<uint64_t>(peers.ldc) * out_es};
+      uint32_t box[2] = {static_cast<uint32_t>(128 / out_es), 32u};
+      void* base = static_cast<uint8_t*>(peers.c[i]) + peers.col0 * static_cast<int64_t>(out_es);
+      rc = encode_tmap(&peer_maps.m[i], a.out_dtype, 2, base, dims, strides, box);
+      if (rc) return rc;
+    }
+  }
+  const PeerMaps& pm = p.peer_tma ? peer_maps : kNoPeerMaps;
   const int64_t num_tiles = static_cast<int64_t>(tiles_m) * tiles_n * batch;
   if (num_tiles > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "gemm: too many tiles");
   if (split > 1) {
@@ -720,9 +751,9 @@ int launch_gemm_impl(const b200k_gemm_args& a, const PeerTargets& peers, cudaStr
     return launch_gemm_splitk(ta, tb, p, bn, a.in_dtype, a.out_dtype, stream);
   }
   const int grid = static_cast<int>(num_tiles < sms ? num_tiles : sms);
-  if (bm == 256) return dispatch_dtype<256, 2>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
-  if (bn == 256) return dispatch_dtype<256, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
-  return dispatch_dtype<128, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, grid, stream);
+  if (bm == 256) return dispatch_dtype<256, 2>(a.in_dtype, a.out_dtype, ta, tb, tc, p, pm, grid, stream);
+  if (bn == 256) return dispatch_dtype<256, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, pm, grid, stream);
+  return dispatch_dtype<128, 1>(a.in_dtype, a.out_dtype, ta, tb, tc, p, pm, grid, stream);
 }
 }  // namespace
 

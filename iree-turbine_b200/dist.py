@@ -119,10 +119,12 @@ class FusedColumnParallelGemm:
     """
 
     def __init__(self, m: int, n: int, out_dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None,
-                 multicast: bool = False):
+                 multicast: bool = False, plain_stores: bool = False):
         """``multicast``: store each piece once to the NVSwitch multicast address of the result matrix
         (``multimem.st``; the switch replicates it to every rank) instead of once per peer.  Needs
-        multicast support in the symmetric-memory allocation; raises if it is missing."""
+        multicast support in the symmetric-memory allocation; raises if it is missing.
+        ``plain_stores``: send the pieces with 16-byte stores from the epilogue warps instead of bulk
+        tensor stores (same bits; the slower of the two per-peer forms)."""
         import torch.distributed._symmetric_memory as symm_mem
 
         self.group = group if group is not None else dist.group.WORLD
@@ -135,6 +137,7 @@ class FusedColumnParallelGemm:
         self.bufs = [symm_mem.empty((m, n), dtype=out_dtype, device=dev) for _ in range(2)]
         self.handles = [symm_mem.rendezvous(c, self.group) for c in self.bufs]
         self.multicast = bool(multicast)
+        self.plain_stores = bool(plain_stores)
         if self.multicast and any(int(getattr(h, "multicast_ptr", 0) or 0) == 0 for h in self.handles):
             raise RuntimeError("FusedColumnParallelGemm: this symmetric-memory allocation has no multicast address")
         self.turn = ResultTurn(2)
@@ -170,6 +173,7 @@ class FusedColumnParallelGemm:
         g.num_peers = self.world
         g.self_index = self.rank
         g.multicast_c = int(self.handles[idx].multicast_ptr) if self.multicast else None
+        g.plain_stores = int(self.plain_stores)
         g.peer_ldc = c.stride(0)
         g.col_offset = lo
         stream = C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)

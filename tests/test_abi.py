@@ -48,7 +48,7 @@ def test_struct_layouts_match_the_header():
                                                           "head_dim", "q_stride_b", "do_stride_h", "dv_stride_s",
                                                           "dtype", "scale", "status", "lse"]),
         "b200k_gemm_allgather_args": (L.GemmAllGatherArgs, ["gemm", "peer_c", "num_peers", "self_index", "peer_ldc", "col_offset",
-                                                             "multicast_c"]),
+                                                             "multicast_c", "plain_stores"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for cname, (_, fs) in fields.items():

@@ -70,6 +70,32 @@ def _worker(rank, world, port, results):
             ok_mc = torch.equal(fused_mc.finish(), c_fused)
             torch.cuda.synchronize()
 
+        # the same exchange with 16-byte stores from the epilogue warps instead of bulk tensor stores:
+        # identical bits (ragged shard width too: 520 columns per rank is not a multiple of a 128-byte piece)
+        fused_plain = tdist.FusedColumnParallelGemm(m, n, torch.bfloat16, plain_stores=True)
+        for buf in fused_plain.bufs:
+            buf.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        fused_plain(ad, bd, sad, sbd)
+        ok_mc = ok_mc and torch.equal(fused_plain.finish(), c_fused)
+        torch.cuda.synchronize()
+        n3 = 520 * world
+        a3, b3, sa3, sb3 = oracle.make_fp8_gemm_inputs(300, n3, k, seed=29)
+        lo3, hi3 = tdist.shard_range(n3, world, rank)
+        outs = []
+        for plain in (False, True):
+            f3 = tdist.FusedColumnParallelGemm(300, n3, torch.bfloat16, plain_stores=plain)
+            for buf in f3.bufs:
+                buf.fill_(-7.0)
+            torch.cuda.synchronize()
+            dist.barrier()
+            f3(a3.to(dev), b3[lo3:hi3].to(dev), sa3.to(dev), sb3.to(dev))
+            outs.append(f3.finish().clone())
+            torch.cuda.synchronize()
+        fro3, mx3 = oracle.fp8_errors(outs[0], oracle.gemm_fp8_nt(a3, b3, sa3, sb3))
+        ok_mc = ok_mc and torch.equal(outs[0], outs[1]) and fro3 <= 3e-2 and mx3 <= 3e-2
+
         # the unfused baseline: local GEMM, then NCCL all-gather + de-interleave
         c_nccl = tdist.column_parallel_gemm(lambda l, h: torch.ops.b200k.gemm_fp8_nt(ad, bd, sad, sbd), n, world, rank,
                                             gather=True)
