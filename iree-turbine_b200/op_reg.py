@@ -423,10 +423,17 @@ def _meta_impl(op: CustomOp):
     return meta
 
 
+_get_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+def _current_device() -> int:
+    return _get_device() if _get_device is not None else torch.cuda.current_device()
+
+
 def _impl_trampoline(op: CustomOp):
     def handler(*args):
         dev = _check_one_device(op, args)
-        if dev is not None and dev.type == "cuda":
+        if dev is not None and dev.type == "cuda" and dev.index is not None and dev.index != _current_device():
             # launch on the tensors' device, whatever device happens to be current (the reference
             # takes the device from the tensors as well, runtime/op_reg/eager.py:71-100)
             with torch.cuda.device(dev):

@@ -78,7 +78,14 @@ def reset_device_status(device=None) -> None:
     _status_words[idx].zero_()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t: Tensor) -> C.c_void_p:
+    """The current stream of the tensor's device as a raw cudaStream_t (the direct binding when torch
+    has it: building a Stream object per launch costs several microseconds)."""
+    if _raw_stream is not None and t.device.index is not None:
+        return C.c_void_p(_raw_stream(t.device.index))
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
@@ -388,11 +395,8 @@ class quantize_e4m3(CustomOp):
 # attention forward
 # ---------------------------------------------------------------------------------------------
 def _bhsd(t: Tensor) -> Tensor:
-    ok = (
-        t.stride(3) == 1
-        and all(s > 0 and s % 8 == 0 for s in t.stride()[:3])
-        and t.data_ptr() % 16 == 0
-    )
+    s0, s1, s2, s3 = t.stride()
+    ok = (s3 == 1 and s0 > 0 and s1 > 0 and s2 > 0 and (s0 | s1 | s2) % 8 == 0 and t.data_ptr() % 16 == 0)
     return t if ok else t.contiguous()
 
 
@@ -404,14 +408,14 @@ ATTENTION_KERNEL = L.ATTN_AUTO
 
 def _fill_attention_args(q: Tensor, k: Tensor, v: Tensor, o: Tensor, scale: float, causal: bool) -> L.AttentionArgs:
     args = L.AttentionArgs()
-    args.kernel = ATTENTION_KERNEL if q.size(3) == 128 else L.ATTN_AUTO
+    args.batch, args.q_heads, args.seq_q, args.head_dim = q.shape
+    args.kernel = ATTENTION_KERNEL if args.head_dim == 128 else L.ATTN_AUTO
     args.q, args.k, args.v, args.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
-    args.batch, args.q_heads, args.seq_q, args.head_dim = q.size(0), q.size(1), q.size(2), q.size(3)
-    args.kv_heads, args.seq_kv = k.size(1), k.size(2)
-    args.q_stride_b, args.q_stride_h, args.q_stride_s = q.stride(0), q.stride(1), q.stride(2)
-    args.k_stride_b, args.k_stride_h, args.k_stride_s = k.stride(0), k.stride(1), k.stride(2)
-    args.v_stride_b, args.v_stride_h, args.v_stride_s = v.stride(0), v.stride(1), v.stride(2)
-    args.o_stride_b, args.o_stride_h, args.o_stride_s = o.stride(0), o.stride(1), o.stride(2)
+    _, args.kv_heads, args.seq_kv, _ = k.shape
+    args.q_stride_b, args.q_stride_h, args.q_stride_s, _ = q.stride()
+    args.k_stride_b, args.k_stride_h, args.k_stride_s, _ = k.stride()
+    args.v_stride_b, args.v_stride_h, args.v_stride_s, _ = v.stride()
+    args.o_stride_b, args.o_stride_h, args.o_stride_s, _ = o.stride()
     args.dtype = L.DTYPE_CODES[q.dtype]
     args.causal = 1 if causal else 0
     args.scale = float(scale)
