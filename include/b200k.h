@@ -227,8 +227,8 @@ int b200k_attention_fwd(const b200k_attention_args* args, void* stream);
 /*
  * Attention backward: given q, k, v, the forward output o and its gradient d_o (layouts, head
  * grouping, causal alignment and scale as in b200k_attention_fwd), writes
- *   d_q [batch, q_heads, seq_q, 128],  d_k and d_v [batch, kv_heads, seq_kv, 128]
- * (for grouped-query heads d_k / d_v are summed over the query heads of a group).  Nothing but o is
+ *   d_q [batch, q_heads, seq_q, head_dim],  d_k and d_v [batch, kv_heads, seq_kv, head_dim]
+ * (head_dim 128 or 64; for grouped-query heads d_k / d_v are summed over the query heads of a group).  Nothing but o is
  * needed from the forward call: the row statistics are recomputed.  No atomics are used; results
  * do not depend on the grid.  workspace: device memory, 16-byte aligned, at least
  * b200k_attention_bwd_workspace_bytes(args) bytes (two fp32 values per query row); contents need

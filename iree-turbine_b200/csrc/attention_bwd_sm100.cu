@@ -1,4 +1,4 @@
-// Attention backward (head dim 128, f16 / bf16, grouped-query heads, optional causal mask aligned
+// Attention backward (head dim 128 or 64, f16 / bf16, grouped-query heads, optional causal mask aligned
 // to the bottom-right corner as in the forward kernel):
 //   P  = exp(scale * Q K^T - LSE)          dV = P^T dO
 //   dP = dO V^T                            dS = P o (dP - delta),  delta[i] = sum_d dO[i, d] O[i, d]
@@ -108,10 +108,7 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 // an iteration (64 per thread, 256 threads) would otherwise occupy the special-function unit for
 // 1024 cycles between the score product and the dV product.  Measured on the causal bf16 B4 H32
 // S4096 backward: none 2.055 ms, 3 of 8 2.038 ms, 4 of 8 2.023 ms.
-#ifndef B200K_BWD_POLY_MASK
-#define B200K_BWD_POLY_MASK 0x55u
-#endif
-constexpr uint32_t kBwdPolyMask = B200K_BWD_POLY_MASK;
+constexpr uint32_t kBwdPolyMask = 0x55u;
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -137,29 +134,34 @@ __device__ __forceinline__ void store_row_chunk(uint8_t* tile, int r, int c0, co
         make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
-// D[128 x 128] (+)= A * B with both operands in shared memory; eight K = 16 steps.
+// D[128 x N] (+)= A * B with both operands in shared memory; KSTEPS steps of K = 16 (8 for a
+// contraction over 128 rows or columns, 4 for one over a head dim of 64); N is in the instruction
+// descriptor.
 // K-major operand: step = 32 bytes inside a 64-column block, second block 16 KB further.
 // MN-major operand: step = 16 rows = 2 KB.
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int KSTEPS = 8>
 __device__ __forceinline__ void mma_128x128x128(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
                                                 bool accumulate) {
   const uint64_t a0 = A_MN ? make_desc_mnmajor_sw128(a_addr, kHalfBytes) : make_desc_kmajor_sw128(a_addr);
   const uint64_t b0 = B_MN ? make_desc_mnmajor_sw128(b_addr, kHalfBytes) : make_desc_kmajor_sw128(b_addr);
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
+  for (int ks = 0; ks < KSTEPS; ++ks) {
     const uint32_t a_off = A_MN ? ks * (2048 >> 4) : (ks >> 2) * (kHalfBytes >> 4) + (ks & 3) * 2;
     const uint32_t b_off = B_MN ? ks * (2048 >> 4) : (ks >> 2) * (kHalfBytes >> 4) + (ks & 3) * 2;
     umma_f16_ss(d_tmem, a0 + a_off, b0 + b_off, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
+// A 128-row x HD-column operand tile: one 64-column block (head dim 64) or two; the tile's slot in
+// shared memory is 32 KB either way.
+template <int HD>
 __device__ __forceinline__ void load_tile_4d(uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, int row0, int head,
                                              int batch) {
   tma_load_4d(dst, tmap, bar, 0, row0, head, batch);
-  tma_load_4d(dst + kHalfBytes, tmap, bar, 64, row0, head, batch);
+  if (HD == 128) tma_load_4d(dst + kHalfBytes, tmap, bar, 64, row0, head, batch);
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
     attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -167,9 +169,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     const __grid_constant__ CUtensorMap tmap_out1,  // dK (kModeDKV)
                     const BwdParams p) {
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
-  constexpr uint32_t kIdKK = make_idesc(kFmt, kFmt, 128, 128, 0, 0);
-  constexpr uint32_t kIdKM = make_idesc(kFmt, kFmt, 128, 128, 0, 1);
-  constexpr uint32_t kIdMM = make_idesc(kFmt, kFmt, 128, 128, 1, 1);
+  static_assert(HD == 128 || HD == 64, "head dim 128 or 64");
+  constexpr uint32_t kIdKK = make_idesc(kFmt, kFmt, 128, 128, 0, 0);  // S, dP: 128 x 128, contraction over the head dim
+  constexpr uint32_t kIdKM = make_idesc(kFmt, kFmt, 128, HD, 0, 1);   // dQ: 128 x HD
+  constexpr uint32_t kIdMM = make_idesc(kFmt, kFmt, 128, HD, 1, 1);   // dV, dK: 128 x HD
+  constexpr int kDSteps = HD / 16;                                     // K steps of a contraction over the head dim
+  constexpr int kOpBytes = kRows * HD * 2;                             // bytes TMA brings per operand tile
   constexpr bool DQ = MODE == kModeDQ;
 
   extern __shared__ uint8_t smem_raw[];
@@ -255,13 +260,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0 && total > 0) {
-      mbar_arrive_expect_tx(fix_full, 2 * kTileBytes);
+      mbar_arrive_expect_tx(fix_full, 2 * kOpBytes);
       if (DQ) {
-        load_tile_4d(smem + kOffQ, &tmap_q, fix_full, row0, head, batch);
-        load_tile_4d(smem + kOffDO, &tmap_do, fix_full, row0, head, batch);
+        load_tile_4d<HD>(smem + kOffQ, &tmap_q, fix_full, row0, head, batch);
+        load_tile_4d<HD>(smem + kOffDO, &tmap_do, fix_full, row0, head, batch);
       } else {
-        load_tile_4d(smem + kOffK, &tmap_k, fix_full, row0, kvh, batch);
-        load_tile_4d(smem + kOffV, &tmap_v, fix_full, row0, kvh, batch);
+        load_tile_4d<HD>(smem + kOffK, &tmap_k, fix_full, row0, kvh, batch);
+        load_tile_4d<HD>(smem + kOffV, &tmap_v, fix_full, row0, kvh, batch);
       }
       for (int i = 0; i < total; ++i) {
         const int buf = i % kBufs;
@@ -271,18 +276,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if (DQ) {
           const bool stats = i < n_stats;
           const int j = stats ? i : i - n_stats;
-          mbar_arrive_expect_tx(full, stats ? kTileBytes : 2 * kTileBytes);
-          load_tile_4d(smem + (buf ? kOffK1 : kOffK), &tmap_k, full, j * kRows, kvh, batch);
-          if (!stats) load_tile_4d(smem + (buf ? kOffV1 : kOffV), &tmap_v, full, j * kRows, kvh, batch);
+          mbar_arrive_expect_tx(full, stats ? kOpBytes : 2 * kOpBytes);
+          load_tile_4d<HD>(smem + (buf ? kOffK1 : kOffK), &tmap_k, full, j * kRows, kvh, batch);
+          if (!stats) load_tile_4d<HD>(smem + (buf ? kOffV1 : kOffV), &tmap_v, full, j * kRows, kvh, batch);
         } else {
           const int g = i / n;
           const int qt = qt_lo + (i - g * n);
-          mbar_arrive_expect_tx(full, kTileBytes);
-          load_tile_4d(smem + (buf ? kOffQ1 : kOffQ), &tmap_q, full, qt * kRows, kvh * group + g, batch);
+          mbar_arrive_expect_tx(full, kOpBytes);
+          load_tile_4d<HD>(smem + (buf ? kOffQ1 : kOffQ), &tmap_q, full, qt * kRows, kvh * group + g, batch);
           // one dO buffer: free once the previous iteration's dV product has read it
           if (i > 0 && !mbar_wait(do_free, (i - 1) & 1, abort_word)) break;
-          mbar_arrive_expect_tx(do_full, kTileBytes);
-          load_tile_4d(smem + kOffDO, &tmap_do, do_full, qt * kRows, kvh * group + g, batch);
+          mbar_arrive_expect_tx(do_full, kOpBytes);
+          load_tile_4d<HD>(smem + kOffDO, &tmap_do, do_full, qt * kRows, kvh * group + g, batch);
         }
       }
     }
@@ -300,11 +305,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         tc_fence_after();
         const int sb = DQ ? (it & 1) : 0;
         if (DQ)
-          mma_128x128x128<false, false>(tmem_base + (sb ? kTmS1 : kTmS), sq, smem_u32(smem + (b ? kOffK1 : kOffK)),
-                                        kIdKK, false);
+          mma_128x128x128<false, false, kDSteps>(tmem_base + (sb ? kTmS1 : kTmS), sq,
+                                                 smem_u32(smem + (b ? kOffK1 : kOffK)), kIdKK, false);
         else
-          mma_128x128x128<false, false>(tmem_base + kTmS, smem_u32(smem + (b ? kOffQ1 : kOffQ)),
-                                        smem_u32(smem + kOffK), kIdKK, false);
+          mma_128x128x128<false, false, kDSteps>(tmem_base + kTmS, smem_u32(smem + (b ? kOffQ1 : kOffQ)),
+                                                 smem_u32(smem + kOffK), kIdKK, false);
         umma_commit(s_full + sb);
         return true;
       };
@@ -324,7 +329,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             if (!mbar_wait(do_full, i & 1, abort_word)) break;
             tc_fence_after();
           }
-          mma_128x128x128<false, false>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
+          mma_128x128x128<false, false, kDSteps>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
           umma_commit(dp_full);
         }
         if (DQ && i + 1 < total && !issue_s(i + 1)) break;
@@ -520,6 +525,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 #pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
           const int c4 = half * 2 + cc;
+          if (c4 * 32 >= HD) continue;  // head dim 64: the accumulators have 64 columns
           uint32_t v[32], w[16];
           if (total > 0) {
             tmem_ld_32x32b_x32(acc + c4 * 32, v);
@@ -539,12 +545,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       if (r == 0 && half == 0) {
         if (DQ) {
           tma_store_4d(&tmap_out0, smem + kOffDS, 0, row0, head, batch);
-          tma_store_4d(&tmap_out0, smem + kOffDS + kHalfBytes, 64, row0, head, batch);
+          if (HD == 128) tma_store_4d(&tmap_out0, smem + kOffDS + kHalfBytes, 64, row0, head, batch);
         } else {
           tma_store_4d(&tmap_out0, smem + kOffP, 0, row0, kvh, batch);
-          tma_store_4d(&tmap_out0, smem + kOffP + kHalfBytes, 64, row0, kvh, batch);
+          if (HD == 128) tma_store_4d(&tmap_out0, smem + kOffP + kHalfBytes, 64, row0, kvh, batch);
           tma_store_4d(&tmap_out1, smem + kOffDS, 0, row0, kvh, batch);
-          tma_store_4d(&tmap_out1, smem + kOffDS + kHalfBytes, 64, row0, kvh, batch);
+          if (HD == 128) tma_store_4d(&tmap_out1, smem + kOffDS + kHalfBytes, 64, row0, kvh, batch);
         }
         tma_store_commit();
         tma_store_wait<0>();
@@ -562,8 +568,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   }
 }
 
-// delta[b, h, i] = sum_d dO[b, h, i, d] * O[b, h, i, d]; one warp per row, four columns per lane.
-template <typename T>
+// delta[b, h, i] = sum_d dO[b, h, i, d] * O[b, h, i, d]; one warp per row, four columns per lane
+// (head dim 64: the upper half of the warp adds zeros).
+template <typename T, int HD>
 __global__ void attn_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta,
                                       int64_t rows, int q_heads, int seq_q, int64_t o_sb, int64_t o_sh, int64_t o_ss,
                                       int64_t do_sb, int64_t do_sh, int64_t do_ss) {
@@ -573,13 +580,15 @@ __global__ void attn_bwd_delta_kernel(const T* __restrict__ o, const T* __restri
   const int64_t bh = row / seq_q;
   const int i = static_cast<int>(row - bh * seq_q);
   const int64_t b = bh / q_heads, h = bh - b * q_heads;
-  const uint2 ov = *reinterpret_cast<const uint2*>(o + b * o_sb + h * o_sh + i * o_ss + lane * 4);
-  const uint2 dv = *reinterpret_cast<const uint2*>(d_o + b * do_sb + h * do_sh + i * do_ss + lane * 4);
-  const T* oe = reinterpret_cast<const T*>(&ov);
-  const T* de = reinterpret_cast<const T*>(&dv);
   float acc = 0.f;
+  if (lane * 4 < HD) {
+    const uint2 ov = *reinterpret_cast<const uint2*>(o + b * o_sb + h * o_sh + i * o_ss + lane * 4);
+    const uint2 dv = *reinterpret_cast<const uint2*>(d_o + b * do_sb + h * do_sh + i * do_ss + lane * 4);
+    const T* oe = reinterpret_cast<const T*>(&ov);
+    const T* de = reinterpret_cast<const T*>(&dv);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) acc += static_cast<float>(oe[k]) * static_cast<float>(de[k]);
+    for (int k = 0; k < 4; ++k) acc += static_cast<float>(oe[k]) * static_cast<float>(de[k]);
+  }
 #pragma unroll
   for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
   if (lane == 0) delta[row] = acc;
@@ -589,18 +598,18 @@ struct BwdMaps {
   CUtensorMap q, d_o, k, v, dq, dk, dv;
 };
 
-int encode_bshd(CUtensorMap* out, int dtype, const void* base, int seq, int heads, int batch, int64_t sb, int64_t sh,
-                int64_t ss) {
+int encode_bshd(CUtensorMap* out, int dtype, const void* base, int head_dim, int seq, int heads, int batch, int64_t sb,
+                int64_t sh, int64_t ss) {
   const uint32_t box[4] = {64, kRows, 1, 1};
-  uint64_t dims[4] = {kD, static_cast<uint64_t>(seq), static_cast<uint64_t>(heads), static_cast<uint64_t>(batch)};
+  uint64_t dims[4] = {static_cast<uint64_t>(head_dim), static_cast<uint64_t>(seq), static_cast<uint64_t>(heads), static_cast<uint64_t>(batch)};
   uint64_t st[3] = {static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(sb) * 2};
   return encode_tmap(out, dtype, 4, const_cast<void*>(base), dims, st, box);
 }
 
-template <typename T>
+template <typename T, int HD>
 int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const BwdParams& p, cudaStream_t stream) {
-  auto k_dq = attn_bwd_kernel<T, kModeDQ>;
-  auto k_dkv = attn_bwd_kernel<T, kModeDKV>;
+  auto k_dq = attn_bwd_kernel<T, kModeDQ, HD>;
+  auto k_dkv = attn_bwd_kernel<T, kModeDKV, HD>;
   static bool configured_dq[64] = {}, configured_dkv[64] = {};  // per instantiation and device ordinal
   int rc = ensure_dynamic_smem(k_dq, bwd_smem_bytes(kModeDQ), configured_dq, "cudaFuncSetAttribute(attention bwd dq smem)");
   if (rc) return rc;
@@ -608,7 +617,7 @@ int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const
   if (rc) return rc;
   const int64_t rows = static_cast<int64_t>(a.batch) * a.q_heads * a.seq_q;
   const int warps_per_block = 8;
-  attn_bwd_delta_kernel<T><<<static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block),
+  attn_bwd_delta_kernel<T, HD><<<static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block),
                              warps_per_block * 32, 0, stream>>>(
       static_cast<const T*>(a.o), static_cast<const T*>(a.d_o), p.delta, rows, a.q_heads, a.seq_q, a.o_stride_b,
       a.o_stride_h, a.o_stride_s, a.do_stride_b, a.do_stride_h, a.do_stride_s);
@@ -635,7 +644,8 @@ int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream)
     return set_error(B200K_ERR_NULL, "attention_bwd: q, k, v, o, d_o, d_q, d_k, d_v must be non-NULL");
   if (a.batch <= 0 || a.q_heads <= 0 || a.kv_heads <= 0 || a.seq_q <= 0 || a.seq_kv <= 0)
     return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: all dimensions must be positive");
-  if (a.head_dim != kD) return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: head_dim must be 128");
+  if (a.head_dim != 128 && a.head_dim != 64)
+    return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: head_dim must be 128 or 64");
   if (a.q_heads % a.kv_heads != 0)
     return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: q_heads must be a multiple of kv_heads");
   if (a.dtype != B200K_F16 && a.dtype != B200K_BF16)
@@ -662,13 +672,13 @@ int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream)
   if (rc) return rc;
 
   BwdMaps tm;
-  rc = encode_bshd(&tm.q, a.dtype, a.q, a.seq_q, a.q_heads, a.batch, a.q_stride_b, a.q_stride_h, a.q_stride_s);
-  if (!rc) rc = encode_bshd(&tm.d_o, a.dtype, a.d_o, a.seq_q, a.q_heads, a.batch, a.do_stride_b, a.do_stride_h, a.do_stride_s);
-  if (!rc) rc = encode_bshd(&tm.k, a.dtype, a.k, a.seq_kv, a.kv_heads, a.batch, a.k_stride_b, a.k_stride_h, a.k_stride_s);
-  if (!rc) rc = encode_bshd(&tm.v, a.dtype, a.v, a.seq_kv, a.kv_heads, a.batch, a.v_stride_b, a.v_stride_h, a.v_stride_s);
-  if (!rc) rc = encode_bshd(&tm.dq, a.dtype, a.d_q, a.seq_q, a.q_heads, a.batch, a.dq_stride_b, a.dq_stride_h, a.dq_stride_s);
-  if (!rc) rc = encode_bshd(&tm.dk, a.dtype, a.d_k, a.seq_kv, a.kv_heads, a.batch, a.dk_stride_b, a.dk_stride_h, a.dk_stride_s);
-  if (!rc) rc = encode_bshd(&tm.dv, a.dtype, a.d_v, a.seq_kv, a.kv_heads, a.batch, a.dv_stride_b, a.dv_stride_h, a.dv_stride_s);
+  rc = encode_bshd(&tm.q, a.dtype, a.q, a.head_dim, a.seq_q, a.q_heads, a.batch, a.q_stride_b, a.q_stride_h, a.q_stride_s);
+  if (!rc) rc = encode_bshd(&tm.d_o, a.dtype, a.d_o, a.head_dim, a.seq_q, a.q_heads, a.batch, a.do_stride_b, a.do_stride_h, a.do_stride_s);
+  if (!rc) rc = encode_bshd(&tm.k, a.dtype, a.k, a.head_dim, a.seq_kv, a.kv_heads, a.batch, a.k_stride_b, a.k_stride_h, a.k_stride_s);
+  if (!rc) rc = encode_bshd(&tm.v, a.dtype, a.v, a.head_dim, a.seq_kv, a.kv_heads, a.batch, a.v_stride_b, a.v_stride_h, a.v_stride_s);
+  if (!rc) rc = encode_bshd(&tm.dq, a.dtype, a.d_q, a.head_dim, a.seq_q, a.q_heads, a.batch, a.dq_stride_b, a.dq_stride_h, a.dq_stride_s);
+  if (!rc) rc = encode_bshd(&tm.dk, a.dtype, a.d_k, a.head_dim, a.seq_kv, a.kv_heads, a.batch, a.dk_stride_b, a.dk_stride_h, a.dk_stride_s);
+  if (!rc) rc = encode_bshd(&tm.dv, a.dtype, a.d_v, a.head_dim, a.seq_kv, a.kv_heads, a.batch, a.dv_stride_b, a.dv_stride_h, a.dv_stride_s);
   if (rc) return rc;
 
   BwdParams p;
@@ -690,8 +700,12 @@ int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream)
   p.lse2 = static_cast<float*>(a.workspace);
   p.delta = p.lse2 + static_cast<int64_t>(a.batch) * a.q_heads * a.seq_q;
   p.status = a.status;
-  if (a.dtype == B200K_F16) return launch_bwd_typed<__half>(a, tm, p, stream);
-  return launch_bwd_typed<__nv_bfloat16>(a, tm, p, stream);
+  if (a.head_dim == 64) {
+    if (a.dtype == B200K_F16) return launch_bwd_typed<__half, 64>(a, tm, p, stream);
+    return launch_bwd_typed<__nv_bfloat16, 64>(a, tm, p, stream);
+  }
+  if (a.dtype == B200K_F16) return launch_bwd_typed<__half, 128>(a, tm, p, stream);
+  return launch_bwd_typed<__nv_bfloat16, 128>(a, tm, p, stream);
 }
 
 }  // namespace b200k

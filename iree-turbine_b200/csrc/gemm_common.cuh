@@ -113,16 +113,26 @@ __device__ __forceinline__ float load_bias(const void* bias, int dtype, int col)
   return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(bias) + col));
 }
 
+// A bias of zero for calls without one (see fused_epilogue).
+static __device__ const float kZeroBias = 0.0f;
+
 // Fused epilogue on N accumulator values of one row (columns col0 .. col0 + N - 1), in place:
 // r = act(r * scale + bias).  Every lane of a warp reads the same bias element (one broadcast
 // load per column).  Afterwards the caller's own scaling must be 1.
+// No load here is guarded by a test the compiler could move it across: without a bias the pointer
+// is switched to a zero that lives in device memory, and the column index is clamped to the vector
+// instead of predicated (columns past n are never stored).  A guarded form of this loop was seen to
+// fault on a null bias in one kernel, its loads having been issued ahead of the null test.
 template <int N>
 __device__ __forceinline__ void fused_epilogue(uint32_t (&r)[N], float scale, const void* bias, int bias_dtype, int act,
                                                int col0, int n) {
+  const bool has_bias = bias != nullptr;
+  const void* b = has_bias ? bias : static_cast<const void*>(&kZeroBias);
+  const int dt = has_bias ? bias_dtype : static_cast<int>(B200K_F32);
+  const int last = has_bias ? n - 1 : 0;
 #pragma unroll
   for (int j = 0; j < N; ++j) {
-    float x = __uint_as_float(r[j]) * scale;
-    if (bias != nullptr && col0 + j < n) x += load_bias(bias, bias_dtype, col0 + j);
+    const float x = __uint_as_float(r[j]) * scale + load_bias(b, dt, min(col0 + j, last));
     r[j] = __float_as_uint(apply_act(x, act));
   }
 }

@@ -497,7 +497,8 @@ def _attention_bwd_checks(q: Tensor, k: Tensor, v: Tensor, o: Tensor, d_o: Tenso
         torch._check(lse.dtype == torch.float32 and tuple(lse.shape) == tuple(q.shape[:3]),
                      lambda: "attention_bwd: lse must be float32 [B, Hq, Sq]")
     for t in (q, k, v, o, d_o):
-        torch._check(t.dim() == 4 and t.size(3) == 128, lambda: "attention_bwd: tensors must be [B,H,S,128]")
+        torch._check(t.dim() == 4 and t.size(3) in (64, 128) and t.size(3) == q.size(3),
+                     lambda: "attention_bwd: tensors must be [B,H,S,D] with D = 128 or 64, the same for all")
         torch._check(t.dtype == q.dtype, lambda: "attention_bwd: all tensors must share a dtype")
     torch._check(q.dtype in _HALF_TYPES, lambda: f"attention_bwd: dtype must be float16 or bfloat16, got {q.dtype}")
     torch._check(k.shape == v.shape, lambda: "attention_bwd: k and v must have the same shape")
@@ -538,7 +539,7 @@ class attention_bwd(CustomOp):
             setattr(a, {"do": "d_o", "dq": "d_q", "dk": "d_k", "dv": "d_v"}.get(name, name), t.data_ptr())
             for d, i in (("b", 0), ("h", 1), ("s", 2)):
                 setattr(a, f"{name}_stride_{d}", t.stride(i))
-        a.batch, a.q_heads, a.seq_q, a.head_dim = q.size(0), q.size(1), q.size(2), 128
+        a.batch, a.q_heads, a.seq_q, a.head_dim = q.shape
         a.kv_heads, a.seq_kv = k.size(1), k.size(2)
         a.dtype = L.DTYPE_CODES[q.dtype]
         a.causal = 1 if is_causal else 0
@@ -572,11 +573,10 @@ class _AttentionFunction(torch.autograd.Function):
 
 
 def sdpa(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, is_causal: bool = False) -> Tensor:
-    """Differentiable scaled-dot-product attention on the b200k kernels ([B, H, S, 128] f16 / bf16
-    CUDA tensors; grouped-query heads; causal mask aligned to the bottom-right corner).  The backward
-    kernels cover head dim 128 only; for head dim 64 use ``torch.ops.b200k.attention`` (forward)."""
-    if q.size(-1) != 128:
-        raise ValueError("sdpa: the backward kernels cover head dim 128 only")
+    """Differentiable scaled-dot-product attention on the b200k kernels ([B, H, S, D] f16 / bf16
+    CUDA tensors, D = 128 or 64; grouped-query heads; causal mask aligned to the bottom-right corner)."""
+    if q.size(-1) not in (64, 128):
+        raise ValueError("sdpa: head dim must be 128 or 64")
     if scale is None:
         scale = 1.0 / (q.size(-1) ** 0.5)
     return _AttentionFunction.apply(q, k, v, float(scale), bool(is_causal))

@@ -55,6 +55,39 @@ def test_matches_oracle(b, hq, hkv, sq, skv, causal, dtype):
         _assert_close(g, r)
 
 
+@pytest.mark.parametrize("b,hq,hkv,sq,skv,causal", CASES)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_64_matches_oracle(b, hq, hkv, sq, skv, causal, dtype):
+    scale = 0.125
+    q, k, v = oracle.make_attention_inputs(b, hq, hkv, sq, skv, head_dim=64, dtype=dtype, seed=6)
+    d_o = _d_o((b, hq, sq, 64), dtype)
+    got = _run(q, k, v, d_o, causal, scale)
+    ref = oracle.attention_bwd(q, k, v, d_o, scale, causal)
+    for g, r in zip(got, ref):
+        assert g.shape[-1] == 64
+        _assert_close(g, r)
+
+
+def test_head_dim_64_autograd_wrapper_with_forward_lse():
+    """ops.sdpa at head dim 64 (forward LSE handed to the backward) against torch's own autograd in fp32."""
+    from iree_turbine_b200 import ops
+
+    g = torch.Generator().manual_seed(15)
+    q, k, v = (torch.randn(2, h, 320, 64, generator=g).to(torch.bfloat16) for h in (4, 2, 2))
+    d_o = _d_o((2, 4, 320, 64), torch.bfloat16)
+    qd, kd, vd = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    o = ops.sdpa(qd, kd, vd, None, True)
+    o.backward(d_o.to(DEV))
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref = torch.nn.functional.scaled_dot_product_attention(qr, kr, vr, is_causal=True, enable_gqa=True)
+    ref.backward(d_o.float())
+    _assert_close(o.detach(), ref.detach())
+    for got, want in ((qd.grad, qr.grad), (kd.grad, kr.grad), (vd.grad, vr.grad)):
+        _assert_close(got, want)
+
+
 def test_rows_without_a_visible_key_get_zero_gradient():
     q, k, v = oracle.make_attention_inputs(1, 1, 1, 300, 200, dtype=torch.float16, seed=6)
     d_q, _, _ = _run(q, k, v, _d_o(q.shape, torch.float16), True)
