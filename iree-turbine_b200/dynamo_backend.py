@@ -5,9 +5,10 @@ forward compiler rewrites ATen nodes through a replacement schema and then hands
 nested backend (iree/turbine/dynamo/backends/boo.py:55-126; schema of offloaded ops
 iree/turbine/kernel/boo/fusion/schema.py:106-135; the SDPA variants are matched as in
 iree/turbine/kernel/boo/fusion/replacement.py:239-290: a multi-output fused-attention node is only
-replaced when nothing but its first output is used).
+replaced when nothing but its first output is used -- this backend goes one step further for the
+flash form, see below).
 
-What is rewritten (forward graph only; the backward graph, if any, goes to the nested backend as is):
+What is rewritten (in the forward graph and, with the same schema, in the backward graph):
 
 * ``aten.mm(a, t(w))``           -> ``b200k.gemm_nt(a, w, out_dtype=a.dtype)``
 * ``aten.mm`` in the other three storage forms (``mm(a, b)``, ``mm(t(a), b)``, ``mm(t(a), t(b))``)
@@ -23,6 +24,12 @@ What is rewritten (forward graph only; the backward graph, if any, goes to the n
   for [B, H, S, 128 or 64] f16 / bf16 CUDA tensors, no mask / bias, dropout 0, q_heads a multiple of
   kv_heads, and -- when causal -- equal query and key lengths (torch aligns the causal mask to the
   top-left corner, the kernel to the bottom-right; they coincide only then).
+* training graphs: ``aten._scaled_dot_product_{flash,cudnn}_attention`` whose log-sum-exp output is
+  saved for the backward -> ``b200k.attention_lse`` (same statistic: float32 [B, H, Sq] -- with a
+  trailing 1 for cuDNN -- natural log; the random-number state and sequence-length outputs,
+  meaningless without dropout and nested tensors, become empty stand-ins), and
+  ``aten._scaled_dot_product_{flash,cudnn}_attention_backward`` ->
+  ``b200k.attention_bwd(q, k, v, out, grad_out, scale, is_causal, lse)``, under the same conditions.
 
 Everything else is left alone.  ``backend()`` returns the compiler; it is also registered under the
 name ``"b200k"``: ``torch.compile(model, backend="b200k")``.
@@ -47,6 +54,7 @@ __all__ = [
     "replace_mm",
     "replace_addmm",
     "replace_fused_sdpa",
+    "replace_flash_sdpa_backward",
     "replace_sdpa",
 ]
 
@@ -224,9 +232,105 @@ def _fused_args(node: fx.Node):
             bool(_arg(node, 6, "is_causal", False)))
 
 
+def _replace_flash_training_forward(node: fx.Node, getitems) -> bool:
+    """The flash-attention node of a training graph: its log-sum-exp (output 1, float32 [B, H, Sq], natural
+    log of the scaled scores' exp-sum -- the statistic ``b200k.attention_lse`` returns) is saved for the
+    backward, and so are the random-number state tensors and the sequence-length outputs, which mean
+    nothing without dropout and nested tensors.  Rewritten to ``attention_lse``; the other used outputs
+    become empty tensors of the recorded shape and type (or the recorded integers)."""
+    q, k, v, _, _, is_causal = _fused_args(node)
+    g = node.graph
+    plans = []
+    for u in getitems:
+        idx = u.args[1]
+        if idx in (0, 1) or len(u.users) == 0:
+            continue
+        val = u.meta.get("val")
+        if idx == 8 or not isinstance(val, (torch.Tensor, int)):  # the debug mask, or nothing recorded
+            return False
+        plans.append((u, val))
+    lse_users = [u for u in getitems if u.args[1] == 1 and len(u.users) > 0]
+    for u in lse_users:
+        if _lse_form(u.meta.get("val"), _val(q)) is None:
+            return False
+    with g.inserting_before(node):
+        new = g.call_function(torch.ops.b200k.attention_lse.default, args=(q, k, v, _scale_of(node, q), is_causal))
+        new.meta = {k_: v_ for k_, v_ in node.meta.items() if k_ != "val"}
+        for u in getitems:
+            idx = u.args[1]
+            if idx in (0, 1):
+                piece = g.call_function(operator.getitem, (new, idx))
+                piece.meta = dict(u.meta)
+                if idx == 1 and len(u.users) > 0 and _lse_form(u.meta.get("val"), _val(q)) == 4:
+                    piece = g.call_function(aten.unsqueeze.default, (piece, -1))  # the cuDNN form: [B, H, Sq, 1]
+                    piece.meta = dict(u.meta)
+                u.replace_all_uses_with(piece)
+        for u, val in plans:
+            if isinstance(val, int):
+                u.replace_all_uses_with(val)
+            else:
+                stand_in = g.call_function(aten.empty.memory_format, (list(val.shape),),
+                                           {"dtype": val.dtype, "device": val.device})
+                stand_in.meta = dict(u.meta)
+                u.replace_all_uses_with(stand_in)
+    for u in getitems:
+        g.erase_node(u)
+    g.erase_node(node)
+    return True
+
+
+def _lse_form(val, vq) -> Optional[int]:
+    """3 for a float32 [B, H, Sq] statistic (flash), 4 for [B, H, Sq, 1] (cuDNN), None for anything else."""
+    if not isinstance(val, torch.Tensor) or vq is None or val.dtype != torch.float32:
+        return None
+    if tuple(val.shape) == tuple(vq.shape[:3]):
+        return 3
+    if tuple(val.shape) == tuple(vq.shape[:3]) + (1,):
+        return 4
+    return None
+
+
+def replace_sdpa_backward(node: fx.Node) -> bool:
+    """The backward node of flash or cuDNN attention -> ``b200k.attention_bwd``: the same three
+    gradients from the same saved tensors.
+    flash: (grad_out, q, k, v, out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, dropout_p, is_causal,
+    philox_seed, philox_offset, *, scale); cuDNN: (grad_out, q, k, v, out, logsumexp, philox_seed,
+    philox_offset, attn_bias, cum_seq_q, cum_seq_k, max_q, max_k, dropout_p, is_causal, *, scale)."""
+    flash = node.target is aten._scaled_dot_product_flash_attention_backward.default
+    if len(node.args) < (12 if flash else 15):
+        return False
+    grad_out, q, k, v, out, lse = node.args[:6]
+    if flash:
+        bias, dropout_p, is_causal = None, node.args[10], bool(node.args[11])
+    else:
+        bias, dropout_p, is_causal = node.args[8], node.args[13], bool(node.args[14])
+    if not _sdpa_supported(q, k, v, bias, dropout_p, is_causal):
+        return False
+    vq, vo, vg = _val(q), _val(out), _val(grad_out)
+    if vo is None or vg is None or tuple(vo.shape) != tuple(vq.shape) or tuple(vg.shape) != tuple(vq.shape):
+        return False
+    form = _lse_form(_val(lse), vq)
+    if vo.dtype != vq.dtype or vg.dtype != vq.dtype or form is None:
+        return False
+    g = node.graph
+    with g.inserting_before(node):
+        if form == 4:
+            lse = g.call_function(aten.squeeze.dim, (lse, -1))
+        new = g.call_function(torch.ops.b200k.attention_bwd.default,
+                              args=(q, k, v, out, grad_out, _scale_of(node, q), is_causal, lse))
+    new.meta = dict(node.meta)
+    node.replace_all_uses_with(new)
+    g.erase_node(node)
+    return True
+
+
+replace_flash_sdpa_backward = replace_sdpa_backward  # the name under which the flash form was first covered
+
+
 def replace_fused_sdpa(node: fx.Node) -> bool:
-    """A fused-attention node returns (output, logsumexp, ...): replaced only when nothing but
-    output is used (so never in a graph whose backward needs the log-sum-exp)."""
+    """A fused-attention node returns (output, logsumexp, ...).  When nothing but output is used it
+    becomes ``b200k.attention``; the flash form of a training graph, whose log-sum-exp the backward
+    reads, becomes ``b200k.attention_lse`` (see _replace_flash_training_forward)."""
     q, k, v, mask, dropout_p, is_causal = _fused_args(node)
     if not _sdpa_supported(q, k, v, mask, dropout_p, is_causal):
         return False
@@ -234,11 +338,16 @@ def replace_fused_sdpa(node: fx.Node) -> bool:
     if len(getitems) != len(node.users):
         return False
     out_user = None
+    extra_used = False
     for u in getitems:
         if u.args[1] == 0:
             out_user = u
         elif len(u.users) > 0:
-            return False
+            extra_used = True
+    if extra_used:
+        if node.target is getattr(aten, "_scaled_dot_product_efficient_attention").default:
+            return False  # its statistic is padded to a multiple of 32 rows
+        return _replace_flash_training_forward(node, getitems)
     if out_user is None:
         return False
     g = node.graph
@@ -264,6 +373,10 @@ def _default_replacements() -> ReplacementSchema:
         pkt = getattr(aten, name, None)
         if pkt is not None:
             schema[pkt.default] = replace_fused_sdpa
+    for name in ("_scaled_dot_product_flash_attention_backward", "_scaled_dot_product_cudnn_attention_backward"):
+        pkt = getattr(aten, name, None)
+        if pkt is not None:
+            schema[pkt.default] = replace_sdpa_backward
     return schema
 
 
@@ -298,12 +411,14 @@ def backend(*, nested_backend="eager", replacements: ReplacementSchema = DEFAULT
         return make_boxed_func(nested(gm, example_inputs))
 
     def bw_compiler(gm: fx.GraphModule, example_inputs):
+        backend.last_replaced_backward = apply_replacements(gm, replacements)
         return make_boxed_func(nested(gm, example_inputs))
 
     return aot_autograd(fw_compiler=fw_compiler, bw_compiler=bw_compiler)
 
 
 backend.last_replaced = 0  # set by the most recent forward compilation (for tests and diagnostics)
+backend.last_replaced_backward = 0  # likewise for the most recent backward graph
 
 
 def _register():

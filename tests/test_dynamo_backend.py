@@ -158,12 +158,124 @@ def test_flash_sdpa_is_routed_with_scale_and_causal_flag():
     assert operator.getitem not in _targets(gm)
 
 
-@pytest.mark.parametrize("kw", [dict(aux_used=True), dict(causal=True, sq=128, skv=256), dict(d=96),
-                                dict(dropout=0.1), dict(hq=8, hkv=3)])
+def test_flash_sdpa_with_its_statistic_in_use_becomes_attention_lse():
+    gm = _flash_graph(aux_used=True)
+    assert db.apply_replacements(gm) == 1
+    assert torch.ops.b200k.attention_lse.default in _targets(gm)
+
+
+@pytest.mark.parametrize("kw", [dict(causal=True, sq=128, skv=256), dict(d=96), dict(dropout=0.1), dict(hq=8, hkv=3),
+                                dict(aux_used=True, d=96)])
 def test_flash_sdpa_left_alone(kw):
     gm = _flash_graph(**kw)
     assert db.apply_replacements(gm) == 0
     assert aten._scaled_dot_product_flash_attention.default in _targets(gm)
+
+
+def _flash_training_graph(d=128, causal=True):
+    """Forward graph of a training step: output, log-sum-exp and the random-number state are graph outputs."""
+    def build(g):
+        q = _ph(g, "q", _fake((2, 8, 256, d), torch.bfloat16))
+        k = _ph(g, "k", _fake((2, 4, 256, d), torch.bfloat16))
+        v = _ph(g, "v", _fake((2, 4, 256, d), torch.bfloat16))
+        n = g.call_function(aten._scaled_dot_product_flash_attention.default, (q, k, v, 0.0, causal, False),
+                            {"scale": 0.1})
+        outs = []
+        for idx, val in ((0, _fake((2, 8, 256, d), torch.bfloat16)), (1, _fake((2, 8, 256), torch.float32)),
+                         (6, _fake((2,), torch.uint64)), (7, _fake((), torch.uint64))):
+            u = g.call_function(operator.getitem, (n, idx))
+            u.meta["val"] = val
+            outs.append(u)
+        mq = g.call_function(operator.getitem, (n, 4))
+        mq.meta["val"] = 256
+        outs.append(mq)
+        return tuple(outs)
+
+    return _graph(build)
+
+
+@pytest.mark.parametrize("d", [128, 64])
+def test_flash_sdpa_of_a_training_graph_becomes_attention_lse(d):
+    gm = _flash_training_graph(d)
+    assert db.apply_replacements(gm) == 1
+    t = _targets(gm)
+    assert torch.ops.b200k.attention_lse.default in t and aten._scaled_dot_product_flash_attention.default not in t
+    node = next(n for n in gm.graph.nodes if n.target is torch.ops.b200k.attention_lse.default)
+    assert node.args[3] == 0.1 and node.args[4] is True
+    out = next(n for n in gm.graph.nodes if n.op == "output").args[0]
+    assert out[0].target is operator.getitem and out[0].args == (node, 0)
+    assert out[1].target is operator.getitem and out[1].args == (node, 1)
+    assert out[2].target is aten.empty.memory_format and out[2].kwargs["dtype"] == torch.uint64
+    assert out[4] == 256
+
+
+def test_flash_sdpa_backward_is_routed_and_unsupported_left_alone():
+    def build(dropout, d=128):
+        def f(g):
+            names = ("grad", "q", "k", "v", "out")
+            shapes = ((2, 8, 256, d), (2, 8, 256, d), (2, 4, 256, d), (2, 4, 256, d), (2, 8, 256, d))
+            grad, q, k, v, out = (_ph(g, n, _fake(s, torch.bfloat16)) for n, s in zip(names, shapes))
+            lse = _ph(g, "lse", _fake((2, 8, 256), torch.float32))
+            seed = _ph(g, "seed", _fake((2,), torch.uint64))
+            off = _ph(g, "off", _fake((), torch.uint64))
+            n = g.call_function(aten._scaled_dot_product_flash_attention_backward.default,
+                                (grad, q, k, v, out, lse, None, None, 256, 256, dropout, True, seed, off), {"scale": 0.1})
+            pieces = []
+            for i, shp in enumerate(((2, 8, 256, d), (2, 4, 256, d), (2, 4, 256, d))):
+                u = g.call_function(operator.getitem, (n, i))
+                u.meta["val"] = _fake(shp, torch.bfloat16)
+                pieces.append(u)
+            return tuple(pieces)
+        return f
+
+    gm = _graph(build(0.0))
+    assert db.apply_replacements(gm) == 1
+    node = next(n for n in gm.graph.nodes if n.target is torch.ops.b200k.attention_bwd.default)
+    assert [a.name for a in node.args[:5]] == ["q", "k", "v", "out", "grad"]
+    assert node.args[5] == 0.1 and node.args[6] is True and node.args[7].name == "lse"
+    out = next(n for n in gm.graph.nodes if n.op == "output").args[0]
+    assert all(o.args[0] is node and o.args[1] == i for i, o in enumerate(out))
+    for kw in (dict(dropout=0.1), dict(dropout=0.0, d=96)):
+        gm = _graph(build(**kw))
+        assert db.apply_replacements(gm) == 0
+
+
+def test_cudnn_sdpa_of_a_training_graph_and_its_backward_are_routed():
+    """The cuDNN form keeps its statistic as [B, H, Sq, 1]: the forward rewrite appends that axis, the backward
+    rewrite drops it again."""
+    def fwd(g):
+        q = _ph(g, "q", _fake((2, 8, 256, 128), torch.bfloat16))
+        k = _ph(g, "k", _fake((2, 8, 256, 128), torch.bfloat16))
+        v = _ph(g, "v", _fake((2, 8, 256, 128), torch.bfloat16))
+        n = g.call_function(aten._scaled_dot_product_cudnn_attention.default, (q, k, v, None, True, 0.0, True, False),
+                            {"scale": 0.1})
+        o = g.call_function(operator.getitem, (n, 0))
+        o.meta["val"] = _fake((2, 8, 256, 128), torch.bfloat16)
+        lse = g.call_function(operator.getitem, (n, 1))
+        lse.meta["val"] = _fake((2, 8, 256, 1), torch.float32)
+        return (o, lse)
+
+    gm = _graph(fwd)
+    assert db.apply_replacements(gm) == 1
+    out = next(n for n in gm.graph.nodes if n.op == "output").args[0]
+    assert out[1].target is aten.unsqueeze.default
+    assert out[1].args[0].args[0].target is torch.ops.b200k.attention_lse.default
+
+    def bwd(g):
+        names = ("grad", "q", "k", "v", "out")
+        grad, q, k, v, out = (_ph(g, n, _fake((2, 8, 256, 128), torch.bfloat16)) for n in names)
+        lse = _ph(g, "lse", _fake((2, 8, 256, 1), torch.float32))
+        seed = _ph(g, "seed", _fake((), torch.int64))
+        n = g.call_function(aten._scaled_dot_product_cudnn_attention_backward.default,
+                            (grad, q, k, v, out, lse, seed, seed, None, None, None, 256, 256, 0.0, True), {"scale": 0.1})
+        u = g.call_function(operator.getitem, (n, 0))
+        u.meta["val"] = _fake((2, 8, 256, 128), torch.bfloat16)
+        return u
+
+    gm = _graph(bwd)
+    assert db.apply_replacements(gm) == 1
+    node = next(n for n in gm.graph.nodes if n.target is torch.ops.b200k.attention_bwd.default)
+    assert node.args[7].target is aten.squeeze.dim and node.args[4].name == "grad"
 
 
 def test_flash_sdpa_head_dim_64_is_routed():

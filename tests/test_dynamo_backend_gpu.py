@@ -41,3 +41,30 @@ def test_compiled_block_matches_eager(causal):
     assert tb.device_status() == 0
     assert db.backend.last_replaced >= 3, "qkv mm, attention and proj addmm should all have been routed"
     torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_compiled_training_step_routes_attention_forward_and_backward(head_dim):
+    """A training step through torch.compile: the forward graph's fused attention (whose log-sum-exp is saved)
+    and the backward graph's attention-backward node both run on the b200k kernels; gradients match eager."""
+    import copy
+
+    torch.manual_seed(1)
+    m = Block(dim=4 * head_dim, heads=4).to(DEV).to(torch.bfloat16)
+    ref_m = copy.deepcopy(m)
+    x = (torch.randn(2, 256, 4 * head_dim, device=DEV) * 0.5).to(torch.bfloat16)
+    ref = ref_m(x, True)
+    ref.float().square().mean().backward()
+    torch._dynamo.reset()
+    db.backend.last_replaced = db.backend.last_replaced_backward = 0
+    out = torch.compile(m, backend="b200k")(x, True)
+    out.float().square().mean().backward()
+    torch.cuda.synchronize()
+    assert tb.device_status() == 0
+    assert db.backend.last_replaced >= 3
+    assert db.backend.last_replaced_backward >= 1, "the backward graph's attention node should have been routed"
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+    for (name, p), (_, pr) in zip(m.named_parameters(), ref_m.named_parameters()):
+        scale = pr.grad.float().abs().max().item()
+        err = (p.grad.float() - pr.grad.float()).abs().max().item()
+        assert err <= 3e-2 * max(scale, 1e-6), (name, err, scale)
