@@ -752,17 +752,21 @@ int fill_units(AttnParams& p, const char* who) {
 // timing loop, one-tile / tile-pair in microseconds: non-causal 8x32x1024 130 / 140, 8x32x2048
 // 514 / 537, 1x16x16384 1809 / 1932; causal 4x32x4096 521 / 505, 2x32(8)x8192 960 / 924,
 // 1x32(8)x16384 2214 / 2052, 64x16x256 80 / 66, but 4x32(8)x2048 155 / 173, where the pair
-// kernel's 512 units leave the last of four rounds over 148 SMs half empty.  So: head dim 64 only
-// exists in the pair kernel; causal problems take it when its units fill the SMs to 90 % or more;
-// everything else takes the one-tile kernel.
-bool choose_pair_kernel(int kernel, int head_dim, bool causal, int64_t pair_units) {
+// kernel's 512 units leave the last of four rounds over 148 SMs half empty.  Problems that are one
+// round of units (a head shard of a long causal prefill on 8 GPUs): 4x4(1)x4096 92.5 / 80.3,
+// 1x8x8192 172 / 142 (128 units, the one-tile kernel balances its 512 unequal items badly), but
+// 8x8x1024 40.3 / 40.3 and 4x6(2)x2048 (96 units) 45.4 / 49.5.  So: head dim 64 only exists in the
+// pair kernel; causal problems take it when its units fill the SMs to 90 % or more, or fill one
+// round to 80 % with at least 24 K/V tiles to walk; everything else takes the one-tile kernel.
+bool choose_pair_kernel(int kernel, int head_dim, bool causal, int64_t pair_units, int64_t kv_tiles) {
   if (head_dim != 128) return true;
   if (kernel == B200K_ATTN_TILE_PAIR) return true;
   if (kernel == B200K_ATTN_ONE_TILE) return false;
   if (!causal) return false;
   const int64_t sms = num_sms();
   const int64_t rounds = (pair_units + sms - 1) / sms;
-  return pair_units * 10 >= rounds * sms * 9;
+  if (pair_units * 10 >= rounds * sms * 9) return true;
+  return rounds == 1 && pair_units * 10 >= sms * 8 && kv_tiles >= 24;
 }
 
 }  // namespace
@@ -796,7 +800,8 @@ int launch_attention_fwd(const b200k_attention_args& a, cudaStream_t stream) {
   {
     const int64_t pairs = (a.seq_q + kPairRows - 1) / kPairRows;
     const int64_t units = static_cast<int64_t>(a.batch) * a.q_heads * (a.causal ? (pairs + 1) / 2 : pairs);
-    if (!choose_pair_kernel(a.kernel, a.head_dim, a.causal != 0, units)) return launch_attention_fwd_tile(a, stream);
+    if (!choose_pair_kernel(a.kernel, a.head_dim, a.causal != 0, units, (a.seq_kv + 127) / 128))
+      return launch_attention_fwd_tile(a, stream);
   }
 
   CUtensorMap tq, tk, tv, to;
@@ -889,7 +894,8 @@ int launch_paged_attention_fwd(const b200k_paged_attention_args& a, cudaStream_t
   {
     const int64_t pairs = (a.seq_q + kPairRows - 1) / kPairRows;
     const int64_t units = static_cast<int64_t>(a.batch) * a.q_heads * (a.causal ? (pairs + 1) / 2 : pairs);
-    if (!choose_pair_kernel(a.kernel, a.head_dim, a.causal != 0, units)) return launch_paged_attention_fwd_tile(a, stream);
+    if (!choose_pair_kernel(a.kernel, a.head_dim, a.causal != 0, units, (a.max_seq_kv + 127) / 128))
+      return launch_paged_attention_fwd_tile(a, stream);
   }
 
   CUtensorMap tq, tk, tv, to;
