@@ -568,30 +568,356 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   }
 }
 
-// delta[b, h, i] = sum_d dO[b, h, i, d] * O[b, h, i, d]; one warp per row, four columns per lane
-// (head dim 64: the upper half of the warp adds zeros).
+// ---------------------------------------------------------------------------------------------
+// dK / dV in the TRANSPOSED orientation.  One CTA per (batch, K/V head, tile of 128 keys) holds K
+// and V and sweeps the query tiles of the head group that see these keys.  Every product has the
+// keys as its M dimension:
+//     S^T  = K Q^T      dP^T = V dO^T      (K, V, Q, dO tiles all K-major in shared memory)
+//     dV  += P^T dO     dK  += dS^T Q      (A = P^T / dS^T straight from TENSOR memory, B MN-major)
+// so P^T and dS^T never go through shared memory: the thread that owns a key row turns its S^T
+// entries into 16-bit probabilities and stores them over its own S^T columns (two threads per
+// row, each over the first half of its 64 columns), the way the forward kernel hands P to its
+// second product, and likewise dS^T over dP^T.  The row
+// statistics belong to the query, i.e. to the COLUMN here; the 128 (lse, delta) pairs of a query
+// tile are brought into shared memory once per iteration and read by broadcast.
+// MMA order (one in-order stream): dV(i) : S^T(i+1) : dK(i) : dP^T(i+1).  S^T(i+1) may overwrite
+// P^T(i) and dP^T(i+1) may overwrite dS^T(i) without a barrier because they are issued behind the
+// products that read them.  Shared memory: K, V, two Q buffers, two dO buffers (6 x 32 KB).
+// Tensor memory: S^T / P^T | dP^T / dS^T | dV | dK (128 columns each).
+// ---------------------------------------------------------------------------------------------
+constexpr int kTK = 0, kTV = kTileBytes, kTQ0 = 2 * kTileBytes, kTQ1 = 3 * kTileBytes, kTDO0 = 4 * kTileBytes,
+              kTDO1 = 5 * kTileBytes, kTVec = 6 * kTileBytes;  // kTVec: [2 buffers][lse2 128 | delta 128] floats
+constexpr int kTVecBytes = 2 * 256 * 4;
+// fix_full, ld_full[2], it_done[2], s_full, dp_full, p_full, ds_full
+constexpr int kNumDkvtBars = 9;
+constexpr int dkvt_smem_bytes() { return 6 * kTileBytes + kTVecBytes + kNumDkvtBars * 8 + 16 + 1024; }
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    attn_bwd_dkv_t_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                          const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                          const __grid_constant__ CUtensorMap tmap_dv, const __grid_constant__ CUtensorMap tmap_dk,
+                          const BwdParams p) {
+  static_assert(HD == 128 || HD == 64, "head dim 128 or 64");
+  constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
+  constexpr uint32_t kIdS = make_idesc(kFmt, kFmt, 128, 128, 0, 0);  // S^T, dP^T: 128 keys x 128 queries
+  constexpr uint32_t kIdG = make_idesc(kFmt, kFmt, 128, HD, 0, 1);   // dV, dK: 128 keys x HD, B MN-major
+  constexpr int kDSteps = HD / 16;
+  constexpr int kOpBytes = kRows * HD * 2;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  float* vec = reinterpret_cast<float*>(smem + kTVec);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTVec + kTVecBytes);
+  uint64_t* fix_full = bars;     // K and V have landed
+  uint64_t* ld_full = bars + 1;  // [buffer] Q and dO of an iteration have landed
+  uint64_t* it_done = bars + 3;  // [buffer] every product that reads the buffer has completed
+  uint64_t* s_full = bars + 5;   // S^T is in tensor memory
+  uint64_t* dp_full = bars + 6;  // dP^T is in tensor memory
+  uint64_t* p_full = bars + 7;   // all rows of P^T stored (S^T read)
+  uint64_t* ds_full = bars + 8;  // all rows of dS^T stored (dP^T read)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumDkvtBars);
+  volatile uint32_t* abort_word = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int group = p.q_heads / p.kv_heads;
+
+  const int bh = blockIdx.x / p.num_kv_tiles;
+  const int tile = blockIdx.x - bh * p.num_kv_tiles;
+  const int batch = bh / p.kv_heads;
+  const int kvh = bh - batch * p.kv_heads;
+  const int row0 = tile * kRows;  // first key of the tile
+  int qt_lo = 0;
+  if (p.causal) qt_lo = max(0, row0 - p.causal_offset) / kRows;
+  const int n = max(0, p.num_q_tiles - qt_lo);  // query tiles per head that see these keys
+  const int total = group * n;
+
+  if (threadIdx.x == 0) {
+    mbar_init(fix_full, 1);
+    mbar_init(ld_full, 1);
+    mbar_init(ld_full + 1, 1);
+    mbar_init(it_done, 1);
+    mbar_init(it_done + 1, 1);
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_full, kSoftmaxThreads / 32);   // one arrival per warp
+    mbar_init(ds_full, kSoftmaxThreads / 32);
+    *abort_word = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_do);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0 && total > 0) {
+      mbar_arrive_expect_tx(fix_full, 2 * kOpBytes);
+      load_tile_4d<HD>(smem + kTK, &tmap_k, fix_full, row0, kvh, batch);
+      load_tile_4d<HD>(smem + kTV, &tmap_v, fix_full, row0, kvh, batch);
+      for (int i = 0; i < total; ++i) {
+        const int b = i & 1;
+        if (i >= 2 && !mbar_wait(it_done + b, ((i - 2) >> 1) & 1, abort_word)) break;
+        const int g = i / n;
+        const int qt = qt_lo + (i - g * n);
+        mbar_arrive_expect_tx(ld_full + b, 2 * kOpBytes);
+        load_tile_4d<HD>(smem + (b ? kTQ1 : kTQ0), &tmap_q, ld_full + b, qt * kRows, kvh * group + g, batch);
+        load_tile_4d<HD>(smem + (b ? kTDO1 : kTDO0), &tmap_do, ld_full + b, qt * kRows, kvh * group + g, batch);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && total > 0) {
+      const uint32_t sk = smem_u32(smem + kTK), sv = smem_u32(smem + kTV);
+      auto sq = [&](int b) { return smem_u32(smem + (b ? kTQ1 : kTQ0)); };
+      auto sdo = [&](int b) { return smem_u32(smem + (b ? kTDO1 : kTDO0)); };
+      // D[keys x HD] (+)= A^T-from-tensor-memory * B, B = an MN-major tile (rows = queries): 8 steps of 16 queries
+      // The 16-bit A tile sits in two pieces: queries 0..63 in columns 0..31 of the region, queries
+      // 64..127 in columns 64..95 (each of the two threads of a row writes over its own S columns).
+      auto mma_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate) {
+        const uint64_t b0 = make_desc_mnmajor_sw128(b_addr, kHalfBytes);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_f16_ts(d_tmem, a_tmem + (ks >> 2) * 64 + (ks & 3) * 8, b0 + ks * (2048 >> 4), kIdG,
+                      (accumulate || ks > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(fix_full, 0, abort_word);
+      if (ok) ok = mbar_wait(ld_full, 0, abort_word);
+      if (ok) {
+        tc_fence_after();
+        mma_128x128x128<false, false, kDSteps>(tmem_base + kTmS, sk, sq(0), kIdS, false);   // S^T(0)
+        umma_commit(s_full);
+        mma_128x128x128<false, false, kDSteps>(tmem_base + kTmDP, sv, sdo(0), kIdS, false);  // dP^T(0)
+        umma_commit(dp_full);
+      }
+      for (int i = 0; i < total && ok; ++i) {
+        const int b = i & 1;
+        if (!mbar_wait(p_full, i & 1, abort_word)) break;
+        tc_fence_after();
+        mma_ts(tmem_base + kTmAcc0, tmem_base + kTmS, sdo(b), i > 0);  // dV += P^T dO
+        if (i + 1 < total) {
+          if (!mbar_wait(ld_full + (b ^ 1), ((i + 1) >> 1) & 1, abort_word)) break;
+          tc_fence_after();
+          mma_128x128x128<false, false, kDSteps>(tmem_base + kTmS, sk, sq(b ^ 1), kIdS, false);  // S^T(i+1), behind dV(i)
+          umma_commit(s_full);
+        }
+        if (!mbar_wait(ds_full, i & 1, abort_word)) break;
+        tc_fence_after();
+        mma_ts(tmem_base + kTmAcc1, tmem_base + kTmDP, sq(b), i > 0);  // dK += dS^T Q
+        umma_commit(it_done + b);
+        if (i + 1 < total) {
+          mma_128x128x128<false, false, kDSteps>(tmem_base + kTmDP, sv, sdo(b ^ 1), kIdS, false);  // dP^T(i+1), behind dK(i)
+          umma_commit(dp_full);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- algebra, then the epilogue: two threads per KEY row ----------------
+    // Warps 2..5 take the query columns 0..63 of their rows, warps 6..9 the columns 64..127.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;
+    const int tid = threadIdx.x - 64;  // 0 .. 255
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int key = row0 + r;
+    // query q (global index) sees this key iff q >= q_min (and q < seq_q, which the statistics encode)
+    const int q_min = (key < p.seq_kv) ? (p.causal ? key - p.causal_offset : INT32_MIN) : INT32_MAX;
+    bool ok = true;
+    // The (lse2, delta) pairs of the 128 queries of a tile go to shared memory, one value per thread
+    // (threads 0..127 the statistic, 128..255 delta).  The values of iteration i + 1 are fetched at
+    // the top of iteration i and stored at its end, so the global-memory latency is off the chain.
+    auto fetch_stat = [&](int it) -> float {
+      float val = (tid < 128) ? INFINITY : 0.f;  // a query past the end: P = exp2(x - inf) = 0
+      if (it < total) {
+        const int g_ = it / n;
+        const int q_g = (qt_lo + (it - g_ * n)) * kRows + (tid & 127);
+        if (q_g < p.seq_q) {
+          const int64_t idx = (static_cast<int64_t>(batch) * p.q_heads + kvh * group + g_) * p.seq_q + q_g;
+          if (tid < 128)
+            val = p.lse_in ? lse_to_log2(__ldg(p.lse_in + idx)) : __ldg(p.lse2 + idx);
+          else
+            val = __ldg(p.delta + idx);
+        }
+      }
+      return val;
+    };
+    if (total > 0) {
+      vec[tid] = fetch_stat(0);
+      asm volatile("bar.sync 3, 256;" ::: "memory");
+    }
+    for (int i = 0; i < total; ++i) {
+      const int g = i / n;
+      const int qt = qt_lo + (i - g * n);
+      const int q_base = qt * kRows;
+      const float next_stat = fetch_stat(i + 1);
+      const float* lse_v = vec + (i & 1) * 256 + half * 64;
+      const float* dl_v = lse_v + 128;
+      const int q0 = q_base + half * 64;  // first query column of this thread
+      float pf[64];
+      if (ok && !mbar_wait(s_full, i & 1, abort_word)) ok = false;
+      if (ok) {
+        tc_fence_after();
+        uint32_t s64[64];
+        tmem_ld_32x32b_x64(lane_base + kTmS + half * 64, s64);
+        tmem_wait_ld();
+        uint32_t pw[32];
+        if (q0 >= q_min) {  // every query of the chunk sees this key: no per-element test
+#pragma unroll
+          for (int c = 0; c < 64; c += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse_v + c);
+            const float x0 = fmaf(__uint_as_float(s64[c]), p.scale_log2, -l4.x);
+            const float x1 = fmaf(__uint_as_float(s64[c + 1]), p.scale_log2, -l4.y);
+            const float x2 = fmaf(__uint_as_float(s64[c + 2]), p.scale_log2, -l4.z);
+            const float x3 = fmaf(__uint_as_float(s64[c + 3]), p.scale_log2, -l4.w);
+            const float2 e0 = exp2_poly2(make_float2(x0, x1));  // one pair on the FMA pipe, one on the SFU
+            pf[c] = e0.x;
+            pf[c + 1] = e0.y;
+            pf[c + 2] = ex2_approx(x2);
+            pf[c + 3] = ex2_approx(x3);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            pf[c] = (q0 + c >= q_min) ? ex2_approx(fmaf(__uint_as_float(s64[c]), p.scale_log2, -lse_v[c])) : 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) pw[c >> 1] = pack2<T>(pf[c], pf[c + 1]);
+        tmem_st_32x32b_x32(lane_base + kTmS + half * 64, pw);  // over the first half of this thread's own S columns
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      if (ok && !mbar_wait(dp_full, i & 1, abort_word)) ok = false;
+      if (ok) {
+        tc_fence_after();
+        uint32_t dp64[64];
+        tmem_ld_32x32b_x64(lane_base + kTmDP + half * 64, dp64);
+        tmem_wait_ld();
+        uint32_t dsw[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(dl_v + c);
+          dsw[c >> 1] = pack2<T>(pf[c] * (__uint_as_float(dp64[c]) - d4.x), pf[c + 1] * (__uint_as_float(dp64[c + 1]) - d4.y));
+          dsw[(c >> 1) + 1] =
+              pack2<T>(pf[c + 2] * (__uint_as_float(dp64[c + 2]) - d4.z), pf[c + 3] * (__uint_as_float(dp64[c + 3]) - d4.w));
+        }
+        tmem_st_32x32b_x32(lane_base + kTmDP + half * 64, dsw);
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+      // every thread is done with this iteration's statistics and with the other buffer (read one
+      // iteration ago): publish the next ones
+      vec[((i + 1) & 1) * 256 + tid] = next_stat;
+      asm volatile("bar.sync 3, 256;" ::: "memory");
+    }
+    if (ok && total > 0) ok = mbar_wait(it_done + ((total - 1) & 1), ((total - 1) >> 1) & 1, abort_word);
+    ok = bar_red_and(1, kSoftmaxThreads, ok);
+    if (ok) {
+      tc_fence_after();
+      // accumulators -> 16-bit tiles in the (now unused) Q / dO buffers -> TMA stores
+#pragma unroll
+      for (int o = 0; o < 2; ++o) {
+        uint8_t* stage = smem + (o == 0 ? kTQ0 : kTDO0);
+        const uint32_t acc = lane_base + (o == 0 ? kTmAcc0 : kTmAcc1);
+        const float f = o == 1 ? p.scale : 1.f;  // dK carries the softmax scale
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c4 = half * 2 + cc;
+          if (c4 * 32 >= HD) continue;
+          uint32_t v[32], w[16];
+          if (total > 0) {
+            tmem_ld_32x32b_x32(acc + c4 * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = 0u;  // no query sees these keys
+          }
+#pragma unroll
+          for (int k = 0; k < 32; k += 2)
+            w[k >> 1] = pack2<T>(__uint_as_float(v[k]) * f, __uint_as_float(v[k + 1]) * f);
+          store_row_chunk(stage, r, c4 * 32, w);
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (r == 0 && half == 0) {
+        tma_store_4d(&tmap_dv, smem + kTQ0, 0, row0, kvh, batch);
+        if (HD == 128) tma_store_4d(&tmap_dv, smem + kTQ0 + kHalfBytes, 64, row0, kvh, batch);
+        tma_store_4d(&tmap_dk, smem + kTDO0, 0, row0, kvh, batch);
+        if (HD == 128) tma_store_4d(&tmap_dk, smem + kTDO0 + kHalfBytes, 64, row0, kvh, batch);
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0 && threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusBwdTimeout);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, i] = sum_d dO[b, h, i, d] * O[b, h, i, d].  A row of HD 16-bit values is HD / 8 lanes
+// of 16 bytes; a warp takes 32 / (HD / 8) rows at a time and eight such groups, all loads issued
+// before the first use, so that enough bytes are in flight to run at memory speed.
 template <typename T, int HD>
 __global__ void attn_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta,
                                       int64_t rows, int q_heads, int seq_q, int64_t o_sb, int64_t o_sh, int64_t o_ss,
                                       int64_t do_sb, int64_t do_sh, int64_t do_ss) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  constexpr int kLanesPerRow = HD / 8;
+  constexpr int kRowsPerPass = 32 / kLanesPerRow;
+  constexpr int kPasses = 8;
   const int lane = threadIdx.x & 31;
-  const int64_t bh = row / seq_q;
-  const int i = static_cast<int>(row - bh * seq_q);
-  const int64_t b = bh / q_heads, h = bh - b * q_heads;
-  float acc = 0.f;
-  if (lane * 4 < HD) {
-    const uint2 ov = *reinterpret_cast<const uint2*>(o + b * o_sb + h * o_sh + i * o_ss + lane * 4);
-    const uint2 dv = *reinterpret_cast<const uint2*>(d_o + b * do_sb + h * do_sh + i * do_ss + lane * 4);
-    const T* oe = reinterpret_cast<const T*>(&ov);
-    const T* de = reinterpret_cast<const T*>(&dv);
+  const int sub = lane / kLanesPerRow, col = (lane % kLanesPerRow) * 8;
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t row_base = warp_id * (kRowsPerPass * kPasses);
+  uint4 ov[kPasses], dv[kPasses];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) acc += static_cast<float>(oe[k]) * static_cast<float>(de[k]);
+  for (int ps = 0; ps < kPasses; ++ps) {
+    const int64_t row = row_base + ps * kRowsPerPass + sub;
+    ov[ps] = make_uint4(0, 0, 0, 0);
+    dv[ps] = make_uint4(0, 0, 0, 0);
+    if (row < rows) {
+      const int r32 = static_cast<int>(row);  // the host keeps rows below 2^31: 32-bit divisions
+      const int bh = r32 / seq_q;
+      const int i = r32 - bh * seq_q;
+      const int b = bh / q_heads, h = bh - b * q_heads;
+      ov[ps] = *reinterpret_cast<const uint4*>(o + b * o_sb + h * o_sh + i * o_ss + col);
+      dv[ps] = *reinterpret_cast<const uint4*>(d_o + b * do_sb + h * do_sh + i * do_ss + col);
+    }
   }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) delta[row] = acc;
+  for (int ps = 0; ps < kPasses; ++ps) {
+    const T* oe = reinterpret_cast<const T*>(&ov[ps]);
+    const T* de = reinterpret_cast<const T*>(&dv[ps]);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc += static_cast<float>(oe[k]) * static_cast<float>(de[k]);
+#pragma unroll
+    for (int sft = kLanesPerRow / 2; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+    const int64_t row = row_base + ps * kRowsPerPass + sub;
+    if (lane % kLanesPerRow == 0 && row < rows) delta[row] = acc;
+  }
 }
 
 struct BwdMaps {
@@ -609,15 +935,17 @@ int encode_bshd(CUtensorMap* out, int dtype, const void* base, int head_dim, int
 template <typename T, int HD>
 int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const BwdParams& p, cudaStream_t stream) {
   auto k_dq = attn_bwd_kernel<T, kModeDQ, HD>;
-  auto k_dkv = attn_bwd_kernel<T, kModeDKV, HD>;
+  auto k_dkv = attn_bwd_dkv_t_kernel<T, HD>;
   static bool configured_dq[64] = {}, configured_dkv[64] = {};  // per instantiation and device ordinal
   int rc = ensure_dynamic_smem(k_dq, bwd_smem_bytes(kModeDQ), configured_dq, "cudaFuncSetAttribute(attention bwd dq smem)");
   if (rc) return rc;
-  rc = ensure_dynamic_smem(k_dkv, bwd_smem_bytes(kModeDKV), configured_dkv, "cudaFuncSetAttribute(attention bwd dkv smem)");
+  rc = ensure_dynamic_smem(k_dkv, dkvt_smem_bytes(), configured_dkv, "cudaFuncSetAttribute(attention bwd dkv smem)");
   if (rc) return rc;
   const int64_t rows = static_cast<int64_t>(a.batch) * a.q_heads * a.seq_q;
+  if (rows > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: batch * q_heads * seq_q must be below 2^31");
   const int warps_per_block = 8;
-  attn_bwd_delta_kernel<T, HD><<<static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block),
+  const int64_t rows_per_block = static_cast<int64_t>(warps_per_block) * (32 / (HD / 8)) * 8;
+  attn_bwd_delta_kernel<T, HD><<<static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block),
                              warps_per_block * 32, 0, stream>>>(
       static_cast<const T*>(a.o), static_cast<const T*>(a.d_o), p.delta, rows, a.q_heads, a.seq_q, a.o_stride_b,
       a.o_stride_h, a.o_stride_s, a.do_stride_b, a.do_stride_h, a.do_stride_s);
@@ -628,7 +956,7 @@ int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const
   rc = check_cuda(cudaGetLastError(), "attn_bwd_kernel (dQ) launch");
   if (rc) return rc;
   const int grid_dkv = a.batch * a.kv_heads * p.num_kv_tiles;
-  k_dkv<<<grid_dkv, kBwdThreads, bwd_smem_bytes(kModeDKV), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dv, tm.dk, p);
+  k_dkv<<<grid_dkv, kBwdThreads, dkvt_smem_bytes(), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dv, tm.dk, p);
   return check_cuda(cudaGetLastError(), "attn_bwd_kernel (dK, dV) launch");
 }
 
