@@ -6,31 +6,32 @@
 //
 // Three launches.  Only the forward's output O is required from the forward call; its row
 // log-sum-exp, if the caller kept it, spares the statistics sweep of the second launch:
-//   1. attn_bwd_delta_kernel: delta (one warp per query row).
-//   2. attn_bwd_kernel<T, kModeDQ>: one CTA per (batch, query head, tile of 128 queries).  It holds
-//      Q and dO and sweeps the visible K/V tiles: first a statistics sweep when no LSE was given
-//      (S = Q K^T only, running row maximum and sum -> LSE, kept in registers and written to the
-//      workspace), then the gradient sweep (S, dP -> dS in shared memory -> dQ += dS K).
-//   3. attn_bwd_kernel<T, kModeDKV>: one CTA per (batch, K/V head, tile of 128 keys).  It holds K
-//      and V and sweeps the query tiles of every query head of the group that see these keys:
-//      S, dP -> P, dS in shared memory -> dV += P^T dO, dK += dS^T Q.
+//   1. attn_bwd_delta_kernel: delta.
+//   2. attn_bwd_dq_kernel: one CTA per (batch, query head, tile of 128 queries).  It holds Q and dO
+//      and sweeps the visible K/V tiles: first a statistics sweep when no LSE was given, then the
+//      gradient sweep (S, dP -> dS -> dQ += dS K).
+//   3. attn_bwd_dkv_t_kernel: one CTA per (batch, K/V head, tile of 128 keys).  It holds K and V
+//      and sweeps the query tiles of every query head of the group that see these keys, with the
+//      keys as the M dimension of every product: S^T, dP^T -> P^T, dS^T -> dV += P^T dO,
+//      dK += dS^T Q.
 // No atomics: every output element is accumulated by one CTA in a fixed order, so results do not
 // depend on the grid or on how heads are sharded over devices.
 //
-// All five products are tcgen05 MMAs (M = N = K = 128, fp32 accumulators in tensor memory).  Every
-// operand tile is 128 rows x 128 16-bit columns stored as two 64-column blocks of 16 KB with the
-// 128-byte swizzle -- what TMA writes for Q, K, V, dO and what the softmax threads write for P and
-// dS -- and is described to the tensor core as K-major (contraction along the 128-byte rows) or
-// MN-major (contraction along the row index) as the product needs:
-//   S  = Q K^T    A = Q  K-major    B = K  K-major       dV += P^T dO   A = P   MN-major  B = dO MN-major
-//   dP = dO V^T   A = dO K-major    B = V  K-major       dK += dS^T Q   A = dS  MN-major  B = Q  MN-major
-//                                                        dQ += dS K     A = dS  K-major   B = K  MN-major
+// All products are tcgen05 MMAs (M = 128, fp32 accumulators in tensor memory).  An operand tile in
+// shared memory is 128 rows x head-dim 16-bit columns in 64-column blocks of 16 KB with the
+// 128-byte swizzle, as TMA writes it, and is described to the tensor core as K-major (contraction
+// along the 128-byte rows) or MN-major (contraction along the row index) as the product needs.
+// The probabilities and dS never go through shared memory: the threads that computed them store
+// them to tensor memory as 16-bit pairs over the columns they were computed from, and the next
+// product takes them from there as its A operand (the forward kernel's way of handing P on).
+//   S   = Q K^T    A = Q  K-major   B = K  K-major      dQ += dS K     A = dS   (TMEM)  B = K  MN-major
+//   dP  = dO V^T   A = dO K-major   B = V  K-major
+//   S^T = K Q^T    A = K  K-major   B = Q  K-major      dV += P^T dO   A = P^T  (TMEM)  B = dO MN-major
+//   dP^T= V dO^T   A = V  K-major   B = dO K-major      dK += dS^T Q   A = dS^T (TMEM)  B = Q  MN-major
 //
 // Roles (10 warps): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 2..9 the
-// softmax algebra (two threads per query row = lane of tensor memory, 64 columns each), then the
-// epilogue.  Within an iteration: S -> (P while dP is computed) -> (dS while dV accumulates) ->
-// dK or dQ; the dQ kernel loads the next K / V tiles meanwhile (two buffers), the dK/dV kernel
-// has no shared memory left for that.  Every wait is bounded.
+// softmax algebra (two threads per lane of tensor memory, 64 columns each), then the epilogue.
+// Every wait is bounded.
 #include <type_traits>
 
 #include "common.cuh"
@@ -45,22 +46,18 @@ constexpr int kBwdThreads = 320;      // TMA warp, MMA warp, eight softmax / epi
 constexpr int kSoftmaxThreads = 256;  // two threads per query row, 64 columns each
 constexpr int kTileBytes = kRows * kD * 2;  // 32 KB
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column block
-constexpr int kModeDQ = 0, kModeDKV = 1;
 
-// Shared-memory tiles.  dQ kernel: Q, dO (held), two K and two V buffers (streamed, the next tiles
-// load while the current ones are used), dS.  dK/dV kernel: K, V (held), two Q buffers and one dO
-// buffer (streamed: the next Q loads during the iteration, the next dO as soon as dV += P^T dO has
-// read the current one), P, dS.
+// Shared-memory tiles of the dQ kernel (32 KB slots): Q, dO (held), two K and two V buffers (streamed,
+// the next tiles load while the current ones are used) and a staging tile (statistics exchange, epilogue).
 constexpr int kOffQ = 0, kOffDO = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 3 * kTileBytes;
-constexpr int kOffP = 4 * kTileBytes, kOffDS = 5 * kTileBytes;
-constexpr int kOffK1 = kOffP, kOffV1 = 6 * kTileBytes;  // dQ kernel only (it has no P tile)
-constexpr int kOffQ1 = 6 * kTileBytes;                  // dK/dV kernel: second Q buffer
-constexpr int kNumTiles[2] = {7, 7};                    // by mode
-// fix_full, ld_full[2], s_full[2], pds_full, it_done[2], dp_full, p_full, do_full, do_free
-constexpr int kNumBwdBars = 12;
-constexpr int bwd_smem_bytes(int mode) { return kNumTiles[mode] * kTileBytes + kNumBwdBars * 8 + 16 + 1024; }
+constexpr int kOffK1 = 4 * kTileBytes, kOffDS = 5 * kTileBytes, kOffV1 = 6 * kTileBytes;
+constexpr int kDqTiles = 7;
+// fix_full, ld_full[2], s_full[2], pds_full, it_done[2], dp_full
+constexpr int kNumDqBars = 9;
+constexpr int dq_smem_bytes() { return kDqTiles * kTileBytes + kNumDqBars * 8 + 16 + 1024; }
 // Tensor-memory columns.  The dQ kernel has one accumulator and uses the fourth quarter as a second
-// S buffer, so that the next score product runs while the algebra reads the current one.
+// S buffer, so that the next score product runs while the algebra reads the current one; the dK / dV
+// kernel has two accumulators.
 constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384, kTmS1 = 384;
 constexpr float kLog2eBwd = 1.4426950408889634f;
 constexpr int kStatusBwdTimeout = 64;
@@ -161,36 +158,38 @@ __device__ __forceinline__ void load_tile_4d(uint8_t* dst, const CUtensorMap* tm
   if (HD == 128) tma_load_4d(dst + kHalfBytes, tmap, bar, 64, row0, head, batch);
 }
 
-template <typename T, int MODE, int HD>
+// ---------------------------------------------------------------------------------------------
+// dQ.  One CTA per (batch, query head, tile of 128 queries) holds Q and dO and sweeps the visible
+// K / V tiles: first a statistics sweep when no LSE was given (S = Q K^T only; running row maximum
+// and sum -> LSE, kept in registers and written to the workspace), then the gradient sweep
+//     S = Q K^T    dP = dO V^T    dS = P o (dP - delta)    dQ += dS K
+// with two K / V buffers (the next tiles load while the current ones are used) and two S buffers in
+// tensor memory (S_0 | dP | dQ | S_1), so that the next score product runs under the algebra.  dS
+// goes back to tensor memory as 16-bit pairs over dP and is the A operand of the dQ product there.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-    attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
-                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                    const __grid_constant__ CUtensorMap tmap_out0,  // dQ (kModeDQ) or dV (kModeDKV)
-                    const __grid_constant__ CUtensorMap tmap_out1,  // dK (kModeDKV)
-                    const BwdParams p) {
-  constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
+    attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                       const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                       const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
   static_assert(HD == 128 || HD == 64, "head dim 128 or 64");
+  constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
   constexpr uint32_t kIdKK = make_idesc(kFmt, kFmt, 128, 128, 0, 0);  // S, dP: 128 x 128, contraction over the head dim
-  constexpr uint32_t kIdKM = make_idesc(kFmt, kFmt, 128, HD, 0, 1);   // dQ: 128 x HD
-  constexpr uint32_t kIdMM = make_idesc(kFmt, kFmt, 128, HD, 1, 1);   // dV, dK: 128 x HD
+  constexpr uint32_t kIdKM = make_idesc(kFmt, kFmt, 128, HD, 0, 1);   // dQ: 128 x HD, B MN-major
   constexpr int kDSteps = HD / 16;                                     // K steps of a contraction over the head dim
   constexpr int kOpBytes = kRows * HD * 2;                             // bytes TMA brings per operand tile
-  constexpr bool DQ = MODE == kModeDQ;
+  constexpr int kBufs = 2;                                             // K / V buffers
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  constexpr int kBufs = 2;  // buffers for the streamed tiles (dQ kernel: K and V; dK/dV kernel: Q)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kNumTiles[MODE] * kTileBytes);
-  uint64_t* fix_full = bars;      // the tiles held for the whole item have landed
-  uint64_t* ld_full = bars + 1;   // [buffer] the streamed tiles of an iteration have landed
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDqTiles * kTileBytes);
+  uint64_t* fix_full = bars;      // Q and dO have landed
+  uint64_t* ld_full = bars + 1;   // [buffer] the K (and V) tiles of an iteration have landed
   uint64_t* s_full = bars + 3;    // [S buffer] S is in tensor memory
-  uint64_t* pds_full = bars + 5;  // all rows of P / dS written (and S / dP read)
+  uint64_t* pds_full = bars + 5;  // all rows of dS stored (and S / dP read)
   uint64_t* it_done = bars + 6;   // [buffer] the last MMAs of an iteration that used it have completed
   uint64_t* dp_full = bars + 8;   // dP is in tensor memory (gradient iterations)
-  uint64_t* p_full = bars + 9;    // all rows of P written (dK/dV kernel)
-  uint64_t* do_full = bars + 10;  // (dK/dV kernel) the iteration's dO tile has landed
-  uint64_t* do_free = bars + 11;  // (dK/dV kernel) dV += P^T dO, the last reader of the dO tile, has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBwdBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumDqBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -198,34 +197,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int group = p.q_heads / p.kv_heads;
 
   // ---- work item ----
-  int batch, kvh, row0;          // row0: first query (DQ) / first key (DKV) of the held tile
-  int head = 0;                  // DQ: the query head
-  int n = 0;                     // DQ: visible K/V tiles;  DKV: query tiles per head that see these keys
-  int qt_lo = 0;                 // DKV: first such query tile
-  if (DQ) {
-    const int bh = blockIdx.x / p.num_q_tiles;
-    const int tile = p.num_q_tiles - 1 - (blockIdx.x - bh * p.num_q_tiles);  // heaviest tiles first
-    batch = bh / p.q_heads;
-    head = bh - batch * p.q_heads;
-    kvh = head / group;
-    row0 = tile * kRows;
-    n = p.num_kv_tiles;
-    if (p.causal) {
-      const int last_col = row0 + kRows - 1 + p.causal_offset;
-      n = last_col < 0 ? 0 : min(last_col / kRows + 1, p.num_kv_tiles);
-    }
-  } else {
-    const int bh = blockIdx.x / p.num_kv_tiles;
-    const int tile = blockIdx.x - bh * p.num_kv_tiles;
-    batch = bh / p.kv_heads;
-    kvh = bh - batch * p.kv_heads;
-    row0 = tile * kRows;
-    if (p.causal) qt_lo = max(0, row0 - p.causal_offset) / kRows;
-    n = max(0, p.num_q_tiles - qt_lo);
+  const int bh = blockIdx.x / p.num_q_tiles;
+  const int tile = p.num_q_tiles - 1 - (blockIdx.x - bh * p.num_q_tiles);  // heaviest tiles first
+  const int batch = bh / p.q_heads;
+  const int head = bh - batch * p.q_heads;
+  const int kvh = head / group;
+  const int row0 = tile * kRows;  // first query of the tile
+  int n = p.num_kv_tiles;         // visible K / V tiles
+  if (p.causal) {
+    const int last_col = row0 + kRows - 1 + p.causal_offset;
+    n = last_col < 0 ? 0 : min(last_col / kRows + 1, p.num_kv_tiles);
   }
-  // dQ kernel: a statistics sweep over the n tiles first, unless the caller supplied the forward's LSE
-  const int n_stats = (DQ && p.lse_in == nullptr) ? n : 0;
-  const int total = DQ ? n_stats + n : group * n;  // iterations
+  // a statistics sweep over the n tiles first, unless the caller supplied the forward's LSE
+  const int n_stats = p.lse_in == nullptr ? n : 0;
+  const int total = n_stats + n;  // iterations
 
   if (threadIdx.x == 0) {
     mbar_init(fix_full, 1);
@@ -237,9 +222,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     mbar_init(it_done, 1);
     mbar_init(it_done + 1, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_full, kSoftmaxThreads);
-    mbar_init(do_full, 1);
-    mbar_init(do_free, 1);
     *abort_word = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -261,95 +243,60 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     // ---------------- TMA producer ----------------
     if (lane == 0 && total > 0) {
       mbar_arrive_expect_tx(fix_full, 2 * kOpBytes);
-      if (DQ) {
-        load_tile_4d<HD>(smem + kOffQ, &tmap_q, fix_full, row0, head, batch);
-        load_tile_4d<HD>(smem + kOffDO, &tmap_do, fix_full, row0, head, batch);
-      } else {
-        load_tile_4d<HD>(smem + kOffK, &tmap_k, fix_full, row0, kvh, batch);
-        load_tile_4d<HD>(smem + kOffV, &tmap_v, fix_full, row0, kvh, batch);
-      }
+      load_tile_4d<HD>(smem + kOffQ, &tmap_q, fix_full, row0, head, batch);
+      load_tile_4d<HD>(smem + kOffDO, &tmap_do, fix_full, row0, head, batch);
       for (int i = 0; i < total; ++i) {
         const int buf = i % kBufs;
         // the MMAs of the iteration that last used this buffer have finished reading it
         if (i >= kBufs && !mbar_wait(it_done + buf, ((i - kBufs) / kBufs) & 1, abort_word)) break;
         uint64_t* full = ld_full + buf;
-        if (DQ) {
-          const bool stats = i < n_stats;
-          const int j = stats ? i : i - n_stats;
-          mbar_arrive_expect_tx(full, stats ? kOpBytes : 2 * kOpBytes);
-          load_tile_4d<HD>(smem + (buf ? kOffK1 : kOffK), &tmap_k, full, j * kRows, kvh, batch);
-          if (!stats) load_tile_4d<HD>(smem + (buf ? kOffV1 : kOffV), &tmap_v, full, j * kRows, kvh, batch);
-        } else {
-          const int g = i / n;
-          const int qt = qt_lo + (i - g * n);
-          mbar_arrive_expect_tx(full, kOpBytes);
-          load_tile_4d<HD>(smem + (buf ? kOffQ1 : kOffQ), &tmap_q, full, qt * kRows, kvh * group + g, batch);
-          // one dO buffer: free once the previous iteration's dV product has read it
-          if (i > 0 && !mbar_wait(do_free, (i - 1) & 1, abort_word)) break;
-          mbar_arrive_expect_tx(do_full, kOpBytes);
-          load_tile_4d<HD>(smem + kOffDO, &tmap_do, do_full, qt * kRows, kvh * group + g, batch);
-        }
+        const bool stats = i < n_stats;
+        const int j = stats ? i : i - n_stats;
+        mbar_arrive_expect_tx(full, stats ? kOpBytes : 2 * kOpBytes);
+        load_tile_4d<HD>(smem + (buf ? kOffK1 : kOffK), &tmap_k, full, j * kRows, kvh, batch);
+        if (!stats) load_tile_4d<HD>(smem + (buf ? kOffV1 : kOffV), &tmap_v, full, j * kRows, kvh, batch);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && total > 0) {
-      const uint32_t sq = smem_u32(smem + kOffQ), sdo = smem_u32(smem + kOffDO), sp = smem_u32(smem + kOffP),
-                     sds = smem_u32(smem + kOffDS);
+      const uint32_t sq = smem_u32(smem + kOffQ), sdo = smem_u32(smem + kOffDO);
       bool ok = mbar_wait(fix_full, 0, abort_word);
-      // S of iteration `it`, once its streamed tiles have landed.  dQ kernel: into S buffer it & 1.
+      // S of iteration `it`, once its K tile has landed, into S buffer it & 1
       auto issue_s = [&](int it) -> bool {
         const int b = it % kBufs;
         if (!mbar_wait(ld_full + b, (it / kBufs) & 1, abort_word)) return false;
         tc_fence_after();
-        const int sb = DQ ? (it & 1) : 0;
-        if (DQ)
-          mma_128x128x128<false, false, kDSteps>(tmem_base + (sb ? kTmS1 : kTmS), sq,
-                                                 smem_u32(smem + (b ? kOffK1 : kOffK)), kIdKK, false);
-        else
-          mma_128x128x128<false, false, kDSteps>(tmem_base + kTmS, smem_u32(smem + (b ? kOffQ1 : kOffQ)),
-                                                 smem_u32(smem + kOffK), kIdKK, false);
+        const int sb = it & 1;
+        mma_128x128x128<false, false, kDSteps>(tmem_base + (sb ? kTmS1 : kTmS), sq, smem_u32(smem + (b ? kOffK1 : kOffK)),
+                                               kIdKK, false);
         umma_commit(s_full + sb);
         return true;
       };
-      if (ok && DQ) ok = issue_s(0);
+      if (ok) ok = issue_s(0);
       for (int i = 0; i < total && ok; ++i) {
         const int buf = i % kBufs;
-        const bool stats = DQ && i < n_stats;
-        const uint32_t sk = smem_u32(smem + ((DQ && buf) ? kOffK1 : kOffK)),
-                       sv = smem_u32(smem + ((DQ && buf) ? kOffV1 : kOffV));
-        // The algebra on S starts while dP is still being computed, and dV is issued as soon as P
-        // is in shared memory, while dS is still being computed.  The dQ kernel also issues the
-        // next iteration's S now (its S buffer was released by the previous iteration's algebra).
-        if (!DQ && !issue_s(i)) break;
-        const int gi = DQ ? i - n_stats : i;  // index among the gradient iterations
+        const bool stats = i < n_stats;
+        const uint32_t sk = smem_u32(smem + (buf ? kOffK1 : kOffK)), sv = smem_u32(smem + (buf ? kOffV1 : kOffV));
+        const int gi = i - n_stats;  // index among the gradient iterations
+        // The algebra on S starts while dP is still being computed; the next iteration's S is issued
+        // now as well (its S buffer was released by the previous iteration's algebra).
         if (!stats) {
-          if (!DQ) {
-            if (!mbar_wait(do_full, i & 1, abort_word)) break;
-            tc_fence_after();
-          }
           mma_128x128x128<false, false, kDSteps>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
           umma_commit(dp_full);
         }
-        if (DQ && i + 1 < total && !issue_s(i + 1)) break;
-        if (!stats) {
-          if (!DQ) {
-            if (!mbar_wait(p_full, gi & 1, abort_word)) break;
-            tc_fence_after();
-            mma_128x128x128<true, true>(tmem_base + kTmAcc0, sp, sdo, kIdMM, gi > 0);  // dV += P^T dO
-            umma_commit(do_free);
-          }
-        }
+        if (i + 1 < total && !issue_s(i + 1)) break;
         if (!mbar_wait(pds_full, i & 1, abort_word)) break;
         tc_fence_after();
         if (!stats) {
-          if (DQ) {
-            mma_128x128x128<false, true>(tmem_base + kTmAcc0, sds, sk, kIdKM, gi > 0);  // dQ += dS K
-          } else {
-            mma_128x128x128<true, true>(tmem_base + kTmAcc1, sds, smem_u32(smem + (buf ? kOffQ1 : kOffQ)), kIdMM,
-                                        gi > 0);  // dK += dS^T Q
-          }
+          // dQ += dS K, A = dS from tensor memory (keys 0..63 in columns 0..31 of the dP region,
+          // keys 64..127 in columns 64..95), B = the K tile read MN-major
+          const uint64_t b0 = make_desc_mnmajor_sw128(sk, kHalfBytes);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_f16_ts(tmem_base + kTmAcc0, tmem_base + kTmDP + (ks >> 2) * 64 + (ks & 3) * 8, b0 + ks * (2048 >> 4),
+                        kIdKM, (gi > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(it_done + buf);
       }
@@ -365,45 +312,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float ninf = -INFINITY;
     float m = ninf, l = 0.f, lse2 = INFINITY, dl = 0.f;
-    int q_g = row0 + r;  // DQ: fixed; DKV: set per iteration
-    int64_t stat_idx = 0;
-    if (DQ) {
-      stat_idx = (static_cast<int64_t>(batch) * p.q_heads + head) * p.seq_q + q_g;
-      if (q_g < p.seq_q) {
-        dl = __ldg(p.delta + stat_idx);
-        if (p.lse_in) lse2 = lse_to_log2(__ldg(p.lse_in + stat_idx));
-      }
+    const int q_g = row0 + r;
+    const int64_t stat_idx = (static_cast<int64_t>(batch) * p.q_heads + head) * p.seq_q + q_g;
+    if (q_g < p.seq_q) {
+      dl = __ldg(p.delta + stat_idx);
+      if (p.lse_in) lse2 = lse_to_log2(__ldg(p.lse_in + stat_idx));
+    }
+    // key j (global index) is visible to this row iff j <= col_hi
+    int col_hi = -1;
+    if (q_g < p.seq_q) {
+      col_hi = p.seq_kv - 1;
+      if (p.causal) col_hi = min(col_hi, q_g + p.causal_offset);
     }
     // After a wait has given up the loop keeps its shape (arrivals and named barriers) but skips the work.
     bool ok = true;
     for (int i = 0; i < total; ++i) {
-      const bool stats = DQ && i < n_stats;
-      int kv_base;
-      if (DQ) {
-        kv_base = (stats ? i : i - n_stats) * kRows;
-      } else {
-        const int g = i / n;
-        const int qt = qt_lo + (i - g * n);
-        q_g = qt * kRows + r;
-        kv_base = row0;
-        stat_idx = (static_cast<int64_t>(batch) * p.q_heads + kvh * group + g) * p.seq_q + q_g;
-        lse2 = INFINITY;
-        dl = 0.f;
-        if (q_g < p.seq_q) {
-          lse2 = p.lse_in ? lse_to_log2(__ldg(p.lse_in + stat_idx)) : __ldg(p.lse2 + stat_idx);
-          dl = __ldg(p.delta + stat_idx);
-        }
-      }
-      // key j (global index) is visible to this row iff j <= col_hi
-      int col_hi = -1;
-      if (q_g < p.seq_q) {
-        col_hi = p.seq_kv - 1;
-        if (p.causal) col_hi = min(col_hi, q_g + p.causal_offset);
-      }
-      const int sb = DQ ? (i & 1) : 0;  // S buffer of this iteration
+      const bool stats = i < n_stats;
+      const int kv_base = (stats ? i : i - n_stats) * kRows;
+      const int sb = i & 1;  // S buffer of this iteration
       const uint32_t s_base = lane_base + (sb ? kTmS1 : kTmS);
-      if (ok && !mbar_wait(s_full + sb, (DQ ? (i >> 1) : i) & 1, abort_word)) ok = false;
-      const int gi = DQ ? i - n_stats : i;  // index among the gradient iterations
+      if (ok && !mbar_wait(s_full + sb, (i >> 1) & 1, abort_word)) ok = false;
+      const int gi = i - n_stats;  // index among the gradient iterations
       if (stats) {
         if (ok) {
           tc_fence_after();
@@ -461,17 +390,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 pf[cc * 32 + k] =
                     (kv0 + k <= col_hi) ? ex2_approx(fmaf(__uint_as_float(s[k]), p.scale_log2, -lse2)) : 0.f;
             }
-            if (!DQ) {
-              uint32_t pw[16];
-#pragma unroll
-              for (int k = 0; k < 32; k += 2) pw[k >> 1] = pack2<T>(pf[cc * 32 + k], pf[cc * 32 + k + 1]);
-              store_row_chunk(smem + kOffP, r, c4 * 32, pw);
-            }
           }
-        }
-        if (!DQ) {
-          fence_proxy_async_smem();
-          mbar_arrive(p_full);
         }
         if (ok && !mbar_wait(dp_full, gi & 1, abort_word)) ok = false;
         if (ok) {
@@ -479,22 +398,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
           uint32_t dp64[64];
           tmem_ld_32x32b_x64(lane_base + kTmDP + half * 64, dp64);
           tmem_wait_ld();
+          // dS stays in tensor memory: 16-bit pairs over the first half of this thread's own dP
+          // columns, from where the dQ product takes it as its A operand
+          uint32_t dsw[32];
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            const int c4 = half * 2 + cc;
-            const uint32_t* dp = dp64 + cc * 32;
-            uint32_t dsw[16];
-#pragma unroll
-            for (int k = 0; k < 32; k += 2)
-              dsw[k >> 1] = pack2<T>(pf[cc * 32 + k] * (__uint_as_float(dp[k]) - dl),
-                                     pf[cc * 32 + k + 1] * (__uint_as_float(dp[k + 1]) - dl));
-            store_row_chunk(smem + kOffDS, r, c4 * 32, dsw);
-          }
+          for (int k = 0; k < 64; k += 2)
+            dsw[k >> 1] = pack2<T>(pf[k] * (__uint_as_float(dp64[k]) - dl), pf[k + 1] * (__uint_as_float(dp64[k + 1]) - dl));
+          tmem_st_32x32b_x32(lane_base + kTmDP + half * 64, dsw);
+          tmem_wait_st();
         }
       }
-      if (DQ && stats && i == n_stats - 1) {
-        // The two threads of a row combine their (max, sum) over the dS tile, which nothing uses
-        // before the gradient sweep; both evaluate the same expression, so they agree bitwise.
+      if (stats && i == n_stats - 1) {
+        // The two threads of a row combine their (max, sum) through the staging tile, which nothing
+        // uses before the epilogue; both evaluate the same expression, so they agree bitwise.
         float2* xchg = reinterpret_cast<float2*>(smem + kOffDS);
         xchg[half * kRows + r] = make_float2(m, l);
         asm volatile("bar.sync 3, 256;" ::: "memory");
@@ -506,7 +422,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if (half == 0 && q_g < p.seq_q) p.lse2[stat_idx] = lse2;
       }
       tc_fence_before();
-      if (!stats) fence_proxy_async_smem();
       mbar_arrive(pds_full);
     }
     if (ok && total > 0)
@@ -515,43 +430,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     ok = bar_red_and(1, kSoftmaxThreads, ok);
     if (ok) {
       tc_fence_after();
-      // accumulators -> 16-bit tiles in the (now unused) P / dS buffers -> TMA stores
-      constexpr int kOuts = DQ ? 1 : 2;
-#pragma unroll
-      for (int o = 0; o < kOuts; ++o) {
-        uint8_t* stage = smem + (DQ || o == 1 ? kOffDS : kOffP);
-        const uint32_t acc = lane_base + (o == 0 ? kTmAcc0 : kTmAcc1);
-        const float f = (DQ || o == 1) ? p.scale : 1.f;  // dQ and dK carry the softmax scale
+      // accumulator -> 16-bit tile in the staging buffer -> TMA stores
+      uint8_t* stage = smem + kOffDS;
 #pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c4 = half * 2 + cc;
-          if (c4 * 32 >= HD) continue;  // head dim 64: the accumulators have 64 columns
-          uint32_t v[32], w[16];
-          if (total > 0) {
-            tmem_ld_32x32b_x32(acc + c4 * 32, v);
-            tmem_wait_ld();
-          } else {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c4 = half * 2 + cc;
+        if (c4 * 32 >= HD) continue;  // head dim 64: the accumulator has 64 columns
+        uint32_t v[32], w[16];
+        if (total > 0) {
+          tmem_ld_32x32b_x32(lane_base + kTmAcc0 + c4 * 32, v);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] = 0u;  // no query sees these keys / no key is visible
-          }
-#pragma unroll
-          for (int k = 0; k < 32; k += 2)
-            w[k >> 1] = pack2<T>(__uint_as_float(v[k]) * f, __uint_as_float(v[k + 1]) * f);
-          store_row_chunk(stage, r, c4 * 32, w);
+          for (int k = 0; k < 32; ++k) v[k] = 0u;  // no key is visible
         }
+#pragma unroll
+        for (int k = 0; k < 32; k += 2)
+          w[k >> 1] = pack2<T>(__uint_as_float(v[k]) * p.scale, __uint_as_float(v[k + 1]) * p.scale);  // dQ carries the softmax scale
+        store_row_chunk(stage, r, c4 * 32, w);
       }
       fence_proxy_async_smem();
       asm volatile("bar.sync 2, 256;" ::: "memory");
       if (r == 0 && half == 0) {
-        if (DQ) {
-          tma_store_4d(&tmap_out0, smem + kOffDS, 0, row0, head, batch);
-          if (HD == 128) tma_store_4d(&tmap_out0, smem + kOffDS + kHalfBytes, 64, row0, head, batch);
-        } else {
-          tma_store_4d(&tmap_out0, smem + kOffP, 0, row0, kvh, batch);
-          if (HD == 128) tma_store_4d(&tmap_out0, smem + kOffP + kHalfBytes, 64, row0, kvh, batch);
-          tma_store_4d(&tmap_out1, smem + kOffDS, 0, row0, kvh, batch);
-          if (HD == 128) tma_store_4d(&tmap_out1, smem + kOffDS + kHalfBytes, 64, row0, kvh, batch);
-        }
+        tma_store_4d(&tmap_dq, smem + kOffDS, 0, row0, head, batch);
+        if (HD == 128) tma_store_4d(&tmap_dq, smem + kOffDS + kHalfBytes, 64, row0, head, batch);
         tma_store_commit();
         tma_store_wait<0>();
       }
@@ -934,10 +836,10 @@ int encode_bshd(CUtensorMap* out, int dtype, const void* base, int head_dim, int
 
 template <typename T, int HD>
 int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const BwdParams& p, cudaStream_t stream) {
-  auto k_dq = attn_bwd_kernel<T, kModeDQ, HD>;
+  auto k_dq = attn_bwd_dq_kernel<T, HD>;
   auto k_dkv = attn_bwd_dkv_t_kernel<T, HD>;
   static bool configured_dq[64] = {}, configured_dkv[64] = {};  // per instantiation and device ordinal
-  int rc = ensure_dynamic_smem(k_dq, bwd_smem_bytes(kModeDQ), configured_dq, "cudaFuncSetAttribute(attention bwd dq smem)");
+  int rc = ensure_dynamic_smem(k_dq, dq_smem_bytes(), configured_dq, "cudaFuncSetAttribute(attention bwd dq smem)");
   if (rc) return rc;
   rc = ensure_dynamic_smem(k_dkv, dkvt_smem_bytes(), configured_dkv, "cudaFuncSetAttribute(attention bwd dkv smem)");
   if (rc) return rc;
@@ -952,12 +854,12 @@ int launch_bwd_typed(const b200k_attention_bwd_args& a, const BwdMaps& tm, const
   rc = check_cuda(cudaGetLastError(), "attn_bwd_delta_kernel launch");
   if (rc) return rc;
   const int grid_dq = a.batch * a.q_heads * p.num_q_tiles;
-  k_dq<<<grid_dq, kBwdThreads, bwd_smem_bytes(kModeDQ), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dq, tm.dq, p);
-  rc = check_cuda(cudaGetLastError(), "attn_bwd_kernel (dQ) launch");
+  k_dq<<<grid_dq, kBwdThreads, dq_smem_bytes(), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dq, p);
+  rc = check_cuda(cudaGetLastError(), "attn_bwd_dq_kernel launch");
   if (rc) return rc;
   const int grid_dkv = a.batch * a.kv_heads * p.num_kv_tiles;
   k_dkv<<<grid_dkv, kBwdThreads, dkvt_smem_bytes(), stream>>>(tm.q, tm.d_o, tm.k, tm.v, tm.dv, tm.dk, p);
-  return check_cuda(cudaGetLastError(), "attn_bwd_kernel (dK, dV) launch");
+  return check_cuda(cudaGetLastError(), "attn_bwd_dkv_t_kernel launch");
 }
 
 }  // namespace
