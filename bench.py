@@ -7,14 +7,15 @@ batch 4, 32 heads, S = 4096, head dim 128.  With N > 1 it is ONE problem sharded
 heads of every batch element per GPU, no data-path collective): strong scaling.  The other
 workloads of the metric -- ``gemm_f16`` (2048^3, fp32 out), ``attn_noncausal`` (f16 B8 H32 S1024),
 ``paged_decode`` (64 sequences, GQA 32/8, page 16) and ``gemm_fp8`` (8192^3 e4m3, bf16 out;
-column-parallel over N with N > 1) -- are measured in the same run and reported under
+column-parallel over N with N > 1) -- and the backward of the headline problem
+(``attn_bwd_causal``, a next-row of the path) are measured in the same run and reported under
 ``"workloads"`` in the same JSON line, each with its own roofline, end-to-end figure, CPU baseline
 (N = 1) and a parity figure against the CPU oracle on a sampled slice (computed after the timed
 region).  ``--no-extras`` measures the headline workload only.
 
 A step is one pass of the kernel over one batch of synthetic inputs.  Each step is timed with
-CUDA events on the launching stream; between steps either the inputs are larger than L2 or L2 is
-flushed by writing a 256 MB buffer (stated in ``config.l2``).  Timed regions are bracketed by
+CUDA events on the launching stream; the inputs are larger than L2 (``config.l2`` says how; the
+small GEMM walks through operand sets and replays its steps from a CUDA graph).  Timed regions are bracketed by
 barrier + synchronize and the maximum over ranks is used.  Besides the per-step (burst) figure
 a sustained leg runs the headline kernel back to back for at least a second, with the SM clock
 sampled meanwhile, and is compared with the sustained cuBLAS figure of MEASURED_PEAKS.json.
@@ -570,7 +571,7 @@ WORKLOADS = {
 }
 DEFAULT = "attn_causal"
 # the other configurations of the metric, measured in the same run
-EXTRAS = ["gemm_f16", "attn_noncausal", "paged_decode", "gemm_fp8"]
+EXTRAS = ["gemm_f16", "attn_noncausal", "paged_decode", "gemm_fp8", "attn_bwd_causal"]
 
 
 # ---------------------------------------------------------------------------------------------
