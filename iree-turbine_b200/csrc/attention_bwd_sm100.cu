@@ -24,8 +24,8 @@
 // The probabilities and dS never go through shared memory: the threads that computed them store
 // them to tensor memory as 16-bit pairs over the columns they were computed from, and the next
 // product takes them from there as its A operand (the forward kernel's way of handing P on).
-//   S   = Q K^T    A = Q  K-major   B = K  K-major      dQ += dS K     A = dS   (TMEM)  B = K  MN-major
-//   dP  = dO V^T   A = dO K-major   B = V  K-major
+//   S   = Q K^T    A = Q  (TMEM)    B = K  K-major      dQ += dS K     A = dS   (TMEM)  B = K  MN-major
+//   dP  = dO V^T   A = dO (TMEM)    B = V  K-major
 //   S^T = K Q^T    A = K  K-major   B = Q  K-major      dV += P^T dO   A = P^T  (TMEM)  B = dO MN-major
 //   dP^T= V dO^T   A = V  K-major   B = dO K-major      dK += dS^T Q   A = dS^T (TMEM)  B = Q  MN-major
 //
@@ -47,18 +47,21 @@ constexpr int kSoftmaxThreads = 256;  // two threads per query row, 64 columns e
 constexpr int kTileBytes = kRows * kD * 2;  // 32 KB
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column block
 
-// Shared-memory tiles of the dQ kernel (32 KB slots): Q, dO (held), two K and two V buffers (streamed,
-// the next tiles load while the current ones are used) and a staging tile (statistics exchange, epilogue).
+// Shared-memory tiles of the dQ kernel (32 KB slots): Q and dO (copied to tensor memory in the
+// prologue; their slots then become the third K / V buffer), two more K and V buffers (a ring of
+// three, so that a tile is loaded an iteration and a half before its score product) and a staging
+// tile (statistics exchange, epilogue).
 constexpr int kOffQ = 0, kOffDO = kTileBytes, kOffK = 2 * kTileBytes, kOffV = 3 * kTileBytes;
 constexpr int kOffK1 = 4 * kTileBytes, kOffDS = 5 * kTileBytes, kOffV1 = 6 * kTileBytes;
 constexpr int kDqTiles = 7;
-// fix_full, ld_full[2], s_full[2], pds_full, it_done[2], dp_full
-constexpr int kNumDqBars = 9;
+// fix_full, ld_full[3], it_done[3], s_full, s_free, pds_full, dp_full, a_ready
+constexpr int kNumDqBars = 12;
 constexpr int dq_smem_bytes() { return kDqTiles * kTileBytes + kNumDqBars * 8 + 16 + 1024; }
-// Tensor-memory columns.  The dQ kernel has one accumulator and uses the fourth quarter as a second
-// S buffer, so that the next score product runs while the algebra reads the current one; the dK / dV
-// kernel has two accumulators.
-constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384, kTmS1 = 384;
+// Tensor-memory columns.  The dQ kernel has one accumulator and keeps Q and dO in the fourth quarter,
+// so that none of its three products reads an A operand from shared memory; the dK / dV kernel has
+// two accumulators.
+constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAcc0 = 256, kTmAcc1 = 384;
+constexpr uint32_t kTmQ = 384, kTmDO = 448;  // dQ kernel: Q and dO as 16-bit pairs (64 columns each at head dim 128)
 constexpr float kLog2eBwd = 1.4426950408889634f;
 constexpr int kStatusBwdTimeout = 64;
 
@@ -163,9 +166,13 @@ __device__ __forceinline__ void load_tile_4d(uint8_t* dst, const CUtensorMap* tm
 // K / V tiles: first a statistics sweep when no LSE was given (S = Q K^T only; running row maximum
 // and sum -> LSE, kept in registers and written to the workspace), then the gradient sweep
 //     S = Q K^T    dP = dO V^T    dS = P o (dP - delta)    dQ += dS K
-// with two K / V buffers (the next tiles load while the current ones are used) and two S buffers in
-// tensor memory (S_0 | dP | dQ | S_1), so that the next score product runs under the algebra.  dS
-// goes back to tensor memory as 16-bit pairs over dP and is the A operand of the dQ product there.
+// Tensor memory holds S | dP | dQ | Q, dO.  The softmax threads copy Q and dO from shared to tensor
+// memory once (undoing the 128-byte swizzle), after which all three products take their A operand
+// from tensor memory and only the streamed K / V tiles go through the shared-memory port.  The S
+// columns are handed back to the MMA warp as soon as the algebra has them in registers, so that the
+// next score product runs under the algebra; dS goes back to tensor memory as 16-bit pairs over dP
+// and is the A operand of the dQ product there.  K / V tiles stream through a ring of three buffers.
+// Measured per-iteration issue order of the MMA warp: dP(i), S(i+1), dQ(i).
 // ---------------------------------------------------------------------------------------------
 template <typename T, int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -178,17 +185,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   constexpr uint32_t kIdKM = make_idesc(kFmt, kFmt, 128, HD, 0, 1);   // dQ: 128 x HD, B MN-major
   constexpr int kDSteps = HD / 16;                                     // K steps of a contraction over the head dim
   constexpr int kOpBytes = kRows * HD * 2;                             // bytes TMA brings per operand tile
-  constexpr int kBufs = 2;                                             // K / V buffers
+  constexpr int kBufs = 3;  // K / V buffers; the third pair takes over the Q / dO tiles once those are in tensor memory
+  auto k_off = [](int b) { return b == 0 ? kOffK : (b == 1 ? kOffK1 : kOffQ); };
+  auto v_off = [](int b) { return b == 0 ? kOffV : (b == 1 ? kOffV1 : kOffDO); };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDqTiles * kTileBytes);
-  uint64_t* fix_full = bars;      // Q and dO have landed
+  uint64_t* fix_full = bars;      // Q and dO have landed in shared memory
   uint64_t* ld_full = bars + 1;   // [buffer] the K (and V) tiles of an iteration have landed
-  uint64_t* s_full = bars + 3;    // [S buffer] S is in tensor memory
-  uint64_t* pds_full = bars + 5;  // all rows of dS stored (and S / dP read)
-  uint64_t* it_done = bars + 6;   // [buffer] the last MMAs of an iteration that used it have completed
-  uint64_t* dp_full = bars + 8;   // dP is in tensor memory (gradient iterations)
+  uint64_t* it_done = bars + 4;   // [buffer] the last MMAs of an iteration that used it have completed
+  uint64_t* s_full = bars + 7;    // S is in tensor memory
+  uint64_t* s_free = bars + 8;    // every row of S has been read into registers: the next S may be issued
+  uint64_t* pds_full = bars + 9;  // all rows of dS stored (and dP read)
+  uint64_t* dp_full = bars + 10;  // dP is in tensor memory (gradient iterations)
+  uint64_t* a_ready = bars + 11;  // Q and dO have been copied to tensor memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumDqBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -214,13 +225,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(fix_full, 1);
-    mbar_init(ld_full, 1);
-    mbar_init(ld_full + 1, 1);
+    for (int b = 0; b < kBufs; ++b) {
+      mbar_init(ld_full + b, 1);
+      mbar_init(it_done + b, 1);
+    }
     mbar_init(s_full, 1);
-    mbar_init(s_full + 1, 1);
+    mbar_init(s_free, kSoftmaxThreads / 32);
+    mbar_init(a_ready, kSoftmaxThreads / 32);
     mbar_init(pds_full, kSoftmaxThreads);
-    mbar_init(it_done, 1);
-    mbar_init(it_done + 1, 1);
     mbar_init(dp_full, 1);
     *abort_word = 0;
     fence_barrier_init();
@@ -249,44 +261,56 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         const int buf = i % kBufs;
         // the MMAs of the iteration that last used this buffer have finished reading it
         if (i >= kBufs && !mbar_wait(it_done + buf, ((i - kBufs) / kBufs) & 1, abort_word)) break;
+        // the third pair of buffers is where Q and dO landed: not before they are in tensor memory
+        if (i == kBufs - 1 && !mbar_wait(a_ready, 0, abort_word)) break;
         uint64_t* full = ld_full + buf;
         const bool stats = i < n_stats;
         const int j = stats ? i : i - n_stats;
         mbar_arrive_expect_tx(full, stats ? kOpBytes : 2 * kOpBytes);
-        load_tile_4d<HD>(smem + (buf ? kOffK1 : kOffK), &tmap_k, full, j * kRows, kvh, batch);
-        if (!stats) load_tile_4d<HD>(smem + (buf ? kOffV1 : kOffV), &tmap_v, full, j * kRows, kvh, batch);
+        load_tile_4d<HD>(smem + k_off(buf), &tmap_k, full, j * kRows, kvh, batch);
+        if (!stats) load_tile_4d<HD>(smem + v_off(buf), &tmap_v, full, j * kRows, kvh, batch);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && total > 0) {
-      const uint32_t sq = smem_u32(smem + kOffQ), sdo = smem_u32(smem + kOffDO);
-      bool ok = mbar_wait(fix_full, 0, abort_word);
-      // S of iteration `it`, once its K tile has landed, into S buffer it & 1
+      // D[128 x 128] = A B^T, A (128 x HD, 16-bit pairs) in tensor memory at `a_tmem`, B a K-major tile
+      auto mma_ts_k = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr) {
+        const uint64_t b0 = make_desc_kmajor_sw128(b_addr);
+#pragma unroll
+        for (int ks = 0; ks < kDSteps; ++ks)
+          umma_f16_ts(d_tmem, a_tmem + ks * 8, b0 + (ks >> 2) * (kHalfBytes >> 4) + (ks & 3) * 2, kIdKK, ks > 0 ? 1u : 0u);
+      };
+      bool ok = mbar_wait(a_ready, 0, abort_word);
+      // S of iteration `it`, once its K tile has landed
       auto issue_s = [&](int it) -> bool {
         const int b = it % kBufs;
         if (!mbar_wait(ld_full + b, (it / kBufs) & 1, abort_word)) return false;
         tc_fence_after();
-        const int sb = it & 1;
-        mma_128x128x128<false, false, kDSteps>(tmem_base + (sb ? kTmS1 : kTmS), sq, smem_u32(smem + (b ? kOffK1 : kOffK)),
-                                               kIdKK, false);
-        umma_commit(s_full + sb);
+        mma_ts_k(tmem_base + kTmS, tmem_base + kTmQ, smem_u32(smem + k_off(b)));
+        umma_commit(s_full);
         return true;
       };
-      if (ok) ok = issue_s(0);
+      if (ok) {
+        tc_fence_after();
+        ok = issue_s(0);
+      }
       for (int i = 0; i < total && ok; ++i) {
         const int buf = i % kBufs;
         const bool stats = i < n_stats;
-        const uint32_t sk = smem_u32(smem + (buf ? kOffK1 : kOffK)), sv = smem_u32(smem + (buf ? kOffV1 : kOffV));
+        const uint32_t sk = smem_u32(smem + k_off(buf)), sv = smem_u32(smem + v_off(buf));
         const int gi = i - n_stats;  // index among the gradient iterations
         // The algebra on S starts while dP is still being computed; the next iteration's S is issued
-        // now as well (its S buffer was released by the previous iteration's algebra).
+        // as soon as every row of the current one has been read into registers.
         if (!stats) {
-          mma_128x128x128<false, false, kDSteps>(tmem_base + kTmDP, sdo, sv, kIdKK, false);
+          mma_ts_k(tmem_base + kTmDP, tmem_base + kTmDO, sv);
           umma_commit(dp_full);
         }
-        if (i + 1 < total && !issue_s(i + 1)) break;
+        if (i + 1 < total) {
+          if (!mbar_wait(s_free, i & 1, abort_word)) break;
+          if (!issue_s(i + 1)) break;
+        }
         if (!mbar_wait(pds_full, i & 1, abort_word)) break;
         tc_fence_after();
         if (!stats) {
@@ -326,13 +350,46 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     }
     // After a wait has given up the loop keeps its shape (arrivals and named barriers) but skips the work.
     bool ok = true;
+    // Q and dO are the A operands of S and dP for the whole life of the CTA: they move from the
+    // shared-memory tiles TMA wrote into tensor memory once (16-bit pairs, one row per lane), so
+    // that those two products read only their B operand from shared memory.
+    if (total > 0) {
+      ok = mbar_wait(fix_full, 0, abort_word);
+      if (ok) {
+        constexpr int kChunks = HD / 16;  // 16-byte chunks per thread: 64 (or 32) elements of the row
+        const int blk = HD == 128 ? half : 0;
+        const int c0 = HD == 128 ? 0 : half * kChunks;
+#pragma unroll
+        for (int op = 0; op < 2; ++op) {
+          const uint8_t* row = smem + (op == 0 ? kOffQ : kOffDO) + blk * kHalfBytes + r * 128;
+          uint32_t w[kChunks * 4];
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(row + (((c0 + c) ^ (r & 7)) << 4));
+            w[4 * c] = v.x;
+            w[4 * c + 1] = v.y;
+            w[4 * c + 2] = v.z;
+            w[4 * c + 3] = v.w;
+          }
+          const uint32_t dst = lane_base + (op == 0 ? kTmQ : kTmDO) + half * (kChunks * 4);
+          if constexpr (HD == 128)
+            tmem_st_32x32b_x32(dst, w);
+          else
+            tmem_st_32x32b_x16(dst, w);
+        }
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_ready);
+    }
     for (int i = 0; i < total; ++i) {
       const bool stats = i < n_stats;
       const int kv_base = (stats ? i : i - n_stats) * kRows;
-      const int sb = i & 1;  // S buffer of this iteration
-      const uint32_t s_base = lane_base + (sb ? kTmS1 : kTmS);
-      if (ok && !mbar_wait(s_full + sb, (i >> 1) & 1, abort_word)) ok = false;
+      const uint32_t s_base = lane_base + kTmS;
+      if (ok && !mbar_wait(s_full, i & 1, abort_word)) ok = false;
       const int gi = i - n_stats;  // index among the gradient iterations
+      ok = __all_sync(0xffffffffu, ok);  // one decision per warp
       if (stats) {
         if (ok) {
           tc_fence_after();
@@ -361,14 +418,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);  // the scores of this tile have been read
       } else {
         // P from S while the tensor core still computes dP; then dS = P o (dP - delta)
         float pf[64];
+        if (!ok && lane == 0) mbar_arrive(s_free);
         if (ok) {
           tc_fence_after();
           uint32_t s64[64];  // this thread's 64 columns in one load
           tmem_ld_32x32b_x64(s_base + half * 64, s64);
           tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_free);  // S is in registers: the next score product may overwrite it
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const int c4 = half * 2 + cc;
