@@ -60,9 +60,9 @@ constexpr int kMmaWarp = 13;
 constexpr int kQWarp = 14;  // (warp 15 issues the MMAs of query tile 1)
 // Registers: 4 warps per SM sub-partition x 128 at launch = 512 per lane, redistributed.  A
 // setmaxnreg.inc beyond what the others gave up never completes.
-constexpr int kRegsSoftmax = 184;
-constexpr int kRegsEpilogue = 80;
-constexpr int kRegsOther = 64;
+constexpr int kRegsSoftmax = 160;
+constexpr int kRegsEpilogue = 96;
+constexpr int kRegsOther = 96;
 static_assert(2 * kRegsSoftmax + kRegsEpilogue + kRegsOther <= 512, "setmaxnreg.inc would never complete");
 constexpr int kTileRows = 128;           // query rows per tile, KV rows per tile
 constexpr int kPairRows = 2 * kTileRows;  // query rows per work item
@@ -70,6 +70,7 @@ constexpr int kHalfTileBytes = kTileRows * 128;  // one 64-element column block 
 constexpr int kKvStages = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
+constexpr bool kUseTurns = true;
 
 template <int HD>
 struct AttnSmem {
@@ -80,8 +81,8 @@ struct AttnSmem {
   static constexpr int kStageOffset = kKvOffset + kKvStages * kTileBytes;  // epilogue staging: one 64-column block
   static constexpr int kLsumOffset = kStageOffset + kHalfTileBytes;        // float [tile][max, sum][128 rows]
   static constexpr int kBarOffset = kLsumOffset + 2 * 2 * kTileRows * 4;
-  // q_full[2] q_empty[2] | kv_full[4] kv_empty[4] | s_full[2] p_full[2] | o_full[2] o_free[2] | l_full[2] l_free[2] | turn[2]
-  static constexpr int kNumBars = 4 + 2 * kKvStages + 4 + 4 + 4 + 2;
+  // q_full[2] q_empty[2] | kv_full[4] kv_empty[4] | s_full[2][2] p_full[2][2] | o_full[2] o_free[2] | l_full[2] l_free[2] | turn[2] | pv_done[2]
+  static constexpr int kNumBars = 4 + 2 * kKvStages + 8 + 4 + 4 + 2 + 2;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16 + 1024;  // + slack for 1024-byte alignment
   // tensor memory columns
   static constexpr uint32_t kTmemS = 0;    // + 128 * tile; P over the first 64 columns
@@ -237,7 +238,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   constexpr int kBlocks = L::kBlocks;
   constexpr int kTileBytes = L::kTileBytes;
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBF16;
-  constexpr uint32_t kIdescS = make_idesc(kFmt, kFmt, 128, 128, 0, 0);  // Q, K both K-major
+  constexpr uint32_t kIdescS = make_idesc(kFmt, kFmt, 128, 64, 0, 0);   // Q, K both K-major; 64 keys per half step
   constexpr uint32_t kIdescPV = make_idesc(kFmt, kFmt, 128, HD, 0, 1);  // V is MN-major
 
   extern __shared__ uint8_t smem_raw[];
@@ -248,13 +249,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   uint64_t* q_empty = q_full + 2;     // [tile] the item's last score MMA of that tile has read Q
   uint64_t* kv_full = q_empty + 2;    // [stage]
   uint64_t* kv_empty = kv_full + kKvStages;
-  uint64_t* s_full = kv_empty + kKvStages;  // [tile] score tile written
-  uint64_t* p_full = s_full + 2;            // [tile] probabilities written (and O rescaled if it had to be)
-  uint64_t* o_full = p_full + 2;            // [tile] last PV of an item complete
+  uint64_t* s_full = kv_empty + kKvStages;  // [tile][half] scores of a half step (64 keys) written
+  uint64_t* p_full = s_full + 4;            // [tile][half] probabilities written (and O rescaled if it had to be)
+  uint64_t* o_full = p_full + 4;            // [tile] last PV of an item complete
   uint64_t* o_free = o_full + 2;            // [tile] epilogue has read the accumulator
   uint64_t* l_full = o_free + 2;            // [tile] (max, sum) of the item written
   uint64_t* l_free = l_full + 2;            // [tile] ... and read
   uint64_t* turn = l_free + 2;              // [tile] it is this tile's turn to put MMAs into the pipe
+  uint64_t* pv_done = turn + 2;             // [tile] one completion per PV group (only waited for before a rescale of O)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -265,8 +267,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     for (int t = 0; t < 2; ++t) {
       mbar_init(q_full + t, 1);
       mbar_init(q_empty + t, 1);
-      mbar_init(s_full + t, 1);
-      mbar_init(p_full + t, 4);
+      for (int hb = 0; hb < 2; ++hb) {
+        mbar_init(s_full + 2 * t + hb, 1);
+        mbar_init(p_full + 2 * t + hb, 4);
+      }
+      mbar_init(pv_done + t, 1);
       mbar_init(o_full + t, 1);
       mbar_init(o_free + t, 4);
       mbar_init(l_full + t, 4);
@@ -404,44 +409,47 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         const uint32_t bar0 = smem_u32(bars);
         // barrier indices in `bars`
         constexpr uint32_t kQFull = 0, kQEmpty = 2, kKvFull = 4, kKvEmpty = 4 + kKvStages, kSFull = 4 + 2 * kKvStages,
-                           kPFull = kSFull + 2, kOFull = kSFull + 4, kOFree = kSFull + 6;
+                           kPFull = kSFull + 4, kOFull = kSFull + 8, kOFree = kSFull + 10, kTurn = kSFull + 16,
+                           kPvDone = kSFull + 18;
         auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
         auto wait = [&](uint32_t index, uint32_t parity) { return mbar_wait_addr(bar0 + 8 * index, parity, abort_word); };
         auto commit = [&](uint32_t index) { umma_commit_addr(bar0 + 8 * index); };
         auto wait_entry = [&](uint32_t e) { return wait(kKvFull + e % kKvStages, (e / kKvStages) & 1); };
         auto free_entry = [&](uint32_t e) { commit(kKvEmpty + e % kKvStages); };  // arrives once this thread's MMAs are done
-        // S = Q K^T with K in ring entry e
-        auto issue_scores = [&](uint32_t e) {
-          const uint32_t b0 = k_lo + (e % kKvStages) * (kTileBytes >> 4);
+        // S(half hb) = Q (K rows 64 hb .. 64 hb + 63 of ring entry e)^T, into columns 64 hb .. of the tile's score region
+        auto issue_scores = [&](uint32_t e, uint32_t hb) {
+          const uint32_t b0 = k_lo + (e % kKvStages) * (kTileBytes >> 4) + hb * (8192u >> 4);
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks) {  // k-steps of 16 over the head dimension (64-wide blocks)
             const uint32_t off = (ks >> 2) * (kHalfTileBytes >> 4) + 2 * (ks & 3);
-            umma_f16_ss(tmem_s, desc(q_lo + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
+            umma_f16_ss(tmem_s + hb * 64, desc(q_lo + off, hi_k), desc(b0 + off, hi_k), kIdescS, ks > 0 ? 1u : 0u);
           }
-          commit(kSFull + t);
+          commit(kSFull + 2 * t + hb);
         };
-        // O (+)= P V with V in ring entry e: 8 k-steps of 16 KV rows; A = P from tensor memory
-        auto issue_pv = [&](uint32_t e, uint32_t accumulate) {
-          const uint32_t b0 = v_lo + (e % kKvStages) * (kTileBytes >> 4);
+        // O (+)= P(half hb) V rows 64 hb .. of ring entry e: 4 k-steps of 16 KV rows; A = P from tensor memory
+        auto issue_pv = [&](uint32_t e, uint32_t hb, uint32_t accumulate) {
+          const uint32_t b0 = v_lo + (e % kKvStages) * (kTileBytes >> 4) + hb * (4u * (2048u >> 4));
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_f16_ts(tmem_o, tmem_s + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV, ks > 0 ? 1u : accumulate);
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ts(tmem_o, tmem_s + hb * 64 + ks * 8, desc(b0 + ks * (2048 >> 4), hi_mn), kIdescPV,
+                        ks > 0 ? 1u : accumulate);
+          commit(kPvDone + t);
         };
         uint32_t e0 = 0;              // ring entry of K_0 of the current item
-        uint32_t cq = 0, cp = 0, co = 0;  // Q tiles, P tiles and accumulators of this query tile consumed so far
-        // The two threads take turns, tile 0 then tile 1, for every KV step.  Without an order the two streams share the pipe evenly, both tiles' MMAs
-        // end together, both softmaxes run together and nothing overlaps; in turns one tile's
-        // softmax runs while the tensor core works for the other.  A thread collects everything
-        // its MMAs need BEFORE it asks for its turn, and hands the turn on as soon as its MMAs are
-        // issued (not completed), so the next group queues up behind them and the pipe stays busy.
+        uint32_t cq = 0, ch = 0, co = 0;  // Q tiles, half steps and accumulators of this query tile consumed so far
+        // The two threads take turns, tile 0 then tile 1, for every half step.  A thread collects
+        // everything its MMAs need BEFORE it asks for its turn, and hands the turn on as soon as its
+        // PV MMAs are issued (not completed), so the next group queues up behind them.
         uint32_t ct = 0;  // turns taken
-        constexpr uint32_t kTurn = kSFull + 12;
         auto take_turn = [&]() {
+          if (!kUseTurns) return true;
           const bool got = wait(kTurn + t, t ? (ct & 1u) : ((ct & 1u) ^ 1u));
           ++ct;
           return got;
         };
-        auto pass_turn = [&]() { mbar_arrive(turn + (t ^ 1u)); };
+        auto pass_turn = [&]() {
+          if (kUseTurns) mbar_arrive(turn + (t ^ 1u));
+        };
         bool ok = true;
         ItemWalk<PAGED> walk(p);
         Item it;
@@ -449,46 +457,52 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           const int n = t ? it.n[1] : it.n[0];
           const int nmax = it.nmax;
           // The first score tile of an item needs no turn: a tile that is done with the previous
-          // item starts the next one at once, whatever the other tile is still doing.
+          // item starts the next one at once, whatever the other tile is still doing.  Both score
+          // buffers are free: the PV groups that read the probabilities in them were issued before.
           if (!wait_entry(e0)) break;
           if (n > 0) {
             if (!wait(kQFull + t, cq & 1u)) break;
             ++cq;
             tc_fence_after();
-            issue_scores(e0);
+            issue_scores(e0, 0);
+            issue_scores(e0, 1);
             if (n == 1) commit(kQEmpty + t);
           }
           free_entry(e0);
-          for (int j = 0; j < nmax; ++j) {
+          for (int j = 0; j < nmax && ok; ++j) {
             const uint32_t ev = e0 + 2 * j + 1;  // V_j; K_(j+1) is entry ev + 1
             const bool more = j + 1 < nmax;
             // Everything that is normally there long before the probabilities first (the K/V tiles,
-            // the turn: the order of turns is fixed, so holding it while waiting delays nobody),
-            // so that the path from "P written" to the first MMA is as short as possible.
-            if (!wait_entry(ev) || (more && !wait_entry(ev + 1)) || !take_turn()) { ok = false; break; }
+            // the turn), so that the path from "P written" to the first MMA is as short as possible.
+            if (!wait_entry(ev) || (more && !wait_entry(ev + 1))) { ok = false; break; }
+#pragma unroll
+            for (uint32_t hb = 0; hb < 2; ++hb) {
+              if (!take_turn()) { ok = false; break; }
+              if (j < n) {
+                if (j == 0 && hb == 0) {  // the accumulator is read by the epilogue of the tile's previous item
+                  if (!wait(kOFree + t, (co & 1u) ^ 1u)) { ok = false; break; }
+                  ++co;
+                }
+                if (!wait(kPFull + 2 * t + hb, (ch >> 1) & 1u)) { ok = false; break; }
+                ++ch;
+                tc_fence_after();
+                issue_pv(ev, hb, (j > 0 || hb > 0) ? 1u : 0u);
+                pass_turn();
+                if (more && j + 1 < n) {
+                  issue_scores(ev + 1, hb);  // over the probabilities the PV group above has just been issued for
+                  if (j + 2 == n && hb == 1) commit(kQEmpty + t);  // that was the item's last score MMA of this tile
+                }
+                if (j == n - 1 && hb == 1) commit(kOFull + t);
+              } else {
+                pass_turn();  // past this tile's diagonal
+              }
+            }
+            if (!ok) break;
             if (j < n) {
-              if (j == 0) {  // the accumulator is read by the epilogue of the tile's previous item
-                if (!wait(kOFree + t, (co & 1u) ^ 1u)) { ok = false; break; }
-                ++co;
-              }
-              if (!wait(kPFull + t, cp & 1u)) { ok = false; break; }
-              ++cp;
-              tc_fence_after();
-              issue_pv(ev, j > 0 ? 1u : 0u);
-              // The other tile's thread needs a few hundred cycles from here to its first MMA: hand
-              // the turn on now, with this tile's score MMAs still to be issued, so that its MMAs
-              // arrive before the pipe runs dry (the two tiles' MMAs may interleave from here on).
-              pass_turn();
-              if (more && j + 1 < n) {
-                issue_scores(ev + 1);  // (its commit to s_full, the one the softmax waits for, goes first)
-                if (j + 2 == n) commit(kQEmpty + t);  // that was the item's last score MMA of this tile
-              }
-              if (j == n - 1) commit(kOFull + t);
               free_entry(ev);
               if (more) free_entry(ev + 1);
             } else {
               // past this tile's diagonal: let the entries go (they have been loaded, see above)
-              pass_turn();
               mbar_arrive(kv_empty + ev % kKvStages);
               if (more) mbar_arrive(kv_empty + (ev + 1) % kKvStages);
             }
@@ -609,19 +623,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       const int causal_offset = it.causal_offset;
       float m_ref = -INFINITY;  // the max the row's P and running sum are relative to
       float2 l2 = make_float2(0.f, 0.f);
-      for (int j = 0; j < n; ++j, ++cs) {
-        ok = mbar_wait(s_full + t, cs & 1, abort_word);
+      for (int h = 0; h < 2 * n; ++h, ++cs) {  // half steps of 64 keys, alternating between the two score buffers
+        const uint32_t hb = cs & 1u;
+        ok = mbar_wait(s_full + 2 * t + hb, (cs >> 1) & 1u, abort_word);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        uint32_t sr[128];
-        tmem_ld_32x32b_x64(t_s, sr);
-        tmem_ld_32x32b_x64(t_s + 64, sr + 64);
+        uint32_t sr[64];
+        tmem_ld_32x32b_x64(t_s + hb * 64, sr);
 
-        const int col0 = j * kTileRows;
-        const bool need_mask =
-            (p.causal && col0 + kTileRows - 1 > tile_r0 + causal_offset) || (col0 + kTileRows > kv_len);
-        int limit = kTileRows;  // columns [0, limit) of this tile are visible to this row
+        const int col0 = h * 64;
+        const bool need_mask = (p.causal && col0 + 63 > tile_r0 + causal_offset) || (col0 + 64 > kv_len);
+        int limit = 64;  // columns [0, limit) of this half step are visible to this row
         if (need_mask) {
           int vis = kv_len;
           if (p.causal) vis = min(vis, q_row + causal_offset + 1);
@@ -630,12 +643,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         tmem_wait_ld();
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
+          for (int i = 0; i < 64; ++i)
             if (i >= limit) sr[i] = 0xff800000u;  // -inf
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 128; i += 8) {
+        for (int i = 0; i < 64; i += 8) {
           mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
           mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
           mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
@@ -643,11 +656,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         }
         const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
         const bool grow = m_new > m_ref + kRescaleThreshold;  // also true for the first finite max
-        if (j > 0 && __any_sync(0xffffffffu, grow)) {
-          // Rescale O in place.  Every MMA issued before this score tile has completed (it was
-          // committed behind them on the same in-order stream), the previous PV of this tile
-          // included, and the next one waits for p_full below.  Rare after the first steps of an
-          // item: the max must grow by 2^8.
+        if (h > 0 && __any_sync(0xffffffffu, grow)) {
+          // Rescale O in place.  The PV group of the previous half step may still be running (the
+          // scores read above were issued before it): wait for its completion, the cs-th of this
+          // tile.  The next group waits for p_full below.  Rare after the first steps of an item:
+          // the max must grow by 2^8.
+          ok = mbar_wait(pv_done + t, (cs - 1u) & 1u, abort_word);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
           const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // m_ref = -inf gives 0
 #pragma unroll 1
           for (int c = 0; c < HD / 16; ++c) {
@@ -665,10 +682,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
         const float2 negm2 = make_float2(-m_sub, -m_sub);
 
-        // probabilities -> tensor memory (16-bit pairs) over the first half of the score tile; masked
-        // scores are -inf and give exactly 0
+        // probabilities -> tensor memory (16-bit pairs) over the first half of the scores they came
+        // from; masked scores are -inf and give exactly 0
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -678,12 +695,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             l2 = fadd2(l2, e);
             pk[i] = pack_pair<T>(e.x, e.y);
           }
-          tmem_st_32x32b_x16(t_s + c * 16, pk);
+          tmem_st_32x32b_x16(t_s + hb * 64 + c * 16, pk);
         }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + t);
+        if (lane == 0) mbar_arrive(p_full + 2 * t + hb);
       }
       if (!ok) break;
       // hand (max, sum) of the item to the epilogue warps
