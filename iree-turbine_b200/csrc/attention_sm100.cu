@@ -19,18 +19,24 @@
 //   warp 15       issues the MMAs of query tile 1 (one thread)
 //
 // Tensor memory (512 columns x 128 lanes):  S[0] | S[1] (128 fp32 columns each) | O[0] | O[1]
-// (head-dim fp32 columns each).  The probabilities P[t] (16-bit, 64 columns) are written over the
-// first half of S[t] by the thread that has just read that row into registers, and are the A
-// operand of the second MMA straight from tensor memory.
+// (head-dim fp32 columns each).  A tile's 128 score columns are TWO buffers of 64: a K/V tile is
+// worked through in two half steps of 64 keys, half step h in buffer h & 1.  The probabilities of a
+// half step (16-bit, 32 columns) are written over the first half of the scores they came from by the
+// thread that has just read that row into registers, and are the A operand of the second MMA
+// straight from tensor memory.
 //
-// Order of the MMAs of query tile t (one in-order stream per tile, issued by its own thread), KV tile j:
-//     wait P[t](j) : O[t] += P[t] V_j : S[t] = Q_t K_(j+1)^T : wait P[t](j+1) : ...
-// so the tensor core computes "PV, next S" of one query tile while the other tile's softmax runs.
-// Because S[t](j+1) is issued behind O[t] += P[t](j) V_j by the same thread, S may overwrite P
-// without a barrier; and when the softmax of tile t sees S[t](j) complete, every earlier MMA of the
-// tile is complete as well, so it may rescale O[t] in place with no further wait.  A stream does
-// not stop at item boundaries: a tile that has issued its last PV of an item goes on with the first
-// score tile of its next item as soon as Q and K are there.
+// Order of the MMAs of query tile t (one in-order stream per tile, issued by its own thread), half step h:
+//     S(0) : S(1) : wait P(0) : O += P(0) V[0:64] : S(2) : wait P(1) : O += P(1) V[64:128] : S(3) : ...
+// so while the softmax of a tile works on half step h, the scores of half step h + 1 are already
+// there or on their way (with one 128-column buffer per tile the next scores could only be issued
+// behind the PV product that reads the probabilities, and the softmax waited out both products on
+// every step).  S(h + 2) is issued behind O += P(h) V by the same thread, so it may overwrite P(h)
+// without a barrier.  A PV group commits to pv_done; the softmax waits there only on the rare step on
+// which it has to rescale O in place (the scores it has just read were issued BEFORE the previous
+// half step's PV group, so their arrival says nothing about it).  A stream does not stop at item
+// boundaries: a tile that has issued its last PV of an item goes on with the first scores of its
+// next item as soon as Q and K are there.  The score MMAs have N = 64, so Q is read from shared
+// memory twice per K/V tile; measured, that costs less than the waiting it removes.
 //
 // Causal items: the two tiles of a pair need a different number of KV tiles (n[0] <= n[1]); tile 0
 // simply stops taking part once it is past its diagonal.  Work is dealt to CTAs in units that pair
@@ -70,7 +76,6 @@ constexpr int kHalfTileBytes = kTileRows * 128;  // one 64-element column block 
 constexpr int kKvStages = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
-constexpr bool kUseTurns = true;
 
 template <int HD>
 struct AttnSmem {
@@ -384,7 +389,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     } else {
       // ---------------- MMA issue: warp 13 for query tile 0, warp 15 for query tile 1 ----------------
       // One thread per query tile, each with its own in-order stream
-      //     wait P(j) : O += P(j) V_j : S = Q K_(j+1)^T : ...
+      //     wait P(h) : O += P(h) V[half h] : S(h + 2) : ...      (half steps of 64 keys)
       // so neither tile ever waits behind the other's barriers, and a tile that is done with an
       // item runs on into its next item as far as the K/V ring lets it.  A tcgen05.mma does not
       // return until the tensor pipe has room for it, so a thread is busy for about as long as its
@@ -439,17 +444,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         uint32_t cq = 0, ch = 0, co = 0;  // Q tiles, half steps and accumulators of this query tile consumed so far
         // The two threads take turns, tile 0 then tile 1, for every half step.  A thread collects
         // everything its MMAs need BEFORE it asks for its turn, and hands the turn on as soon as its
-        // PV MMAs are issued (not completed), so the next group queues up behind them.
+        // PV MMAs are issued (not completed), so the next group queues up behind them.  Measured on
+        // the causal bf16 B4 H32 S4096 problem (same box): turns 1108 TFLOP/s; no order at all 1104
+        // on another box against 1151 with turns; a lock taken once the probabilities are there and
+        // held for the PV MMAs 1077, held for the score MMAs as well 925; the turn handed on before
+        // the PV MMAs 1095, after the score MMAs 852.
         uint32_t ct = 0;  // turns taken
         auto take_turn = [&]() {
-          if (!kUseTurns) return true;
           const bool got = wait(kTurn + t, t ? (ct & 1u) : ((ct & 1u) ^ 1u));
           ++ct;
           return got;
         };
-        auto pass_turn = [&]() {
-          if (kUseTurns) mbar_arrive(turn + (t ^ 1u));
-        };
+        auto pass_turn = [&]() { mbar_arrive(turn + (t ^ 1u)); };
         bool ok = true;
         ItemWalk<PAGED> walk(p);
         Item it;
