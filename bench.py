@@ -559,7 +559,7 @@ class PagedDecodeWL(Workload):
 
 
 WORKLOADS = {
-    "attn_causal": lambda: AttentionWL("attn_causal", 4, 32, 4096, torch.bfloat16, True, 0.5, 526.1e6),
+    "attn_causal": lambda: AttentionWL("attn_causal", 4, 32, 4096, torch.bfloat16, True, 0.5, 528.2e6),
     "attn_noncausal": lambda: AttentionWL("attn_noncausal", 8, 32, 1024, torch.float16, False, 1.0, 249.1e6),
     "attn_bwd_causal": lambda: AttentionBwdWL("attn_bwd_causal", 4, 32, 4096, torch.bfloat16, True, 0.5),
     "gemm_f16": lambda: GemmWL("gemm_f16", 2048, False),
