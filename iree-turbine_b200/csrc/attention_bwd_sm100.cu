@@ -208,8 +208,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int group = p.q_heads / p.kv_heads;
 
   // ---- work item ----
-  const int bh = blockIdx.x / p.num_q_tiles;
-  const int tile = p.num_q_tiles - 1 - (blockIdx.x - bh * p.num_q_tiles);  // heaviest tiles first
+  // Causal: a tile's cost grows with its index, and CTAs are handed out in blockIdx order, so the
+  // heaviest tile of EVERY (batch, head) goes first, then the next one, ... (longest job first over
+  // the whole grid; with the tiles of one head after those of another, the last head's heavy
+  // tiles started when the others were nearly done).  K / V of all heads stay in L2 either way.
+  const int num_bh = gridDim.x / p.num_q_tiles;
+  int bh, tile;
+  if (p.causal) {
+    const int t = blockIdx.x / num_bh;
+    bh = blockIdx.x - t * num_bh;
+    tile = p.num_q_tiles - 1 - t;
+  } else {
+    bh = blockIdx.x / p.num_q_tiles;
+    tile = blockIdx.x - bh * p.num_q_tiles;
+  }
   const int batch = bh / p.q_heads;
   const int head = bh - batch * p.q_heads;
   const int kvh = head / group;
@@ -519,7 +531,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         tma_store_4d(&tmap_dq, smem + kOffDS, 0, row0, head, batch);
         if (HD == 128) tma_store_4d(&tmap_dq, smem + kOffDS + kHalfBytes, 64, row0, head, batch);
         tma_store_commit();
-        tma_store_wait<0>();
+        tma_store_wait_read<0>();  // the staging tile has been read: the CTA may go (the writes land before the grid ends)
       }
     }
   }
@@ -589,8 +601,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int lane = threadIdx.x & 31;
   const int group = p.q_heads / p.kv_heads;
 
-  const int bh = blockIdx.x / p.num_kv_tiles;
-  const int tile = blockIdx.x - bh * p.num_kv_tiles;
+  // Causal: key tile 0 is seen by every query tile, the last one by few: the CTAs of one (batch,
+  // K/V head) differ in cost by up to the number of tiles, so the grid is ordered longest job first
+  // over ALL heads (key tile 0 of every head, then key tile 1, ...).  CTAs of neighbouring key
+  // tiles of a head sweep nearly the same Q / dO tiles at nearly the same time and share them in L2.
+  int bh, tile;
+  if (p.causal) {
+    const int num_bh = gridDim.x / p.num_kv_tiles;
+    tile = blockIdx.x / num_bh;
+    bh = blockIdx.x - tile * num_bh;
+  } else {
+    bh = blockIdx.x / p.num_kv_tiles;
+    tile = blockIdx.x - bh * p.num_kv_tiles;
+  }
   const int batch = bh / p.kv_heads;
   const int kvh = bh - batch * p.kv_heads;
   const int row0 = tile * kRows;  // first key of the tile
@@ -828,7 +851,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         tma_store_4d(&tmap_dk, smem + kTDO0, 0, row0, kvh, batch);
         if (HD == 128) tma_store_4d(&tmap_dk, smem + kTDO0 + kHalfBytes, 64, row0, kvh, batch);
         tma_store_commit();
-        tma_store_wait<0>();
+        tma_store_wait_read<0>();  // the staging tile has been read: the CTA may go (the writes land before the grid ends)
       }
     }
   }
