@@ -69,6 +69,7 @@ struct BwdParams {
   int32_t batch, q_heads, kv_heads, seq_q, seq_kv;
   int32_t causal, causal_offset;  // query i sees keys j <= i + causal_offset
   int32_t num_q_tiles, num_kv_tiles;
+  int32_t bh_group_q, bh_group_kv;  // causal grids: heads whose tiles are interleaved, longest job first (see causal_work_item)
   float scale, scale_log2;
   float* lse2;   // [batch, q_heads, seq_q], log2 domain: log2(sum_j exp2(scale_log2 * s_ij))
   float* delta;  // [batch, q_heads, seq_q]
@@ -109,6 +110,24 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 // 1024 cycles between the score product and the dV product.  Measured on the causal bf16 B4 H32
 // S4096 backward: none 2.055 ms, 3 of 8 2.038 ms, 4 of 8 2.023 ms.
 constexpr uint32_t kBwdPolyMask = 0x55u;
+
+// Which (batch * head, tile rank) a CTA of a causal grid works on.  A tile's cost grows with its
+// rank's complement (rank 0 = the heaviest tile of its head) and CTAs are handed out in blockIdx
+// order, so within a group of `group` heads the heaviest tile of every head goes first, then the
+// next one, ...: longest job first, which matters at the end of the grid, where a head's heavy
+// tiles started late otherwise (dK / dV kernel with grouped heads: 974 -> 909 us).  The groups keep
+// the heads in flight few enough for their K / V (dQ kernel) or Q / dO (dK / dV kernel) to stay in
+// L2: with all 128 heads of the multi-head bench shape interleaved, every CTA streamed its
+// operands from DRAM and the backward took 2.03 ms instead of 1.76.
+__device__ __forceinline__ void causal_work_item(int block, int num_bh, int num_tiles, int group, int& bh, int& rank) {
+  const int per_group = group * num_tiles;
+  const int sg = block / per_group;
+  const int g0 = sg * group;
+  const int gsize = min(group, num_bh - g0);
+  const int r = block - sg * per_group;
+  rank = r / gsize;
+  bh = g0 + (r - rank * gsize);
+}
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -208,16 +227,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int group = p.q_heads / p.kv_heads;
 
   // ---- work item ----
-  // Causal: a tile's cost grows with its index, and CTAs are handed out in blockIdx order, so the
-  // heaviest tile of EVERY (batch, head) goes first, then the next one, ... (longest job first over
-  // the whole grid; with the tiles of one head after those of another, the last head's heavy
-  // tiles started when the others were nearly done).  K / V of all heads stay in L2 either way.
-  const int num_bh = gridDim.x / p.num_q_tiles;
+  // causal: the last query tile of a head is its heaviest
   int bh, tile;
   if (p.causal) {
-    const int t = blockIdx.x / num_bh;
-    bh = blockIdx.x - t * num_bh;
-    tile = p.num_q_tiles - 1 - t;
+    int rank;
+    causal_work_item(blockIdx.x, gridDim.x / p.num_q_tiles, p.num_q_tiles, p.bh_group_q, bh, rank);
+    tile = p.num_q_tiles - 1 - rank;
   } else {
     bh = blockIdx.x / p.num_q_tiles;
     tile = blockIdx.x - bh * p.num_q_tiles;
@@ -601,15 +616,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int lane = threadIdx.x & 31;
   const int group = p.q_heads / p.kv_heads;
 
-  // Causal: key tile 0 is seen by every query tile, the last one by few: the CTAs of one (batch,
-  // K/V head) differ in cost by up to the number of tiles, so the grid is ordered longest job first
-  // over ALL heads (key tile 0 of every head, then key tile 1, ...).  CTAs of neighbouring key
-  // tiles of a head sweep nearly the same Q / dO tiles at nearly the same time and share them in L2.
+  // causal: key tile 0 is seen by every query tile, the last one by few
   int bh, tile;
   if (p.causal) {
-    const int num_bh = gridDim.x / p.num_kv_tiles;
-    tile = blockIdx.x / num_bh;
-    bh = blockIdx.x - tile * num_bh;
+    causal_work_item(blockIdx.x, gridDim.x / p.num_kv_tiles, p.num_kv_tiles, p.bh_group_kv, bh, tile);
   } else {
     bh = blockIdx.x / p.num_kv_tiles;
     tile = blockIdx.x - bh * p.num_kv_tiles;
@@ -1008,6 +1018,16 @@ int launch_attention_bwd(const b200k_attention_bwd_args& a, cudaStream_t stream)
   p.causal_offset = a.seq_kv - a.seq_q;
   p.num_q_tiles = (a.seq_q + kRows - 1) / kRows;
   p.num_kv_tiles = (a.seq_kv + kRows - 1) / kRows;
+  {
+    // heads interleaved at a time: about four waves of CTAs (a handful of CTAs per head in flight)
+    const int sms = num_sms();
+    auto group_for = [&](int tiles, int num_bh) {
+      const int g = (4 * sms + tiles - 1) / tiles;
+      return g < 1 ? 1 : (g > num_bh ? num_bh : g);
+    };
+    p.bh_group_q = group_for(p.num_q_tiles, a.batch * a.q_heads);
+    p.bh_group_kv = group_for(p.num_kv_tiles, a.batch * a.kv_heads);
+  }
   if (static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles > INT32_MAX ||
       static_cast<int64_t>(a.batch) * a.kv_heads * p.num_kv_tiles > INT32_MAX)
     return set_error(B200K_ERR_BAD_SHAPE, "attention_bwd: too many tiles");
