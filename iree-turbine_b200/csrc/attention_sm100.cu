@@ -772,15 +772,16 @@ int fill_units(AttnParams& p, const char* who) {
 }
 
 // Which kernel runs a problem (B200K_ATTN_AUTO).  Measured on B200, head dim 128, same box and
-// timing loop, one-tile / tile-pair in microseconds: non-causal 8x32x1024 130 / 140, 8x32x2048
-// 514 / 537, 1x16x16384 1809 / 1932; causal 4x32x4096 521 / 505, 2x32(8)x8192 960 / 924,
-// 1x32(8)x16384 2214 / 2052, 64x16x256 80 / 66, but 4x32(8)x2048 155 / 173, where the pair
-// kernel's 512 units leave the last of four rounds over 148 SMs half empty.  Problems that are one
-// round of units (a head shard of a long causal prefill on 8 GPUs): 4x4(1)x4096 92.5 / 80.3,
-// 1x8x8192 172 / 142 (128 units, the one-tile kernel balances its 512 unequal items badly), but
-// 8x8x1024 40.3 / 40.3 and 4x6(2)x2048 (96 units) 45.4 / 49.5.  So: head dim 64 only exists in the
-// pair kernel; causal problems take it when its units fill the SMs to 90 % or more, or fill one
-// round to 80 % with at least 24 K/V tiles to walk; everything else takes the one-tile kernel.
+// timing loop, one-tile / tile-pair in microseconds.  Non-causal: 8x32x1024 128 / 134, 8x32x2048
+// 472 / 473, 4x32x4096 992 / 1030, 1x16x16384 1827 / 2026.  Causal, many rounds of units: 4x32x4096
+// 539 / 510, 1x32(8)x16384 2073 / 1995, 2x32(8)x8192 1045 / 1026, but 4x32(8)x2048 155 / 173, where the
+// pair kernel's 512 units leave the last of four rounds over 148 SMs half empty, and 4x8x4096 (256
+// units, 86 % of two rounds) 152 / 158.  Causal, one or two rounds filled to 86 % (a head shard of
+// a long prefill on 8 GPUs): 1x8x8192 144 / 136, 4x4(1)x4096 80 / 76, 1x4x16384 273 / 248, 2x8x8192
+// 285 / 269, 1x16(4)x8192 281 / 266, but 4x6(2)x2048 41 / 45, 8x8x1024 40 / 41, 2x4x2048 41 / 43.
+// So: head dim 64 only exists in the pair kernel; causal problems take it when its units fill the
+// SMs to 90 % or more, or fill one round (two rounds) to 80 % with at least 24 (48) K/V tiles to
+// walk; everything else takes the one-tile kernel.
 bool choose_pair_kernel(int kernel, int head_dim, bool causal, int64_t pair_units, int64_t kv_tiles) {
   if (head_dim != 128) return true;
   if (kernel == B200K_ATTN_TILE_PAIR) return true;
@@ -789,7 +790,7 @@ bool choose_pair_kernel(int kernel, int head_dim, bool causal, int64_t pair_unit
   const int64_t sms = num_sms();
   const int64_t rounds = (pair_units + sms - 1) / sms;
   if (pair_units * 10 >= rounds * sms * 9) return true;
-  return rounds == 1 && pair_units * 10 >= sms * 8 && kv_tiles >= 24;
+  return rounds <= 2 && pair_units * 10 >= rounds * sms * 8 && kv_tiles >= (rounds == 1 ? 24 : 48);
 }
 
 }  // namespace

@@ -7,8 +7,9 @@
 // faster of the two on non-causal problems and where the pair kernel's units fill the SMs badly.
 //
 // Persistent CTAs, one per SM.  A work item is one 128-row query tile of one (batch, head); a CTA
-// takes items blockIdx.x, blockIdx.x + gridDim.x, ... from a list ordered (batch, head)-major with
-// the heaviest query tiles of a head first, so CTAs that run at the same time share K/V in L2.
+// takes items blockIdx.x, blockIdx.x + gridDim.x, ... from a list ordered (batch, head)-major, so
+// CTAs that run at the same time share K/V in L2, heaviest query tiles of a head first; a causal
+// problem of a few rounds of items interleaves the tiles of all heads instead (see decode_item).
 //
 //   warps 0..3    softmax + correction of the even KV steps of the CTA (thread = query row)
 //   warps 4..7    the same for the odd KV steps
@@ -99,6 +100,7 @@ struct AttnParams {
   int32_t causal, causal_offset;
   int32_t num_q_tiles;  // ceil(seq_q / 128)
   int32_t num_items;    // batch * q_heads * num_q_tiles
+  int32_t interleave_heads, item_div;  // order of the item list, see decode_item
   float scale_log2;
   int32_t* status;
   float* lse;  // optional [batch, q_heads, seq_q]: ln sum_j exp(scale * s_ij), -inf for a row without keys
@@ -139,8 +141,19 @@ struct Item {
 template <bool PAGED>
 __device__ __forceinline__ Item decode_item(int idx, const AttnParams& p) {
   Item it;
-  const int bh = idx / p.num_q_tiles;
-  it.qtile = p.num_q_tiles - 1 - (idx - bh * p.num_q_tiles);  // heaviest tiles of a head first
+  // rank 0 = the last query tile of a head, the heaviest one of a causal problem.  The list is
+  // (batch, head)-major, except for a causal problem of a few rounds of items (p.interleave_heads, set
+  // by the host): there the heaviest tile of EVERY head comes first, then the next one, ...  A CTA
+  // takes every gridDim.x-th item, so each gets tiles of every weight and they finish together
+  // (head-major, a CTA of a one-round problem got one tile of arbitrary weight: 1 x 8 heads x 8192
+  // causal 172 -> 148 us, 4 x 4 x 4096 91 -> 84).  Longer lists are mixed well enough by the stride, and
+  // head-major keeps their K / V traffic on few heads.  One division either way: this runs in the
+  // single-thread roles between two items.
+  const int d = p.item_div;  // heads of all batches when interleaved, else query tiles per head
+  const int hi = idx / d, lo = idx - hi * d;
+  const int bh = p.interleave_heads ? lo : hi;
+  const int rank = p.interleave_heads ? hi : lo;
+  it.qtile = p.num_q_tiles - 1 - rank;
   it.batch = bh / p.q_heads;
   it.head = bh - it.batch * p.q_heads;
   // (dense: the two are launch constants and the fields fold away)
@@ -746,6 +759,8 @@ int launch_attention_fwd_tile(const b200k_attention_args& a, cudaStream_t stream
   const int64_t items = static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles;
   if (items > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "attention_fwd: too many query tiles");
   p.num_items = static_cast<int32_t>(items);
+  p.interleave_heads = (p.causal && items <= 4 * static_cast<int64_t>(num_sms())) ? 1 : 0;
+  p.item_div = p.interleave_heads ? p.num_items / p.num_q_tiles : p.num_q_tiles;
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
   p.lse = a.lse;
@@ -826,6 +841,8 @@ int launch_paged_attention_fwd_tile(const b200k_paged_attention_args& a, cudaStr
   const int64_t items = static_cast<int64_t>(a.batch) * a.q_heads * p.num_q_tiles;
   if (items > INT32_MAX) return set_error(B200K_ERR_BAD_SHAPE, "paged_attention_fwd: too many query tiles");
   p.num_items = static_cast<int32_t>(items);
+  p.interleave_heads = (p.causal && items <= 4 * static_cast<int64_t>(num_sms())) ? 1 : 0;
+  p.item_div = p.interleave_heads ? p.num_items / p.num_q_tiles : p.num_q_tiles;
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
   p.lse = nullptr;
